@@ -1,0 +1,243 @@
+#!/usr/bin/env python
+"""Headline benchmark: data-parallel GPT-2-medium training throughput (tokens/s).
+
+Config (the data-parallel row of the baseline): 24 layers, d_model 1024,
+16 heads, seq 1024, vocab 50257, bf16 weights with fp32 master copies, AdamW,
+per-GPU batch 8 of uniform-random token ids, gradients reduced in 25 MB buckets
+by the library's own allreduce kernels overlapped with backward.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Rank 0 prints one JSON line.  ``value`` is the device-timed whole-job tokens/s
+(max over ranks), ``e2e`` the same metric through the public API including the
+per-step host->device copy of the batch from pinned memory and the
+device->host read of the loss.
+
+``--impl reference`` reports that the reference (an Intel SYCL / Level Zero
+library) can not run here; ``--impl nccl`` runs the same model through torch
+DDP over NCCL for comparison on the same box.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+MODEL = "gpt2-medium"
+PER_GPU_BATCH = 8
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl"])
+    ap.add_argument("--model", default=MODEL)
+    ap.add_argument("--batch", type=int, default=PER_GPU_BATCH)
+    ap.add_argument("--bucket-mb", type=float, default=25.0)
+    return ap.parse_args()
+
+
+def reference_arm():
+    # The reference is a C++/SYCL library for Intel GPUs driven through Level Zero; it has no
+    # Python package (pip install of the tree fails: no setup.py / pyproject.toml), its GPU
+    # kernels need a SYCL compiler and an Intel device, and its MPI runtime blobs are absent.
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "reference is a C++/SYCL+Level Zero library without a Python package; "
+                                     "pip install of the tree fails and its GPU path needs Intel hardware"}))
+    return 0
+
+
+def env_world():
+    return int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm()
+    os.environ.setdefault("CCL_CUDA_WAIT_TIMEOUT_MS", "20000")
+    os.environ.setdefault("CCL_CUDA_SYMM_HEAP_SIZE", "2G")
+    import torch
+
+    world, rank, local_rank = env_world()
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            # launched directly: re-exec under torchrun so that one process drives one GPU
+            import subprocess
+
+            port = 29000 + os.getpid() % 2000
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", str(port), __file__] + sys.argv[1:]
+            return subprocess.call(cmd)
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    torch.manual_seed(1234)
+    torch.backends.cuda.matmul.allow_tf32 = True
+
+    from oneccl_b200.models.gpt2 import GPT2, GPT2Config
+    from oneccl_b200.utils.clocks import ClockSampler
+
+    cfg = GPT2Config.named(args.model)
+    B, S = args.batch, cfg.seq_len
+    model = GPT2(cfg).cuda().to(torch.bfloat16)
+
+    # ---- communicator + data-parallel wrapper
+    comm = None
+    if args.impl == "ours":
+        from oneccl_b200.ops import train as train_ops
+        from oneccl_b200.ops.device_group import DeviceGroup
+        from oneccl_b200.parallel.ddp import DataParallel, train_step
+
+        if world == 1:
+            group = DeviceGroup.emulated(1, heap_bytes=(2 << 30), staging_bytes=16 << 20)
+        else:
+            from oneccl_b200.comm import init_from_env
+
+            comm = init_from_env()
+            group = comm.device_group
+        ddp = DataParallel(model, group, bucket_mb=args.bucket_mb)
+        opt = ddp.make_optimizer(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, max_norm=1.0)
+
+        def step(idx, tgt):
+            return train_step(ddp, opt, idx, tgt)
+
+        def my_launches():
+            return train_ops.launch_count + ddp.launches
+
+        def barrier():
+            if world > 1:
+                group.barrier()
+            torch.cuda.synchronize()
+
+        def max_over_ranks(x: float) -> float:
+            if world == 1:
+                return x
+            t = torch.tensor([x], dtype=torch.float32, device="cuda")
+            group.allreduce(t, t, op="max")
+            torch.cuda.synchronize()
+            return float(t.item())
+    else:
+        import torch.distributed as dist
+        from torch.nn.parallel import DistributedDataParallel as TorchDDP
+
+        if world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        net = TorchDDP(model, device_ids=[local_rank], bucket_cap_mb=args.bucket_mb,
+                       gradient_as_bucket_view=True) if world > 1 else model
+        decay, no_decay = model.decay_split()
+        topt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": no_decay, "weight_decay": 0.0}],
+                                 lr=3e-4, betas=(0.9, 0.95), fused=True)
+
+        def step(idx, tgt):
+            topt.zero_grad(set_to_none=True)
+            lg = net(idx)
+            loss = torch.nn.functional.cross_entropy(lg.float(), tgt.reshape(-1))
+            loss.backward()
+            torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+            topt.step()
+            return loss
+
+        def my_launches():
+            return 0
+
+        def barrier():
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        def max_over_ranks(x: float) -> float:
+            if world == 1:
+                return x
+            t = torch.tensor([x], dtype=torch.float32, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+    # ---- synthetic data: uniform-random token ids, a fresh pinned batch per step
+    n_batches = args.steps + args.warmup
+    gen = torch.Generator().manual_seed(1000 + rank)
+    host_idx = [torch.randint(0, cfg.vocab, (B, S), generator=gen).pin_memory() for _ in range(n_batches)]
+    host_tgt = [torch.randint(0, cfg.vocab, (B, S), generator=gen).pin_memory() for _ in range(n_batches)]
+    dev_idx = [t.cuda() for t in host_idx[: args.steps]]
+    dev_tgt = [t.cuda() for t in host_tgt[: args.steps]]
+
+    # ---- warm-up
+    for w in range(args.warmup):
+        loss = step(dev_idx[w % len(dev_idx)], dev_tgt[w % len(dev_tgt)])
+    barrier()
+
+    # ---- device-timed region: exactly K steps
+    l0 = my_launches()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        ev0.record()
+        for k in range(args.steps):
+            loss = step(dev_idx[k], dev_tgt[k])
+        ev1.record()
+        barrier()
+    ms_dev = max_over_ranks(ev0.elapsed_time(ev1))
+    launches = my_launches() - l0
+    final_loss = float(loss.item())
+
+    # ---- end-to-end region: batch from pinned host memory every step, loss read back every step
+    h2d = host_idx[0].numel() * host_idx[0].element_size() + host_tgt[0].numel() * host_tgt[0].element_size()
+    barrier()
+    t0 = time.perf_counter()
+    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev2.record()
+    for k in range(args.steps):
+        idx = host_idx[args.warmup + k].cuda(non_blocking=True)
+        tgt = host_tgt[args.warmup + k].cuda(non_blocking=True)
+        loss = step(idx, tgt)
+        _ = float(loss.item())  # 4-byte device->host read of the step's result
+    ev3.record()
+    barrier()
+    ms_e2e = max_over_ranks(ev2.elapsed_time(ev3))
+    wall_e2e = time.perf_counter() - t0
+
+    tokens_per_step = world * B * S
+    value = tokens_per_step * args.steps / (ms_dev / 1e3)
+    e2e_value = tokens_per_step * args.steps / (ms_e2e / 1e3)
+    if rank == 0:
+        out = {
+            "metric": "dp_training_tokens_per_sec",
+            "value": value,
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": ms_dev / args.steps,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic uniform-random token ids, random-init weights",
+            "impl": args.impl,
+            "config": {"model": args.model, "global_batch": world * B, "seq_len": S, "parallelism": f"dp{world}",
+                       "per_gpu_batch": B, "optimizer": "AdamW fp32 master", "bucket_mb": args.bucket_mb,
+                       "l2": "working set (0.7 GB weights + activations) far larger than the 126 MB L2"},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                    "ms_per_step": ms_e2e / args.steps, "wall_s": wall_e2e},
+            "gpu_launches": launches,
+            "final_loss": final_loss,
+        }
+        print(json.dumps(out))
+    if comm is not None:
+        comm.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,139 @@
+// Environment configuration, parsed once into env_data.
+//
+// Keeps the portable knob names of the reference (src/common/env/vars.hpp:53-1176,
+// defaults src/common/env/env.cpp:77-331) and adds the CUDA-side knobs
+// (CCL_CUDA_*) that replace CCL_ZE_* / CCL_SYCL_*.  Parsing is a small typed
+// helper per kind (int / size with K,M,G suffix / bool / enum / list), all
+// values are printed at first communicator creation when the log level is
+// info or higher.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "core/types.hpp"
+
+namespace cclx {
+
+enum class atl_transport_t { tcp, shm, ofi, mpi };
+enum class priority_mode_t { none, direct, lifo };
+enum class cache_key_t { full, match_id };
+enum class yield_t { none, pause, sleep, sched_yield };
+enum class launcher_t { hydra, torchrun, pmix, none };
+enum class backend_t { native, stub };
+enum class ipc_exchange_t { sockets, pidfd, fabric, cudaipc };
+enum class kvs_mode_t { internal, user };
+
+struct env_data {
+    // logging / debug
+    std::string log_level = "warn";
+    bool abort_on_throw = false;
+    bool sched_profile = false;
+    bool sched_dump = false;
+    bool queue_dump = false;
+    double entry_max_update_time_sec = 0; // 0 = hang detector off
+    int itt_level = 0; // NVTX range level (0 off, 1 API calls, 2 entries)
+
+    // backend / launcher
+    backend_t backend = backend_t::native;
+    launcher_t process_launcher = launcher_t::hydra;
+    int local_rank = -1;
+    int local_size = -1;
+
+    // workers
+    int worker_count = 1;
+    bool worker_offload = true;
+    bool worker_wait = true;
+    std::vector<int> worker_affinity; // empty = auto (no pinning)
+    std::vector<int> worker_mem_affinity;
+    int spin_count = 1000;
+    yield_t yield = yield_t::pause;
+
+    // transport
+    atl_transport_t atl_transport = atl_transport_t::tcp;
+    bool atl_shm = true; // same-host pairs use the shared-memory rings
+    size_t atl_shm_ring_bytes = 4u << 20;
+    bool atl_sync_coll = false;
+    size_t max_short_size = 0;
+    size_t chunk_count = 1;
+    size_t min_chunk_size = 65536;
+    int max_flow_credits = 16;
+
+    // kvs
+    kvs_mode_t kvs_mode = kvs_mode_t::internal;
+    std::string kvs_ip_port; // <ip>_<port>
+    std::string kvs_ip_exchange = "path"; // env | path (address via user)
+    std::string kvs_iface;
+    bool kvs_prefer_ipv6 = false;
+    int kvs_connection_timeout_sec = 120;
+    int kvs_get_timeout_sec = 120;
+
+    // algorithm selection: raw strings, parsed by the selector (coll/selection.cpp)
+    std::map<int, std::string> algo_raw; // coll_type -> spec
+    std::map<int, std::string> algo_scaleout_raw;
+    std::map<int, std::string> algo_gpu_raw; // CCL_CUDA_<COLL>
+
+    // ordering / caching / fusion
+    bool unordered_coll = false;
+    bool fusion = false;
+    size_t fusion_bytes_threshold = 16384;
+    size_t fusion_count_threshold = 256;
+    double fusion_cycle_ms = 0.2;
+    bool fusion_check_urgent = true;
+    priority_mode_t priority_mode = priority_mode_t::none;
+    cache_key_t cache_key = cache_key_t::match_id;
+    bool cache_flush = false;
+    bool strict_order = false;
+    bool op_sync = false;
+    size_t buffer_cache_max_bytes = 256u << 20;
+
+    // allreduce tuning (CPU)
+    size_t ar2d_chunk_count = 1;
+    size_t nreduce_segment_size = 2u << 20;
+    bool nreduce_buffering = false;
+    size_t rs_chunk_count = 1;
+    size_t rs_min_chunk_size = 65536;
+    size_t alltoall_scatter_max_ops = 4;
+    bool check_inplace_aliasing = true;
+
+    // low precision on CPU: "auto" | "scalar" | "avx512f" | "f16c"
+    std::string bf16_impl = "auto";
+    std::string fp16_impl = "auto";
+
+    // topology
+    std::string topo_color = "fixed"; // fixed | cuda | env
+    bool topo_algo = true;
+    std::string topo_p2p_access = "auto"; // auto | 0 | 1
+    bool topo_fabric_check = true;
+
+    // CUDA device path
+    bool cuda_kernels = true; // CCL_ENABLE_CUDA_KERNELS (reference CCL_ENABLE_SYCL_KERNELS)
+    ipc_exchange_t ipc_exchange = ipc_exchange_t::sockets;
+    size_t symm_heap_bytes = 1ull << 30; // peer-mapped heap per rank
+    size_t tmp_buf_bytes = 64ull << 20; // one staging generation; two generations are kept
+    int nvls = -1; // -1 auto, 0 off, 1 force
+    size_t ar_oneshot_threshold = 256u << 10; // <= : one-shot
+    size_t ar_twoshot_threshold = 16u << 20; // <= : two-shot single launch; above: chunked
+    size_t rs_small_threshold = 2u << 20;
+    size_t ag_small_threshold = 128u << 10;
+    int cuda_max_blocks = 0; // 0 = auto (co-resident cap)
+    int cuda_block_threads = 512;
+    size_t wait_timeout_ms = 20000; // bound of every device-side wait
+    bool cuda_copy_engine = false; // large allgather through copy engines
+    bool cuda_graph_safe = true;
+    size_t ipc_cache_entries = 1000;
+
+    void parse();
+    void print(int rank) const;
+    static env_data& get();
+    static void reload(); // re-parse (tests)
+};
+
+// typed helpers (also used by tests through the C API)
+bool env_to_size(const char* s, size_t& out); // accepts 4096, 16K, 2M, 1G
+bool env_to_bool(const char* s, bool& out);
+std::vector<int> env_to_int_list(const char* s); // "1,3,5-7"
+
+} // namespace cclx

@@ -1,0 +1,807 @@
+// Collective kernels for one NVSwitch node: every kernel moves data with plain
+// peer loads/stores (or NVLS multimem) issued from inside the kernel and
+// synchronises with peer_barrier; no host round trip inside a collective.
+//
+// What they replace in the reference:
+//   allreduce_oneshot   <- reduce_sum "read_all" (allreduce_small_sycl_impl.hpp:23-113),
+//                          allreduce_kernel (src/kernels/kernels.cl:190-217)
+//   allreduce_twoshot   <- reduce_sum_general + copy (allreduce_small_sycl_rw_kernel.hpp:43-94),
+//                          allreduce_large_read_write_* (allreduce_large_sycl_impl.hpp:23-230)
+//   allreduce_symm      <- same two-shot on registered (IPC) user buffers, no tmp copy
+//   reduce_scatter      <- reduce_scatter_small/large_impl, reduce_monolithic_* (kernels.cl:269-421)
+//   allgatherv          <- gather / read_write, write_monolithic_* (kernels.cl:424-560)
+//   alltoallv           <- alltoallv_kernel_* (kernels.cl:110-116)
+//   broadcast / reduce  <- ze_copy_entry fan-out, ze_onesided_reduce
+// Design differences: push-style (remote stores, local reduction) so that a
+// collective costs one NVLink one-way trip plus one flag; two staging
+// generations instead of a trailing barrier; fused scale + output cast in the
+// reduction epilogue; bf16/fp16 accumulate in fp32.
+#pragma once
+#include "gpu/device/coll_args.hpp"
+#include "gpu/device/common.cuh"
+
+namespace cclx {
+namespace dev {
+
+__device__ __forceinline__ size_t round_up16(size_t b) {
+    return (b + 15) & ~(size_t)15;
+}
+
+// Load pack `i` (16 bytes) of a T array of `count` elements; zero-fill past the end.
+template <class T>
+__device__ __forceinline__ uint4 load_pack(const T* base, size_t i, size_t count, bool vec) {
+    constexpr int N = pack_traits<T>::N;
+    const size_t e0 = i * N;
+    if (vec && e0 + N <= count)
+        return *reinterpret_cast<const uint4*>(base + e0);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    T* t = reinterpret_cast<T*>(&v);
+#pragma unroll
+    for (int k = 0; k < N; k++)
+        if (e0 + k < count)
+            t[k] = base[e0 + k];
+    return v;
+}
+
+// Store N accumulators as elements [i*N, i*N+N) of a Tout array of `count` elements.
+template <class Tout, class A, int N>
+__device__ __forceinline__ void store_pack(Tout* base, size_t i, size_t count, bool vec, const A (&a)[N],
+                                           float scale, bool do_scale) {
+    const size_t e0 = i * N;
+    if (vec && e0 + N <= count) {
+        store_out<Tout, A, N>(base + e0, a, scale, do_scale);
+    }
+    else {
+#pragma unroll
+        for (int k = 0; k < N; k++)
+            if (e0 + k < count) {
+                A v = a[k];
+                base[e0 + k] = from_acc<Tout, A>(do_scale ? apply_scale<A>(v, scale) : v);
+            }
+    }
+}
+
+template <class Tout, int N>
+__device__ __forceinline__ bool out_vec_ok(const Tout* p) {
+    constexpr int B = N * (int)sizeof(Tout) >= 16 ? 16 : N * (int)sizeof(Tout);
+    return (((uintptr_t)p) & (B - 1)) == 0;
+}
+
+#define CCLX_KERNEL_PROLOGUE()                                   \
+    const int er = a.emu ? (int)blockIdx.y : 0;                  \
+    const comm_dev& c = tab[er];                                 \
+    const rank_args& ra = a.emu ? a.emu_tab[er] : a.r0;          \
+    block_sync s;                                                \
+    sync_begin(c, s);                                            \
+    const size_t tid = threadIdx.x, nt = blockDim.x;             \
+    (void)tid;                                                   \
+    (void)nt;                                                    \
+    (void)ra
+
+// ---------------------------------------------------------------------------
+// one-shot allreduce: push my data into slot[rank] of everybody's staging,
+// one barrier, reduce the `world` slots locally.
+// staging need: world * round_up16(count * sizeof(T)) <= staging_bytes
+// ---------------------------------------------------------------------------
+template <class T, class Tout, class Op>
+__global__ void __launch_bounds__(1024) allreduce_oneshot_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    typedef typename acc_of<T>::type A;
+    constexpr int N = pack_traits<T>::N;
+    const T* send = reinterpret_cast<const T*>(ra.send);
+    Tout* recv = reinterpret_cast<Tout*>(ra.recv);
+    const size_t count = a.count;
+    const size_t slot = round_up16(count * sizeof(T));
+    const size_t npacks = slot >> 4;
+    size_t lo, hi;
+    split_range(npacks, gridDim.x, blockIdx.x, lo, hi);
+    const bool vin = (((uintptr_t)send) & 15) == 0;
+    const bool vout = out_vec_ok<Tout, N>(recv);
+    const size_t goff = (size_t)s.gen * c.staging_bytes + (size_t)c.rank * slot;
+    const bool nvls = (a.flags & CF_NVLS) != 0;
+
+    for (size_t i = lo + tid; i < hi; i += nt) {
+        uint4 v = load_pack<T>(send, i, count, vin);
+        if (nvls) {
+            multimem_st16(c.mc_staging + goff + (i << 4), v);
+        }
+        else {
+#pragma unroll 4
+            for (int p = 0; p < c.world; p++)
+                st16(c.staging[p] + goff + (i << 4), v);
+        }
+    }
+    if (peer_barrier(c, s)) {
+        const char* mine = c.staging[c.rank] + (size_t)s.gen * c.staging_bytes;
+        for (size_t i = lo + tid; i < hi; i += nt) {
+            A acc[N];
+            unpack16<T, A>(ld_cv16(mine + (i << 4)), acc);
+            for (int p = 1; p < c.world; p++)
+                accum16<T, A, Op>(ld_cv16(mine + (size_t)p * slot + (i << 4)), acc);
+            store_pack<Tout, A, N>(recv, i, count, vout, acc, a.scale, a.do_scale != 0);
+        }
+    }
+    sync_end(c, gridDim.x, 1, true);
+}
+
+// ---------------------------------------------------------------------------
+// two-shot allreduce through staging: push my contribution to slice q into
+// slot[rank] at rank q; barrier; reduce my slice, write it to my recv and push
+// it into everybody's OUT region; barrier; copy the other slices from OUT.
+// staging need: world*slice_cap*16 + npacks*N*sizeof(Tout) <= staging_bytes
+// ---------------------------------------------------------------------------
+template <class T, class Tout, class Op>
+__global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    typedef typename acc_of<T>::type A;
+    constexpr int N = pack_traits<T>::N;
+    constexpr size_t OUTP = (size_t)N * sizeof(Tout); // bytes of one reduced pack
+    const T* send = reinterpret_cast<const T*>(ra.send);
+    Tout* recv = reinterpret_cast<Tout*>(ra.recv);
+    const size_t count = a.count;
+    const size_t npacks = round_up16(count * sizeof(T)) >> 4;
+    const int W = c.world;
+    const size_t slice_cap = (npacks + W - 1) / W; // packs per slot
+    const size_t in_bytes = (size_t)W * slice_cap * 16;
+    const size_t gbase = (size_t)s.gen * c.staging_bytes;
+    const bool vin = (((uintptr_t)send) & 15) == 0;
+    const bool vout = out_vec_ok<Tout, N>(recv);
+
+    // phase 1: scatter my contributions
+    for (int k = 1; k < W; k++) {
+        const int q = (c.rank + k) % W;
+        size_t qlo, qhi, lo, hi;
+        split_range(npacks, W, q, qlo, qhi);
+        split_range(qhi - qlo, gridDim.x, blockIdx.x, lo, hi);
+        char* dst = c.staging[q] + gbase + (size_t)c.rank * slice_cap * 16;
+        for (size_t i = lo + tid; i < hi; i += nt)
+            st16(dst + (i << 4), load_pack<T>(send, qlo + i, count, vin));
+    }
+    bool ok = peer_barrier(c, s);
+    // phase 2: reduce my slice and broadcast the result
+    size_t mlo, mhi, lo, hi;
+    split_range(npacks, W, c.rank, mlo, mhi);
+    split_range(mhi - mlo, gridDim.x, blockIdx.x, lo, hi);
+    if (ok) {
+        const char* mine = c.staging[c.rank] + gbase;
+        for (size_t i = lo + tid; i < hi; i += nt) {
+            A acc[N];
+            // fixed rank order so that the rounding is reproducible
+            bool first = true;
+            for (int p = 0; p < W; p++) {
+                uint4 v = (p == c.rank) ? load_pack<T>(send, mlo + i, count, vin)
+                                        : ld_cv16(mine + (size_t)p * slice_cap * 16 + (i << 4));
+                if (first) {
+                    unpack16<T, A>(v, acc);
+                    first = false;
+                }
+                else
+                    accum16<T, A, Op>(v, acc);
+            }
+            store_pack<Tout, A, N>(recv, mlo + i, count, vout, acc, a.scale, a.do_scale != 0);
+            // reduced pack in output precision, pushed to the peers' OUT region
+            alignas(16) Tout o[N];
+#pragma unroll
+            for (int k = 0; k < N; k++)
+                o[k] = from_acc<Tout, A>(a.do_scale ? apply_scale<A>(acc[k], a.scale) : acc[k]);
+            for (int k = 1; k < W; k++) {
+                const int p = (c.rank + k) % W;
+                char* dst = c.staging[p] + gbase + in_bytes + (mlo + i) * OUTP;
+#pragma unroll
+                for (int q = 0; q < (int)(OUTP / 16); q++)
+                    st16(dst + q * 16, reinterpret_cast<const uint4*>(o)[q]);
+            }
+        }
+    }
+    ok = peer_barrier(c, s);
+    // phase 3: collect the other slices
+    if (ok) {
+        const char* outr = c.staging[c.rank] + gbase + in_bytes;
+        for (int k = 1; k < W; k++) {
+            const int q = (c.rank + k) % W;
+            size_t qlo, qhi, l2, h2;
+            split_range(npacks, W, q, qlo, qhi);
+            split_range(qhi - qlo, gridDim.x, blockIdx.x, l2, h2);
+            for (size_t i = l2 + tid; i < h2; i += nt) {
+                const size_t e0 = (qlo + i) * N;
+                const char* src = outr + (qlo + i) * OUTP;
+                if (vout && e0 + N <= count) {
+#pragma unroll
+                    for (int q2 = 0; q2 < (int)(OUTP / 16); q2++)
+                        reinterpret_cast<uint4*>(recv + e0)[q2] = ld_cv16(src + q2 * 16);
+                }
+                else {
+                    alignas(16) Tout o[N];
+#pragma unroll
+                    for (int q2 = 0; q2 < (int)(OUTP / 16); q2++)
+                        reinterpret_cast<uint4*>(o)[q2] = ld_cv16(src + q2 * 16);
+#pragma unroll
+                    for (int k2 = 0; k2 < N; k2++)
+                        if (e0 + k2 < count)
+                            recv[e0 + k2] = o[k2];
+                }
+            }
+        }
+    }
+    sync_end(c, gridDim.x, 2, true);
+}
+
+// ---------------------------------------------------------------------------
+// two-shot allreduce on symmetric (registered) buffers, no staging copy.
+// P2P form: read my slice from every peer, reduce, write it to every peer.
+// NVLS form (sum of f32/bf16/f16): multimem.ld_reduce + multimem.st, the
+// switch does the reduction and the broadcast.
+// The tail that does not fill a 16-byte pack is read before and written after
+// the second barrier so that in-place calls do not race.
+// ---------------------------------------------------------------------------
+template <class T, class Op, bool NVLS>
+__global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    typedef typename acc_of<T>::type A;
+    constexpr int N = pack_traits<T>::N;
+    const int W = c.world;
+    const size_t count = a.count;
+    const size_t full = count / N; // whole packs
+    const size_t tail = count - full * N;
+    size_t mlo, mhi, lo, hi;
+    split_range(full, W, c.rank, mlo, mhi);
+    split_range(mhi - mlo, gridDim.x, blockIdx.x, lo, hi);
+    const bool scale = a.do_scale != 0;
+
+    bool ok = peer_barrier(c, s);
+    A tail_acc = A();
+    if (ok) {
+        if (NVLS) {
+            const char* in = c.mc_heap + a.in_off;
+            char* out = c.mc_heap + a.out_off;
+            size_t i = mlo + lo + tid;
+            const size_t end = mlo + hi;
+            // two packs in flight per thread
+            for (; i + nt < end; i += 2 * nt) {
+                uint4 v0 = multimem_ld_reduce_add16<T>(in + (i << 4));
+                uint4 v1 = multimem_ld_reduce_add16<T>(in + ((i + nt) << 4));
+                if (scale) {
+                    A t0[N], t1[N];
+                    unpack16<T, A>(v0, t0);
+                    unpack16<T, A>(v1, t1);
+                    T* o0 = reinterpret_cast<T*>(&v0);
+                    T* o1 = reinterpret_cast<T*>(&v1);
+#pragma unroll
+                    for (int k = 0; k < N; k++) {
+                        o0[k] = from_acc<T, A>(apply_scale<A>(t0[k], a.scale));
+                        o1[k] = from_acc<T, A>(apply_scale<A>(t1[k], a.scale));
+                    }
+                }
+                multimem_st16(out + (i << 4), v0);
+                multimem_st16(out + ((i + nt) << 4), v1);
+            }
+            for (; i < end; i += nt) {
+                uint4 v0 = multimem_ld_reduce_add16<T>(in + (i << 4));
+                if (scale) {
+                    A t0[N];
+                    unpack16<T, A>(v0, t0);
+                    T* o0 = reinterpret_cast<T*>(&v0);
+#pragma unroll
+                    for (int k = 0; k < N; k++)
+                        o0[k] = from_acc<T, A>(apply_scale<A>(t0[k], a.scale));
+                }
+                multimem_st16(out + (i << 4), v0);
+            }
+        }
+        else {
+            for (size_t i = mlo + lo + tid; i < mlo + hi; i += nt) {
+                A acc[N];
+                unpack16<T, A>(ld_cv16(c.heap[0] + a.in_off + (i << 4)), acc);
+                for (int p = 1; p < W; p++)
+                    accum16<T, A, Op>(ld_cv16(c.heap[p] + a.in_off + (i << 4)), acc);
+                uint4 o;
+                T* t = reinterpret_cast<T*>(&o);
+#pragma unroll
+                for (int k = 0; k < N; k++)
+                    t[k] = from_acc<T, A>(scale ? apply_scale<A>(acc[k], a.scale) : acc[k]);
+                for (int k = 0; k < W; k++) {
+                    const int p = (c.rank + k) % W;
+                    st16(c.heap[p] + a.out_off + (i << 4), o);
+                }
+            }
+        }
+        if (blockIdx.x == 0 && tid < tail) {
+            const size_t e = full * N + tid;
+            tail_acc = to_acc<A, T>(reinterpret_cast<const T*>(c.heap[0] + a.in_off)[e]);
+            for (int p = 1; p < W; p++)
+                tail_acc = Op::apply(tail_acc,
+                                     to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(c.heap[p] + a.in_off) + e)));
+        }
+    }
+    ok = peer_barrier(c, s);
+    if (ok && blockIdx.x == 0 && tid < tail) {
+        const size_t e = full * N + tid;
+        reinterpret_cast<T*>(c.heap[c.rank] + a.out_off)[e] =
+            from_acc<T, A>(scale ? apply_scale<A>(tail_acc, a.scale) : tail_acc);
+    }
+    // nobody reads a peer's input after the second barrier, so the next
+    // operation on the stream may overwrite it
+    sync_end(c, gridDim.x, 2, false);
+}
+
+// ---------------------------------------------------------------------------
+// reduce_scatter: recv[i] = op_p send_p[rank*rc + i]; push block q to rank q.
+// staging need: world * round_up16(rc*sizeof(T)) <= staging_bytes
+// ---------------------------------------------------------------------------
+template <class T, class Tout, class Op>
+__global__ void __launch_bounds__(1024) reduce_scatter_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    typedef typename acc_of<T>::type A;
+    constexpr int N = pack_traits<T>::N;
+    const T* send = reinterpret_cast<const T*>(ra.send);
+    Tout* recv = reinterpret_cast<Tout*>(ra.recv);
+    const size_t rc = a.count; // elements per rank
+    const int W = c.world;
+    const size_t slot = round_up16(rc * sizeof(T));
+    const size_t npacks = slot >> 4;
+    size_t lo, hi;
+    split_range(npacks, gridDim.x, blockIdx.x, lo, hi);
+    const size_t gbase = (size_t)s.gen * c.staging_bytes;
+    const bool vout = out_vec_ok<Tout, N>(recv);
+
+    for (int k = 1; k < W; k++) {
+        const int q = (c.rank + k) % W;
+        const T* blk = send + (size_t)q * a.stride;
+        const bool vin = (((uintptr_t)blk) & 15) == 0;
+        char* dst = c.staging[q] + gbase + (size_t)c.rank * slot;
+        for (size_t i = lo + tid; i < hi; i += nt)
+            st16(dst + (i << 4), load_pack<T>(blk, i, rc, vin));
+    }
+    if (peer_barrier(c, s)) {
+        const char* mine = c.staging[c.rank] + gbase;
+        const T* own = send + (size_t)c.rank * a.stride;
+        const bool vown = (((uintptr_t)own) & 15) == 0;
+        for (size_t i = lo + tid; i < hi; i += nt) {
+            A acc[N];
+            bool first = true;
+            for (int p = 0; p < W; p++) {
+                uint4 v = (p == c.rank) ? load_pack<T>(own, i, rc, vown)
+                                        : ld_cv16(mine + (size_t)p * slot + (i << 4));
+                if (first) {
+                    unpack16<T, A>(v, acc);
+                    first = false;
+                }
+                else
+                    accum16<T, A, Op>(v, acc);
+            }
+            store_pack<Tout, A, N>(recv, i, rc, vout, acc, a.scale, a.do_scale != 0);
+        }
+    }
+    sync_end(c, gridDim.x, 1, true);
+}
+
+// reduce_scatter on symmetric send buffers: pull my block from every peer
+// (NVLS: one multimem.ld_reduce), write locally.  recv is an ordinary pointer.
+template <class T, class Op, bool NVLS>
+__global__ void __launch_bounds__(1024) reduce_scatter_symm_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    typedef typename acc_of<T>::type A;
+    constexpr int N = pack_traits<T>::N;
+    T* recv = reinterpret_cast<T*>(ra.recv);
+    const size_t rc = a.count;
+    const int W = c.world;
+    const size_t boff = a.in_off + (size_t)c.rank * rc * sizeof(T); // my block inside every peer's send
+    const bool aligned = (boff & 15) == 0;
+    const size_t full = aligned ? rc / N : 0;
+    const bool vout = (((uintptr_t)recv) & 15) == 0;
+    size_t lo, hi;
+    split_range(full, gridDim.x, blockIdx.x, lo, hi);
+    bool ok = peer_barrier(c, s);
+    if (ok) {
+        for (size_t i = lo + tid; i < hi; i += nt) {
+            A acc[N];
+            if (NVLS) {
+                unpack16<T, A>(multimem_ld_reduce_add16<T>(c.mc_heap + boff + (i << 4)), acc);
+            }
+            else {
+                unpack16<T, A>(ld_cv16(c.heap[0] + boff + (i << 4)), acc);
+                for (int p = 1; p < W; p++)
+                    accum16<T, A, Op>(ld_cv16(c.heap[p] + boff + (i << 4)), acc);
+            }
+            store_pack<T, A, N>(recv, i, rc, vout, acc, a.scale, a.do_scale != 0);
+        }
+        // elements outside whole aligned packs
+        for (size_t e = full * N + (size_t)blockIdx.x * nt + tid; e < rc; e += (size_t)gridDim.x * nt) {
+            A acc = to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(c.heap[0] + boff) + e));
+            for (int p = 1; p < W; p++)
+                acc = Op::apply(acc, to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(c.heap[p] + boff) + e)));
+            recv[e] = from_acc<T, A>(a.do_scale ? apply_scale<A>(acc, a.scale) : acc);
+        }
+    }
+    peer_barrier(c, s); // peers may still read my send buffer until here
+    sync_end(c, gridDim.x, 2, false);
+}
+
+// ---------------------------------------------------------------------------
+// allgatherv (byte oriented): rank p contributes scount[p] bytes placed at
+// sdispl[p] of every recv buffer.  `send` may be nullptr / equal to
+// recv+sdispl[rank] (in-place).
+//  PUSH (small): write my block into slot[rank] of every staging, barrier, copy out.
+//  PULL (large): copy my block to my staging, barrier, read every peer's staging.
+// staging need: push: sum of blocks rounded per slot; pull: own block.
+// ---------------------------------------------------------------------------
+template <bool PUSH>
+__global__ void __launch_bounds__(1024) allgatherv_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    const int W = c.world;
+    const size_t gbase = (size_t)s.gen * c.staging_bytes;
+    char* recv = reinterpret_cast<char*>(ra.recv);
+    const char* send = ra.send ? reinterpret_cast<const char*>(ra.send) : recv + ra.sdispl[c.rank];
+    const size_t mybytes = ra.scount[c.rank];
+    size_t lo, hi;
+    if (PUSH) {
+        // slot offsets: prefix of rounded sizes (identical on every rank)
+        size_t myoff = 0;
+        for (int p = 0; p < c.rank; p++)
+            myoff += round_up16(ra.scount[p]);
+        split_range((mybytes + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+        const size_t blo = lo << 4, bhi = (hi << 4) < mybytes ? (hi << 4) : mybytes;
+        if (bhi > blo) {
+            for (int k = 1; k < W; k++) {
+                const int p = (c.rank + k) % W;
+                block_copy<false>(c.staging[p] + gbase + myoff + blo, send + blo, bhi - blo);
+            }
+            if (send != recv + ra.sdispl[c.rank])
+                block_copy<false>(recv + ra.sdispl[c.rank] + blo, send + blo, bhi - blo);
+        }
+        if (peer_barrier(c, s)) {
+            size_t off = 0;
+            for (int p = 0; p < W; p++) {
+                const size_t pb = ra.scount[p];
+                if (p != c.rank) {
+                    split_range((pb + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+                    const size_t l = lo << 4, h = (hi << 4) < pb ? (hi << 4) : pb;
+                    if (h > l)
+                        block_copy<true>(recv + ra.sdispl[p] + l, c.staging[c.rank] + gbase + off + l, h - l);
+                }
+                off += round_up16(pb);
+            }
+        }
+        sync_end(c, gridDim.x, 1, true);
+    }
+    else {
+        split_range((mybytes + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+        const size_t blo = lo << 4, bhi = (hi << 4) < mybytes ? (hi << 4) : mybytes;
+        if (bhi > blo) {
+            block_copy<false>(c.staging[c.rank] + gbase + blo, send + blo, bhi - blo);
+            if (send != recv + ra.sdispl[c.rank])
+                block_copy<false>(recv + ra.sdispl[c.rank] + blo, send + blo, bhi - blo);
+        }
+        if (peer_barrier(c, s)) {
+            for (int k = 1; k < W; k++) {
+                const int p = (c.rank + k) % W;
+                const size_t pb = ra.scount[p];
+                split_range((pb + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+                const size_t l = lo << 4, h = (hi << 4) < pb ? (hi << 4) : pb;
+                if (h > l)
+                    block_copy<true>(recv + ra.sdispl[p] + l, c.staging[p] + gbase + l, h - l);
+            }
+        }
+        sync_end(c, gridDim.x, 1, true);
+    }
+}
+
+// allgather into a symmetric recv buffer: every rank stores its block straight
+// into all peers' recv (multimem.st when NVLS), no staging.
+template <bool NVLS>
+__global__ void __launch_bounds__(1024) allgather_symm_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    const int W = c.world;
+    const size_t bytes = a.count; // bytes per rank, multiple of 16, 16-byte aligned offsets
+    const char* send = ra.send ? reinterpret_cast<const char*>(ra.send)
+                               : c.heap[c.rank] + a.out_off + (size_t)c.rank * bytes;
+    const size_t doff = a.out_off + (size_t)c.rank * bytes;
+    size_t lo, hi;
+    split_range(bytes >> 4, gridDim.x, blockIdx.x, lo, hi);
+    // peers must have finished reading the previous contents of recv
+    bool ok = peer_barrier(c, s);
+    if (ok) {
+        const bool vin = (((uintptr_t)send) & 15) == 0;
+        for (size_t i = lo + tid; i < hi; i += nt) {
+            uint4 v = load_pack<unsigned char>(reinterpret_cast<const unsigned char*>(send), i, bytes, vin);
+            if (NVLS) {
+                multimem_st16(c.mc_heap + doff + (i << 4), v);
+            }
+            else {
+                for (int k = 0; k < W; k++) {
+                    const int p = (c.rank + k) % W;
+                    st16(c.heap[p] + doff + (i << 4), v);
+                }
+            }
+        }
+    }
+    peer_barrier(c, s);
+    sync_end(c, gridDim.x, 2, false);
+}
+
+// ---------------------------------------------------------------------------
+// alltoallv (byte oriented).  Every rank owns a slot of slot_bytes =
+// staging_bytes / world in each peer's staging.  Rank r writes the block for q
+// into slot[r] at rank q; after the barrier q copies slot[p] to recv+rdispl[p].
+// Blocks larger than a slot take several rounds inside the kernel.  Whether
+// another round is needed is agreed on the device: every rank pushes a "more"
+// word to all peers before the round's barrier and ORs the words it received,
+// so no rank needs the job-wide maximum block size on the host.
+// ---------------------------------------------------------------------------
+static __global__ void __launch_bounds__(1024) alltoallv_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    const int W = c.world;
+    const size_t slot = (c.staging_bytes / W) & ~(size_t)15;
+    const char* send = reinterpret_cast<const char*>(ra.send);
+    char* recv = reinterpret_cast<char*>(ra.recv);
+    __shared__ int more_s;
+    uint32_t rounds = 0;
+    size_t lo, hi;
+    for (;;) {
+        const size_t round_off = (size_t)rounds * slot;
+        const uint32_t g = (s.gen + rounds) & 1u;
+        const size_t gbase = (size_t)g * c.staging_bytes;
+        bool more = false;
+        for (int k = 0; k < W; k++) {
+            const int q = (c.rank + k) % W;
+            size_t b = ra.scount[q] > round_off ? ra.scount[q] - round_off : 0;
+            if (b > slot) {
+                b = slot;
+                more = true;
+            }
+            if (ra.rcount[q] > round_off + slot)
+                more = true;
+            split_range((b + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+            const size_t l = lo << 4, h = (hi << 4) < b ? (hi << 4) : b;
+            if (h > l) {
+                const char* src = send + ra.sdispl[q] + round_off + l;
+                if (q == c.rank)
+                    block_copy<false>(recv + ra.rdispl[q] + round_off + l, src, h - l);
+                else
+                    block_copy<false>(c.staging[q] + gbase + (size_t)c.rank * slot + l, src, h - l);
+            }
+        }
+        const size_t hdr = ((size_t)g * MAX_BLOCKS + blockIdx.x) * MAX_RANKS;
+        if (tid < (size_t)W)
+            c.aux[tid][hdr + c.rank] = more ? 1u : 0u;
+        if (!peer_barrier(c, s)) {
+            rounds++;
+            break;
+        }
+        for (int k = 1; k < W; k++) {
+            const int p = (c.rank + k) % W;
+            size_t b = ra.rcount[p] > round_off ? ra.rcount[p] - round_off : 0;
+            if (b > slot)
+                b = slot;
+            split_range((b + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+            const size_t l = lo << 4, h = (hi << 4) < b ? (hi << 4) : b;
+            if (h > l)
+                block_copy<true>(recv + ra.rdispl[p] + round_off + l,
+                                 c.staging[c.rank] + gbase + (size_t)p * slot + l, h - l);
+        }
+        if (tid == 0) {
+            uint32_t m = 0;
+            for (int p = 0; p < W; p++)
+                m |= ld_volatile_u32(c.aux[c.rank] + hdr + p);
+            more_s = (int)m;
+        }
+        __syncthreads();
+        const int again = more_s;
+        rounds++;
+        __syncthreads();
+        if (!again)
+            break;
+    }
+    sync_end(c, gridDim.x, rounds, rounds);
+}
+
+// ---------------------------------------------------------------------------
+// broadcast (byte oriented, <= staging_bytes per launch): root pushes into
+// every staging (multimem.st when NVLS), barrier, the others copy out.
+// ---------------------------------------------------------------------------
+static __global__ void __launch_bounds__(1024) broadcast_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    const int W = c.world;
+    const size_t bytes = a.count;
+    const size_t gbase = (size_t)s.gen * c.staging_bytes;
+    const char* send = reinterpret_cast<const char*>(ra.send);
+    char* recv = reinterpret_cast<char*>(ra.recv);
+    size_t lo, hi;
+    split_range((bytes + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+    const size_t l = lo << 4, h = (hi << 4) < bytes ? (hi << 4) : bytes;
+    if (c.rank == a.root && h > l) {
+        if ((a.flags & CF_NVLS) && ((((uintptr_t)send) & 15) == 0)) {
+            for (size_t i = lo + tid; i < hi; i += nt)
+                multimem_st16(c.mc_staging + gbase + (i << 4),
+                              load_pack<unsigned char>(reinterpret_cast<const unsigned char*>(send), i, bytes, true));
+        }
+        else {
+            for (int k = 1; k < W; k++) {
+                const int p = (c.rank + k) % W;
+                block_copy<false>(c.staging[p] + gbase + l, send + l, h - l);
+            }
+        }
+        if (recv != send)
+            block_copy<false>(recv + l, send + l, h - l);
+    }
+    if (peer_barrier(c, s)) {
+        if (c.rank != a.root && h > l)
+            block_copy<true>(recv + l, c.staging[c.rank] + gbase + l, h - l);
+    }
+    sync_end(c, gridDim.x, 1, true);
+}
+
+// ---------------------------------------------------------------------------
+// reduce to root: every rank pushes its buffer into slot[rank] at the root.
+// staging need at root: world * round_up16(count*sizeof(T))
+// ---------------------------------------------------------------------------
+template <class T, class Tout, class Op>
+__global__ void __launch_bounds__(1024) reduce_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    typedef typename acc_of<T>::type A;
+    constexpr int N = pack_traits<T>::N;
+    const T* send = reinterpret_cast<const T*>(ra.send);
+    Tout* recv = reinterpret_cast<Tout*>(ra.recv);
+    const size_t count = a.count;
+    const int W = c.world;
+    const size_t slot = round_up16(count * sizeof(T));
+    const size_t npacks = slot >> 4;
+    size_t lo, hi;
+    split_range(npacks, gridDim.x, blockIdx.x, lo, hi);
+    const size_t gbase = (size_t)s.gen * c.staging_bytes;
+    const bool vin = (((uintptr_t)send) & 15) == 0;
+    if (c.rank != a.root) {
+        char* dst = c.staging[a.root] + gbase + (size_t)c.rank * slot;
+        for (size_t i = lo + tid; i < hi; i += nt)
+            st16(dst + (i << 4), load_pack<T>(send, i, count, vin));
+    }
+    if (peer_barrier(c, s) && c.rank == a.root) {
+        const bool vout = out_vec_ok<Tout, N>(recv);
+        const char* mine = c.staging[c.rank] + gbase;
+        for (size_t i = lo + tid; i < hi; i += nt) {
+            A acc[N];
+            bool first = true;
+            for (int p = 0; p < W; p++) {
+                uint4 v = (p == c.rank) ? load_pack<T>(send, i, count, vin)
+                                        : ld_cv16(mine + (size_t)p * slot + (i << 4));
+                if (first) {
+                    unpack16<T, A>(v, acc);
+                    first = false;
+                }
+                else
+                    accum16<T, A, Op>(v, acc);
+            }
+            store_pack<Tout, A, N>(recv, i, count, vout, acc, a.scale, a.do_scale != 0);
+        }
+    }
+    sync_end(c, gridDim.x, 1, true);
+}
+
+// barrier only
+static __global__ void __launch_bounds__(64) barrier_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    peer_barrier(c, s);
+    sync_end(c, gridDim.x, 1, false);
+}
+
+// ---------------------------------------------------------------------------
+// point-to-point (eager).  Every ordered pair owns one data slot at the
+// receiver, split among P2P_BLOCKS blocks; block b of the sender talks to
+// block b of the receiver through its own pair of sequence words, so no
+// grid-wide synchronisation is needed.
+// p2p flag area of rank x (peer-mapped), in words:
+//   ready[(p*P2P_BLOCKS)+b] : written by sender p  when part b of its message is in x's slot[p]
+//   ack  [(q*P2P_BLOCKS)+b] : written by receiver q when it drained part b of x's message to q
+// send: wait ack >= seq-1 on my side, push, fence, set ready at the peer.
+// recv: wait ready >= seq on my side, copy out, set ack at the peer.
+// Messages larger than the slot are split by the host into rounds; both sides
+// derive the same grid from the byte count.
+// ---------------------------------------------------------------------------
+static __global__ void __launch_bounds__(1024) sendrecv_kernel(const comm_dev* tab, p2p_layout L, coll_args a,
+                                                        int is_send) {
+    const int er = a.emu ? (int)blockIdx.y : 0;
+    const comm_dev& c = tab[er];
+    const rank_args& ra = a.emu ? a.emu_tab[er] : a.r0;
+    const int peer = a.emu ? (int)ra.scount[0] : a.peer;
+    const int do_send = a.emu ? (int)ra.scount[1] : is_send;
+    if (peer < 0)
+        return; // emulated rank that takes no part
+    const size_t bytes = a.count;
+    const int b = blockIdx.x;
+    size_t lo, hi;
+    split_range((bytes + 15) >> 4, gridDim.x, b, lo, hi);
+    const size_t l = lo << 4, h = (hi << 4) < bytes ? (hi << 4) : bytes;
+    __shared__ uint32_t seq_s;
+    __shared__ int fail;
+    uint32_t* seqw = c.p2p_seq + ((do_send ? 0 : MAX_RANKS) + peer) * P2P_BLOCKS + b;
+    if (threadIdx.x == 0) {
+        fail = 0;
+        seq_s = *seqw + 1;
+        if (do_send) {
+            // the receiver must have drained the previous message of this pair
+            if (!wait_flag_sys(c, c.p2p_flags[c.rank] + P2P_ACK_BASE + peer * P2P_BLOCKS + b, seq_s - 1, peer,
+                               ST_FLAG_TIMEOUT))
+                fail = 1;
+        }
+        else {
+            if (!wait_flag_sys(c, c.p2p_flags[c.rank] + peer * P2P_BLOCKS + b, seq_s, peer, ST_FLAG_TIMEOUT))
+                fail = 1;
+        }
+    }
+    __syncthreads();
+    if (fail)
+        return;
+    if (do_send) {
+        if (h > l)
+            block_copy<false>(L.data[peer] + (size_t)c.rank * L.slot_bytes + l,
+                              reinterpret_cast<const char*>(ra.send) + l, h - l);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            st_release_sys(c.p2p_flags[peer] + c.rank * P2P_BLOCKS + b, seq_s);
+            *seqw = seq_s;
+        }
+    }
+    else {
+        if (h > l)
+            block_copy<true>(reinterpret_cast<char*>(ra.recv) + l,
+                             L.data[c.rank] + (size_t)peer * L.slot_bytes + l, h - l);
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            st_release_sys(c.p2p_flags[peer] + P2P_ACK_BASE + c.rank * P2P_BLOCKS + b, seq_s);
+            *seqw = seq_s;
+        }
+    }
+}
+
+// A barrier whose flag nobody sets: used by the failure-detection test to let
+// a wait run out and check that the status word reports it while the context
+// stays usable.  It waits on a private word of this rank's p2p flag area.
+static __global__ void __launch_bounds__(64) wait_unset_flag_kernel(const comm_dev* tab, coll_args a) {
+    const int er = a.emu ? (int)blockIdx.y : 0;
+    const comm_dev& c = tab[er];
+    if (threadIdx.x == 0) {
+        uint32_t* word = c.p2p_flags[c.rank] + P2P_SPARE_WORD; // never written by anyone
+        wait_flag_sys(c, word, 1u, (uint32_t)c.rank, ST_FLAG_TIMEOUT);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// local helpers: out = op(a, b) (reduce_local_* of kernels.cl:219-246),
+// pack / unpack of a tensor list into one fused buffer (fusion copy entries,
+// src/fusion/fusion.cpp:283-362) driven by a pointer table.
+// ---------------------------------------------------------------------------
+template <class T, class Op>
+__global__ void __launch_bounds__(1024) reduce_local_kernel(const T* in, T* inout, size_t count) {
+    typedef typename acc_of<T>::type A;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+        inout[i] = from_acc<T, A>(Op::apply(to_acc<A, T>(inout[i]), to_acc<A, T>(in[i])));
+}
+
+struct pack_table {
+    const void* const* ptrs; // device array of n tensor pointers
+    const size_t* offs; // device array of n+1 byte offsets into the fused buffer (16-byte aligned)
+    int n;
+};
+
+template <bool UNPACK>
+__global__ void __launch_bounds__(512) pack_kernel(pack_table t, char* fused) {
+    // blockIdx.y walks tensors, blockIdx.x strides inside one tensor
+    for (int k = blockIdx.y; k < t.n; k += gridDim.y) {
+        const size_t bytes = t.offs[k + 1] - t.offs[k];
+        size_t lo, hi;
+        split_range((bytes + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+        const size_t l = lo << 4, h = (hi << 4) < bytes ? (hi << 4) : bytes;
+        if (h <= l)
+            continue;
+        char* user = const_cast<char*>(reinterpret_cast<const char*>(t.ptrs[k]));
+        if (UNPACK)
+            block_copy<false>(user + l, fused + t.offs[k] + l, h - l);
+        else
+            block_copy<false>(fused + t.offs[k] + l, user + l, h - l);
+    }
+}
+
+} // namespace dev
+} // namespace cclx

@@ -1,0 +1,64 @@
+// Host-safe definitions shared by host code and kernels: limits, status
+// codes, the per-rank device communicator record and the point-to-point layout.
+#pragma once
+#include <cstddef>
+#include <stdint.h>
+
+namespace cclx {
+namespace dev {
+
+constexpr int MAX_RANKS = 16;
+constexpr int MAX_BLOCKS = 256; // flag slots per rank: MAX_BLOCKS x MAX_RANKS words
+
+// error codes written to comm_dev::status[0]
+enum : uint32_t {
+    ST_OK = 0,
+    ST_BARRIER_TIMEOUT = 1,
+    ST_ABORTED = 2,
+    ST_FLAG_TIMEOUT = 3,
+    ST_MBAR_TIMEOUT = 4,
+    ST_BAD_ARGS = 5
+};
+
+// words of comm_dev::state
+enum { STATE_EPOCH = 0, STATE_GEN = 1, STATE_DONE = 2, STATE_WORDS = 8 };
+
+struct comm_dev {
+    int rank;
+    int world;
+    uint32_t* flags[MAX_RANKS]; // barrier slots of every rank, peer-mapped
+    char* staging[MAX_RANKS]; // two generations of staging_bytes each, peer-mapped
+    char* heap[MAX_RANKS]; // symmetric heap bases, peer-mapped (zero-copy paths)
+    char* mc_heap; // NVLS multicast window over the heap (nullptr when NVLS is off)
+    char* mc_staging; // multicast address of staging generation 0
+    uint32_t* mc_flags;
+    uint32_t* p2p_flags[MAX_RANKS]; // point-to-point sequence words, peer-mapped
+    uint32_t* aux[MAX_RANKS]; // auxiliary flag words (alltoallv round consensus, fused-GEMM tile flags), peer-mapped
+    size_t heap_bytes;
+    size_t staging_bytes; // one generation
+    uint32_t* state; // local device words: epoch, generation, finished-block counter
+    uint32_t* p2p_seq; // local device words: per (direction, peer, block) message sequence numbers
+    volatile uint32_t* status; // host-mapped: [0] code, [1] block, [2] peer, [3] detail
+    volatile uint32_t* abort_flag; // host-mapped, set by communicator abort
+    unsigned long long timeout_ns;
+};
+
+
+// point-to-point flag area (see sendrecv_kernel)
+constexpr int P2P_BLOCKS = 16;
+constexpr int P2P_ACK_BASE = MAX_RANKS * P2P_BLOCKS;
+constexpr int P2P_SPARE_WORD = 2 * MAX_RANKS * P2P_BLOCKS; // never written: timeout test
+constexpr int P2P_FLAG_WORDS = 2 * MAX_RANKS * P2P_BLOCKS + 16;
+constexpr int P2P_SEQ_WORDS = 2 * MAX_RANKS * P2P_BLOCKS;
+
+// auxiliary flag region (words): [0, A2A_HDR_WORDS) alltoallv consensus, the rest is
+// handed out to the fused kernels by the host
+constexpr int A2A_HDR_WORDS = 2 * MAX_BLOCKS * MAX_RANKS;
+
+struct p2p_layout {
+    char* data[MAX_RANKS]; // p2p data areas, peer-mapped; slot s of rank x holds data from sender s
+    size_t slot_bytes;
+};
+
+} // namespace dev
+} // namespace cclx

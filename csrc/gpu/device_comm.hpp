@@ -1,0 +1,137 @@
+// Host-side owner of one node communicator's device state, and the launch
+// entry points of the collective kernels.
+//
+// Role in the layer map: this is the replacement of the reference's SYCL
+// collective runtime (coll_init / invoke_collective / size dispatch,
+// src/coll/algorithms/utils/sycl_coll_base.cpp:200-302, sycl_coll_base.hpp:351-408,
+// sycl_selection.cpp:18-155): one-time exchange of barrier counters and
+// temporary buffers per communicator, then per-call selection by message size
+// and a kernel launch on the caller's stream.  Nothing here touches the CPU
+// scheduler or worker threads.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "core/types.hpp"
+#include "gpu/device/coll_args.hpp"
+#include "gpu/device/layout.hpp"
+#include "gpu/symm_heap.hpp"
+
+namespace cclx {
+namespace gpu {
+
+enum gpu_algo : int {
+    ga_auto = 0,
+    ga_oneshot, // push + local reduce, staged
+    ga_twoshot, // reduce-scatter + allgather through staging
+    ga_symm, // zero-copy peer loads/stores on symmetric buffers
+    ga_nvls, // multimem on symmetric buffers
+    ga_nvls_oneshot, // one-shot with a multimem.st push
+    ga_push, // allgather: push into peers' staging
+    ga_pull, // allgather: pull from peers' staging
+    ga_copy, // single rank / local copy
+    ga_last
+};
+const char* gpu_algo_name(int a);
+int gpu_algo_from_name(const std::string& s); // -1 when unknown
+
+class device_comm {
+public:
+    device_comm() = default;
+    ~device_comm();
+    device_comm(const device_comm&) = delete;
+    device_comm& operator=(const device_comm&) = delete;
+
+    void init(bootstrap_if& bs); // real: one process per GPU (device already current)
+    void init_emulated(int world, size_t heap_bytes, size_t staging_bytes);
+    void destroy();
+
+    int rank() const { return rank_; }
+    int world() const { return world_; }
+    bool emulated() const { return emulated_; }
+    bool nvls() const { return heap_.has_multicast(); }
+    symm_heap& heap() { return heap_; }
+    const dev::comm_dev* table() const { return table_dev_; }
+    const dev::comm_dev& host_entry(int r) const { return table_host_[r]; }
+    const dev::p2p_layout& p2p() const { return p2p_; }
+    int sm_count() const { return sm_count_; }
+    int max_blocks() const; // per rank, keeps every block co-resident
+    int threads() const { return threads_; }
+    dev::rank_args* emu_args_dev() const { return emu_args_dev_; }
+    size_t staging_bytes() const { return heap_.regions().staging_bytes; }
+
+    // error status written by kernels (0 = ok); throws with a description when set
+    uint32_t status_code(int r = 0) const;
+    void check_status() const;
+    void clear_status();
+    void abort(); // raise the abort flag polled by every device-side wait
+    void set_timeout_ms(size_t ms);
+
+    // symmetric allocation helpers (collective in real mode)
+    void* symm_alloc(size_t bytes, int emu_rank = 0);
+    void symm_free(void* p, int emu_rank = 0);
+    // offset of p inside the heap of `owner` (emulated rank or my rank), -1 if not symmetric
+    size_t symm_offset(const void* p, int owner = -1) const;
+
+    // per-algorithm launch counters (observability)
+    std::vector<unsigned long long> algo_hits = std::vector<unsigned long long>(ga_last * (int)coll_last, 0);
+
+private:
+    void build_tables();
+    int rank_ = 0, world_ = 0;
+    bool emulated_ = false;
+    symm_heap heap_;
+    std::vector<dev::comm_dev> table_host_;
+    dev::comm_dev* table_dev_ = nullptr;
+    dev::p2p_layout p2p_{};
+    uint32_t* state_dev_ = nullptr; // per emulated rank STATE_WORDS
+    uint32_t* p2p_seq_dev_ = nullptr;
+    uint32_t* status_host_ = nullptr; // pinned + mapped: per rank 8 words, then abort word
+    uint32_t* status_devptr_ = nullptr;
+    dev::rank_args* emu_args_dev_ = nullptr;
+    int sm_count_ = 0;
+    int threads_ = 512;
+    size_t timeout_ms_ = 20000;
+};
+
+// ---- launchers -------------------------------------------------------------------
+// `ra` points at one rank_args in real mode and at world() entries in
+// emulation mode.  Counts are in elements of dt_in unless stated.
+struct launch_opts {
+    int algo = ga_auto;
+    int blocks = 0; // 0 = automatic
+    float scale = 1.0f;
+    bool do_scale = false;
+};
+
+void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, int dt_in, int dt_out, int op,
+                      const launch_opts& o, cudaStream_t st);
+void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t recv_count, int dt_in, int dt_out,
+                           int op, const launch_opts& o, cudaStream_t st);
+void launch_reduce(device_comm& dc, const dev::rank_args* ra, size_t count, int dt_in, int dt_out, int op,
+                   int root, const launch_opts& o, cudaStream_t st);
+// scount/sdispl of ra[*] in BYTES: block sizes / offsets inside recv (identical on every rank)
+void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_opts& o, cudaStream_t st);
+// scount/sdispl/rcount/rdispl of ra[*] in BYTES
+void launch_alltoallv(device_comm& dc, const dev::rank_args* ra, const launch_opts& o, cudaStream_t st);
+void launch_broadcast(device_comm& dc, const dev::rank_args* ra, size_t bytes, int root, const launch_opts& o,
+                      cudaStream_t st);
+void launch_barrier(device_comm& dc, cudaStream_t st);
+// point to point; in emulation mode ra[r].scount[0] = peer (or -1), ra[r].scount[1] = 1 for send
+void launch_sendrecv(device_comm& dc, const dev::rank_args* ra, size_t bytes, int peer, bool is_send,
+                     cudaStream_t st);
+// a wait that nothing satisfies; returns after the device time limit with status ST_FLAG_TIMEOUT
+void launch_wait_unset_flag(device_comm& dc, cudaStream_t st);
+
+// local helpers
+void launch_reduce_local(const void* in, void* inout, size_t count, int dt, int op, cudaStream_t st);
+void launch_pack(const void* const* ptrs_dev, const size_t* offs_dev, int n, void* fused, bool unpack,
+                 size_t max_tensor_bytes, cudaStream_t st);
+
+int selected_allreduce_algo(const device_comm& dc, size_t bytes, bool symmetric, int dt, int op);
+
+} // namespace gpu
+} // namespace cclx

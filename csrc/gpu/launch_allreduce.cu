@@ -1,0 +1,168 @@
+// Allreduce on GPU buffers: selection by size / registration and launch.
+// Counterpart of allreduce_sycl_single_node (reference
+// src/coll/algorithms/allreduce/sycl/allreduce_sycl.cpp:27-168): world==1 is a
+// copy, small messages take the one-shot kernel, larger ones the two-shot
+// kernel (chunked to the staging size), registered buffers skip staging.
+#include "gpu/launch_common.cuh"
+
+namespace cclx {
+namespace gpu {
+
+namespace {
+
+template <class T, class Tout>
+__global__ void __launch_bounds__(1024) scale_cast_kernel(const T* in, Tout* out, size_t count, float scale,
+                                                          int do_scale) {
+    typedef typename dev::acc_of<T>::type A;
+    constexpr int N = dev::pack_traits<T>::N;
+    const size_t npacks = (count + N - 1) / N;
+    const bool vin = (((uintptr_t)in) & 15) == 0;
+    const bool vout = dev::out_vec_ok<Tout, N>(out);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < npacks;
+         i += (size_t)gridDim.x * blockDim.x) {
+        A acc[N];
+        dev::unpack16<T, A>(dev::load_pack<T>(in, i, count, vin), acc);
+        dev::store_pack<Tout, A, N>(out, i, count, vout, acc, scale, do_scale != 0);
+    }
+}
+
+} // namespace
+
+int selected_allreduce_algo(const device_comm& dc, size_t bytes, bool symmetric, int dt, int op) {
+    const env_data& env = env_data::get();
+    if (dc.world() == 1)
+        return ga_copy;
+    const bool fits_oneshot = (size_t)dc.world() * ((bytes + 15) & ~(size_t)15) <= dc.staging_bytes();
+    if (bytes <= env.ar_oneshot_threshold && fits_oneshot)
+        return (dc.nvls() && bytes >= 4096) ? ga_nvls_oneshot : ga_oneshot;
+    if (symmetric)
+        return (dc.nvls() && nvls_type_ok(dt, op)) ? ga_nvls : ga_symm;
+    return ga_twoshot;
+}
+
+void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, int dt_in, int dt_out, int op,
+                      const launch_opts& o, cudaStream_t st) {
+    if (count == 0)
+        return;
+    const int W = dc.world();
+    const size_t esz = predefined_dtype_size(dt_in);
+    const size_t bytes = count * esz;
+    const int entries = dc.emulated() ? W : 1;
+
+    // are both buffers of every (emulated) rank inside the symmetric heap at equal offsets?
+    bool symmetric = dt_in == dt_out;
+    size_t in_off = 0, out_off = 0;
+    for (int e = 0; e < entries && symmetric; e++) {
+        const int owner = dc.emulated() ? e : dc.rank();
+        size_t io = dc.symm_offset(ra[e].send, owner), oo = dc.symm_offset(ra[e].recv, owner);
+        if (io == (size_t)-1 || oo == (size_t)-1 || (io & 15) || (oo & 15) || (e > 0 && (io != in_off || oo != out_off)))
+            symmetric = false;
+        in_off = io;
+        out_off = oo;
+    }
+
+    int algo = o.algo;
+    if (algo == ga_auto)
+        algo = selected_allreduce_algo(dc, bytes, symmetric, dt_in, op);
+    if ((algo == ga_symm || algo == ga_nvls) && !symmetric)
+        CCL_THROW("allreduce algorithm ", gpu_algo_name(algo), " needs buffers from the symmetric heap");
+    if ((algo == ga_nvls || algo == ga_nvls_oneshot) && !dc.nvls())
+        algo = algo == ga_nvls ? ga_symm : ga_oneshot;
+    if (algo == ga_nvls && !nvls_type_ok(dt_in, op))
+        algo = ga_symm;
+    if (W == 1)
+        algo = ga_copy;
+    dc.algo_hits[coll_allreduce * ga_last + algo]++;
+
+    dev::coll_args a{};
+    a.scale = o.scale;
+    a.do_scale = o.do_scale ? 1 : 0;
+    a.flags = 0;
+    const int threads = dc.threads();
+
+    if (algo == ga_copy) {
+        dispatch_reduce_types(dt_in, dt_out, op, [&](auto tin, auto tout, auto) {
+            typedef decltype(tin) T;
+            typedef decltype(tout) Tout;
+            for (int e = 0; e < entries; e++) {
+                if (ra[e].send == ra[e].recv && !o.do_scale && dt_in == dt_out)
+                    continue;
+                const size_t npacks = (bytes + 15) / 16;
+                int blocks = (int)std::min<size_t>((npacks + threads - 1) / threads, (size_t)dc.sm_count() * 4);
+                scale_cast_kernel<T, Tout><<<std::max(blocks, 1), threads, 0, st>>>(
+                    (const T*)ra[e].send, (Tout*)ra[e].recv, count, o.scale, a.do_scale);
+                CUDA_CHECK(cudaGetLastError());
+            }
+        });
+        return;
+    }
+
+    if (algo == ga_symm || algo == ga_nvls) {
+        a.count = count;
+        a.in_off = in_off;
+        a.out_off = out_off;
+        a.flags = dev::CF_SYMM_IN | dev::CF_SYMM_OUT | (algo == ga_nvls ? dev::CF_NVLS : 0);
+        prepare_args(dc, a, ra, st);
+        // per-rank slice, 16 KiB of it per block
+        const int blocks = pick_blocks(dc, bytes / 16 / W + 1, 1024, o.blocks);
+        CCLX_DISPATCH_DTYPE(dt_in, T, {
+            if (algo == ga_nvls) {
+                if constexpr (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value ||
+                              std::is_same<T, __half>::value)
+                    launch_kernel(dc, dev::allreduce_symm_kernel<T, dev::op_sum, true>, blocks, threads, st,
+                                  dc.table(), a);
+            }
+            else {
+                CCLX_DISPATCH_OP(op, OP,
+                                 launch_kernel(dc, dev::allreduce_symm_kernel<T, OP, false>, blocks, threads, st,
+                                               dc.table(), a));
+            }
+        });
+        return;
+    }
+
+    if (algo == ga_oneshot || algo == ga_nvls_oneshot) {
+        const size_t slot = (bytes + 15) & ~(size_t)15;
+        if ((size_t)W * slot > dc.staging_bytes())
+            algo = ga_twoshot;
+        else {
+            a.count = count;
+            a.flags = algo == ga_nvls_oneshot ? dev::CF_NVLS : 0;
+            prepare_args(dc, a, ra, st);
+            const int blocks = pick_blocks(dc, slot / 16, 2048, o.blocks);
+            dispatch_reduce_types(dt_in, dt_out, op, [&](auto tin, auto tout, auto opv) {
+                launch_kernel(dc, dev::allreduce_oneshot_kernel<decltype(tin), decltype(tout), decltype(opv)>, blocks,
+                              threads, st, dc.table(), a);
+            });
+            return;
+        }
+    }
+
+    // two-shot, chunked so that IN slots + OUT region fit one staging generation
+    CCL_THROW_IF_NOT(algo == ga_twoshot, "unknown allreduce algorithm ", algo);
+    const size_t osz = predefined_dtype_size(dt_out);
+    const size_t N = 16 / esz;
+    const size_t out_pack = N * osz;
+    size_t max_packs = (dc.staging_bytes() - 16 * (size_t)W) / (16 + out_pack);
+    max_packs = max_packs / W * W; // whole slices
+    CCL_THROW_IF_NOT(max_packs >= (size_t)W, "staging buffer too small for a two-shot allreduce");
+    const size_t chunk_elems = max_packs * N;
+    std::vector<dev::rank_args> cur(ra, ra + entries);
+    for (size_t done = 0; done < count; done += chunk_elems) {
+        const size_t n = std::min(chunk_elems, count - done);
+        for (int e = 0; e < entries; e++) {
+            cur[e].send = (const char*)ra[e].send + done * esz;
+            cur[e].recv = (char*)ra[e].recv + done * osz;
+        }
+        a.count = n;
+        prepare_args(dc, a, cur.data(), st);
+        const int blocks = pick_blocks(dc, (n * esz + 15) / 16 / W + 1, 1024, o.blocks);
+        dispatch_reduce_types(dt_in, dt_out, op, [&](auto tin, auto tout, auto opv) {
+            launch_kernel(dc, dev::allreduce_twoshot_kernel<decltype(tin), decltype(tout), decltype(opv)>, blocks,
+                          threads, st, dc.table(), a);
+        });
+    }
+}
+
+} // namespace gpu
+} // namespace cclx

@@ -1,0 +1,106 @@
+// Shared pieces of the launch translation units: datatype / reduction dispatch
+// and the real-vs-emulated launch helper.
+#pragma once
+#include <algorithm>
+
+#include "core/env.hpp"
+#include "core/log.hpp"
+#include "gpu/cuda_driver.hpp"
+#include "gpu/device/collectives.cuh"
+#include "gpu/device_comm.hpp"
+
+namespace cclx {
+namespace gpu {
+
+#define CCLX_DISPATCH_DTYPE(dt, T, ...)                                  \
+    switch (dt) {                                                        \
+        case dt_int8: { typedef signed char T; __VA_ARGS__; } break;     \
+        case dt_uint8: { typedef unsigned char T; __VA_ARGS__; } break;  \
+        case dt_int16: { typedef short T; __VA_ARGS__; } break;          \
+        case dt_uint16: { typedef unsigned short T; __VA_ARGS__; } break; \
+        case dt_int32: { typedef int T; __VA_ARGS__; } break;            \
+        case dt_uint32: { typedef unsigned int T; __VA_ARGS__; } break;  \
+        case dt_int64: { typedef long long T; __VA_ARGS__; } break;      \
+        case dt_uint64: { typedef unsigned long long T; __VA_ARGS__; } break; \
+        case dt_float16: { typedef __half T; __VA_ARGS__; } break;       \
+        case dt_float32: { typedef float T; __VA_ARGS__; } break;        \
+        case dt_float64: { typedef double T; __VA_ARGS__; } break;       \
+        case dt_bfloat16: { typedef __nv_bfloat16 T; __VA_ARGS__; } break; \
+        default: CCL_THROW("datatype ", dt, " is not supported by the GPU reduction kernels"); \
+    }
+
+#define CCLX_DISPATCH_OP(op, OP, ...)                                   \
+    switch (op) {                                                       \
+        case red_sum: { typedef dev::op_sum OP; __VA_ARGS__; } break;   \
+        case red_prod: { typedef dev::op_prod OP; __VA_ARGS__; } break; \
+        case red_min: { typedef dev::op_min OP; __VA_ARGS__; } break;   \
+        case red_max: { typedef dev::op_max OP; __VA_ARGS__; } break;   \
+        default: CCL_THROW("reduction ", op, " is not supported on GPU buffers"); \
+    }
+
+// Reductions: every same-type pair for the four built-in ops, plus the
+// widening / narrowing sum pairs used by mixed-precision data parallelism.
+// F is a generic lambda called as F(Tin{}, Tout{}, Op{}).
+template <class F>
+void dispatch_reduce_types(int dt_in, int dt_out, int op, F&& f) {
+    if (dt_in == dt_out) {
+        CCLX_DISPATCH_DTYPE(dt_in, T, CCLX_DISPATCH_OP(op, OP, f(T(), T(), OP())));
+        return;
+    }
+    CCL_THROW_IF_NOT(op == red_sum, "mixed-precision reductions support sum only");
+    if (dt_in == dt_bfloat16 && dt_out == dt_float32)
+        f(__nv_bfloat16(), float(), dev::op_sum());
+    else if (dt_in == dt_float16 && dt_out == dt_float32)
+        f(__half(), float(), dev::op_sum());
+    else if (dt_in == dt_float32 && dt_out == dt_bfloat16)
+        f(float(), __nv_bfloat16(), dev::op_sum());
+    else
+        CCL_THROW("unsupported datatype pair ", dt_in, " -> ", dt_out);
+}
+
+inline bool nvls_type_ok(int dt, int op) {
+    return op == red_sum && (dt == dt_float32 || dt == dt_bfloat16 || dt == dt_float16);
+}
+
+inline int pick_blocks(const device_comm& dc, size_t units, size_t units_per_block, int requested) {
+    int cap = dc.max_blocks();
+    if (requested > 0)
+        return std::max(1, std::min(requested, cap));
+    size_t want = (units + units_per_block - 1) / std::max<size_t>(units_per_block, 1);
+    return (int)std::max<size_t>(1, std::min<size_t>(want, (size_t)cap));
+}
+
+// Fill the mode-dependent part of coll_args.  In emulation mode the per-rank
+// table is uploaded to the device (the stream is drained first because an
+// earlier launch may still read the previous table).
+inline void prepare_args(device_comm& dc, dev::coll_args& a, const dev::rank_args* ra, cudaStream_t st) {
+    if (dc.emulated()) {
+        CUDA_CHECK(cudaStreamSynchronize(st));
+        CUDA_CHECK(cudaMemcpy(dc.emu_args_dev(), ra, dc.world() * sizeof(dev::rank_args), cudaMemcpyHostToDevice));
+        a.emu = 1;
+        a.emu_tab = dc.emu_args_dev();
+        a.r0 = ra[0];
+    }
+    else {
+        a.emu = 0;
+        a.emu_tab = nullptr;
+        a.r0 = ra[0];
+    }
+}
+
+template <class K, class... Args>
+void launch_kernel(device_comm& dc, K kernel, int blocks, int threads, cudaStream_t st, Args... args) {
+    dc.check_status();
+    if (dc.emulated()) {
+        void* argv[] = { (void*)&args... };
+        dim3 grid(blocks, dc.world());
+        CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)kernel, grid, dim3(threads), argv, 0, st));
+    }
+    else {
+        kernel<<<blocks, threads, 0, st>>>(args...);
+        CUDA_CHECK(cudaGetLastError());
+    }
+}
+
+} // namespace gpu
+} // namespace cclx

@@ -1,0 +1,354 @@
+// Launchers of the remaining GPU collectives (reduce_scatter, reduce,
+// allgatherv, alltoallv, broadcast, barrier, point-to-point) and the local
+// helper kernels.  Size thresholds follow the reference's structure
+// (small / large variants, src/common/env/env.cpp:171-184) with values tuned
+// for NVLink 5.
+#include "gpu/launch_common.cuh"
+
+namespace cclx {
+namespace gpu {
+
+namespace {
+size_t r16(size_t b) {
+    return (b + 15) & ~(size_t)15;
+}
+} // namespace
+
+void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t rc, int dt_in, int dt_out, int op,
+                           const launch_opts& o, cudaStream_t st) {
+    if (rc == 0)
+        return;
+    const int W = dc.world();
+    const int entries = dc.emulated() ? W : 1;
+    const size_t esz = predefined_dtype_size(dt_in), osz = predefined_dtype_size(dt_out);
+    const int threads = dc.threads();
+    dev::coll_args a{};
+    a.scale = o.scale;
+    a.do_scale = o.do_scale ? 1 : 0;
+
+    // registered send buffers: pull (or NVLS) without staging
+    bool symmetric = dt_in == dt_out;
+    size_t in_off = 0;
+    for (int e = 0; e < entries && symmetric; e++) {
+        size_t io = dc.symm_offset(ra[e].send, dc.emulated() ? e : dc.rank());
+        if (io == (size_t)-1 || (e > 0 && io != in_off))
+            symmetric = false;
+        in_off = io;
+    }
+    int algo = o.algo;
+    if (algo == ga_auto)
+        algo = (symmetric && W > 1 && rc * esz > env_data::get().rs_small_threshold)
+                   ? ((dc.nvls() && nvls_type_ok(dt_in, op)) ? ga_nvls : ga_symm)
+                   : ga_push;
+    if ((algo == ga_symm || algo == ga_nvls) && !symmetric)
+        CCL_THROW("reduce_scatter algorithm ", gpu_algo_name(algo), " needs a send buffer from the symmetric heap");
+    if (algo == ga_nvls && (!dc.nvls() || !nvls_type_ok(dt_in, op)))
+        algo = ga_symm;
+    dc.algo_hits[coll_reduce_scatter * ga_last + algo]++;
+
+    if (algo == ga_symm || algo == ga_nvls) {
+        a.count = rc;
+        a.in_off = in_off;
+        prepare_args(dc, a, ra, st);
+        const int blocks = pick_blocks(dc, rc * esz / 16 + 1, 1024, o.blocks);
+        CCLX_DISPATCH_DTYPE(dt_in, T, {
+            if (algo == ga_nvls) {
+                if constexpr (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value ||
+                              std::is_same<T, __half>::value)
+                    launch_kernel(dc, dev::reduce_scatter_symm_kernel<T, dev::op_sum, true>, blocks, threads, st,
+                                  dc.table(), a);
+            }
+            else {
+                CCLX_DISPATCH_OP(op, OP,
+                                 launch_kernel(dc, dev::reduce_scatter_symm_kernel<T, OP, false>, blocks, threads,
+                                               st, dc.table(), a));
+            }
+        });
+        return;
+    }
+
+    // staged push, chunked over the per-rank block so that world slots fit
+    const size_t N = 16 / esz;
+    size_t max_packs = dc.staging_bytes() / 16 / W;
+    CCL_THROW_IF_NOT(max_packs >= 1, "staging buffer too small for reduce_scatter");
+    const size_t chunk = max_packs * N;
+    std::vector<dev::rank_args> cur(ra, ra + entries);
+    if (rc <= chunk) {
+        a.count = rc;
+        a.stride = rc;
+        prepare_args(dc, a, ra, st);
+        const int blocks = pick_blocks(dc, r16(rc * esz) / 16, 1024, o.blocks);
+        dispatch_reduce_types(dt_in, dt_out, op, [&](auto tin, auto tout, auto opv) {
+            launch_kernel(dc, dev::reduce_scatter_kernel<decltype(tin), decltype(tout), decltype(opv)>, blocks,
+                          threads, st, dc.table(), a);
+        });
+        return;
+    }
+    // large: chunks of every rank block, addressed through the block stride
+    for (size_t done = 0; done < rc; done += chunk) {
+        const size_t n = std::min(chunk, rc - done);
+        for (int e = 0; e < entries; e++) {
+            cur[e].send = (const char*)ra[e].send + done * esz;
+            cur[e].recv = (char*)ra[e].recv + done * osz;
+        }
+        a.count = n;
+        a.stride = rc;
+        prepare_args(dc, a, cur.data(), st);
+        const int blocks = pick_blocks(dc, r16(n * esz) / 16, 1024, o.blocks);
+        dispatch_reduce_types(dt_in, dt_out, op, [&](auto tin, auto tout, auto opv) {
+            launch_kernel(dc, dev::reduce_scatter_kernel<decltype(tin), decltype(tout), decltype(opv)>, blocks,
+                          threads, st, dc.table(), a);
+        });
+    }
+}
+
+void launch_reduce(device_comm& dc, const dev::rank_args* ra, size_t count, int dt_in, int dt_out, int op, int root,
+                   const launch_opts& o, cudaStream_t st) {
+    if (count == 0)
+        return;
+    const int W = dc.world();
+    const int entries = dc.emulated() ? W : 1;
+    const size_t esz = predefined_dtype_size(dt_in), osz = predefined_dtype_size(dt_out);
+    const size_t N = 16 / esz;
+    size_t max_packs = dc.staging_bytes() / 16 / W;
+    const size_t chunk = max_packs * N;
+    dev::coll_args a{};
+    a.scale = o.scale;
+    a.do_scale = o.do_scale ? 1 : 0;
+    a.root = root;
+    dc.algo_hits[coll_reduce * ga_last + ga_push]++;
+    std::vector<dev::rank_args> cur(ra, ra + entries);
+    for (size_t done = 0; done < count; done += chunk) {
+        const size_t n = std::min(chunk, count - done);
+        for (int e = 0; e < entries; e++) {
+            cur[e].send = (const char*)ra[e].send + done * esz;
+            cur[e].recv = ra[e].recv ? (char*)ra[e].recv + done * osz : nullptr;
+        }
+        a.count = n;
+        prepare_args(dc, a, cur.data(), st);
+        const int blocks = pick_blocks(dc, r16(n * esz) / 16, 1024, o.blocks);
+        dispatch_reduce_types(dt_in, dt_out, op, [&](auto tin, auto tout, auto opv) {
+            launch_kernel(dc, dev::reduce_kernel<decltype(tin), decltype(tout), decltype(opv)>, blocks,
+                          dc.threads(), st, dc.table(), a);
+        });
+    }
+}
+
+void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_opts& o, cudaStream_t st) {
+    const int W = dc.world();
+    const int entries = dc.emulated() ? W : 1;
+    size_t total = 0, maxb = 0, rounded = 0;
+    for (int p = 0; p < W; p++) {
+        total += ra[0].scount[p];
+        maxb = std::max(maxb, ra[0].scount[p]);
+        rounded += r16(ra[0].scount[p]);
+    }
+    if (total == 0)
+        return;
+    const int threads = dc.threads();
+    dev::coll_args a{};
+
+    // equal 16-byte-multiple blocks into a symmetric recv buffer: direct stores
+    bool symm = W > 1;
+    size_t out_off = 0;
+    for (int e = 0; e < entries && symm; e++) {
+        size_t oo = dc.symm_offset(ra[e].recv, dc.emulated() ? e : dc.rank());
+        if (oo == (size_t)-1 || (oo & 15) || (e > 0 && oo != out_off))
+            symm = false;
+        out_off = oo;
+    }
+    for (int p = 0; p < W && symm; p++)
+        if (ra[0].scount[p] != maxb || (maxb & 15) || ra[0].sdispl[p] != (size_t)p * maxb)
+            symm = false;
+
+    int algo = o.algo;
+    if (algo == ga_auto) {
+        if (W == 1)
+            algo = ga_copy;
+        else if (symm && maxb > env_data::get().ag_small_threshold)
+            algo = dc.nvls() ? ga_nvls : ga_symm;
+        else if (maxb <= env_data::get().ag_small_threshold && rounded <= dc.staging_bytes())
+            algo = ga_push;
+        else
+            algo = ga_pull;
+    }
+    if ((algo == ga_symm || algo == ga_nvls) && !symm)
+        CCL_THROW("allgather algorithm ", gpu_algo_name(algo),
+                  " needs equal 16-byte-multiple blocks and a recv buffer from the symmetric heap");
+    if (algo == ga_nvls && !dc.nvls())
+        algo = ga_symm;
+    dc.algo_hits[coll_allgatherv * ga_last + algo]++;
+
+    if (algo == ga_copy) {
+        for (int e = 0; e < entries; e++) {
+            const int r = dc.emulated() ? e : dc.rank();
+            char* dst = (char*)ra[e].recv + ra[e].sdispl[r];
+            if (ra[e].send && ra[e].send != dst)
+                CUDA_CHECK(cudaMemcpyAsync(dst, ra[e].send, ra[e].scount[r], cudaMemcpyDeviceToDevice, st));
+        }
+        return;
+    }
+    if (algo == ga_symm || algo == ga_nvls) {
+        a.count = maxb;
+        a.out_off = out_off;
+        prepare_args(dc, a, ra, st);
+        const int blocks = pick_blocks(dc, maxb / 16, 2048, o.blocks);
+        if (algo == ga_nvls)
+            launch_kernel(dc, dev::allgather_symm_kernel<true>, blocks, threads, st, dc.table(), a);
+        else
+            launch_kernel(dc, dev::allgather_symm_kernel<false>, blocks, threads, st, dc.table(), a);
+        return;
+    }
+    if (algo == ga_push && rounded > dc.staging_bytes())
+        algo = ga_pull;
+    if (algo == ga_push) {
+        prepare_args(dc, a, ra, st);
+        const int blocks = pick_blocks(dc, r16(maxb) / 16, 2048, o.blocks);
+        launch_kernel(dc, dev::allgatherv_kernel<true>, blocks, threads, st, dc.table(), a);
+        return;
+    }
+    // pull, in rounds of at most one staging generation per block
+    const size_t cap = dc.staging_bytes() & ~(size_t)15;
+    std::vector<dev::rank_args> cur(ra, ra + entries);
+    for (size_t done = 0; done < maxb; done += cap) {
+        for (int e = 0; e < entries; e++) {
+            const int r = dc.emulated() ? e : dc.rank();
+            const char* src = ra[e].send ? (const char*)ra[e].send : (const char*)ra[e].recv + ra[e].sdispl[r];
+            cur[e].send = src + done;
+            for (int p = 0; p < W; p++) {
+                size_t b = ra[e].scount[p] > done ? ra[e].scount[p] - done : 0;
+                cur[e].scount[p] = std::min(b, cap);
+                cur[e].sdispl[p] = ra[e].sdispl[p] + done;
+            }
+        }
+        prepare_args(dc, a, cur.data(), st);
+        const int blocks = pick_blocks(dc, std::min(cap, maxb - done) / 16 + 1, 2048, o.blocks);
+        launch_kernel(dc, dev::allgatherv_kernel<false>, blocks, threads, st, dc.table(), a);
+    }
+}
+
+void launch_alltoallv(device_comm& dc, const dev::rank_args* ra, const launch_opts& o, cudaStream_t st) {
+    const int W = dc.world();
+    const int entries = dc.emulated() ? W : 1;
+    // local estimate only sizes the grid; the number of rounds is agreed inside the kernel
+    size_t lmax = 0;
+    for (int e = 0; e < entries; e++)
+        for (int p = 0; p < W; p++)
+            lmax = std::max(lmax, std::max(ra[e].scount[p], ra[e].rcount[p]));
+    dc.algo_hits[coll_alltoallv * ga_last + ga_push]++;
+    const size_t slot = (dc.staging_bytes() / W) & ~(size_t)15;
+    CCL_THROW_IF_NOT(slot >= 16, "staging buffer too small for alltoallv");
+    dev::coll_args a{};
+    prepare_args(dc, a, ra, st);
+    // every rank must use the same grid: derive it from the slot size, not from local counts
+    (void)lmax;
+    const int blocks = o.blocks > 0 ? pick_blocks(dc, 1, 1, o.blocks) : std::min(dc.max_blocks(), 32);
+    launch_kernel(dc, dev::alltoallv_kernel, blocks, dc.threads(), st, dc.table(), a);
+}
+
+void launch_broadcast(device_comm& dc, const dev::rank_args* ra, size_t bytes, int root, const launch_opts& o,
+                      cudaStream_t st) {
+    if (bytes == 0)
+        return;
+    const int W = dc.world();
+    const int entries = dc.emulated() ? W : 1;
+    if (W == 1) {
+        if (ra[0].send != ra[0].recv)
+            CUDA_CHECK(cudaMemcpyAsync(ra[0].recv, ra[0].send, bytes, cudaMemcpyDeviceToDevice, st));
+        return;
+    }
+    dc.algo_hits[coll_broadcast * ga_last + (dc.nvls() ? ga_nvls : ga_push)]++;
+    const size_t cap = dc.staging_bytes() & ~(size_t)15;
+    dev::coll_args a{};
+    a.root = root;
+    a.flags = dc.nvls() ? dev::CF_NVLS : 0;
+    std::vector<dev::rank_args> cur(ra, ra + entries);
+    for (size_t done = 0; done < bytes; done += cap) {
+        const size_t n = std::min(cap, bytes - done);
+        for (int e = 0; e < entries; e++) {
+            cur[e].send = ra[e].send ? (const char*)ra[e].send + done : nullptr;
+            cur[e].recv = (char*)ra[e].recv + done;
+        }
+        a.count = n;
+        prepare_args(dc, a, cur.data(), st);
+        const int blocks = pick_blocks(dc, n / 16 + 1, 2048, o.blocks);
+        launch_kernel(dc, dev::broadcast_kernel, blocks, dc.threads(), st, dc.table(), a);
+    }
+}
+
+void launch_barrier(device_comm& dc, cudaStream_t st) {
+    if (dc.world() == 1)
+        return;
+    dev::coll_args a{};
+    dev::rank_args dummy[dev::MAX_RANKS] = {};
+    prepare_args(dc, a, dummy, st);
+    dc.algo_hits[coll_barrier * ga_last + ga_push]++;
+    launch_kernel(dc, dev::barrier_kernel, 1, 64, st, dc.table(), a);
+}
+
+void launch_sendrecv(device_comm& dc, const dev::rank_args* ra, size_t bytes, int peer, bool is_send,
+                     cudaStream_t st) {
+    const int entries = dc.emulated() ? dc.world() : 1;
+    const size_t slot = dc.p2p().slot_bytes;
+    dev::coll_args a{};
+    a.peer = peer;
+    std::vector<dev::rank_args> cur(ra, ra + entries);
+    dc.algo_hits[(is_send ? coll_send : coll_recv) * ga_last + ga_push]++;
+    // zero-byte messages still synchronise the pair (one round)
+    for (size_t done = 0; done < std::max<size_t>(bytes, 1); done += slot) {
+        const size_t n = bytes ? std::min(slot, bytes - done) : 0;
+        for (int e = 0; e < entries; e++) {
+            cur[e].send = ra[e].send ? (const char*)ra[e].send + done : nullptr;
+            cur[e].recv = ra[e].recv ? (char*)ra[e].recv + done : nullptr;
+        }
+        a.count = n;
+        prepare_args(dc, a, cur.data(), st);
+        int blocks = (int)std::min<size_t>(dev::P2P_BLOCKS, std::max<size_t>(1, n / (64 << 10)));
+        launch_kernel(dc, dev::sendrecv_kernel, blocks, dc.threads(), st, dc.table(), dc.p2p(), a, is_send ? 1 : 0);
+    }
+}
+
+void launch_wait_unset_flag(device_comm& dc, cudaStream_t st) {
+    dev::coll_args a{};
+    dev::rank_args dummy[dev::MAX_RANKS] = {};
+    prepare_args(dc, a, dummy, st);
+    if (dc.emulated()) {
+        void* argv[] = { (void*)nullptr, (void*)&a };
+        const dev::comm_dev* t = dc.table();
+        argv[0] = (void*)&t;
+        CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)dev::wait_unset_flag_kernel, dim3(1, dc.world()),
+                                               dim3(64), argv, 0, st));
+    }
+    else {
+        dev::wait_unset_flag_kernel<<<1, 64, 0, st>>>(dc.table(), a);
+        CUDA_CHECK(cudaGetLastError());
+    }
+}
+
+void launch_reduce_local(const void* in, void* inout, size_t count, int dt, int op, cudaStream_t st) {
+    if (count == 0)
+        return;
+    const int threads = 512;
+    const int blocks = (int)std::min<size_t>((count + threads - 1) / threads, 148 * 4);
+    CCLX_DISPATCH_DTYPE(dt, T, CCLX_DISPATCH_OP(op, OP, {
+                            dev::reduce_local_kernel<T, OP><<<blocks, threads, 0, st>>>((const T*)in, (T*)inout, count);
+                        }));
+    CUDA_CHECK(cudaGetLastError());
+}
+
+void launch_pack(const void* const* ptrs_dev, const size_t* offs_dev, int n, void* fused, bool unpack,
+                 size_t max_tensor_bytes, cudaStream_t st) {
+    if (n <= 0)
+        return;
+    dev::pack_table t{ ptrs_dev, offs_dev, n };
+    const int bx = (int)std::max<size_t>(1, std::min<size_t>(max_tensor_bytes / (64 << 10) + 1, 32));
+    dim3 grid(bx, std::min(n, 1024));
+    if (unpack)
+        dev::pack_kernel<true><<<grid, 512, 0, st>>>(t, (char*)fused);
+    else
+        dev::pack_kernel<false><<<grid, 512, 0, st>>>(t, (char*)fused);
+    CUDA_CHECK(cudaGetLastError());
+}
+
+} // namespace gpu
+} // namespace cclx

@@ -1,0 +1,285 @@
+// Device kernels of the data-parallel training step that sit next to the
+// gradient allreduce: squared-norm of the reduced gradient bucket, fused AdamW
+// on flat buffers (fp32 master weights, bf16 model weights written in the same
+// pass, gradient read in the bucket's own dtype, clipping factor taken from
+// the device-resident norm), and a fused softmax cross-entropy that turns the
+// bf16 logits into their gradient in place.
+//
+// The reference library stops at the collective; these kernels are what makes
+// "allreduce fused with 1/world scale and cast" end to end: the bucket stays
+// bf16 on the wire and is widened exactly once, inside the optimizer.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "capi/capi_common.hpp"
+#include "core/log.hpp"
+#include "gpu/cuda_driver.hpp"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+template <class T>
+__device__ __forceinline__ float ldf(const T* p, size_t i);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p, size_t i) {
+    return p[i];
+}
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, size_t i) {
+    return __bfloat162float(p[i]);
+}
+
+// out[0] += sum(g^2); 8 elements per thread per step, grid-stride
+template <class T>
+__global__ void __launch_bounds__(512) sq_norm_kernel(const T* g, size_t n, float* out) {
+    float acc = 0.f;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float v = ldf<T>(g, i);
+        acc += v * v;
+    }
+    __shared__ float part[16];
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0)
+        part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0)
+            atomicAdd(out, v);
+    }
+}
+
+struct adamw_args {
+    float lr, beta1, beta2, eps, weight_decay;
+    float bias1, bias2; // 1 - beta^t
+    float grad_scale; // multiplies the gradient (1/world when the allreduce did not scale)
+    float max_norm; // <= 0: no clipping
+    size_t n_decay; // elements [0, n_decay) get weight decay
+};
+
+// one pass: read grad (T) + master/m/v (fp32), write master/m/v and the bf16 model copy
+template <class T>
+__global__ void __launch_bounds__(512)
+    adamw_flat_kernel(float* __restrict__ master, const T* __restrict__ grad, float* __restrict__ m,
+                      float* __restrict__ v, __nv_bfloat16* __restrict__ model, size_t n, adamw_args a,
+                      const float* __restrict__ sq_norm) {
+    float clip = 1.f;
+    if (a.max_norm > 0.f && sq_norm) {
+        const float norm = sqrtf(*sq_norm) * a.grad_scale;
+        clip = fminf(1.f, a.max_norm / (norm + 1e-6f));
+    }
+    const float gs = a.grad_scale * clip;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float g = ldf<T>(grad, i) * gs;
+        float p = master[i];
+        float mi = m[i] * a.beta1 + (1.f - a.beta1) * g;
+        float vi = v[i] * a.beta2 + (1.f - a.beta2) * g * g;
+        const float wd = i < a.n_decay ? a.weight_decay : 0.f;
+        p -= a.lr * (wd * p + (mi / a.bias1) / (sqrtf(vi / a.bias2) + a.eps));
+        master[i] = p;
+        m[i] = mi;
+        v[i] = vi;
+        if (model)
+            model[i] = __float2bfloat16_rn(p);
+    }
+}
+
+// One block per row of logits [rows, vocab] (bf16, row pitch ld).  Computes
+// loss_row = logsumexp - logit[target] and overwrites the row with
+// (softmax - onehot) * grad_scale, all math in fp32.  Rows whose target is
+// negative (ignore) produce zero loss and zero gradient.  Columns
+// [vocab, vocab + pad_cols) are alignment padding and receive zeros.
+__global__ void __launch_bounds__(1024)
+    softmax_xent_kernel(__nv_bfloat16* logits, const long long* targets, float* loss_rows, int vocab, size_t ld,
+                        float grad_scale, int pad_cols) {
+    const size_t row = blockIdx.x;
+    __nv_bfloat16* x = logits + row * ld;
+    const long long tgt = targets[row];
+    __shared__ float red[32];
+    __shared__ float s_max, s_sum;
+    const int nv = vocab / 8; // whole 16-byte packs (row start is 16-byte aligned when ld % 8 == 0)
+    const bool vec = (ld % 8 == 0) && ((((uintptr_t)logits) & 15) == 0);
+
+    float mx = -INFINITY;
+    if (vec) {
+        const uint4* xv = reinterpret_cast<const uint4*>(x);
+        for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+            uint4 u = xv[i];
+            const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+            for (int k = 0; k < 8; k++)
+                mx = fmaxf(mx, __bfloat162float(h[k]));
+        }
+        for (int i = nv * 8 + threadIdx.x; i < vocab; i += blockDim.x)
+            mx = fmaxf(mx, __bfloat162float(x[i]));
+    }
+    else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x)
+            mx = fmaxf(mx, __bfloat162float(x[i]));
+    }
+    mx = warp_max(mx);
+    if ((threadIdx.x & 31) == 0)
+        red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : -INFINITY;
+        v = warp_max(v);
+        if (threadIdx.x == 0)
+            s_max = v;
+    }
+    __syncthreads();
+    mx = s_max;
+
+    float sum = 0.f;
+    if (vec) {
+        const uint4* xv = reinterpret_cast<const uint4*>(x);
+        for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+            uint4 u = xv[i];
+            const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+            for (int k = 0; k < 8; k++)
+                sum += __expf(__bfloat162float(h[k]) - mx);
+        }
+        for (int i = nv * 8 + threadIdx.x; i < vocab; i += blockDim.x)
+            sum += __expf(__bfloat162float(x[i]) - mx);
+    }
+    else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x)
+            sum += __expf(__bfloat162float(x[i]) - mx);
+    }
+    sum = warp_sum(sum);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0)
+        red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+        v = warp_sum(v);
+        if (threadIdx.x == 0)
+            s_sum = v;
+    }
+    __syncthreads();
+    sum = s_sum;
+    const bool ignore = tgt < 0 || tgt >= vocab;
+    if (threadIdx.x == 0)
+        loss_rows[row] = ignore ? 0.f : (logf(sum) + mx - __bfloat162float(x[tgt]));
+    __syncthreads(); // x[tgt] is read before any thread overwrites the row
+    const float inv = ignore ? 0.f : grad_scale / sum;
+    // alignment padding behind the vocabulary takes no part in the softmax: zero gradient
+    for (int i = vocab + threadIdx.x; i < vocab + pad_cols; i += blockDim.x)
+        x[i] = __float2bfloat16_rn(0.f);
+    if (vec) {
+        uint4* xv = reinterpret_cast<uint4*>(x);
+        for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+            uint4 u = xv[i];
+            __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(&u);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                float p = __expf(__bfloat162float(h[k]) - mx) * inv;
+                if ((long long)(i * 8 + k) == tgt)
+                    p -= grad_scale;
+                h[k] = __float2bfloat16_rn(p);
+            }
+            xv[i] = u;
+        }
+        for (int i = nv * 8 + threadIdx.x; i < vocab; i += blockDim.x) {
+            float p = __expf(__bfloat162float(x[i]) - mx) * inv;
+            if (i == tgt)
+                p -= grad_scale;
+            x[i] = __float2bfloat16_rn(p);
+        }
+    }
+    else {
+        for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+            float p = __expf(__bfloat162float(x[i]) - mx) * inv;
+            if (!ignore && i == tgt)
+                p -= grad_scale;
+            x[i] = __float2bfloat16_rn(p);
+        }
+    }
+}
+
+int grid_for(size_t n, int threads) {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    size_t want = (n + threads - 1) / threads;
+    size_t cap = (size_t)sms * 4;
+    return (int)(want < cap ? (want ? want : 1) : cap);
+}
+
+} // namespace
+
+// dt: 9 = float32, 11 = bfloat16 (ccl datatype codes)
+CCLX_API int cclx_sq_norm(const void* g, size_t n, int dt, float* out, void* stream) {
+    return cclx::capi::guard([&] {
+        if (n == 0)
+            return;
+        const int blocks = grid_for(n, 512);
+        if (dt == 11)
+            sq_norm_kernel<__nv_bfloat16><<<blocks, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)g, n, out);
+        else if (dt == 9)
+            sq_norm_kernel<float><<<blocks, 512, 0, (cudaStream_t)stream>>>((const float*)g, n, out);
+        else
+            CCL_THROW("sq_norm supports float32 and bfloat16 gradients");
+        CUDA_CHECK(cudaGetLastError());
+    });
+}
+
+CCLX_API int cclx_adamw_flat(float* master, const void* grad, int grad_dt, float* m, float* v, void* model_bf16,
+                             size_t n, size_t n_decay, float lr, float beta1, float beta2, float eps,
+                             float weight_decay, int step, float grad_scale, float max_norm, const float* sq_norm,
+                             void* stream) {
+    return cclx::capi::guard([&] {
+        if (n == 0)
+            return;
+        adamw_args a;
+        a.lr = lr;
+        a.beta1 = beta1;
+        a.beta2 = beta2;
+        a.eps = eps;
+        a.weight_decay = weight_decay;
+        a.bias1 = 1.f - powf(beta1, (float)step);
+        a.bias2 = 1.f - powf(beta2, (float)step);
+        a.grad_scale = grad_scale;
+        a.max_norm = max_norm;
+        a.n_decay = n_decay;
+        const int blocks = grid_for(n, 512);
+        if (grad_dt == 11)
+            adamw_flat_kernel<__nv_bfloat16><<<blocks, 512, 0, (cudaStream_t)stream>>>(
+                master, (const __nv_bfloat16*)grad, m, v, (__nv_bfloat16*)model_bf16, n, a, sq_norm);
+        else if (grad_dt == 9)
+            adamw_flat_kernel<float><<<blocks, 512, 0, (cudaStream_t)stream>>>(master, (const float*)grad, m, v,
+                                                                               (__nv_bfloat16*)model_bf16, n, a, sq_norm);
+        else
+            CCL_THROW("adamw_flat supports float32 and bfloat16 gradients");
+        CUDA_CHECK(cudaGetLastError());
+    });
+}
+
+CCLX_API int cclx_softmax_xent(void* logits_bf16, const long long* targets, float* loss_rows, size_t rows, int vocab,
+                               size_t ld, float grad_scale, int pad_cols, void* stream) {
+    return cclx::capi::guard([&] {
+        if (rows == 0)
+            return;
+        softmax_xent_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits_bf16, targets,
+                                                                              loss_rows, vocab, ld, grad_scale, pad_cols);
+        CUDA_CHECK(cudaGetLastError());
+    });
+}

@@ -1,0 +1,320 @@
+"""Collective kernels against a plain PyTorch fp32 restatement, with all ranks
+emulated on one GPU (cooperative launch, blockIdx.y = rank).  Mirrors the
+reference's functional matrix (tests/functional/conf.cpp:51-53: sizes 17,
+32771, 262144; every datatype / reduction; in-place and out-of-place) with
+canary padding around every output buffer."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+WORLDS = [2, 4, 8]
+SIZES = [1, 17, 4096, 32771, 262144]
+CANARY = 64
+
+
+@pytest.fixture(scope="module", params=WORLDS)
+def group(request):
+    from oneccl_b200.ops.device_group import DeviceGroup
+
+    g = DeviceGroup.emulated(request.param, heap_bytes=96 << 20, staging_bytes=8 << 20)
+    yield g
+    g.close()
+
+
+def _padded(n, dtype, fill=None):
+    """Tensor of n elements inside a larger buffer with canary words on both sides."""
+    buf = torch.full((n + 2 * CANARY,), 77, dtype=dtype, device="cuda")
+    view = buf[CANARY:CANARY + n]
+    if fill is not None:
+        view.copy_(fill)
+    return buf, view
+
+
+def _canary_ok(buf, n):
+    ref = torch.full((CANARY,), 77, dtype=buf.dtype, device="cuda")
+    return torch.equal(buf[:CANARY], ref) and torch.equal(buf[CANARY + n:], ref)
+
+
+def _inputs(world, n, dtype, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    outs = []
+    for r in range(world):
+        if dtype.is_floating_point:
+            x = (torch.rand(n, generator=g, device="cuda") * 2 - 1).to(dtype)
+        else:
+            x = torch.randint(-3, 4, (n,), generator=g, device="cuda").to(dtype)
+        outs.append(x)
+    return outs
+
+
+def _tol(dtype, world):
+    if dtype == torch.bfloat16:
+        return dict(rtol=2e-2, atol=2e-2 * world ** 0.5)
+    if dtype == torch.float16:
+        return dict(rtol=2e-3, atol=2e-3 * world ** 0.5)
+    if dtype == torch.float32:
+        return dict(rtol=1e-5, atol=1e-5)
+    return dict(rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("n", SIZES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.int32])
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot"])
+def test_allreduce_sum(group, n, dtype, algo):
+    W = group.world
+    xs = _inputs(W, n, dtype)
+    ref = torch.stack([x.double() for x in xs]).sum(0)
+    bufs = [_padded(n, dtype) for _ in range(W)]
+    group.allreduce(xs, [b[1] for b in bufs], op="sum", algo=algo)
+    torch.cuda.synchronize()
+    group.check()
+    for buf, out in bufs:
+        torch.testing.assert_close(out.double(), ref, **_tol(dtype, W))
+        assert _canary_ok(buf, n)
+    # every rank holds bit-identical results
+    for _, out in bufs[1:]:
+        assert torch.equal(out, bufs[0][1])
+
+
+@pytest.mark.parametrize("op", ["prod", "min", "max"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.int64, torch.bfloat16])
+def test_allreduce_other_ops(group, op, dtype):
+    W, n = group.world, 3001
+    xs = _inputs(W, n, dtype, seed=3)
+    st = torch.stack([x.double() for x in xs])
+    ref = {"prod": st.prod(0), "min": st.min(0).values, "max": st.max(0).values}[op]
+    outs = [torch.empty_like(x) for x in xs]
+    group.allreduce(xs, outs, op=op, algo="auto")
+    torch.cuda.synchronize()
+    group.check()
+    for o in outs:
+        torch.testing.assert_close(o.double(), ref, **_tol(dtype, W))
+
+
+def test_allreduce_inplace_unaligned_and_repeat(group):
+    """In-place, pointer offset by one element (not 16-byte aligned), called several
+    times in a row so that both staging generations and the epoch flags are reused."""
+    W, n = group.world, 5003
+    for it in range(5):
+        for algo in ("oneshot", "twoshot"):
+            base = [torch.zeros(n + 1, dtype=torch.float32, device="cuda") for _ in range(W)]
+            xs = [b[1:] for b in base]
+            src = _inputs(W, n, torch.float32, seed=10 + it)
+            for x, s in zip(xs, src):
+                x.copy_(s)
+            ref = torch.stack(src).sum(0)
+            group.allreduce(xs, xs, algo=algo)
+            torch.cuda.synchronize()
+            group.check()
+            for x in xs:
+                torch.testing.assert_close(x, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_allreduce_scale_and_cast(group):
+    """bf16 in, fp32 out, fused 1/world scale (the data-parallel epilogue)."""
+    W, n = group.world, 70001
+    xs = _inputs(W, n, torch.bfloat16, seed=5)
+    ref = torch.stack([x.float() for x in xs]).sum(0) / W
+    for algo in ("oneshot", "twoshot"):
+        outs = [torch.empty(n, dtype=torch.float32, device="cuda") for _ in range(W)]
+        group.allreduce(xs, outs, algo=algo, scale=1.0 / W)
+        torch.cuda.synchronize()
+        group.check()
+        for o in outs:
+            torch.testing.assert_close(o, ref, rtol=1e-5, atol=1e-5)
+
+
+def test_allreduce_twoshot_chunked(group):
+    """Message larger than one staging generation: several launches alternate generations."""
+    W = group.world
+    n = (20 << 20) // 4  # 20 MiB of fp32 with 8 MiB staging
+    xs = _inputs(W, n, torch.float32, seed=7)
+    ref = torch.stack(xs).sum(0)
+    outs = [torch.empty_like(x) for x in xs]
+    group.allreduce(xs, outs, algo="twoshot")
+    torch.cuda.synchronize()
+    group.check()
+    for o in outs:
+        torch.testing.assert_close(o, ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [24, 1000, 40003])
+def test_allreduce_symmetric_zero_copy(group, dtype, n):
+    W = group.world
+    bufs = group.symm_empty((n,), dtype=dtype)
+    src = _inputs(W, n, dtype, seed=11)
+    for b, s in zip(bufs, src):
+        b.copy_(s)
+    ref = torch.stack([s.double() for s in src]).sum(0)
+    group.allreduce(bufs, bufs, algo="symm")
+    torch.cuda.synchronize()
+    group.check()
+    for b in bufs:
+        torch.testing.assert_close(b.double(), ref, **_tol(dtype, W))
+    assert group.algo_hits("allreduce", "symm") >= 1
+    group.symm_free(bufs)
+
+
+@pytest.mark.parametrize("n", [1, 17, 32771])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_reduce_scatter(group, n, dtype):
+    W = group.world
+    xs = _inputs(W, n * W, dtype, seed=2)
+    full = torch.stack([x.double() for x in xs]).sum(0)
+    bufs = [_padded(n, dtype) for _ in range(W)]
+    group.reduce_scatter(xs, [b[1] for b in bufs])
+    torch.cuda.synchronize()
+    group.check()
+    for r, (buf, out) in enumerate(bufs):
+        torch.testing.assert_close(out.double(), full[r * n:(r + 1) * n], **_tol(dtype, W))
+        assert _canary_ok(buf, n)
+
+
+def test_reduce_scatter_symmetric(group):
+    W, n = group.world, 4099
+    send = group.symm_empty((n * W,), dtype=torch.float32)
+    src = _inputs(W, n * W, torch.float32, seed=4)
+    for b, s in zip(send, src):
+        b.copy_(s)
+    full = torch.stack(src).sum(0)
+    outs = [torch.empty(n, dtype=torch.float32, device="cuda") for _ in range(W)]
+    group.reduce_scatter(send, outs, algo="symm")
+    torch.cuda.synchronize()
+    group.check()
+    for r, o in enumerate(outs):
+        torch.testing.assert_close(o, full[r * n:(r + 1) * n], rtol=1e-5, atol=1e-5)
+    group.symm_free(send)
+
+
+@pytest.mark.parametrize("root", [0, 1])
+def test_reduce_and_broadcast(group, root):
+    W, n = group.world, 10007
+    xs = _inputs(W, n, torch.float32, seed=8)
+    ref = torch.stack(xs).sum(0)
+    outs = [torch.zeros(n, device="cuda") if r == root else None for r in range(W)]
+    group.reduce(xs, outs, root=root)
+    torch.cuda.synchronize()
+    group.check()
+    torch.testing.assert_close(outs[root], ref, rtol=1e-5, atol=1e-5)
+    # broadcast the result back out, in place
+    bufs = [outs[root].clone() if r == root else torch.zeros(n, device="cuda") for r in range(W)]
+    group.broadcast(bufs, bufs, root=root)
+    torch.cuda.synchronize()
+    group.check()
+    for b in bufs:
+        assert torch.equal(b, bufs[root])
+
+
+@pytest.mark.parametrize("algo", ["push", "pull"])
+def test_allgatherv_unequal(group, algo):
+    W = group.world
+    counts = [1000 + 37 * r for r in range(W)]
+    counts[0] = 1  # tiny and odd blocks
+    src = [torch.arange(c, device="cuda", dtype=torch.float32) + 1000 * r for r, c in enumerate(counts)]
+    ref = torch.cat(src)
+    total = sum(counts)
+    bufs = [_padded(total, torch.float32) for _ in range(W)]
+    group.allgatherv(src, [b[1] for b in bufs], counts=counts, algo=algo)
+    torch.cuda.synchronize()
+    group.check()
+    for buf, out in bufs:
+        assert torch.equal(out, ref)
+        assert _canary_ok(buf, total)
+
+
+def test_allgather_inplace_and_symmetric(group):
+    W, per = group.world, 2048
+    outs = [torch.zeros(per * W, device="cuda") for _ in range(W)]
+    for r, o in enumerate(outs):
+        o[r * per:(r + 1) * per] = torch.arange(per, device="cuda") + r * 10000
+    ref = torch.cat([torch.arange(per, device="cuda", dtype=torch.float32) + r * 10000 for r in range(W)])
+    group.allgatherv(None, outs)  # in place: send == recv + offset(rank)
+    torch.cuda.synchronize()
+    group.check()
+    for o in outs:
+        assert torch.equal(o, ref)
+    sym = group.symm_empty((per * W,), dtype=torch.float32)
+    src = [ref[r * per:(r + 1) * per].clone() for r in range(W)]
+    group.allgatherv(src, sym, algo="symm")
+    torch.cuda.synchronize()
+    group.check()
+    for s in sym:
+        assert torch.equal(s, ref)
+    group.symm_free(sym)
+
+
+def test_alltoallv_variable_counts(group):
+    W = group.world
+    g = torch.Generator().manual_seed(1)
+    cnt = torch.randint(0, 700, (W, W), generator=g).tolist()  # cnt[r][q]: r sends to q
+    send = [torch.cat([torch.full((cnt[r][q],), float(r * 100 + q), device="cuda") for q in range(W)])
+            for r in range(W)]
+    recv_counts = [[cnt[p][r] for p in range(W)] for r in range(W)]
+    bufs = [_padded(sum(recv_counts[r]), torch.float32) for r in range(W)]
+    group.alltoallv(send, [b[1] for b in bufs], send_counts=cnt, recv_counts=recv_counts)
+    torch.cuda.synchronize()
+    group.check()
+    for r, (buf, out) in enumerate(bufs):
+        ref = torch.cat([torch.full((cnt[p][r],), float(p * 100 + r), device="cuda") for p in range(W)])
+        assert torch.equal(out, ref)
+        assert _canary_ok(buf, ref.numel())
+
+
+def test_alltoall_multi_round(group):
+    """Blocks larger than a staging slot: the kernel agrees on extra rounds on the device."""
+    W = group.world
+    per = ((8 << 20) // W // 4) * 2 + 123  # two slots and a bit, in fp32 elements
+    send = [torch.arange(per * W, device="cuda", dtype=torch.float32) + r * 1e6 for r in range(W)]
+    recv = [torch.zeros(per * W, device="cuda") for _ in range(W)]
+    group.alltoallv(send, recv)
+    torch.cuda.synchronize()
+    group.check()
+    for r in range(W):
+        ref = torch.cat([send[p][r * per:(r + 1) * per] for p in range(W)])
+        assert torch.equal(recv[r], ref)
+
+
+def test_barrier_and_sendrecv(group):
+    W = group.world
+    group.barrier()
+    n = 300000
+    src = [torch.arange(n, device="cuda", dtype=torch.float32) + r for r in range(W)]
+    dst = [torch.zeros(n, device="cuda") for _ in range(W)]
+    # ring: even ranks send to rank+1, odd ranks receive from rank-1 (one launch holds both sides)
+    peers, is_send = [], []
+    for r in range(W):
+        if r % 2 == 0:
+            peers.append(r + 1 if r + 1 < W else -1)
+            is_send.append(True)
+        else:
+            peers.append(r - 1)
+            is_send.append(False)
+    for _ in range(2):  # twice: sequence numbers advance
+        group.sendrecv(src, dst, peers, is_send)
+    torch.cuda.synchronize()
+    group.check()
+    for r in range(1, W, 2):
+        assert torch.equal(dst[r], src[r - 1])
+
+
+def test_wait_timeout_reports_status():
+    """A device-side wait that nothing satisfies runs out after its limit, the
+    kernel returns, the status word says so and the context keeps working."""
+    from oneccl_b200 import CclError
+    from oneccl_b200.ops.device_group import DeviceGroup
+
+    g = DeviceGroup.emulated(2, heap_bytes=48 << 20, staging_bytes=1 << 20)
+    g.set_timeout_ms(300)
+    g.wait_unset_flag()
+    torch.cuda.synchronize()
+    assert g.status(0) == 3 and g.status(1) == 3  # ST_FLAG_TIMEOUT
+    with pytest.raises(CclError):
+        g.check()
+    g.clear_status()
+    xs = [torch.ones(100, device="cuda") for _ in range(2)]
+    g.allreduce(xs, xs)
+    torch.cuda.synchronize()
+    assert torch.equal(xs[0], torch.full((100,), 2.0, device="cuda"))
+    g.close()

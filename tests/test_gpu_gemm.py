@@ -1,0 +1,97 @@
+"""tcgen05 GEMM (plain and fused with a collective) against torch fp32 matmul."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, w, silu=False):
+    y = a.float() @ w.float().t()
+    if silu:
+        y = torch.nn.functional.silu(y)
+    return y
+
+
+def _check(out, ref, K):
+    # bf16 output of an fp32 accumulation: one rounding of the result
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err <= 1.0e-2 * scale + 1e-3, f"max err {err} vs scale {scale} (K={K})"
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 64), (128, 256, 256), (256, 512, 512), (1024, 1792, 1024),
+                                   (384, 128, 192), (200, 264, 136)])
+def test_gemm_plain(shape):
+    from oneccl_b200.ops.gemm import gemm_bf16
+
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.1).to(torch.bfloat16)
+    out = gemm_bf16(a, w, check=True)
+    torch.cuda.synchronize()
+    _check(out, _ref(a, w), K)
+
+
+def test_gemm_silu_and_persistence():
+    """More tiles than CTAs (each CTA loops, both TMEM accumulators are reused) + SiLU epilogue."""
+    from oneccl_b200.ops.gemm import gemm_bf16
+
+    M, N, K = 2048, 1024, 512
+    g = torch.Generator(device="cuda").manual_seed(1)
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    out = gemm_bf16(a, w, epilogue="silu", ctas=8, check=True)
+    torch.cuda.synchronize()
+    _check(out, _ref(a, w, silu=True), K)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ag_gemm_emulated(world):
+    from oneccl_b200.ops.device_group import DeviceGroup
+    from oneccl_b200.ops.gemm import FusedPlan
+
+    M, N, K = world * 256, 512, 256
+    grp = DeviceGroup.emulated(world, heap_bytes=64 << 20, staging_bytes=1 << 20)
+    plan = FusedPlan(grp, "ag_gemm", M, N, K, epilogue="silu", n_comm=2)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(world)]
+    per = M // world
+    for it in range(2):  # twice: flags and sequence numbers are reused
+        for r in range(world):
+            plan.x_shard(r).copy_(x[r * per:(r + 1) * per] * (it + 1))
+        outs = plan.run(None, ws)
+        torch.cuda.synchronize()
+        grp.check()
+        for r in range(world):
+            assert plan.error(r) == 0
+            assert torch.equal(plan.x_full(r), x * (it + 1))
+            _check(outs[r], _ref(x * (it + 1), ws[r], silu=True), K)
+    plan.close()
+    grp.close()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gemm_rs_emulated(world):
+    from oneccl_b200.ops.device_group import DeviceGroup
+    from oneccl_b200.ops.gemm import FusedPlan
+
+    M, N, K = world * 128, 512, 192
+    grp = DeviceGroup.emulated(world, heap_bytes=64 << 20, staging_bytes=1 << 20)
+    plan = FusedPlan(grp, "gemm_rs", M, N, K)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    hs = [torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(world)]
+    # every partial is rounded to bf16 before the fp32 reduction
+    full = sum(_ref(h, w).to(torch.bfloat16).float() for h, w in zip(hs, ws))
+    per = M // world
+    for it in range(2):
+        outs = plan.run(hs, ws)
+        torch.cuda.synchronize()
+        grp.check()
+        for r in range(world):
+            assert plan.error(r) == 0
+            _check(outs[r], full[r * per:(r + 1) * per], K)
+    plan.close()
+    grp.close()

@@ -1,0 +1,68 @@
+"""Fused cross-entropy, gradient norm and flat AdamW against PyTorch fp32."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,vocab,pad", [(64, 1000, 24), (33, 50257, 47), (8, 257, 0)])
+def test_softmax_xent(rows, vocab, pad):
+    from oneccl_b200.ops.train import softmax_cross_entropy
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    logits = (torch.randn(rows, vocab + pad, generator=g, device="cuda") * 3).to(torch.bfloat16)
+    tgt = torch.randint(0, vocab, (rows,), generator=g, device="cuda")
+    ref_in = logits[:, :vocab].float().clone().requires_grad_(True)
+    ref_loss = torch.nn.functional.cross_entropy(ref_in, tgt)
+    ref_loss.backward()
+    x = logits.clone().requires_grad_(True)
+    y = x * 1.0  # non-leaf, like the output of the lm head
+    loss = softmax_cross_entropy(y, tgt, vocab)
+    loss.backward()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(loss, ref_loss, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(x.grad[:, :vocab].float(), ref_in.grad, rtol=2e-2, atol=1e-5)
+    if pad:
+        assert torch.count_nonzero(x.grad[:, vocab:]) == 0
+
+
+def test_flat_adamw_matches_torch():
+    from oneccl_b200.ops.train import FlatAdamW
+
+    n, n_decay = 10007, 8000
+    g = torch.Generator(device="cuda").manual_seed(1)
+    p0 = torch.randn(n, generator=g, device="cuda")
+    model = p0.to(torch.bfloat16)
+    ref_p = model.float().clone().requires_grad_(True)
+    ref_a = ref_p[:n_decay].detach().clone().requires_grad_(True)
+    ref_b = ref_p[n_decay:].detach().clone().requires_grad_(True)
+    ropt = torch.optim.AdamW([{"params": [ref_a], "weight_decay": 0.1}, {"params": [ref_b], "weight_decay": 0.0}],
+                             lr=1e-2, betas=(0.9, 0.95), eps=1e-8)
+    opt = FlatAdamW(model, n_decay, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_norm=1.0)
+    for step in range(3):
+        grad = (torch.randn(n, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+        gf = grad.float()
+        clip = min(1.0, 1.0 / (gf.norm().item() + 1e-6))
+        ref_a.grad = gf[:n_decay] * clip
+        ref_b.grad = gf[n_decay:] * clip
+        ropt.step()
+        opt.step(grad)
+    torch.cuda.synchronize()
+    ref = torch.cat([ref_a.detach(), ref_b.detach()])
+    torch.testing.assert_close(opt.master, ref, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(model.float(), ref, rtol=1e-2, atol=1e-2)
+
+
+def test_reduce_local_and_pack():
+    from oneccl_b200.ops.device_group import reduce_local
+
+    a = torch.arange(1000, device="cuda", dtype=torch.float32)
+    b = torch.ones(1000, device="cuda")
+    reduce_local(a, b, op="sum")
+    torch.cuda.synchronize()
+    assert torch.equal(b, a + 1)
+    c = torch.full((1000,), 5, device="cuda", dtype=torch.int32)
+    d = torch.arange(1000, device="cuda", dtype=torch.int32)
+    reduce_local(c, d, op="max")
+    torch.cuda.synchronize()
+    assert torch.equal(d, torch.clamp(torch.arange(1000, device="cuda", dtype=torch.int32), min=5))
