@@ -1,0 +1,102 @@
+// Abstract transport layer for CPU buffers: tagged non-blocking send / recv with
+// N endpoints (one per worker), explicit progress, communicator split.
+//
+// Same contract as the reference's atl_base_comm (src/atl/atl_base_comm.hpp:32-281)
+// and its 64-bit tag layout (src/comm/atl_tag.hpp:28-190): a message is matched
+// by (source rank, tag) where tag = comm_id | sched_id | op_id.  The transports
+// behind it are this library's own: `tcp` (a socket mesh, any host) and `shm`
+// (single-producer rings in POSIX shared memory between ranks of one host,
+// layered under tcp); MPI / libfabric are not linked.
+#pragma once
+#include <atomic>
+#include <cstddef>
+#include <cstdint>
+#include <memory>
+#include <vector>
+
+namespace cclx {
+
+class pmi;
+
+struct atl_req {
+    std::atomic<int> done{ 0 };
+    size_t bytes = 0; // received size
+    void reset() {
+        done.store(0, std::memory_order_relaxed);
+        bytes = 0;
+    }
+    bool is_done() const { return done.load(std::memory_order_acquire) != 0; }
+};
+
+// tag = [comm_id:16][sched_id:24][op_id:24]
+struct atl_tag {
+    static constexpr uint64_t MAX_COMM = (1u << 16) - 1;
+    static constexpr uint64_t MAX_SCHED = (1u << 24) - 1;
+    static constexpr uint64_t MAX_OP = (1u << 24) - 1;
+    static uint64_t make(uint64_t comm_id, uint64_t sched_id, uint64_t op_id) {
+        return ((comm_id & MAX_COMM) << 48) | ((sched_id & MAX_SCHED) << 24) | (op_id & MAX_OP);
+    }
+    // reserved sched ids for point-to-point traffic (never cached, reference atl_tag.hpp:33-49)
+    static constexpr uint64_t PT2PT_SCHED = MAX_SCHED;
+    static constexpr uint64_t PT2PT_ACK_SCHED = MAX_SCHED - 1;
+    static constexpr uint64_t INTERNAL_SCHED = MAX_SCHED - 2;
+};
+
+// process-wide mesh of connections among the ranks of one "world" (one KVS rendezvous)
+class atl_transport {
+public:
+    virtual ~atl_transport() = default;
+    virtual int world_rank() const = 0;
+    virtual int world_size() const = 0;
+    virtual int ep_count() const = 0;
+    // `dst` / `src` are world ranks of this transport
+    virtual void send(int ep, const void* buf, size_t len, int dst, uint64_t tag, atl_req* req) = 0;
+    virtual void recv(int ep, void* buf, size_t len, int src, uint64_t tag, atl_req* req) = 0;
+    virtual bool probe(int ep, int src, uint64_t tag, size_t* len) = 0;
+    virtual void poll(int ep) = 0;
+    virtual bool same_host(int peer) const = 0;
+    virtual const char* name() const = 0;
+    // statistics
+    std::atomic<uint64_t> bytes_sent{ 0 }, bytes_received{ 0 }, msgs_sent{ 0 }, unexpected_msgs{ 0 };
+};
+
+std::shared_ptr<atl_transport> create_tcp_transport(pmi& pm, int ep_count);
+
+// A communicator's view of the transport: rank translation + comm id.
+class atl_comm {
+public:
+    atl_comm(std::shared_ptr<atl_transport> tr, std::vector<int> world_ranks, int my_index, uint64_t comm_id);
+    int rank() const { return rank_; }
+    int size() const { return (int)ranks_.size(); }
+    uint64_t id() const { return comm_id_; }
+    int ep_count() const { return tr_->ep_count(); }
+    int world_rank_of(int r) const { return ranks_[r]; }
+    atl_transport& transport() { return *tr_; }
+    std::shared_ptr<atl_transport> transport_ptr() { return tr_; }
+
+    void send(int ep, const void* buf, size_t len, int dst, uint64_t tag, atl_req* req) {
+        tr_->send(ep, buf, len, ranks_[dst], tag, req);
+    }
+    void recv(int ep, void* buf, size_t len, int src, uint64_t tag, atl_req* req) {
+        tr_->recv(ep, buf, len, ranks_[src], tag, req);
+    }
+    void poll(int ep) { tr_->poll(ep); }
+    void wait(int ep, atl_req* req);
+
+    // blocking helpers used during setup (run on endpoint 0 with internal tags)
+    void allgather(const void* send, void* recv, size_t bytes_per_rank);
+    void barrier();
+    // children created by split get ids that are unique inside the world
+    std::shared_ptr<atl_comm> split(int color, int key);
+    static uint64_t next_comm_id(); // process-wide counter
+    static void bump_comm_id(uint64_t at_least);
+
+private:
+    std::shared_ptr<atl_transport> tr_;
+    std::vector<int> ranks_;
+    int rank_;
+    uint64_t comm_id_;
+    uint64_t internal_op_ = 0;
+};
+
+} // namespace cclx

@@ -1,0 +1,529 @@
+// TCP mesh transport: one non-blocking socket per (endpoint, peer), tag matching
+// with posted / unexpected queues, progress driven by poll().
+//
+// Stands where the reference has atl_ofi with the tcp provider
+// (src/atl/ofi/atl_ofi.cpp:30-1196: tagged send/recv, per-worker endpoints,
+// address table exchanged through PMI), written directly on sockets: the
+// address table is the list of "<ip>:<port>" strings published in the KVS, the
+// higher rank of a pair dials the lower one, and a 16-byte header (tag, length)
+// frames every message so that a receive posted later still matches.
+#include <arpa/inet.h>
+#include <fcntl.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
+#include <sys/epoll.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <cstring>
+#include <deque>
+#include <list>
+#include <mutex>
+#include <string>
+
+#include "bootstrap/pmi.hpp"
+#include "core/env.hpp"
+#include "core/log.hpp"
+#include "transport/atl.hpp"
+
+namespace cclx {
+
+namespace {
+
+struct wire_header {
+    uint64_t tag;
+    uint64_t len;
+};
+
+struct out_msg {
+    wire_header hdr;
+    const char* payload;
+    size_t sent = 0; // of header + payload
+    atl_req* req;
+};
+
+struct posted_recv {
+    uint64_t tag;
+    char* buf;
+    size_t cap;
+    atl_req* req;
+};
+
+struct unexpected_msg {
+    uint64_t tag;
+    std::vector<char> data;
+    bool complete = false;
+};
+
+struct peer_state {
+    int fd = -1;
+    std::deque<out_msg> outq;
+    // incoming
+    wire_header in_hdr{};
+    size_t hdr_got = 0;
+    bool in_body = false;
+    char* in_dst = nullptr;
+    size_t in_got = 0;
+    atl_req* in_req = nullptr; // when receiving straight into a posted buffer
+    unexpected_msg* in_unexp = nullptr;
+    std::list<posted_recv> posted;
+    std::list<unexpected_msg> unexp;
+};
+
+struct endpoint {
+    std::vector<peer_state> peers;
+    std::mutex mu;
+    int epfd = -1;
+};
+
+void set_nonblock(int fd) {
+    int fl = fcntl(fd, F_GETFL, 0);
+    fcntl(fd, F_SETFL, fl | O_NONBLOCK);
+    int one = 1;
+    setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+    int sz = 4 << 20;
+    setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &sz, sizeof(sz));
+    setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &sz, sizeof(sz));
+}
+
+bool write_blocking(int fd, const void* b, size_t n) {
+    const char* p = (const char*)b;
+    while (n) {
+        ssize_t r = ::send(fd, p, n, MSG_NOSIGNAL);
+        if (r < 0) {
+            if (errno == EINTR)
+                continue;
+            return false;
+        }
+        p += r;
+        n -= (size_t)r;
+    }
+    return true;
+}
+bool read_blocking(int fd, void* b, size_t n) {
+    char* p = (char*)b;
+    while (n) {
+        ssize_t r = ::recv(fd, p, n, 0);
+        if (r <= 0) {
+            if (r < 0 && errno == EINTR)
+                continue;
+            return false;
+        }
+        p += r;
+        n -= (size_t)r;
+    }
+    return true;
+}
+
+class tcp_transport : public atl_transport {
+public:
+    tcp_transport(pmi& pm, int ep_count) : rank_(pm.rank()), size_(pm.size()), eps_(ep_count) {
+        const env_data& env = env_data::get();
+        // listening socket on the interface the KVS uses
+        std::string ip = kvs::choose_local_ip(env.kvs_iface, false);
+        if (ip.find(':') != std::string::npos)
+            ip = "127.0.0.1";
+        int lfd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
+        CCL_THROW_IF_NOT(lfd >= 0, "socket failed");
+        int one = 1;
+        setsockopt(lfd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+        sockaddr_in a{};
+        a.sin_family = AF_INET;
+        a.sin_addr.s_addr = htonl(INADDR_ANY);
+        a.sin_port = 0;
+        CCL_THROW_IF_NOT(::bind(lfd, (sockaddr*)&a, sizeof(a)) == 0, "bind failed: ", std::strerror(errno));
+        CCL_THROW_IF_NOT(::listen(lfd, 4096) == 0, "listen failed");
+        socklen_t sl = sizeof(a);
+        getsockname(lfd, (sockaddr*)&a, &sl);
+        char host[256] = { 0 };
+        gethostname(host, sizeof(host) - 1);
+        struct rec {
+            char ip[64];
+            int port;
+            char host[64];
+        } mine{};
+        std::snprintf(mine.ip, sizeof(mine.ip), "%s", ip.c_str());
+        mine.port = ntohs(a.sin_port);
+        std::snprintf(mine.host, sizeof(mine.host), "%s", host);
+        std::vector<rec> table(size_);
+        pm.allgather(&mine, table.data(), sizeof(rec));
+        same_host_.resize(size_);
+        for (int r = 0; r < size_; r++)
+            same_host_[r] = std::strncmp(table[r].host, mine.host, sizeof(mine.host)) == 0;
+
+        for (auto& ep : eps_) {
+            ep.peers.resize(size_);
+            ep.epfd = epoll_create1(EPOLL_CLOEXEC);
+        }
+        // dial every lower rank, once per endpoint
+        for (int e = 0; e < ep_count; e++) {
+            for (int p = 0; p < rank_; p++) {
+                int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
+                sockaddr_in d{};
+                d.sin_family = AF_INET;
+                d.sin_port = htons((uint16_t)table[p].port);
+                const char* dip = same_host_[p] ? "127.0.0.1" : table[p].ip;
+                inet_pton(AF_INET, dip, &d.sin_addr);
+                int tries = 0;
+                while (::connect(fd, (sockaddr*)&d, sizeof(d)) != 0) {
+                    CCL_THROW_IF_NOT(++tries < 2000, "can not connect to rank ", p, " at ", dip, ":", table[p].port,
+                                     ": ", std::strerror(errno));
+                    usleep(5000);
+                }
+                int hello[2] = { rank_, e };
+                CCL_THROW_IF_NOT(write_blocking(fd, hello, sizeof(hello)), "hello failed");
+                eps_[e].peers[p].fd = fd;
+            }
+        }
+        // accept every higher rank
+        const int expect = (size_ - 1 - rank_) * ep_count;
+        for (int i = 0; i < expect; i++) {
+            int fd = ::accept4(lfd, nullptr, nullptr, SOCK_CLOEXEC);
+            CCL_THROW_IF_NOT(fd >= 0, "accept failed: ", std::strerror(errno));
+            int hello[2];
+            CCL_THROW_IF_NOT(read_blocking(fd, hello, sizeof(hello)), "hello read failed");
+            CCL_THROW_IF_NOT(hello[0] > rank_ && hello[0] < size_ && hello[1] >= 0 && hello[1] < ep_count,
+                             "unexpected hello");
+            eps_[hello[1]].peers[hello[0]].fd = fd;
+        }
+        ::close(lfd);
+        for (auto& ep : eps_) {
+            for (int p = 0; p < size_; p++) {
+                if (p == rank_)
+                    continue;
+                set_nonblock(ep.peers[p].fd);
+                epoll_event ev{};
+                ev.events = EPOLLIN;
+                ev.data.u32 = (uint32_t)p;
+                epoll_ctl(ep.epfd, EPOLL_CTL_ADD, ep.peers[p].fd, &ev);
+            }
+        }
+        pm.barrier();
+        LOG_DEBUG("tcp transport up: rank ", rank_, "/", size_, ", endpoints ", ep_count);
+    }
+
+    ~tcp_transport() override {
+        for (auto& ep : eps_) {
+            for (auto& p : ep.peers)
+                if (p.fd >= 0)
+                    ::close(p.fd);
+            if (ep.epfd >= 0)
+                ::close(ep.epfd);
+        }
+    }
+
+    int world_rank() const override { return rank_; }
+    int world_size() const override { return size_; }
+    int ep_count() const override { return (int)eps_.size(); }
+    bool same_host(int peer) const override { return same_host_[peer]; }
+    const char* name() const override { return "tcp"; }
+
+    void send(int e, const void* buf, size_t len, int dst, uint64_t tag, atl_req* req) override {
+        endpoint& ep = eps_[e];
+        std::lock_guard<std::mutex> lk(ep.mu);
+        req->reset();
+        msgs_sent++;
+        bytes_sent += len;
+        peer_state& ps = ep.peers[dst];
+        if (dst == rank_) {
+            deliver_local(ps, (const char*)buf, len, tag);
+            req->done.store(1, std::memory_order_release);
+            return;
+        }
+        out_msg m;
+        m.hdr.tag = tag;
+        m.hdr.len = len;
+        m.payload = (const char*)buf;
+        m.req = req;
+        ps.outq.push_back(m);
+        flush(ps);
+    }
+
+    void recv(int e, void* buf, size_t len, int src, uint64_t tag, atl_req* req) override {
+        endpoint& ep = eps_[e];
+        std::lock_guard<std::mutex> lk(ep.mu);
+        req->reset();
+        peer_state& ps = ep.peers[src];
+        for (auto it = ps.unexp.begin(); it != ps.unexp.end(); ++it) {
+            if (it->tag != tag)
+                continue;
+            if (!it->complete) {
+                // still arriving: redirect the rest into the user buffer
+                CCL_THROW_IF_NOT(it->data.size() <= len, "receive buffer too small: ", len, " < ", it->data.size());
+                std::memcpy(buf, it->data.data(), ps.in_got);
+                ps.in_dst = (char*)buf;
+                ps.in_req = req;
+                ps.in_unexp = nullptr;
+                req->bytes = it->data.size();
+                ps.unexp.erase(it);
+                return;
+            }
+            CCL_THROW_IF_NOT(it->data.size() <= len, "receive buffer too small: ", len, " < ", it->data.size());
+            std::memcpy(buf, it->data.data(), it->data.size());
+            req->bytes = it->data.size();
+            bytes_received += it->data.size();
+            ps.unexp.erase(it);
+            req->done.store(1, std::memory_order_release);
+            return;
+        }
+        ps.posted.push_back(posted_recv{ tag, (char*)buf, len, req });
+    }
+
+    bool probe(int e, int src, uint64_t tag, size_t* len) override {
+        endpoint& ep = eps_[e];
+        std::lock_guard<std::mutex> lk(ep.mu);
+        progress(ep);
+        for (auto& u : ep.peers[src].unexp)
+            if (u.tag == tag && u.complete) {
+                if (len)
+                    *len = u.data.size();
+                return true;
+            }
+        return false;
+    }
+
+    void poll(int e) override {
+        endpoint& ep = eps_[e];
+        std::lock_guard<std::mutex> lk(ep.mu);
+        progress(ep);
+    }
+
+private:
+    void deliver_local(peer_state& ps, const char* buf, size_t len, uint64_t tag) {
+        for (auto it = ps.posted.begin(); it != ps.posted.end(); ++it) {
+            if (it->tag == tag) {
+                CCL_THROW_IF_NOT(len <= it->cap, "receive buffer too small");
+                std::memcpy(it->buf, buf, len);
+                it->req->bytes = len;
+                it->req->done.store(1, std::memory_order_release);
+                ps.posted.erase(it);
+                return;
+            }
+        }
+        ps.unexp.emplace_back();
+        unexpected_msg& u = ps.unexp.back();
+        u.tag = tag;
+        u.data.assign(buf, buf + len);
+        u.complete = true;
+        unexpected_msgs++;
+    }
+
+    void flush(peer_state& ps) {
+        while (!ps.outq.empty()) {
+            out_msg& m = ps.outq.front();
+            const size_t total = sizeof(wire_header) + m.hdr.len;
+            while (m.sent < total) {
+                ssize_t r;
+                if (m.sent < sizeof(wire_header)) {
+                    iovec iov[2];
+                    iov[0].iov_base = (char*)&m.hdr + m.sent;
+                    iov[0].iov_len = sizeof(wire_header) - m.sent;
+                    iov[1].iov_base = const_cast<char*>(m.payload);
+                    iov[1].iov_len = m.hdr.len;
+                    msghdr mh{};
+                    mh.msg_iov = iov;
+                    mh.msg_iovlen = m.hdr.len ? 2 : 1;
+                    r = ::sendmsg(ps.fd, &mh, MSG_NOSIGNAL);
+                }
+                else {
+                    const size_t off = m.sent - sizeof(wire_header);
+                    r = ::send(ps.fd, m.payload + off, m.hdr.len - off, MSG_NOSIGNAL);
+                }
+                if (r < 0) {
+                    if (errno == EAGAIN || errno == EWOULDBLOCK)
+                        return;
+                    if (errno == EINTR)
+                        continue;
+                    CCL_THROW("tcp transport: send failed: ", std::strerror(errno));
+                }
+                m.sent += (size_t)r;
+            }
+            m.req->done.store(1, std::memory_order_release);
+            ps.outq.pop_front();
+        }
+    }
+
+    void finish_incoming(peer_state& ps) {
+        bytes_received += ps.in_hdr.len;
+        if (ps.in_req) {
+            ps.in_req->done.store(1, std::memory_order_release);
+            ps.in_req = nullptr;
+        }
+        else if (ps.in_unexp)
+            ps.in_unexp->complete = true;
+        ps.in_unexp = nullptr;
+        ps.in_dst = nullptr;
+        ps.in_body = false;
+        ps.hdr_got = 0;
+        ps.in_got = 0;
+    }
+
+    void drain(peer_state& ps) {
+        for (;;) {
+            if (!ps.in_body) {
+                ssize_t r = ::recv(ps.fd, (char*)&ps.in_hdr + ps.hdr_got, sizeof(wire_header) - ps.hdr_got, 0);
+                if (r < 0) {
+                    if (errno == EAGAIN || errno == EWOULDBLOCK)
+                        return;
+                    if (errno == EINTR)
+                        continue;
+                    CCL_THROW("tcp transport: recv failed: ", std::strerror(errno));
+                }
+                if (r == 0)
+                    return; // peer closed; pending operations will time out at a higher level
+                ps.hdr_got += (size_t)r;
+                if (ps.hdr_got < sizeof(wire_header))
+                    continue;
+                // header complete: find where the body goes
+                ps.in_body = true;
+                ps.in_got = 0;
+                ps.in_req = nullptr;
+                ps.in_unexp = nullptr;
+                bool matched = false;
+                for (auto it = ps.posted.begin(); it != ps.posted.end(); ++it) {
+                    if (it->tag == ps.in_hdr.tag) {
+                        CCL_THROW_IF_NOT(ps.in_hdr.len <= it->cap, "receive buffer too small: ", it->cap, " < ",
+                                         ps.in_hdr.len);
+                        ps.in_dst = it->buf;
+                        ps.in_req = it->req;
+                        it->req->bytes = ps.in_hdr.len;
+                        ps.posted.erase(it);
+                        matched = true;
+                        break;
+                    }
+                }
+                if (!matched) {
+                    ps.unexp.emplace_back();
+                    unexpected_msg& u = ps.unexp.back();
+                    u.tag = ps.in_hdr.tag;
+                    u.data.resize(ps.in_hdr.len);
+                    ps.in_dst = u.data.data();
+                    ps.in_unexp = &u;
+                    unexpected_msgs++;
+                }
+                if (ps.in_hdr.len == 0) {
+                    finish_incoming(ps);
+                    continue;
+                }
+            }
+            ssize_t r = ::recv(ps.fd, ps.in_dst + ps.in_got, ps.in_hdr.len - ps.in_got, 0);
+            if (r < 0) {
+                if (errno == EAGAIN || errno == EWOULDBLOCK)
+                    return;
+                if (errno == EINTR)
+                    continue;
+                CCL_THROW("tcp transport: recv failed: ", std::strerror(errno));
+            }
+            if (r == 0)
+                return;
+            ps.in_got += (size_t)r;
+            if (ps.in_got == ps.in_hdr.len)
+                finish_incoming(ps);
+        }
+    }
+
+    void progress(endpoint& ep) {
+        for (auto& ps : ep.peers)
+            if (!ps.outq.empty())
+                flush(ps);
+        epoll_event evs[64];
+        int n = epoll_wait(ep.epfd, evs, 64, 0);
+        for (int i = 0; i < n; i++)
+            drain(ep.peers[evs[i].data.u32]);
+    }
+
+    int rank_, size_;
+    std::vector<endpoint> eps_;
+    std::vector<char> same_host_;
+};
+
+} // namespace
+
+std::shared_ptr<atl_transport> create_tcp_transport(pmi& pm, int ep_count) {
+    return std::make_shared<tcp_transport>(pm, ep_count);
+}
+
+// ---- atl_comm ---------------------------------------------------------------------
+
+static std::atomic<uint64_t> g_next_comm_id{ 1 };
+
+uint64_t atl_comm::next_comm_id() {
+    return g_next_comm_id.load();
+}
+void atl_comm::bump_comm_id(uint64_t at_least) {
+    uint64_t cur = g_next_comm_id.load();
+    while (cur < at_least && !g_next_comm_id.compare_exchange_weak(cur, at_least)) {
+    }
+}
+
+atl_comm::atl_comm(std::shared_ptr<atl_transport> tr, std::vector<int> world_ranks, int my_index, uint64_t comm_id)
+        : tr_(std::move(tr)), ranks_(std::move(world_ranks)), rank_(my_index), comm_id_(comm_id) {}
+
+void atl_comm::wait(int ep, atl_req* req) {
+    while (!req->is_done())
+        tr_->poll(ep);
+}
+
+void atl_comm::allgather(const void* send_buf, void* recv_buf, size_t n) {
+    const int W = size();
+    const uint64_t tag = atl_tag::make(comm_id_, atl_tag::INTERNAL_SCHED, internal_op_++ & atl_tag::MAX_OP);
+    std::vector<atl_req> sreq(W), rreq(W);
+    std::memcpy((char*)recv_buf + (size_t)rank_ * n, send_buf, n);
+    for (int p = 0; p < W; p++) {
+        if (p == rank_)
+            continue;
+        recv(0, (char*)recv_buf + (size_t)p * n, n, p, tag, &rreq[p]);
+    }
+    for (int p = 0; p < W; p++) {
+        if (p == rank_)
+            continue;
+        send(0, send_buf, n, p, tag, &sreq[p]);
+    }
+    for (int p = 0; p < W; p++) {
+        if (p == rank_)
+            continue;
+        wait(0, &sreq[p]);
+        wait(0, &rreq[p]);
+    }
+}
+
+void atl_comm::barrier() {
+    char mine = 1;
+    std::vector<char> all(size());
+    allgather(&mine, all.data(), 1);
+}
+
+std::shared_ptr<atl_comm> atl_comm::split(int color, int key) {
+    struct rec {
+        int color, key, world_rank;
+        uint64_t next_id;
+    } mine{ color, key, ranks_[rank_], next_comm_id() };
+    std::vector<rec> all(size());
+    allgather(&mine, all.data(), sizeof(rec));
+    uint64_t base = 0;
+    std::vector<int> colors;
+    for (auto& r : all) {
+        base = std::max(base, r.next_id);
+        if (std::find(colors.begin(), colors.end(), r.color) == colors.end())
+            colors.push_back(r.color);
+    }
+    std::sort(colors.begin(), colors.end());
+    bump_comm_id(base + colors.size());
+    const uint64_t id = base + (uint64_t)(std::find(colors.begin(), colors.end(), color) - colors.begin());
+    // members of my color ordered by (key, parent rank)
+    std::vector<std::pair<std::pair<int, int>, int>> members; // ((key, parent rank), world rank)
+    for (int r = 0; r < size(); r++)
+        if (all[r].color == color)
+            members.push_back({ { all[r].key, r }, all[r].world_rank });
+    std::sort(members.begin(), members.end());
+    std::vector<int> wr;
+    int me = -1;
+    for (size_t i = 0; i < members.size(); i++) {
+        wr.push_back(members[i].second);
+        if (members[i].first.second == rank_)
+            me = (int)i;
+    }
+    return std::make_shared<atl_comm>(tr_, wr, me, id);
+}
+
+} // namespace cclx

@@ -144,6 +144,9 @@ class DeviceGroup:
     # ---- helpers ------------------------------------------------------------------
     def _lists(self, send, recv):
         if self.emulated_mode:
+            if self.world == 1:  # a single emulated rank may pass bare tensors
+                send = [send] if isinstance(send, torch.Tensor) else send
+                recv = [recv] if isinstance(recv, torch.Tensor) else recv
             assert send is None or len(send) == self.world
             assert recv is None or len(recv) == self.world
             return send, recv
