@@ -1,0 +1,349 @@
+// Flat C API over KVS, communicators, collectives (host and device buffers) and events.
+#include <cstring>
+#include <memory>
+
+#include "bootstrap/kvs.hpp"
+#include "capi/capi_common.hpp"
+#include "coll/coll.hpp"
+#include "coll/selection.hpp"
+#include "comm/host_comm.hpp"
+#include "core/comp.hpp"
+#include "core/datatype.hpp"
+#include "core/env.hpp"
+#include "core/log.hpp"
+#include "fusion/fusion.hpp"
+#include "gpu/device_comm.hpp"
+#include "topo/topo.hpp"
+
+using namespace cclx;
+
+namespace {
+struct kvs_handle {
+    std::shared_ptr<kvs::internal_kvs> k;
+};
+struct comm_handle {
+    std::shared_ptr<host_comm> c;
+};
+struct event_handle {
+    event_ptr e;
+};
+} // namespace
+
+// ---- kvs ---------------------------------------------------------------------------------------
+CCLX_API void* cclx_kvs_create_main(const char* ip_port) {
+    kvs_handle* h = nullptr;
+    capi::guard([&] {
+        env_data::get();
+        h = new kvs_handle{ kvs::internal_kvs::create_main(ip_port ? ip_port : "") };
+    });
+    return h;
+}
+
+CCLX_API void* cclx_kvs_create_peer(const char* addr) {
+    kvs_handle* h = nullptr;
+    capi::guard([&] {
+        env_data::get();
+        h = new kvs_handle{ kvs::internal_kvs::create_peer(kvs::address::from_string(addr)) };
+    });
+    return h;
+}
+
+CCLX_API int cclx_kvs_address(void* h, char* out, size_t cap) {
+    return capi::guard([&] {
+        std::string s = ((kvs_handle*)h)->k->get_address().str();
+        CCL_THROW_IF_NOT(s.size() + 1 <= cap, "address buffer too small");
+        std::memcpy(out, s.c_str(), s.size() + 1);
+    });
+}
+
+CCLX_API int cclx_kvs_set(void* h, const char* key, const void* val, size_t len) {
+    return capi::guard([&] { ((kvs_handle*)h)->k->raw().set(key, val, len); });
+}
+
+// returns the value length or -1; copies at most cap bytes
+CCLX_API long long cclx_kvs_get(void* h, const char* key, void* out, size_t cap, int timeout_ms) {
+    long long n = -1;
+    capi::guard([&] {
+        kvs::bytes b;
+        if (timeout_ms < 0) {
+            if (!((kvs_handle*)h)->k->raw().try_get(key, b))
+                return;
+        }
+        else
+            b = ((kvs_handle*)h)->k->raw().get(key, timeout_ms);
+        std::memcpy(out, b.data(), std::min(cap, b.size()));
+        n = (long long)b.size();
+    });
+    return n;
+}
+
+CCLX_API long long cclx_kvs_add(void* h, const char* key, long long delta) {
+    long long v = 0;
+    capi::guard([&] { v = ((kvs_handle*)h)->k->raw().add(key, delta); });
+    return v;
+}
+
+CCLX_API long long cclx_kvs_count(void* h, const char* prefix) {
+    long long v = -1;
+    capi::guard([&] { v = (long long)((kvs_handle*)h)->k->raw().count(prefix); });
+    return v;
+}
+
+CCLX_API int cclx_kvs_del(void* h, const char* key) {
+    return capi::guard([&] { ((kvs_handle*)h)->k->raw().del(key); });
+}
+
+CCLX_API int cclx_kvs_barrier(void* h, const char* name, int participants, int timeout_ms) {
+    return capi::guard([&] { ((kvs_handle*)h)->k->raw().barrier(name, (uint32_t)participants, timeout_ms); });
+}
+
+CCLX_API int cclx_kvs_destroy(void* h) {
+    return capi::guard([&] { delete (kvs_handle*)h; });
+}
+
+// ---- communicator ------------------------------------------------------------------------------
+CCLX_API void* cclx_comm_create(int size, int rank, void* kvs_h) {
+    comm_handle* h = nullptr;
+    capi::guard([&] { h = new comm_handle{ host_comm::create(size, rank, ((kvs_handle*)kvs_h)->k) }; });
+    return h;
+}
+
+CCLX_API void* cclx_comm_split(void* c, int color, int key) {
+    comm_handle* h = nullptr;
+    capi::guard([&] { h = new comm_handle{ ((comm_handle*)c)->c->split(color, key) }; });
+    return h;
+}
+
+CCLX_API void* cclx_comm_node(void* c) {
+    comm_handle* h = nullptr;
+    capi::guard([&] { h = new comm_handle{ ((comm_handle*)c)->c->node_comm() }; });
+    return h;
+}
+
+CCLX_API void* cclx_comm_r2r(void* c) {
+    comm_handle* h = nullptr;
+    capi::guard([&] { h = new comm_handle{ ((comm_handle*)c)->c->r2r_comm() }; });
+    return h;
+}
+
+CCLX_API int cclx_comm_rank(void* c) {
+    return ((comm_handle*)c)->c->rank();
+}
+CCLX_API int cclx_comm_size(void* c) {
+    return ((comm_handle*)c)->c->size();
+}
+CCLX_API long long cclx_comm_id(void* c) {
+    return (long long)((comm_handle*)c)->c->id();
+}
+CCLX_API int cclx_comm_local_rank(void* c) {
+    int v = -1;
+    capi::guard([&] { v = ((comm_handle*)c)->c->local_rank(); });
+    return v;
+}
+CCLX_API int cclx_comm_local_size(void* c) {
+    int v = -1;
+    capi::guard([&] { v = ((comm_handle*)c)->c->local_size(); });
+    return v;
+}
+
+// device communicator of this node (created on first use, collective); not owned by the caller
+CCLX_API void* cclx_comm_device(void* c) {
+    gpu::device_comm* d = nullptr;
+    capi::guard([&] { d = ((comm_handle*)c)->c->device(); });
+    return d;
+}
+
+CCLX_API int cclx_comm_release_device(void* c) {
+    return capi::guard([&] { ((comm_handle*)c)->c->release_device(); });
+}
+
+CCLX_API int cclx_comm_abort(void* c) {
+    return capi::guard([&] { ((comm_handle*)c)->c->abort(); });
+}
+
+CCLX_API int cclx_comm_heartbeat(void* c) {
+    return capi::guard([&] { ((comm_handle*)c)->c->pm()->heartbeat(); });
+}
+
+CCLX_API int cclx_comm_peer_alive(void* c, int peer, int max_age_ms) {
+    int v = -1;
+    capi::guard([&] { v = ((comm_handle*)c)->c->pm()->peer_alive(peer, max_age_ms) ? 1 : 0; });
+    return v;
+}
+
+CCLX_API int cclx_comm_destroy(void* c) {
+    return capi::guard([&] { delete (comm_handle*)c; });
+}
+
+CCLX_API long long cclx_comm_cache_size(void* c) {
+    return (long long)((comm_handle*)c)->c->cache().size();
+}
+
+// ---- collectives -------------------------------------------------------------------------------
+struct cclx_coll_desc {
+    int ctype;
+    const void* send_buf;
+    void* recv_buf;
+    size_t count;
+    int dtype;
+    int reduction;
+    int root;
+    int peer;
+    const size_t* send_counts; // world entries or null
+    const size_t* recv_counts;
+    void* const* recv_bufs; // world entries or null (allgatherv vector form)
+    void* stream; // cudaStream_t when device != 0
+    int device;
+    // attributes
+    int priority;
+    int synchronous;
+    int to_cache;
+    const char* match_id;
+    void* reduction_fn;
+    int do_scale;
+    float scale;
+    int out_dtype;
+    const char* gpu_algo;
+    // dependencies
+    void* const* deps;
+    int n_deps;
+};
+
+CCLX_API void* cclx_coll(void* c, const cclx_coll_desc* d) {
+    event_handle* h = nullptr;
+    capi::guard([&] {
+        host_comm& comm = *((comm_handle*)c)->c;
+        const int N = comm.size();
+        coll_param p;
+        p.ctype = (coll_type)d->ctype;
+        p.send_buf = d->send_buf;
+        p.recv_buf = d->recv_buf;
+        p.count = d->count;
+        p.dtype = d->dtype;
+        p.reduction = d->reduction;
+        p.root = d->root;
+        p.peer = d->peer;
+        if (d->send_counts)
+            p.send_counts.assign(d->send_counts, d->send_counts + N);
+        if (d->recv_counts)
+            p.recv_counts.assign(d->recv_counts, d->recv_counts + N);
+        if (d->recv_bufs)
+            p.recv_bufs.assign(d->recv_bufs, d->recv_bufs + N);
+        p.stream = d->stream;
+        p.device = d->device != 0;
+        for (int i = 0; i < d->n_deps; i++)
+            if (d->deps[i])
+                p.deps.push_back(((event_handle*)d->deps[i])->e);
+        coll_attr a;
+        a.priority = d->priority;
+        a.synchronous = d->synchronous != 0;
+        a.to_cache = d->to_cache != 0;
+        if (d->match_id)
+            a.match_id = d->match_id;
+        a.reduction_fn = (reduction_fn_t)d->reduction_fn;
+        a.do_scale = d->do_scale != 0;
+        a.scale = d->scale;
+        a.out_dtype = d->out_dtype;
+        if (d->gpu_algo)
+            a.gpu_algo = d->gpu_algo;
+        h = new event_handle{ coll_create(comm, p, a) };
+    });
+    return h;
+}
+
+CCLX_API int cclx_event_wait(void* e) {
+    return capi::guard([&] { ((event_handle*)e)->e->wait(); });
+}
+// 1 complete, 0 pending, -1 error
+CCLX_API int cclx_event_test(void* e) {
+    int v = -1;
+    capi::guard([&] { v = ((event_handle*)e)->e->test() ? 1 : 0; });
+    return v;
+}
+CCLX_API void* cclx_event_native(void* e) {
+    return ((event_handle*)e)->e->native();
+}
+CCLX_API int cclx_event_destroy(void* e) {
+    return capi::guard([&] { delete (event_handle*)e; });
+}
+
+CCLX_API int cclx_group_start() {
+    return capi::guard([] { group_start(); });
+}
+CCLX_API int cclx_group_end() {
+    return capi::guard([] { group_end(); });
+}
+CCLX_API int cclx_fusion_flush() {
+    return capi::guard([] { fusion_manager::get().flush(nullptr); });
+}
+
+// ---- misc ---------------------------------------------------------------------------------------
+CCLX_API int cclx_datatype_create(size_t size) {
+    int v = -1;
+    capi::guard([&] { v = datatype_table::get().create(size); });
+    return v;
+}
+CCLX_API int cclx_datatype_free(int idx) {
+    return capi::guard([&] { datatype_table::get().free(idx); });
+}
+CCLX_API long long cclx_datatype_size(int idx) {
+    long long v = -1;
+    capi::guard([&] { v = (long long)dtype_size(idx); });
+    return v;
+}
+
+CCLX_API int cclx_comp_reduce(const void* in, size_t count, void* inout, int dtype, int op) {
+    return capi::guard([&] { comp_reduce(in, count, inout, dtype, op); });
+}
+CCLX_API const char* cclx_comp_impl(int which) {
+    return which == 0 ? comp_bf16_impl_name() : comp_fp16_impl_name();
+}
+
+// name of the CPU algorithm the selector picks
+CCLX_API int cclx_select_cpu_algo(int ctype, size_t bytes, int comm_size, char* out, size_t cap) {
+    return capi::guard([&] {
+        selector_param sp;
+        sp.ctype = (coll_type)ctype;
+        sp.bytes = bytes;
+        sp.count = bytes;
+        sp.comm_size = comm_size;
+        std::string a = algorithm_selector::get().select_cpu(sp);
+        CCL_THROW_IF_NOT(a.size() + 1 <= cap, "buffer too small");
+        std::memcpy(out, a.c_str(), a.size() + 1);
+    });
+}
+CCLX_API int cclx_selector_reload() {
+    return capi::guard([] {
+        env_data::reload();
+        algorithm_selector::get().reload();
+    });
+}
+CCLX_API int cclx_parse_algo_spec(int ctype, const char* spec) {
+    return capi::guard(
+        [&] { algorithm_selector::parse(spec, algorithm_selector::known_cpu_algos((coll_type)ctype)); });
+}
+
+// stats: which = 0 calls, 1 device calls, 2 fused ops, 3 fused batches, 4 cache hits
+CCLX_API long long cclx_stats(int which, int ctype) {
+    coll_stats& s = stats();
+    switch (which) {
+        case 0: return (long long)s.calls[ctype];
+        case 1: return (long long)s.device_calls[ctype];
+        case 2: return (long long)s.fused_ops;
+        case 3: return (long long)s.fused_batches;
+        case 4: return (long long)s.cache_hits;
+        default: return -1;
+    }
+}
+
+CCLX_API int cclx_topo_describe(char* out, size_t cap) {
+    return capi::guard([&] {
+        std::string s = topo_info::local().describe();
+        CCL_THROW_IF_NOT(s.size() + 1 <= cap, "buffer too small");
+        std::memcpy(out, s.c_str(), s.size() + 1);
+    });
+}
+
+CCLX_API int cclx_env_size(const char* text, size_t* out) {
+    return env_to_size(text, *out) ? 0 : -1;
+}

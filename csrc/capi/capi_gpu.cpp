@@ -219,18 +219,30 @@ CCLX_API int cclx_dc_barrier(void* h, void* stream) {
     return capi::guard([&] { launch_barrier(*(device_comm*)h, (cudaStream_t)stream); });
 }
 
-// real mode: one call is a send or a recv.  emulation mode: peers[r] (or -1) and
-// is_send[r] describe what every emulated rank does in this launch.
-CCLX_API int cclx_dc_sendrecv(void* h, const void* const* send, void* const* recv, size_t bytes, const int* peers,
-                              const int* is_send, void* stream) {
+// real mode: n_ops operations of this rank (arrays of n_ops).  emulation mode: one
+// operation per emulated rank (arrays of world entries, peer -1 = idle).
+CCLX_API int cclx_dc_sendrecv(void* h, const void* const* send, void* const* recv, const size_t* bytes,
+                              const int* peers, const int* is_send, int n_ops, void* stream) {
     return capi::guard([&] {
         device_comm* dc = (device_comm*)h;
-        auto ra = make_ra(dc, send, recv);
-        for (size_t e = 0; e < ra.size(); e++) {
-            ra[e].scount[0] = (size_t)(long long)peers[e];
-            ra[e].scount[1] = (size_t)is_send[e];
+        if (dc->emulated()) {
+            std::vector<dev::p2p_ops> ops(dc->world());
+            for (int e = 0; e < dc->world(); e++) {
+                ops[e].n = 1;
+                ops[e].op[0] = dev::p2p_op{ send ? send[e] : nullptr, recv ? recv[e] : nullptr, bytes[e], peers[e],
+                                            is_send[e] };
+            }
+            launch_sendrecv(*dc, ops.data(), (cudaStream_t)stream);
         }
-        launch_sendrecv(*dc, ra.data(), bytes, peers[0], is_send[0] != 0, (cudaStream_t)stream);
+        else {
+            dev::p2p_ops ops{};
+            CCL_THROW_IF_NOT(n_ops <= dev::P2P_MAX_OPS, "at most ", dev::P2P_MAX_OPS, " operations per launch");
+            ops.n = n_ops;
+            for (int i = 0; i < n_ops; i++)
+                ops.op[i] = dev::p2p_op{ send ? send[i] : nullptr, recv ? recv[i] : nullptr, bytes[i], peers[i],
+                                         is_send[i] };
+            launch_sendrecv(*dc, &ops, (cudaStream_t)stream);
+        }
     });
 }
 

@@ -1,0 +1,690 @@
+#include "coll/algorithms.hpp"
+
+#include <algorithm>
+#include <functional>
+
+#include "comm/host_comm.hpp"
+#include "core/datatype.hpp"
+#include "core/env.hpp"
+#include "core/log.hpp"
+#include "sched/entries.hpp"
+
+namespace cclx {
+namespace algo {
+
+namespace {
+
+inline char* at(void* base, size_t elems, size_t esz) {
+    return (char*)base + elems * esz;
+}
+inline const char* at(const void* base, size_t elems, size_t esz) {
+    return (const char*)base + elems * esz;
+}
+
+int pof2_floor(int n) {
+    int p = 1;
+    while (p * 2 <= n)
+        p *= 2;
+    return p;
+}
+
+// out-of-place collectives work in place on recv after this copy
+void copy_in(sched& s, const void* send, void* recv, size_t bytes) {
+    if (send && send != recv && bytes) {
+        s.add<copy_entry>(send, recv, bytes);
+        s.add_barrier();
+    }
+}
+
+// Non-power-of-two fold used by recursive doubling / halving: the first 2*rem
+// ranks pair up, even ones hand their data to the odd neighbour and sit out.
+struct fold {
+    int pof2, rem, newrank; // newrank == -1: this rank sits out
+    int real(int nr) const { return nr < rem ? nr * 2 + 1 : nr + rem; }
+};
+
+fold make_fold(int N, int r) {
+    fold f;
+    f.pof2 = pof2_floor(N);
+    f.rem = N - f.pof2;
+    if (r < 2 * f.rem)
+        f.newrank = (r % 2 == 0) ? -1 : r / 2;
+    else
+        f.newrank = r - f.rem;
+    return f;
+}
+
+// Recursive-halving reduce-scatter over the pof2 participants, in place on buf.
+// Blocks = block_partition(count, pof2).  On return newrank holds block newrank.
+void rs_recursive_halving(sched& s, void* buf, const fold& f, const std::vector<size_t>& cnt,
+                          const std::vector<size_t>& off, int dtype, int op, reduction_fn_t fn, uint64_t step_base) {
+    const size_t esz = dtype_size(dtype);
+    int lo = 0, hi = f.pof2;
+    uint64_t step = step_base;
+    size_t max_half = 0;
+    for (int i = 0; i < f.pof2; i++)
+        max_half += cnt[i];
+    void* tmp = s.alloc_tmp((max_half / 2 + cnt[0] + 1) * esz + 64);
+    for (int mask = f.pof2 / 2; mask >= 1; mask /= 2, step++) {
+        const int mid = (lo + hi) / 2;
+        const int partner = f.real(f.newrank ^ mask);
+        int klo, khi, slo, shi; // keep / send ranges in blocks
+        if ((f.newrank & mask) == 0) {
+            klo = lo, khi = mid, slo = mid, shi = hi;
+        }
+        else {
+            klo = mid, khi = hi, slo = lo, shi = mid;
+        }
+        auto span = [&](int a, int b) { return (b > a) ? (off[b - 1] + cnt[b - 1] - off[a]) : (size_t)0; };
+        s.add<send_entry>(at(buf, off[slo], esz), span(slo, shi) * esz, partner, step);
+        s.add<recv_reduce_entry>(at(buf, off[klo], esz), span(klo, khi), dtype, op, partner, step, fn, tmp);
+        s.add_barrier();
+        lo = klo;
+        hi = khi;
+    }
+}
+
+// Recursive-doubling allgather, the mirror image of the function above.
+void ag_recursive_doubling(sched& s, void* buf, const fold& f, const std::vector<size_t>& cnt,
+                           const std::vector<size_t>& off, int dtype, uint64_t step_base) {
+    const size_t esz = dtype_size(dtype);
+    int lo = f.newrank, hi = f.newrank + 1;
+    uint64_t step = step_base;
+    auto span = [&](int a, int b) { return (b > a) ? (off[b - 1] + cnt[b - 1] - off[a]) : (size_t)0; };
+    for (int mask = 1; mask < f.pof2; mask *= 2, step++) {
+        const int partner = f.real(f.newrank ^ mask);
+        const int size = hi - lo;
+        int plo, phi;
+        if ((f.newrank & mask) == 0) {
+            plo = hi, phi = hi + size;
+        }
+        else {
+            plo = lo - size, phi = lo;
+        }
+        s.add<send_entry>(at(buf, off[lo], esz), span(lo, hi) * esz, partner, step);
+        s.add<recv_entry>(at(buf, off[plo], esz), span(plo, phi) * esz, partner, step);
+        s.add_barrier();
+        lo = std::min(lo, plo);
+        hi = std::max(hi, phi);
+    }
+}
+
+} // namespace
+
+void block_partition(size_t count, int parts, std::vector<size_t>& counts, std::vector<size_t>& offs) {
+    counts.assign(parts, 0);
+    offs.assign(parts, 0);
+    const size_t base = count / parts, rem = count % parts;
+    size_t o = 0;
+    for (int i = 0; i < parts; i++) {
+        counts[i] = base + ((size_t)i < rem ? 1 : 0);
+        offs[i] = o;
+        o += counts[i];
+    }
+}
+
+// ---------------------------------------------------------------------------- reduce_scatter
+void reduce_scatter_ring_v(sched& s, void* inout, const std::vector<size_t>& counts, const std::vector<size_t>& offs,
+                           int dtype, int op, reduction_fn_t fn, uint64_t step_base) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    if (N == 1)
+        return;
+    const size_t esz = dtype_size(dtype);
+    size_t maxc = *std::max_element(counts.begin(), counts.end());
+    void* tmp = s.alloc_tmp(maxc * esz + 64);
+    const int next = (r + 1) % N, prev = (r - 1 + N) % N;
+    for (int st = 0; st < N - 1; st++) {
+        const int sb = (r - st - 1 + 2 * N) % N, rb = (r - st - 2 + 2 * N) % N;
+        s.add<send_entry>(at(inout, offs[sb], esz), counts[sb] * esz, next, step_base + st);
+        s.add<recv_reduce_entry>(at(inout, offs[rb], esz), counts[rb], dtype, op, prev, step_base + st, fn, tmp);
+        s.add_barrier();
+    }
+}
+
+void reduce_scatter_ring(sched& s, const buf_desc& b) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(b.dtype);
+    const size_t rc = b.count;
+    if (N == 1) {
+        copy_in(s, b.send, b.recv, rc * esz);
+        return;
+    }
+    // work on a scratch copy of the whole send buffer so that send stays intact
+    void* work = s.alloc_tmp(rc * N * esz + 64);
+    s.add<copy_entry>(b.send, work, rc * N * esz);
+    s.add_barrier();
+    std::vector<size_t> cnt(N, rc), off(N);
+    for (int i = 0; i < N; i++)
+        off[i] = (size_t)i * rc;
+    reduce_scatter_ring_v(s, work, cnt, off, b.dtype, b.op, b.fn, 0);
+    s.add<copy_entry>(at(work, off[r], esz), b.recv, rc * esz);
+}
+
+void reduce_scatter_naive(sched& s, const buf_desc& b) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(b.dtype);
+    const size_t rc = b.count;
+    const bool inplace = b.recv == at(b.send, (size_t)r * rc, esz);
+    std::vector<void*> tmps(N, nullptr);
+    for (int k = 1; k < N; k++) {
+        const int p = (r + k) % N;
+        tmps[p] = s.alloc_tmp(rc * esz + 64);
+        s.add<recv_entry>(tmps[p], rc * esz, p, 0);
+        s.add<send_entry>(at(b.send, (size_t)p * rc, esz), rc * esz, p, 0);
+    }
+    s.add_barrier();
+    if (!inplace)
+        s.add<copy_entry>(at(b.send, (size_t)r * rc, esz), b.recv, rc * esz);
+    s.add_barrier();
+    for (int p = 0; p < N; p++) // fixed order: reproducible rounding
+        if (p != r) {
+            s.add<reduce_local_entry>(tmps[p], b.recv, rc, b.dtype, b.op, b.fn);
+            s.add_barrier();
+        }
+}
+
+// ---------------------------------------------------------------------------- allgatherv
+void allgatherv_naive(sched& s, const void* send, void* recv, const std::vector<size_t>& counts,
+                      const std::vector<size_t>& offs, int dtype, uint64_t step_base) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(dtype);
+    char* mine = at(recv, offs[r], esz);
+    if (send && send != mine) {
+        s.add<copy_entry>(send, mine, counts[r] * esz);
+        s.add_barrier();
+    }
+    for (int k = 1; k < N; k++) {
+        const int p = (r + k) % N;
+        s.add<recv_entry>(at(recv, offs[p], esz), counts[p] * esz, p, step_base);
+        s.add<send_entry>(mine, counts[r] * esz, p, step_base);
+    }
+    s.add_barrier();
+}
+
+void allgatherv_ring(sched& s, const void* send, void* recv, const std::vector<size_t>& counts,
+                     const std::vector<size_t>& offs, int dtype, uint64_t step_base) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(dtype);
+    char* mine = at(recv, offs[r], esz);
+    if (send && send != mine) {
+        s.add<copy_entry>(send, mine, counts[r] * esz);
+        s.add_barrier();
+    }
+    const int next = (r + 1) % N, prev = (r - 1 + N) % N;
+    for (int st = 0; st < N - 1; st++) {
+        const int sb = (r - st + N) % N, rb = (r - st - 1 + N) % N;
+        s.add<send_entry>(at(recv, offs[sb], esz), counts[sb] * esz, next, step_base + st);
+        s.add<recv_entry>(at(recv, offs[rb], esz), counts[rb] * esz, prev, step_base + st);
+        s.add_barrier();
+    }
+}
+
+void allgatherv_multi_bcast(sched& s, const void* send, void* recv, const std::vector<size_t>& counts,
+                            const std::vector<size_t>& offs, int dtype) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(dtype);
+    char* mine = at(recv, offs[r], esz);
+    if (send && send != mine) {
+        s.add<copy_entry>(send, mine, counts[r] * esz);
+        s.add_barrier();
+    }
+    // one tree broadcast per root, all running concurrently on disjoint step ranges
+    for (int root = 0; root < N; root++) {
+        void* blk = at(recv, offs[root], esz);
+        const size_t bytes = counts[root] * esz;
+        const uint64_t base = (uint64_t)(root + 1) * 64;
+        s.add<subsched_entry>([=](sched& sub) { bcast_tree(sub, blk, bytes, root, base); }, "AGV_BCAST");
+    }
+    s.add_barrier();
+}
+
+void allgatherv_naive_vec(sched& s, const void* send, const std::vector<void*>& recv_bufs,
+                          const std::vector<size_t>& counts, int dtype) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(dtype);
+    if (send && send != recv_bufs[r]) {
+        s.add<copy_entry>(send, recv_bufs[r], counts[r] * esz);
+        s.add_barrier();
+    }
+    for (int k = 1; k < N; k++) {
+        const int p = (r + k) % N;
+        s.add<recv_entry>(recv_bufs[p], counts[p] * esz, p, 0);
+        s.add<send_entry>(send ? send : recv_bufs[r], counts[r] * esz, p, 0);
+    }
+    s.add_barrier();
+}
+
+// ---------------------------------------------------------------------------- allreduce
+void allreduce_ring(sched& s, const buf_desc& b) {
+    host_comm* c = s.comm();
+    const int N = c->size();
+    const size_t esz = dtype_size(b.dtype);
+    copy_in(s, b.send, b.recv, b.count * esz);
+    if (N == 1)
+        return;
+    std::vector<size_t> cnt, off;
+    block_partition(b.count, N, cnt, off);
+    reduce_scatter_ring_v(s, b.recv, cnt, off, b.dtype, b.op, b.fn, 0);
+    allgatherv_ring(s, nullptr, b.recv, cnt, off, b.dtype, 1000);
+}
+
+void allreduce_recursive_doubling(sched& s, const buf_desc& b) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(b.dtype);
+    const size_t bytes = b.count * esz;
+    copy_in(s, b.send, b.recv, bytes);
+    if (N == 1)
+        return;
+    const fold f = make_fold(N, r);
+    void* tmp = s.alloc_tmp(bytes + 64);
+    if (r < 2 * f.rem) {
+        if (f.newrank < 0) {
+            s.add<send_entry>(b.recv, bytes, r + 1, 0);
+        }
+        else {
+            s.add<recv_reduce_entry>(b.recv, b.count, b.dtype, b.op, r - 1, 0, b.fn, tmp);
+        }
+        s.add_barrier();
+    }
+    if (f.newrank >= 0) {
+        uint64_t step = 1;
+        for (int mask = 1; mask < f.pof2; mask *= 2, step++) {
+            const int partner = f.real(f.newrank ^ mask);
+            // exchange whole buffers; reduce only after my send has left the buffer
+            s.add<send_entry>(b.recv, bytes, partner, step);
+            s.add<recv_entry>(tmp, bytes, partner, step);
+            s.add_barrier();
+            s.add<reduce_local_entry>(tmp, b.recv, b.count, b.dtype, b.op, b.fn);
+            s.add_barrier();
+        }
+    }
+    if (r < 2 * f.rem) {
+        if (f.newrank < 0)
+            s.add<recv_entry>(b.recv, bytes, r + 1, 999);
+        else
+            s.add<send_entry>(b.recv, bytes, r - 1, 999);
+        s.add_barrier();
+    }
+}
+
+void allreduce_rabenseifner(sched& s, const buf_desc& b) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(b.dtype);
+    const size_t bytes = b.count * esz;
+    copy_in(s, b.send, b.recv, bytes);
+    if (N == 1)
+        return;
+    const fold f = make_fold(N, r);
+    if ((size_t)f.pof2 > b.count) { // fewer elements than participants: blocks would be empty
+        allreduce_recursive_doubling(s, buf_desc{ nullptr, b.recv, b.count, b.dtype, b.op, b.fn });
+        return;
+    }
+    if (r < 2 * f.rem) {
+        if (f.newrank < 0)
+            s.add<send_entry>(b.recv, bytes, r + 1, 0);
+        else
+            s.add<recv_reduce_entry>(b.recv, b.count, b.dtype, b.op, r - 1, 0, b.fn);
+        s.add_barrier();
+    }
+    if (f.newrank >= 0) {
+        std::vector<size_t> cnt, off;
+        block_partition(b.count, f.pof2, cnt, off);
+        rs_recursive_halving(s, b.recv, f, cnt, off, b.dtype, b.op, b.fn, 1);
+        ag_recursive_doubling(s, b.recv, f, cnt, off, b.dtype, 100);
+    }
+    if (r < 2 * f.rem) {
+        if (f.newrank < 0)
+            s.add<recv_entry>(b.recv, bytes, r + 1, 999);
+        else
+            s.add<send_entry>(b.recv, bytes, r - 1, 999);
+        s.add_barrier();
+    }
+}
+
+void allreduce_nreduce(sched& s, const buf_desc& b) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(b.dtype);
+    if (N == 1) {
+        copy_in(s, b.send, b.recv, b.count * esz);
+        return;
+    }
+    const void* src = b.send ? b.send : b.recv;
+    std::vector<size_t> cnt, off;
+    block_partition(b.count, N, cnt, off);
+    // every rank owns one block: gather the N-1 foreign contributions, reduce in rank order
+    std::vector<void*> tmps(N, nullptr);
+    for (int k = 1; k < N; k++) {
+        const int p = (r + k) % N;
+        tmps[p] = s.alloc_tmp(cnt[r] * esz + 64);
+        s.add<recv_entry>(tmps[p], cnt[r] * esz, p, 0);
+        s.add<send_entry>(at(src, off[p], esz), cnt[p] * esz, p, 0);
+    }
+    s.add_barrier();
+    if (src != b.recv)
+        s.add<copy_entry>(at(src, off[r], esz), at(b.recv, off[r], esz), cnt[r] * esz);
+    s.add_barrier();
+    for (int p = 0; p < N; p++)
+        if (p != r) {
+            s.add<reduce_local_entry>(tmps[p], at(b.recv, off[r], esz), cnt[r], b.dtype, b.op, b.fn);
+            s.add_barrier();
+        }
+    allgatherv_naive(s, nullptr, b.recv, cnt, off, b.dtype, 1);
+}
+
+void allreduce_2d(sched& s, const buf_desc& b) {
+    host_comm* c = s.comm();
+    const size_t esz = dtype_size(b.dtype);
+    auto node = c->node_comm();
+    auto r2r = c->r2r_comm();
+    if (!node || !r2r || r2r->size() == 1 || node->size() == 1 || node->size() * r2r->size() != c->size()) {
+        allreduce_ring(s, b);
+        return;
+    }
+    copy_in(s, b.send, b.recv, b.count * esz);
+    // reduce-scatter inside the node, allreduce of my block across nodes, allgather inside the node
+    std::vector<size_t> cnt, off;
+    block_partition(b.count, node->size(), cnt, off);
+    const int lr = node->rank();
+    void* recv = b.recv;
+    const int dtype = b.dtype, op = b.op;
+    reduction_fn_t fn = b.fn;
+    host_comm* node_p = node.get();
+    host_comm* r2r_p = r2r.get();
+    s.add<subsched_entry>(
+        [=](sched& sub) { reduce_scatter_ring_v(sub, recv, cnt, off, dtype, op, fn, 0); }, "2D_RS", node_p);
+    s.add_barrier();
+    s.add<subsched_entry>(
+        [=](sched& sub) {
+            allreduce_ring(sub, buf_desc{ nullptr, at(recv, off[lr], dtype_size(dtype)), cnt[lr], dtype, op, fn });
+        },
+        "2D_AR", r2r_p);
+    s.add_barrier();
+    s.add<subsched_entry>([=](sched& sub) { allgatherv_ring(sub, nullptr, recv, cnt, off, dtype, 0); }, "2D_AG",
+                          node_p);
+    s.add_barrier();
+}
+
+void allreduce_double_tree(sched& s, const buf_desc& b) {
+    host_comm* c = s.comm();
+    const int N = c->size();
+    const size_t esz = dtype_size(b.dtype);
+    copy_in(s, b.send, b.recv, b.count * esz);
+    if (N == 1)
+        return;
+    // two halves travel through two binomial trees with different roots, so a rank
+    // that is an inner node of one tree is a leaf (or near-leaf) of the other
+    const size_t h0 = b.count / 2, h1 = b.count - h0;
+    const int root0 = 0, root1 = N / 2;
+    void* recv = b.recv;
+    const int dtype = b.dtype, op = b.op;
+    reduction_fn_t fn = b.fn;
+    if (h0)
+        s.add<subsched_entry>(
+            [=](sched& sub) {
+                reduce_tree(sub, buf_desc{ nullptr, recv, h0, dtype, op, fn }, root0, 0);
+                bcast_tree(sub, recv, h0 * dtype_size(dtype), root0, 500);
+            },
+            "DTREE_A");
+    s.add<subsched_entry>(
+        [=](sched& sub) {
+            void* p = at(recv, h0, dtype_size(dtype));
+            reduce_tree(sub, buf_desc{ nullptr, p, h1, dtype, op, fn }, root1, 1000);
+            bcast_tree(sub, p, h1 * dtype_size(dtype), root1, 1500);
+        },
+        "DTREE_B");
+    s.add_barrier();
+}
+
+// ---------------------------------------------------------------------------- alltoallv
+void alltoallv_naive(sched& s, const void* send, const std::vector<size_t>& scounts, const std::vector<size_t>& soffs,
+                     void* recv, const std::vector<size_t>& rcounts, const std::vector<size_t>& roffs, int dtype) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(dtype);
+    s.add<copy_entry>(at(send, soffs[r], esz), at(recv, roffs[r], esz), std::min(scounts[r], rcounts[r]) * esz);
+    for (int k = 1; k < N; k++) {
+        const int src = (r - k + N) % N, dst = (r + k) % N;
+        s.add<recv_entry>(at(recv, roffs[src], esz), rcounts[src] * esz, src, 0);
+        s.add<send_entry>(at(send, soffs[dst], esz), scounts[dst] * esz, dst, 0);
+    }
+    s.add_barrier();
+}
+
+void alltoallv_scatter(sched& s, const void* send, const std::vector<size_t>& scounts,
+                       const std::vector<size_t>& soffs, void* recv, const std::vector<size_t>& rcounts,
+                       const std::vector<size_t>& roffs, int dtype, size_t max_ops) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(dtype);
+    if (max_ops == 0)
+        max_ops = 1;
+    s.add<copy_entry>(at(send, soffs[r], esz), at(recv, roffs[r], esz), std::min(scounts[r], rcounts[r]) * esz);
+    // flow control: at most max_ops exchanges in flight, then a barrier point
+    size_t in_batch = 0;
+    for (int k = 1; k < N; k++) {
+        const int src = (r - k + N) % N, dst = (r + k) % N;
+        s.add<recv_entry>(at(recv, roffs[src], esz), rcounts[src] * esz, src, (uint64_t)k);
+        s.add<send_entry>(at(send, soffs[dst], esz), scounts[dst] * esz, dst, (uint64_t)k);
+        if (++in_batch == max_ops) {
+            s.add_barrier();
+            in_batch = 0;
+        }
+    }
+    s.add_barrier();
+}
+
+// ---------------------------------------------------------------------------- barrier
+void barrier_dissemination(sched& s) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    uint64_t step = 0;
+    for (int d = 1; d < N; d *= 2, step++) {
+        s.add<send_entry>(nullptr, 0, (r + d) % N, step);
+        s.add<recv_entry>(nullptr, 0, (r - d + N) % N, step);
+        s.add_barrier();
+    }
+}
+
+void barrier_ring(sched& s) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    if (N == 1)
+        return;
+    // two trips of a token around the ring
+    for (uint64_t trip = 0; trip < 2; trip++) {
+        if (r == 0) {
+            s.add<send_entry>(nullptr, 0, 1 % N, trip);
+            s.add<recv_entry>(nullptr, 0, N - 1, trip);
+        }
+        else {
+            s.add<recv_entry>(nullptr, 0, r - 1, trip);
+            s.add_barrier();
+            s.add<send_entry>(nullptr, 0, (r + 1) % N, trip);
+        }
+        s.add_barrier();
+    }
+}
+
+// ---------------------------------------------------------------------------- bcast
+void bcast_naive(sched& s, void* buf, size_t bytes, int root, uint64_t step_base) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    if (r == root) {
+        for (int p = 0; p < N; p++)
+            if (p != root)
+                s.add<send_entry>(buf, bytes, p, step_base);
+    }
+    else
+        s.add<recv_entry>(buf, bytes, root, step_base);
+    s.add_barrier();
+}
+
+void bcast_tree(sched& s, void* buf, size_t bytes, int root, uint64_t step_base, int shift) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    (void)shift;
+    if (N == 1)
+        return;
+    const int v = (r - root + N) % N;
+    int mask = 1;
+    while (mask < N) {
+        if (v & mask) {
+            s.add<recv_entry>(buf, bytes, ((v - mask) + root) % N, step_base);
+            s.add_barrier();
+            break;
+        }
+        mask <<= 1;
+    }
+    mask >>= 1;
+    while (mask > 0) {
+        if (v + mask < N)
+            s.add<send_entry>(buf, bytes, ((v + mask) + root) % N, step_base);
+        mask >>= 1;
+    }
+    s.add_barrier();
+}
+
+void bcast_ring(sched& s, void* buf, size_t count, int dtype, int root) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(dtype);
+    if (N == 1)
+        return;
+    std::vector<size_t> cnt, off;
+    block_partition(count, N, cnt, off);
+    // scatter from the root, then a ring allgather
+    if (r == root) {
+        for (int p = 0; p < N; p++)
+            if (p != root)
+                s.add<send_entry>(at(buf, off[p], esz), cnt[p] * esz, p, 0);
+    }
+    else
+        s.add<recv_entry>(at(buf, off[r], esz), cnt[r] * esz, root, 0);
+    s.add_barrier();
+    allgatherv_ring(s, nullptr, buf, cnt, off, dtype, 10);
+}
+
+// ---------------------------------------------------------------------------- reduce
+void reduce_tree(sched& s, const buf_desc& b, int root, uint64_t step_base, int shift) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    (void)shift;
+    const size_t esz = dtype_size(b.dtype);
+    const size_t bytes = b.count * esz;
+    // non-root ranks accumulate in scratch unless the caller reduces in place (send == nullptr)
+    void* acc = b.recv;
+    if (b.send) {
+        if (r != root || !b.recv)
+            acc = s.alloc_tmp(bytes + 64);
+        if (acc != b.send) {
+            s.add<copy_entry>(b.send, acc, bytes);
+            s.add_barrier();
+        }
+    }
+    if (N == 1)
+        return;
+    const int v = (r - root + N) % N;
+    void* tmp = s.alloc_tmp(bytes + 64);
+    int mask = 1;
+    while (mask < N) {
+        if (v & mask) {
+            s.add<send_entry>(acc, bytes, ((v & ~mask) + root) % N, step_base);
+            s.add_barrier();
+            break;
+        }
+        const int child = v | mask;
+        if (child < N) {
+            s.add<recv_reduce_entry>(acc, b.count, b.dtype, b.op, (child + root) % N, step_base, b.fn, tmp);
+            s.add_barrier();
+        }
+        mask <<= 1;
+    }
+}
+
+void reduce_ring(sched& s, const buf_desc& b, int root) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(b.dtype);
+    const size_t bytes = b.count * esz;
+    if (N == 1) {
+        copy_in(s, b.send, b.recv, bytes);
+        return;
+    }
+    void* work = (r == root) ? b.recv : s.alloc_tmp(bytes + 64);
+    if (b.send && b.send != work) {
+        s.add<copy_entry>(b.send, work, bytes);
+        s.add_barrier();
+    }
+    std::vector<size_t> cnt, off;
+    block_partition(b.count, N, cnt, off);
+    reduce_scatter_ring_v(s, work, cnt, off, b.dtype, b.op, b.fn, 0);
+    // gather the reduced blocks at the root
+    if (r == root) {
+        for (int p = 0; p < N; p++)
+            if (p != root)
+                s.add<recv_entry>(at(work, off[p], esz), cnt[p] * esz, p, 2000);
+    }
+    else
+        s.add<send_entry>(at(work, off[r], esz), cnt[r] * esz, root, 2000);
+    s.add_barrier();
+}
+
+void reduce_rabenseifner(sched& s, const buf_desc& b, int root) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(b.dtype);
+    const size_t bytes = b.count * esz;
+    const fold f = make_fold(N, r);
+    if (N == 1 || (size_t)f.pof2 > b.count) {
+        reduce_tree(s, b, root);
+        return;
+    }
+    void* work = (r == root) ? b.recv : s.alloc_tmp(bytes + 64);
+    if (b.send && b.send != work) {
+        s.add<copy_entry>(b.send, work, bytes);
+        s.add_barrier();
+    }
+    if (r < 2 * f.rem) {
+        if (f.newrank < 0)
+            s.add<send_entry>(work, bytes, r + 1, 0);
+        else
+            s.add<recv_reduce_entry>(work, b.count, b.dtype, b.op, r - 1, 0, b.fn);
+        s.add_barrier();
+    }
+    std::vector<size_t> cnt, off;
+    block_partition(b.count, f.pof2, cnt, off);
+    if (f.newrank >= 0)
+        rs_recursive_halving(s, work, f, cnt, off, b.dtype, b.op, b.fn, 1);
+    // every participant sends its block to the root
+    if (r == root) {
+        for (int nr = 0; nr < f.pof2; nr++) {
+            const int p = f.real(nr);
+            if (p != root)
+                s.add<recv_entry>(at(work, off[nr], esz), cnt[nr] * esz, p, 3000);
+        }
+    }
+    else if (f.newrank >= 0)
+        s.add<send_entry>(at(work, off[f.newrank], esz), cnt[f.newrank] * esz, root, 3000);
+    s.add_barrier();
+}
+
+// ---------------------------------------------------------------------------- point to point
+void send_direct(sched& s, const void* buf, size_t bytes, int peer, uint64_t seq) {
+    s.add<send_entry>(buf, bytes, peer, seq & 0xffff);
+}
+void recv_direct(sched& s, void* buf, size_t bytes, int peer, uint64_t seq) {
+    s.add<recv_entry>(buf, bytes, peer, seq & 0xffff);
+}
+
+} // namespace algo
+} // namespace cclx

@@ -1,0 +1,752 @@
+#include "coll/coll.hpp"
+
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <list>
+#include <sstream>
+
+#include "coll/algorithms.hpp"
+#include "coll/selection.hpp"
+#include "core/datatype.hpp"
+#include "core/env.hpp"
+#include "core/log.hpp"
+#include "fusion/fusion.hpp"
+#include "gpu/cuda_driver.hpp"
+#include "gpu/device_comm.hpp"
+#include "sched/entries.hpp"
+
+namespace cclx {
+
+coll_stats& stats() {
+    static coll_stats s;
+    return s;
+}
+
+// ---- events -----------------------------------------------------------------------------
+namespace {
+
+class completed_event : public event_impl {
+public:
+    void wait() override {}
+    bool test() override { return true; }
+};
+
+// masters whose event was dropped before completion live here until they finish
+// (reference: recycle_storage of the schedule cache)
+std::mutex recycle_mu;
+std::list<std::pair<std::unique_ptr<master_sched>, uint64_t>> recycle;
+
+void purge_recycle() {
+    std::lock_guard<std::mutex> lk(recycle_mu);
+    for (auto it = recycle.begin(); it != recycle.end();) {
+        if (it->first->ticket_complete(it->second))
+            it = recycle.erase(it);
+        else
+            ++it;
+    }
+}
+
+class host_event : public event_impl {
+public:
+    host_event(master_sched* m, uint64_t ticket, std::unique_ptr<master_sched> owned)
+            : m_(m), ticket_(ticket), owned_(std::move(owned)) {}
+    ~host_event() override {
+        if (owned_ && !owned_->ticket_complete(ticket_)) {
+            std::lock_guard<std::mutex> lk(recycle_mu);
+            recycle.emplace_back(std::move(owned_), ticket_);
+        }
+    }
+    void wait() override { executor::get().wait(m_, ticket_); }
+    bool test() override {
+        bool done = executor::get().test(m_, ticket_);
+        if (done && m_->req().has_error())
+            CCL_THROW("collective failed: ", m_->req().error());
+        return done;
+    }
+
+private:
+    master_sched* m_;
+    uint64_t ticket_;
+    std::unique_ptr<master_sched> owned_;
+};
+
+class cuda_event_impl : public event_impl {
+public:
+    cuda_event_impl(gpu::device_comm* dc, cudaStream_t st) : dc_(dc) {
+        CUDA_CHECK(cudaSetDevice(dc->device_id()));
+        CUDA_CHECK(cudaEventCreateWithFlags(&ev_, cudaEventDisableTiming));
+        CUDA_CHECK(cudaEventRecord(ev_, st));
+    }
+    ~cuda_event_impl() override { cudaEventDestroy(ev_); }
+    void wait() override {
+        CUDA_CHECK(cudaEventSynchronize(ev_));
+        dc_->check_status();
+    }
+    bool test() override {
+        cudaError_t e = cudaEventQuery(ev_);
+        if (e == cudaErrorNotReady)
+            return false;
+        CUDA_CHECK(e);
+        dc_->check_status();
+        return true;
+    }
+    void* native() override { return (void*)ev_; }
+
+private:
+    gpu::device_comm* dc_;
+    cudaEvent_t ev_;
+};
+
+// placeholder returned for send/recv inside a group; bound at group_end
+class group_event : public event_impl {
+public:
+    void bind(event_ptr e) { real_ = std::move(e); }
+    void wait() override {
+        CCL_THROW_IF_NOT(real_, "an operation issued inside a group can be waited only after group_end");
+        real_->wait();
+    }
+    bool test() override { return real_ ? real_->test() : false; }
+    void* native() override { return real_ ? real_->native() : nullptr; }
+
+private:
+    event_ptr real_;
+};
+
+struct group_item {
+    host_comm* comm;
+    coll_param param;
+    coll_attr attr;
+    std::shared_ptr<group_event> ev;
+};
+thread_local bool tl_group_active = false;
+thread_local std::vector<group_item> tl_group;
+
+size_t total(const std::vector<size_t>& v) {
+    size_t s = 0;
+    for (size_t x : v)
+        s += x;
+    return s;
+}
+
+std::vector<size_t> prefix(const std::vector<size_t>& v) {
+    std::vector<size_t> o(v.size(), 0);
+    for (size_t i = 1; i < v.size(); i++)
+        o[i] = o[i - 1] + v[i - 1];
+    return o;
+}
+
+// message size the selection tables are keyed by
+size_t selection_bytes(const host_comm& comm, const coll_param& p) {
+    const size_t esz = dtype_size(p.dtype);
+    switch (p.ctype) {
+        case coll_allgather: return p.count * esz * comm.size();
+        case coll_allgatherv: return total(p.recv_counts) * esz;
+        case coll_alltoall: return p.count * esz * comm.size();
+        case coll_alltoallv: return total(p.send_counts) * esz;
+        case coll_reduce_scatter: return p.count * esz * comm.size();
+        case coll_barrier: return 0;
+        default: return p.count * esz;
+    }
+}
+
+} // namespace
+
+event_ptr make_completed_event() {
+    return std::make_shared<completed_event>();
+}
+
+// ---- validation -------------------------------------------------------------------------
+void coll_validate(const host_comm& comm, const coll_param& p, const coll_attr& attr) {
+    const int N = comm.size();
+    if (p.ctype == coll_barrier)
+        return;
+    CCL_THROW_IF_NOT(datatype_table::get().exists(p.dtype), "unknown datatype ", p.dtype);
+    const bool reduces = p.ctype == coll_allreduce || p.ctype == coll_reduce || p.ctype == coll_reduce_scatter;
+    if (reduces) {
+        CCL_THROW_IF_NOT(p.reduction >= red_sum && p.reduction <= red_custom, "invalid reduction ", p.reduction);
+        if (p.reduction == red_custom)
+            CCL_THROW_IF_NOT(attr.reduction_fn != nullptr, "custom reduction needs attr reduction_fn");
+        if (p.dtype >= dt_custom_base)
+            CCL_THROW_IF_NOT(p.reduction == red_custom, "custom datatypes can only be reduced with a custom reduction");
+        if (p.reduction == red_custom)
+            CCL_THROW_IF_NOT(!p.device, "custom reductions run on host buffers only");
+    }
+    switch (p.ctype) {
+        case coll_allgatherv:
+            CCL_THROW_IF_NOT((int)p.recv_counts.size() == N, "allgatherv: recv_counts needs ", N, " entries");
+            CCL_THROW_IF_NOT(p.recv_counts[comm.rank()] == p.count, "allgatherv: send_count (", p.count,
+                             ") differs from recv_counts[rank] (", p.recv_counts[comm.rank()], ")");
+            if (!p.recv_bufs.empty())
+                CCL_THROW_IF_NOT((int)p.recv_bufs.size() == N, "allgatherv: recv_bufs needs ", N, " entries");
+            break;
+        case coll_alltoallv:
+            CCL_THROW_IF_NOT((int)p.send_counts.size() == N && (int)p.recv_counts.size() == N,
+                             "alltoallv: send_counts and recv_counts need ", N, " entries");
+            break;
+        case coll_bcast:
+        case coll_broadcast:
+        case coll_reduce:
+            CCL_THROW_IF_NOT(p.root >= 0 && p.root < N, "root ", p.root, " outside the communicator");
+            break;
+        case coll_send:
+        case coll_recv:
+            CCL_THROW_IF_NOT(p.peer >= 0 && p.peer < N && p.peer != comm.rank(), "invalid peer ", p.peer);
+            break;
+        default: break;
+    }
+    const size_t bytes = selection_bytes(comm, p);
+    if (bytes == 0)
+        return;
+    const bool needs_send = p.ctype != coll_recv && p.ctype != coll_bcast;
+    const bool needs_recv = p.ctype != coll_send && !(p.ctype == coll_reduce && comm.rank() != p.root);
+    if (needs_send && p.ctype != coll_allgatherv && p.ctype != coll_allgather && p.ctype != coll_broadcast)
+        CCL_THROW_IF_NOT(p.send_buf != nullptr, coll_name(p.ctype), ": send buffer is null");
+    if (needs_recv && p.recv_bufs.empty())
+        CCL_THROW_IF_NOT(p.recv_buf != nullptr, coll_name(p.ctype), ": recv buffer is null");
+    // in-place aliasing rules (reference src/coll/coll_util.cpp:650-760)
+    if (env_data::get().check_inplace_aliasing && p.send_buf && p.recv_buf && p.recv_bufs.empty()) {
+        const size_t esz = dtype_size(p.dtype);
+        const char* s = (const char*)p.send_buf;
+        const char* r = (const char*)p.recv_buf;
+        if (p.ctype == coll_allgatherv || p.ctype == coll_allgather) {
+            std::vector<size_t> counts = p.recv_counts.empty() ? std::vector<size_t>(N, p.count) : p.recv_counts;
+            const size_t off = prefix(counts)[comm.rank()] * esz;
+            const size_t all = total(counts) * esz;
+            const bool overlap = s < r + all && r < s + p.count * esz;
+            if (overlap)
+                CCL_THROW_IF_NOT(s == r + off, coll_name(p.ctype),
+                                 ": send buffer overlaps recv buffer but is not at the in-place offset of this rank");
+        }
+        else if (p.ctype == coll_reduce_scatter) {
+            const size_t off = (size_t)comm.rank() * p.count * esz;
+            const bool overlap = r < s + p.count * N * esz && s < r + p.count * esz;
+            if (overlap)
+                CCL_THROW_IF_NOT(r == s + off,
+                                 "reduce_scatter: recv buffer overlaps send buffer but is not at send + rank*recv_count");
+        }
+    }
+}
+
+bool coll_is_inplace(const host_comm& comm, const coll_param& p) {
+    const size_t esz = dtype_size(p.dtype);
+    switch (p.ctype) {
+        case coll_allgather:
+        case coll_allgatherv: {
+            if (!p.send_buf)
+                return true;
+            std::vector<size_t> counts = p.recv_counts.empty() ? std::vector<size_t>(comm.size(), p.count) : p.recv_counts;
+            return p.send_buf == (const char*)p.recv_buf + prefix(counts)[comm.rank()] * esz;
+        }
+        case coll_reduce_scatter: return p.recv_buf == (const char*)p.send_buf + (size_t)comm.rank() * p.count * esz;
+        default: return p.send_buf == p.recv_buf;
+    }
+}
+
+std::string coll_cache_key(const host_comm& comm, const coll_param& p, const coll_attr& attr) {
+    std::ostringstream ss;
+    ss << (int)p.ctype << '|' << p.send_buf << '|' << p.recv_buf << '|' << p.count << '|' << p.dtype << '|'
+       << p.reduction << '|' << p.root << '|' << p.peer << '|' << (const void*)attr.reduction_fn << '|'
+       << attr.priority;
+    for (size_t c : p.send_counts)
+        ss << ',' << c;
+    ss << '|';
+    for (size_t c : p.recv_counts)
+        ss << ',' << c;
+    ss << '|';
+    for (void* b : p.recv_bufs)
+        ss << ',' << b;
+    if (env_data::get().cache_key == cache_key_t::match_id && !attr.match_id.empty())
+        ss << "|m:" << attr.match_id;
+    return ss.str();
+}
+
+// ---- CPU schedule construction --------------------------------------------------------------
+namespace {
+
+void build_cpu(sched& s, host_comm& comm, const coll_param& p, const coll_attr& attr, size_t off_elems,
+               size_t count_elems) {
+    const int N = comm.size();
+    const size_t esz = dtype_size(p.dtype);
+    selector_param sp;
+    sp.ctype = p.ctype;
+    sp.comm_size = N;
+    sp.vector_buf = !p.recv_bufs.empty();
+    sp.custom_fn = attr.reduction_fn != nullptr;
+    const char* sbuf = p.send_buf ? (const char*)p.send_buf + off_elems * esz : nullptr;
+    char* rbuf = p.recv_buf ? (char*)p.recv_buf + off_elems * esz : nullptr;
+    switch (p.ctype) {
+        case coll_allreduce: {
+            sp.count = count_elems;
+            sp.bytes = count_elems * esz;
+            const std::string a = algorithm_selector::get().select_cpu(sp);
+            algo::buf_desc b{ sbuf, rbuf, count_elems, p.dtype, p.reduction, attr.reduction_fn };
+            if (a == "ring")
+                algo::allreduce_ring(s, b);
+            else if (a == "recursive_doubling")
+                algo::allreduce_recursive_doubling(s, b);
+            else if (a == "rabenseifner")
+                algo::allreduce_rabenseifner(s, b);
+            else if (a == "nreduce")
+                algo::allreduce_nreduce(s, b);
+            else if (a == "2d")
+                algo::allreduce_2d(s, b);
+            else if (a == "double_tree")
+                algo::allreduce_double_tree(s, b);
+            else
+                CCL_THROW("allreduce: unknown algorithm ", a);
+            break;
+        }
+        case coll_allgather:
+        case coll_allgatherv: {
+            std::vector<size_t> counts = p.ctype == coll_allgather ? std::vector<size_t>(N, p.count) : p.recv_counts;
+            sp.bytes = total(counts) * esz;
+            const std::string a = algorithm_selector::get().select_cpu(sp);
+            if (!p.recv_bufs.empty()) {
+                algo::allgatherv_naive_vec(s, p.send_buf, p.recv_bufs, counts, p.dtype);
+                break;
+            }
+            std::vector<size_t> offs = prefix(counts);
+            if (a == "ring")
+                algo::allgatherv_ring(s, p.send_buf, p.recv_buf, counts, offs, p.dtype);
+            else if (a == "multi_bcast")
+                algo::allgatherv_multi_bcast(s, p.send_buf, p.recv_buf, counts, offs, p.dtype);
+            else
+                algo::allgatherv_naive(s, p.send_buf, p.recv_buf, counts, offs, p.dtype);
+            break;
+        }
+        case coll_alltoall:
+        case coll_alltoallv: {
+            std::vector<size_t> sc = p.ctype == coll_alltoall ? std::vector<size_t>(N, p.count) : p.send_counts;
+            std::vector<size_t> rc = p.ctype == coll_alltoall ? std::vector<size_t>(N, p.count) : p.recv_counts;
+            sp.bytes = total(sc) * esz;
+            const std::string a = algorithm_selector::get().select_cpu(sp);
+            if (a == "scatter")
+                algo::alltoallv_scatter(s, p.send_buf, sc, prefix(sc), p.recv_buf, rc, prefix(rc), p.dtype,
+                                        env_data::get().alltoall_scatter_max_ops);
+            else
+                algo::alltoallv_naive(s, p.send_buf, sc, prefix(sc), p.recv_buf, rc, prefix(rc), p.dtype);
+            break;
+        }
+        case coll_barrier: {
+            sp.bytes = 0;
+            const std::string a = algorithm_selector::get().select_cpu(sp);
+            if (a == "ring")
+                algo::barrier_ring(s);
+            else
+                algo::barrier_dissemination(s);
+            break;
+        }
+        case coll_bcast:
+        case coll_broadcast: {
+            sp.bytes = count_elems * esz;
+            const std::string a = algorithm_selector::get().select_cpu(sp);
+            // out-of-place form: the root's data travels from send_buf, lands in recv_buf everywhere
+            if (p.ctype == coll_broadcast && comm.rank() == p.root && sbuf && sbuf != rbuf) {
+                s.add<copy_entry>(sbuf, rbuf, count_elems * esz);
+                s.add_barrier();
+            }
+            if (a == "naive")
+                algo::bcast_naive(s, rbuf, count_elems * esz, p.root);
+            else if (a == "ring")
+                algo::bcast_ring(s, rbuf, count_elems, p.dtype, p.root);
+            else
+                algo::bcast_tree(s, rbuf, count_elems * esz, p.root);
+            break;
+        }
+        case coll_reduce: {
+            sp.bytes = count_elems * esz;
+            const std::string a = algorithm_selector::get().select_cpu(sp);
+            algo::buf_desc b{ sbuf, comm.rank() == p.root ? rbuf : nullptr, count_elems, p.dtype, p.reduction,
+                              attr.reduction_fn };
+            if (a == "rabenseifner")
+                algo::reduce_rabenseifner(s, b, p.root);
+            else if (a == "ring")
+                algo::reduce_ring(s, b, p.root);
+            else
+                algo::reduce_tree(s, b, p.root);
+            break;
+        }
+        case coll_reduce_scatter: {
+            sp.bytes = p.count * esz * N;
+            const std::string a = algorithm_selector::get().select_cpu(sp);
+            algo::buf_desc b{ p.send_buf, p.recv_buf, p.count, p.dtype, p.reduction, attr.reduction_fn };
+            if (a == "ring")
+                algo::reduce_scatter_ring(s, b);
+            else
+                algo::reduce_scatter_naive(s, b);
+            break;
+        }
+        case coll_send: algo::send_direct(s, p.send_buf, p.count * esz, p.peer, 0); break;
+        case coll_recv: algo::recv_direct(s, p.recv_buf, p.count * esz, p.peer, 0); break;
+        default: CCL_THROW("unsupported collective ", (int)p.ctype);
+    }
+}
+
+// how many partial schedules (reference parallelizer.cpp:77-154)
+int part_count(const host_comm& comm, const coll_param& p, size_t bytes) {
+    const int workers = executor::get().worker_count();
+    if (workers <= 1)
+        return 1;
+    const bool splittable = p.ctype == coll_allreduce || p.ctype == coll_reduce || p.ctype == coll_bcast ||
+                            p.ctype == coll_broadcast;
+    if (!splittable || bytes < (size_t)workers * env_data::get().min_chunk_size || p.count < (size_t)workers * 64)
+        return 1;
+    return workers;
+}
+
+std::unique_ptr<master_sched> build_master(host_comm& comm, const coll_param& p, const coll_attr& attr,
+                                           uint64_t sched_id) {
+    std::unique_ptr<master_sched> m(new master_sched(&comm, sched_id));
+    const env_data& env = env_data::get();
+    static std::atomic<int> lifo_counter{ 0 };
+    m->priority = env.priority_mode == priority_mode_t::lifo
+                      ? lifo_counter.fetch_add(1)
+                      : (env.priority_mode == priority_mode_t::direct ? attr.priority : 0);
+    if (p.ctype == coll_barrier)
+        m->priority = 1 << 30; // barriers drain first
+    const size_t bytes = selection_bytes(comm, p);
+    const int parts = part_count(comm, p, bytes);
+    std::vector<size_t> cnt, off;
+    algo::block_partition(p.count, parts, cnt, off);
+    std::vector<std::function<bool()>> deps;
+    for (auto& d : p.deps)
+        if (d)
+            deps.push_back([d] { return d->test(); });
+    for (int i = 0; i < parts; i++) {
+        sched* s = m->add_partial(i);
+        if (!deps.empty()) {
+            s->add<deps_entry>(deps);
+            s->add_barrier();
+        }
+        if (parts == 1)
+            build_cpu(*s, comm, p, attr, 0, p.count);
+        else
+            build_cpu(*s, comm, p, attr, off[i], cnt[i]);
+    }
+    if (env.sched_dump) {
+        std::string d;
+        for (auto& s : m->partials())
+            s->dump(d);
+        LOG_INFO("built ", coll_name(p.ctype), ": ", d);
+    }
+    return m;
+}
+
+// host staging of device buffers (the node has no device communicator, or kernels are disabled)
+event_ptr staged_device_coll(host_comm& comm, coll_param p, const coll_attr& attr);
+
+// ---- device path ----------------------------------------------------------------------------
+event_ptr device_coll(host_comm& comm, coll_param& p, const coll_attr& attr) {
+    gpu::device_comm* dc = comm.device();
+    cudaStream_t st = (cudaStream_t)p.stream;
+    CUDA_CHECK(cudaSetDevice(dc->device_id()));
+    const int N = comm.size(), r = comm.rank();
+    const size_t esz = dtype_size(p.dtype);
+    stats().device_calls[p.ctype]++;
+    gpu::launch_opts o;
+    o.scale = attr.scale;
+    o.do_scale = attr.do_scale;
+    const size_t sel_bytes = selection_bytes(comm, p);
+    std::string forced = attr.gpu_algo.empty() ? algorithm_selector::get().forced_gpu(p.ctype, sel_bytes) : attr.gpu_algo;
+    if (!forced.empty()) {
+        o.algo = gpu::gpu_algo_from_name(forced);
+        CCL_THROW_IF_NOT(o.algo >= 0, "unknown GPU algorithm ", forced);
+    }
+    const int out_dt = attr.out_dtype >= 0 ? attr.out_dtype : p.dtype;
+    dev::rank_args ra;
+    std::memset(&ra, 0, sizeof(ra));
+    ra.send = p.send_buf;
+    ra.recv = p.recv_buf;
+    switch (p.ctype) {
+        case coll_allreduce: gpu::launch_allreduce(*dc, &ra, p.count, p.dtype, out_dt, p.reduction, o, st); break;
+        case coll_reduce_scatter:
+            gpu::launch_reduce_scatter(*dc, &ra, p.count, p.dtype, out_dt, p.reduction, o, st);
+            break;
+        case coll_reduce: gpu::launch_reduce(*dc, &ra, p.count, p.dtype, out_dt, p.reduction, p.root, o, st); break;
+        case coll_allgather:
+        case coll_allgatherv: {
+            std::vector<size_t> counts = p.ctype == coll_allgather ? std::vector<size_t>(N, p.count) : p.recv_counts;
+            if (!p.recv_bufs.empty()) {
+                // one destination buffer per rank: a broadcast per contributor
+                for (int q = 0; q < N; q++) {
+                    dev::rank_args b;
+                    std::memset(&b, 0, sizeof(b));
+                    b.send = q == r ? (p.send_buf ? p.send_buf : p.recv_bufs[q]) : nullptr;
+                    b.recv = p.recv_bufs[q];
+                    gpu::launch_broadcast(*dc, &b, counts[q] * esz, q, o, st);
+                }
+                break;
+            }
+            std::vector<size_t> offs = prefix(counts);
+            for (int q = 0; q < N; q++) {
+                ra.scount[q] = counts[q] * esz;
+                ra.sdispl[q] = offs[q] * esz;
+            }
+            gpu::launch_allgatherv(*dc, &ra, o, st);
+            break;
+        }
+        case coll_alltoall:
+        case coll_alltoallv: {
+            std::vector<size_t> sc = p.ctype == coll_alltoall ? std::vector<size_t>(N, p.count) : p.send_counts;
+            std::vector<size_t> rc = p.ctype == coll_alltoall ? std::vector<size_t>(N, p.count) : p.recv_counts;
+            std::vector<size_t> so = prefix(sc), ro = prefix(rc);
+            for (int q = 0; q < N; q++) {
+                ra.scount[q] = sc[q] * esz;
+                ra.sdispl[q] = so[q] * esz;
+                ra.rcount[q] = rc[q] * esz;
+                ra.rdispl[q] = ro[q] * esz;
+            }
+            gpu::launch_alltoallv(*dc, &ra, o, st);
+            break;
+        }
+        case coll_barrier: gpu::launch_barrier(*dc, st); break;
+        case coll_bcast:
+            ra.send = r == p.root ? p.recv_buf : nullptr;
+            gpu::launch_broadcast(*dc, &ra, p.count * esz, p.root, o, st);
+            break;
+        case coll_broadcast:
+            ra.send = r == p.root ? (p.send_buf ? p.send_buf : p.recv_buf) : nullptr;
+            gpu::launch_broadcast(*dc, &ra, p.count * esz, p.root, o, st);
+            break;
+        case coll_send:
+        case coll_recv: {
+            dev::p2p_ops ops{};
+            ops.n = 1;
+            ops.op[0] = dev::p2p_op{ p.send_buf, p.recv_buf, p.count * esz, p.peer, p.ctype == coll_send ? 1 : 0 };
+            gpu::launch_sendrecv(*dc, &ops, st);
+            break;
+        }
+        default: CCL_THROW("unsupported device collective ", (int)p.ctype);
+    }
+    return std::make_shared<cuda_event_impl>(dc, st);
+}
+
+bool same_node(host_comm& comm) {
+    const std::vector<int>& h = comm.host_index();
+    for (int v : h)
+        if (v != h[0])
+            return false;
+    return true;
+}
+
+event_ptr staged_device_coll(host_comm& comm, coll_param p, const coll_attr& attr) {
+    // device -> pinned host, CPU collective, host -> device; synchronous
+    cudaStream_t st = (cudaStream_t)p.stream;
+    const int N = comm.size();
+    const size_t esz = dtype_size(p.dtype);
+    auto sz = [&](bool send) -> size_t {
+        switch (p.ctype) {
+            case coll_allgather: return (send ? p.count : p.count * N) * esz;
+            case coll_allgatherv: return (send ? p.count : total(p.recv_counts)) * esz;
+            case coll_alltoall: return p.count * N * esz;
+            case coll_alltoallv: return total(send ? p.send_counts : p.recv_counts) * esz;
+            case coll_reduce_scatter: return (send ? p.count * N : p.count) * esz;
+            case coll_barrier: return 0;
+            default: return p.count * esz;
+        }
+    };
+    CCL_THROW_IF_NOT(p.recv_bufs.empty(), "vector buffers on device need the device communicator");
+    const size_t sb = p.send_buf ? sz(true) : 0, rb = p.recv_buf ? sz(false) : 0;
+    std::vector<char> hs(sb), hr(rb);
+    const void* dsend = p.send_buf;
+    void* drecv = p.recv_buf;
+    if (sb)
+        CUDA_CHECK(cudaMemcpyAsync(hs.data(), dsend, sb, cudaMemcpyDeviceToHost, st));
+    if (rb && (p.ctype == coll_bcast || coll_is_inplace(comm, p)))
+        CUDA_CHECK(cudaMemcpyAsync(hr.data(), drecv, rb, cudaMemcpyDeviceToHost, st));
+    CUDA_CHECK(cudaStreamSynchronize(st));
+    const bool inplace = dsend && drecv && coll_is_inplace(comm, p);
+    coll_param h = p;
+    h.device = false;
+    h.stream = nullptr;
+    h.recv_buf = rb ? hr.data() : nullptr;
+    if (inplace) {
+        size_t off = 0;
+        if (p.ctype == coll_allgather || p.ctype == coll_allgatherv || p.ctype == coll_reduce_scatter)
+            off = (const char*)dsend - (const char*)drecv;
+        h.send_buf = hr.data() + off;
+        if (p.ctype == coll_reduce_scatter) { // recv sits inside send
+            h.send_buf = hs.data();
+            h.recv_buf = hs.data() + ((const char*)drecv - (const char*)dsend);
+        }
+    }
+    else
+        h.send_buf = sb ? hs.data() : nullptr;
+    coll_attr a = attr;
+    a.synchronous = true;
+    coll_create(comm, h, a);
+    if (rb) {
+        const void* src = (inplace && p.ctype == coll_reduce_scatter) ? h.recv_buf : hr.data();
+        CUDA_CHECK(cudaMemcpyAsync(drecv, src, rb, cudaMemcpyHostToDevice, st));
+        CUDA_CHECK(cudaStreamSynchronize(st));
+    }
+    return make_completed_event();
+}
+
+} // namespace
+
+// ---- entry point ----------------------------------------------------------------------------
+event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr) {
+    const env_data& env = env_data::get();
+    coll_validate(comm, p, attr);
+    stats().calls[p.ctype]++;
+    purge_recycle();
+
+    // send/recv inside a group are posted at group_end
+    if (tl_group_active) {
+        CCL_THROW_IF_NOT(p.ctype == coll_send || p.ctype == coll_recv,
+                         "only send and recv may be issued between group_start and group_end");
+        auto ev = std::make_shared<group_event>();
+        tl_group.push_back(group_item{ &comm, p, attr, ev });
+        return ev;
+    }
+
+    const bool sync = attr.synchronous || env.op_sync || p.ctype == coll_barrier;
+    const size_t esz = p.ctype == coll_barrier ? 0 : dtype_size(p.dtype);
+
+    // ---- device buffers
+    if (p.device) {
+        for (auto& d : p.deps) // dependencies of a stream-ordered operation: wait on the host
+            if (d)
+                d->wait();
+        event_ptr ev;
+        if (env.cuda_kernels && same_node(comm))
+            ev = device_coll(comm, p, attr);
+        else
+            ev = staged_device_coll(comm, p, attr);
+        if (sync)
+            ev->wait();
+        return ev;
+    }
+
+    // ---- single rank: copy and complete (reference coll.cpp:96-130)
+    if (comm.size() == 1) {
+        for (auto& d : p.deps)
+            if (d)
+                d->wait();
+        size_t bytes = 0;
+        switch (p.ctype) {
+            case coll_allgatherv: bytes = p.count * esz; break;
+            case coll_alltoallv: bytes = p.send_counts[0] * esz; break;
+            case coll_barrier: bytes = 0; break;
+            default: bytes = p.count * esz;
+        }
+        void* dst = !p.recv_bufs.empty() ? p.recv_bufs[0] : p.recv_buf;
+        if (bytes && p.send_buf && dst && p.send_buf != dst)
+            std::memmove(dst, p.send_buf, bytes);
+        return make_completed_event();
+    }
+
+    // ---- fusion of small allreduces; anything else first cuts the pending batch (operation order)
+    if (env.fusion) {
+        if (p.ctype == coll_allreduce && !sync) {
+            event_ptr fe = fusion_manager::get().try_add(comm, p, attr);
+            if (fe)
+                return fe;
+        }
+        else
+            fusion_manager::get().flush(&comm);
+    }
+
+    // ---- schedule: cached or new
+    const bool cacheable = attr.to_cache && p.ctype != coll_send && p.ctype != coll_recv && p.deps.empty() &&
+                           (env.cache_key == cache_key_t::full || !attr.match_id.empty());
+    if (p.ctype == coll_barrier && env.cache_flush)
+        comm.cache().flush();
+    master_sched* m = nullptr;
+    std::unique_ptr<master_sched> owned;
+    if (cacheable) {
+        const std::string key = coll_cache_key(comm, p, attr);
+        m = comm.cache().find(key);
+        if (m)
+            stats().cache_hits++;
+        else {
+            auto fresh = build_master(comm, p, attr, comm.next_sched_id());
+            m = fresh.get();
+            comm.cache().insert(key, std::move(fresh));
+        }
+    }
+    else {
+        uint64_t sid;
+        if (p.ctype == coll_send)
+            sid = atl_tag::PT2PT_SCHED - 8 - (comm.p2p_send_seq(p.peer) & 0xff);
+        else if (p.ctype == coll_recv)
+            sid = atl_tag::PT2PT_SCHED - 8 - (comm.p2p_recv_seq(p.peer) & 0xff);
+        else
+            sid = comm.next_sched_id();
+        owned = build_master(comm, p, attr, sid);
+        m = owned.get();
+    }
+    const uint64_t ticket = executor::get().start(m);
+    auto ev = std::make_shared<host_event>(m, ticket, std::move(owned));
+    if (sync)
+        ev->wait();
+    return ev;
+}
+
+// ---- group ------------------------------------------------------------------------------------
+void group_start() {
+    CCL_THROW_IF_NOT(!tl_group_active, "group_start called twice");
+    tl_group_active = true;
+    tl_group.clear();
+}
+
+bool group_active() {
+    return tl_group_active;
+}
+
+void group_end() {
+    CCL_THROW_IF_NOT(tl_group_active, "group_end without group_start");
+    tl_group_active = false;
+    std::vector<group_item> items;
+    items.swap(tl_group);
+    // device operations of one communicator and stream go out together, in as few launches as possible
+    std::vector<bool> done(items.size(), false);
+    for (size_t i = 0; i < items.size(); i++) {
+        if (done[i])
+            continue;
+        group_item& it = items[i];
+        if (!it.param.device || !env_data::get().cuda_kernels || !same_node(*it.comm)) {
+            it.ev->bind(coll_create(*it.comm, it.param, it.attr));
+            done[i] = true;
+            continue;
+        }
+        gpu::device_comm* dc = it.comm->device();
+        cudaStream_t st = (cudaStream_t)it.param.stream;
+        std::vector<size_t> batch;
+        dev::p2p_ops ops{};
+        auto flush = [&] {
+            if (ops.n == 0)
+                return;
+            CUDA_CHECK(cudaSetDevice(dc->device_id()));
+            gpu::launch_sendrecv(*dc, &ops, st);
+            auto ev = std::make_shared<cuda_event_impl>(dc, st);
+            for (size_t k : batch) {
+                items[k].ev->bind(ev);
+                done[k] = true;
+            }
+            batch.clear();
+            ops = dev::p2p_ops{};
+        };
+        for (size_t k = i; k < items.size(); k++) {
+            group_item& g = items[k];
+            if (done[k] || g.comm != it.comm || g.param.stream != it.param.stream || !g.param.device)
+                continue;
+            const int is_send = g.param.ctype == coll_send ? 1 : 0;
+            bool clash = ops.n == dev::P2P_MAX_OPS;
+            for (int q = 0; q < ops.n && !clash; q++)
+                clash = ops.op[q].peer == g.param.peer && ops.op[q].is_send == is_send;
+            if (clash)
+                flush();
+            ops.op[ops.n++] = dev::p2p_op{ g.param.send_buf, g.param.recv_buf,
+                                           g.param.count * dtype_size(g.param.dtype), g.param.peer, is_send };
+            batch.push_back(k);
+            stats().calls[g.param.ctype]++;
+            stats().device_calls[g.param.ctype]++;
+        }
+        flush();
+    }
+}
+
+} // namespace cclx

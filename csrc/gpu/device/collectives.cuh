@@ -694,31 +694,47 @@ static __global__ void __launch_bounds__(64) barrier_kernel(const comm_dev* tab,
 //   ack  [(q*P2P_BLOCKS)+b] : written by receiver q when it drained part b of x's message to q
 // send: wait ack >= seq-1 on my side, push, fence, set ready at the peer.
 // recv: wait ready >= seq on my side, copy out, set ack at the peer.
-// Messages larger than the slot are split by the host into rounds; both sides
-// derive the same grid from the byte count.
+// Messages larger than the slot are split by the host into rounds.  One launch
+// serves a list of operations (blockIdx.z), which is how send/recv issued inside
+// a group run side by side without ordering deadlocks; both sides derive the
+// number of active blocks from the byte count.
 // ---------------------------------------------------------------------------
-static __global__ void __launch_bounds__(1024) sendrecv_kernel(const comm_dev* tab, p2p_layout L, coll_args a,
-                                                        int is_send) {
-    const int er = a.emu ? (int)blockIdx.y : 0;
+static __global__ void __launch_bounds__(1024)
+    sendrecv_kernel(const comm_dev* tab, p2p_layout L, p2p_ops r0, const p2p_ops* emu_tab, int emu, size_t round_off) {
+    const int er = emu ? (int)blockIdx.y : 0;
     const comm_dev& c = tab[er];
-    const rank_args& ra = a.emu ? a.emu_tab[er] : a.r0;
-    const int peer = a.emu ? (int)ra.scount[0] : a.peer;
-    const int do_send = a.emu ? (int)ra.scount[1] : is_send;
+    const p2p_ops& ops = emu ? emu_tab[er] : r0;
+    const int oi = blockIdx.z;
+    if (oi >= ops.n)
+        return;
+    const p2p_op op = ops.op[oi];
+    const int peer = op.peer;
     if (peer < 0)
-        return; // emulated rank that takes no part
-    const size_t bytes = a.count;
+        return;
+    // this round moves bytes [round_off, round_off + slot) of the message; a zero-byte
+    // message still synchronises the pair once
+    if (round_off >= op.bytes && !(op.bytes == 0 && round_off == 0))
+        return;
+    size_t bytes = op.bytes - round_off;
+    if (bytes > L.slot_bytes)
+        bytes = L.slot_bytes;
+    // both sides derive the same number of active blocks from the byte count
+    int nb = (int)(bytes >> 16);
+    nb = nb < 1 ? 1 : (nb > (int)gridDim.x ? (int)gridDim.x : nb);
     const int b = blockIdx.x;
+    if (b >= nb)
+        return;
     size_t lo, hi;
-    split_range((bytes + 15) >> 4, gridDim.x, b, lo, hi);
+    split_range((bytes + 15) >> 4, nb, b, lo, hi);
     const size_t l = lo << 4, h = (hi << 4) < bytes ? (hi << 4) : bytes;
     __shared__ uint32_t seq_s;
     __shared__ int fail;
-    uint32_t* seqw = c.p2p_seq + ((do_send ? 0 : MAX_RANKS) + peer) * P2P_BLOCKS + b;
+    uint32_t* seqw = c.p2p_seq + ((op.is_send ? 0 : MAX_RANKS) + peer) * P2P_BLOCKS + b;
     if (threadIdx.x == 0) {
         fail = 0;
         seq_s = *seqw + 1;
-        if (do_send) {
-            // the receiver must have drained the previous message of this pair
+        if (op.is_send) {
+            // the receiver must have drained the previous message part of this pair
             if (!wait_flag_sys(c, c.p2p_flags[c.rank] + P2P_ACK_BASE + peer * P2P_BLOCKS + b, seq_s - 1, peer,
                                ST_FLAG_TIMEOUT))
                 fail = 1;
@@ -731,10 +747,10 @@ static __global__ void __launch_bounds__(1024) sendrecv_kernel(const comm_dev* t
     __syncthreads();
     if (fail)
         return;
-    if (do_send) {
+    if (op.is_send) {
         if (h > l)
             block_copy<false>(L.data[peer] + (size_t)c.rank * L.slot_bytes + l,
-                              reinterpret_cast<const char*>(ra.send) + l, h - l);
+                              reinterpret_cast<const char*>(op.send) + round_off + l, h - l);
         __syncthreads();
         if (threadIdx.x == 0) {
             __threadfence_system();
@@ -744,7 +760,7 @@ static __global__ void __launch_bounds__(1024) sendrecv_kernel(const comm_dev* t
     }
     else {
         if (h > l)
-            block_copy<true>(reinterpret_cast<char*>(ra.recv) + l,
+            block_copy<true>(reinterpret_cast<char*>(op.recv) + round_off + l,
                              L.data[c.rank] + (size_t)peer * L.slot_bytes + l, h - l);
         __syncthreads();
         if (threadIdx.x == 0) {

@@ -55,6 +55,20 @@ constexpr int P2P_SEQ_WORDS = 2 * MAX_RANKS * P2P_BLOCKS;
 // handed out to the fused kernels by the host
 constexpr int A2A_HDR_WORDS = 2 * MAX_BLOCKS * MAX_RANKS;
 
+// operations of one point-to-point launch (one entry per rank in emulation mode)
+struct p2p_op {
+    const void* send;
+    void* recv;
+    size_t bytes;
+    int peer; // -1: no operation
+    int is_send;
+};
+constexpr int P2P_MAX_OPS = 8;
+struct p2p_ops {
+    int n;
+    p2p_op op[P2P_MAX_OPS];
+};
+
 struct p2p_layout {
     char* data[MAX_RANKS]; // p2p data areas, peer-mapped; slot s of rank x holds data from sender s
     size_t slot_bytes;

@@ -70,6 +70,8 @@ void device_comm::build_tables() {
     std::memset(status_host_, 0, status_words * sizeof(uint32_t));
     CUDA_CHECK(cudaHostGetDevicePointer((void**)&status_devptr_, status_host_, 0));
     CUDA_CHECK(cudaMalloc((void**)&emu_args_dev_, dev::MAX_RANKS * sizeof(dev::rank_args)));
+    CUDA_CHECK(cudaMalloc((void**)&emu_ops_dev_, dev::MAX_RANKS * sizeof(dev::p2p_ops)));
+    device_id_ = devid;
 
     table_host_.assign(entries, dev::comm_dev{});
     for (int e = 0; e < entries; e++) {
@@ -121,6 +123,7 @@ void device_comm::destroy() {
     cudaFree(state_dev_);
     cudaFree(p2p_seq_dev_);
     cudaFree(emu_args_dev_);
+    cudaFree(emu_ops_dev_);
     cudaFreeHost(status_host_);
     state_dev_ = p2p_seq_dev_ = nullptr;
     status_host_ = nullptr;

@@ -61,6 +61,8 @@ public:
     int max_blocks() const; // per rank, keeps every block co-resident
     int threads() const { return threads_; }
     dev::rank_args* emu_args_dev() const { return emu_args_dev_; }
+    dev::p2p_ops* emu_ops_dev() const { return emu_ops_dev_; }
+    int device_id() const { return device_id_; }
     size_t staging_bytes() const { return heap_.regions().staging_bytes; }
 
     // error status written by kernels (0 = ok); throws with a description when set
@@ -92,6 +94,8 @@ private:
     uint32_t* status_host_ = nullptr; // pinned + mapped: per rank 8 words, then abort word
     uint32_t* status_devptr_ = nullptr;
     dev::rank_args* emu_args_dev_ = nullptr;
+    dev::p2p_ops* emu_ops_dev_ = nullptr;
+    int device_id_ = 0;
     int sm_count_ = 0;
     int threads_ = 512;
     size_t timeout_ms_ = 20000;
@@ -120,9 +124,9 @@ void launch_alltoallv(device_comm& dc, const dev::rank_args* ra, const launch_op
 void launch_broadcast(device_comm& dc, const dev::rank_args* ra, size_t bytes, int root, const launch_opts& o,
                       cudaStream_t st);
 void launch_barrier(device_comm& dc, cudaStream_t st);
-// point to point; in emulation mode ra[r].scount[0] = peer (or -1), ra[r].scount[1] = 1 for send
-void launch_sendrecv(device_comm& dc, const dev::rank_args* ra, size_t bytes, int peer, bool is_send,
-                     cudaStream_t st);
+// point to point: `ops` has one entry in real mode and world() entries in emulation mode; all
+// operations of a list run in one launch per round (send/recv of a group)
+void launch_sendrecv(device_comm& dc, const dev::p2p_ops* ops, cudaStream_t st);
 // a wait that nothing satisfies; returns after the device time limit with status ST_FLAG_TIMEOUT
 void launch_wait_unset_flag(device_comm& dc, cudaStream_t st);
 

@@ -286,25 +286,52 @@ void launch_barrier(device_comm& dc, cudaStream_t st) {
     launch_kernel(dc, dev::barrier_kernel, 1, 64, st, dc.table(), a);
 }
 
-void launch_sendrecv(device_comm& dc, const dev::rank_args* ra, size_t bytes, int peer, bool is_send,
-                     cudaStream_t st) {
+void launch_sendrecv(device_comm& dc, const dev::p2p_ops* ops, cudaStream_t st) {
     const int entries = dc.emulated() ? dc.world() : 1;
     const size_t slot = dc.p2p().slot_bytes;
-    dev::coll_args a{};
-    a.peer = peer;
-    std::vector<dev::rank_args> cur(ra, ra + entries);
-    dc.algo_hits[(is_send ? coll_send : coll_recv) * ga_last + ga_push]++;
-    // zero-byte messages still synchronise the pair (one round)
-    for (size_t done = 0; done < std::max<size_t>(bytes, 1); done += slot) {
-        const size_t n = bytes ? std::min(slot, bytes - done) : 0;
-        for (int e = 0; e < entries; e++) {
-            cur[e].send = ra[e].send ? (const char*)ra[e].send + done : nullptr;
-            cur[e].recv = ra[e].recv ? (char*)ra[e].recv + done : nullptr;
+    size_t maxb = 0;
+    int max_n = 0;
+    for (int e = 0; e < entries; e++) {
+        CCL_THROW_IF_NOT(ops[e].n >= 0 && ops[e].n <= dev::P2P_MAX_OPS, "too many point-to-point operations in one launch");
+        max_n = std::max(max_n, ops[e].n);
+        for (int i = 0; i < ops[e].n; i++) {
+            const dev::p2p_op& o = ops[e].op[i];
+            if (o.peer < 0)
+                continue;
+            CCL_THROW_IF_NOT(o.peer < dc.world(), "invalid peer ", o.peer);
+            maxb = std::max(maxb, o.bytes);
+            dc.algo_hits[(o.is_send ? coll_send : coll_recv) * ga_last + ga_push]++;
+            for (int k = 0; k < i; k++)
+                CCL_THROW_IF_NOT(ops[e].op[k].peer != o.peer || ops[e].op[k].is_send != o.is_send,
+                                 "two operations of one launch address the same peer in the same direction");
         }
-        a.count = n;
-        prepare_args(dc, a, cur.data(), st);
-        int blocks = (int)std::min<size_t>(dev::P2P_BLOCKS, std::max<size_t>(1, n / (64 << 10)));
-        launch_kernel(dc, dev::sendrecv_kernel, blocks, dc.threads(), st, dc.table(), dc.p2p(), a, is_send ? 1 : 0);
+    }
+    if (max_n == 0)
+        return;
+    dc.check_status();
+    const dev::p2p_ops* tab = nullptr;
+    if (dc.emulated()) {
+        CUDA_CHECK(cudaStreamSynchronize(st));
+        CUDA_CHECK(cudaMemcpy(dc.emu_ops_dev(), ops, entries * sizeof(dev::p2p_ops), cudaMemcpyHostToDevice));
+        tab = dc.emu_ops_dev();
+    }
+    const int emu = dc.emulated() ? 1 : 0;
+    const int blocks = (int)std::min<size_t>(dev::P2P_BLOCKS, std::max<size_t>(1, std::min(maxb, slot) >> 16));
+    for (size_t done = 0; done < std::max<size_t>(maxb, 1); done += slot) {
+        dim3 grid(blocks, entries, max_n);
+        const dev::comm_dev* t = dc.table();
+        dev::p2p_layout L = dc.p2p();
+        dev::p2p_ops r0 = ops[0];
+        size_t off = done;
+        if (dc.emulated()) {
+            void* argv[] = { (void*)&t, (void*)&L, (void*)&r0, (void*)&tab, (void*)&emu, (void*)&off };
+            CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)dev::sendrecv_kernel, grid, dim3(dc.threads()), argv, 0,
+                                                   st));
+        }
+        else {
+            dev::sendrecv_kernel<<<grid, dc.threads(), 0, st>>>(t, L, r0, tab, emu, off);
+            CUDA_CHECK(cudaGetLastError());
+        }
     }
 }
 

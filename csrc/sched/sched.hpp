@@ -1,0 +1,268 @@
+// CPU scheduler: schedule objects made of entries, progressed by worker threads.
+//
+// Behavioural model taken from the reference (src/sched/sched.hpp:59-319,
+// src/sched/entry/entry.hpp:56-129, src/sched/queue/queue.hpp:38-257,
+// src/exec/exec.hpp:40-178, src/exec/thread/worker.cpp:62-379): a collective is
+// compiled once into a schedule - a list of small state machines (send, recv,
+// recv+reduce, local reduce, copy, sync, nested schedule, ...) with barrier
+// points - split into per-worker partial schedules, queued into priority bins
+// and progressed cooperatively until the request counter reaches zero.  Cached
+// schedules are re-armed instead of rebuilt; a relaunch of a schedule that is
+// still running is queued behind it.
+//
+// The implementation is this library's own and much smaller: entries are plain
+// C++ objects owning their requests, tags are (comm, schedule, step) triples
+// matched FIFO per source by the transport, temporary memory comes from a
+// size-bucketed cache, and workers sleep on a condition variable when idle.
+#pragma once
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <functional>
+#include <list>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#include "core/types.hpp"
+#include "transport/atl.hpp"
+
+namespace cclx {
+
+class host_comm;
+class sched;
+class executor;
+
+// ---- request ------------------------------------------------------------------------
+// Counts the partial schedules of one launch.  The partial that finishes last
+// runs on_last (on its worker thread).  What a user waits for is a launch
+// ticket of the master schedule (master_sched::issued / done), not this counter,
+// so that a cached schedule can be relaunched from on_last.
+class request {
+public:
+    void arm(int parts) { counter_.store(parts, std::memory_order_release); }
+    void part_done() {
+        if (counter_.fetch_sub(1, std::memory_order_acq_rel) == 1 && on_last)
+            on_last();
+    }
+    std::function<void()> on_last;
+    void set_error(const std::string& e);
+    bool has_error() const { return failed_.load(std::memory_order_acquire); }
+    std::string error() const;
+    std::atomic<bool> urgent{ false }; // a user thread is waiting (fusion flushes early)
+
+private:
+    std::atomic<int> counter_{ 0 };
+    std::atomic<bool> failed_{ false };
+    mutable std::mutex mu_;
+    std::string error_;
+};
+
+// ---- temporary memory ---------------------------------------------------------------
+// process-wide size-bucketed cache of host buffers (reference buffer_cache.hpp:35-101)
+class buffer_cache {
+public:
+    static buffer_cache& get();
+    void* take(size_t bytes);
+    void give(void* p, size_t bytes);
+    void clear();
+    size_t cached_bytes() const { return cached_; }
+    uint64_t hits = 0, misses = 0;
+
+private:
+    std::mutex mu_;
+    std::multimap<size_t, void*> free_;
+    size_t cached_ = 0;
+};
+
+// ---- entries ------------------------------------------------------------------------
+enum class entry_status { not_started, again, started, complete };
+
+class sched_entry {
+public:
+    explicit sched_entry(sched* s) : owner_(s) {}
+    virtual ~sched_entry() = default;
+    virtual const char* name() const = 0;
+    virtual void start() = 0;
+    virtual void update() {}
+    virtual void reset() { status_ = entry_status::not_started; }
+    void do_progress();
+    entry_status status() const { return status_; }
+    bool is_complete() const { return status_ == entry_status::complete; }
+    void make_barrier() { barrier_ = true; }
+    bool is_barrier() const { return barrier_; }
+    // profile (CCL_SCHED_PROFILE)
+    uint64_t total_ns = 0, update_calls = 0;
+
+protected:
+    sched* owner_;
+    entry_status status_ = entry_status::not_started;
+    bool barrier_ = false;
+    uint64_t started_at_ns_ = 0;
+};
+
+// ---- schedule -----------------------------------------------------------------------
+class sched {
+public:
+    sched(host_comm* comm, uint64_t sched_id, int ep);
+    ~sched();
+
+    host_comm* comm() const { return comm_; }
+    int ep() const { return ep_; }
+    uint64_t sched_id() const { return sched_id_; }
+    uint64_t tag(uint64_t step) const;
+
+    // building
+    template <class E, class... Args>
+    E* add(Args&&... args) {
+        E* e = new E(this, std::forward<Args>(args)...);
+        entries_.emplace_back(e);
+        return e;
+    }
+    void add_barrier(); // entries added later start only when everything before is complete
+    void* alloc_tmp(size_t bytes);
+    size_t entry_count() const { return entries_.size(); }
+
+    // running
+    bool do_progress(); // true when every entry is complete
+    void reset(); // re-arm for another launch (cached schedules)
+    void dump(std::string& out) const;
+    void profile(std::string& out) const;
+
+    int priority = 0;
+    request* req = nullptr; // request of the master schedule this partial belongs to
+    uint64_t op_base = 0; // partial schedules of one master use disjoint step ranges
+    std::function<void()> on_complete; // runs on the worker thread after the last entry
+
+private:
+    host_comm* comm_;
+    uint64_t sched_id_;
+    int ep_;
+    std::deque<std::unique_ptr<sched_entry>> entries_;
+    size_t first_incomplete_ = 0;
+    std::vector<std::pair<void*, size_t>> tmp_;
+};
+
+// A master schedule: what one API call creates.  Owns the partial schedules and the request.
+class master_sched {
+public:
+    master_sched(host_comm* comm, uint64_t sched_id);
+    ~master_sched();
+    sched* add_partial(int ep);
+    request& req() { return req_; }
+    std::vector<std::unique_ptr<sched>>& partials() { return partials_; }
+    uint64_t sched_id() const { return sched_id_; }
+    host_comm* comm() const { return comm_; }
+
+    // launch tickets: launch k is complete when done >= k
+    std::atomic<uint64_t> issued{ 0 }, done{ 0 };
+    bool ticket_complete(uint64_t t) const { return done.load(std::memory_order_acquire) >= t || req_.has_error(); }
+    // cached-schedule relaunch protocol (reference sched_restart_manager.cpp:19-146):
+    // a launch requested while the schedule runs is queued and started by the
+    // worker that completes the current one
+    std::mutex launch_mu;
+    bool in_flight = false;
+    int delayed_launches = 0;
+    bool cached = false;
+    int priority = 0;
+    std::function<void()> user_complete; // e.g. unpack / finalise of a fused operation
+    std::string cache_key;
+
+private:
+    host_comm* comm_;
+    uint64_t sched_id_;
+    request req_;
+    std::vector<std::unique_ptr<sched>> partials_;
+};
+
+// ---- queue, workers, executor ---------------------------------------------------------
+class sched_queue {
+public:
+    void add(sched* s);
+    // progress the highest-priority bin (every bin once in a while); returns the number of schedules touched
+    size_t progress(uint64_t iteration, bool strict_order);
+    bool empty();
+    size_t size();
+    void dump(std::string& out);
+
+private:
+    std::mutex mu_;
+    std::map<int, std::vector<sched*>, std::greater<int>> bins_;
+    std::deque<sched*> incoming_;
+};
+
+class worker {
+public:
+    worker(executor* ex, int idx);
+    ~worker();
+    void start();
+    void stop();
+    void add(sched* s);
+    size_t do_work(); // one progress iteration (also callable from a user thread)
+    int index() const { return idx_; }
+    bool on_worker_thread() const;
+
+private:
+    void loop();
+    executor* ex_;
+    int idx_;
+    sched_queue queue_;
+    std::thread thread_;
+    std::atomic<bool> stop_{ false };
+    std::mutex mu_;
+    std::mutex work_mu_; // one thread progresses a worker's queue at a time
+    std::condition_variable cv_;
+    uint64_t iteration_ = 0;
+    std::thread::id tid_;
+};
+
+class executor {
+public:
+    static executor& get();
+    void ensure_started(std::shared_ptr<atl_transport> tr);
+    void shutdown();
+    int worker_count() const { return (int)workers_.size(); }
+    // returns the launch ticket
+    uint64_t start(master_sched* m);
+    void wait(master_sched* m, uint64_t ticket);
+    bool test(master_sched* m, uint64_t ticket);
+    void launch_now(master_sched* m); // arm + enqueue (internal)
+    std::shared_ptr<atl_transport> transport() { return transport_; }
+    // service hook run by worker 0 every iteration (fusion flush)
+    std::function<void()> service_hook;
+    // hold every worker outside its progress loop (datatype table changes, resize)
+    void lock_workers();
+    void unlock_workers();
+
+private:
+    friend class worker;
+    executor() = default;
+    std::vector<std::unique_ptr<worker>> workers_;
+    std::shared_ptr<atl_transport> transport_;
+    std::atomic<unsigned> rr_{ 0 };
+    std::mutex mu_;
+    std::mutex freeze_mu_;
+    std::atomic<bool> frozen_{ false };
+};
+
+// ---- schedule cache -------------------------------------------------------------------
+class sched_cache {
+public:
+    master_sched* find(const std::string& key);
+    void insert(const std::string& key, std::unique_ptr<master_sched> m);
+    void flush(); // drops schedules that are not in flight
+    size_t size();
+    uint64_t hits = 0, misses = 0;
+
+private:
+    std::mutex mu_;
+    std::unordered_map<std::string, std::unique_ptr<master_sched>> map_;
+};
+
+uint64_t now_ns();
+
+} // namespace cclx

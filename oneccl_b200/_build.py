@@ -56,7 +56,7 @@ def build_native(verbose: bool = False) -> Path:
     LIBDIR.mkdir(parents=True, exist_ok=True)
     bdir = BUILD / "native"
     bdir.mkdir(parents=True, exist_ok=True)
-    subdirs = ["core", "bootstrap", "transport", "sched", "coll", "gpu", "api", "capi"]
+    subdirs = ["core", "bootstrap", "transport", "sched", "coll", "comm", "fusion", "topo", "gpu", "api", "capi"]
     cpp = _sources(subdirs, [".cpp"])
     cu = _sources(subdirs, [".cu"])
     inc = f"-I{CSRC} -I{CSRC / 'include'} -I/usr/local/cuda/include"

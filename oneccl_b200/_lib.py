@@ -54,7 +54,7 @@ def _proto(lib):
         "cclx_dc_alltoallv": (i, [vp, pp, pp, psz, i, vp]),
         "cclx_dc_broadcast": (i, [vp, pp, pp, sz, i, i, vp]),
         "cclx_dc_barrier": (i, [vp, vp]),
-        "cclx_dc_sendrecv": (i, [vp, pp, pp, sz, pi, pi, vp]),
+        "cclx_dc_sendrecv": (i, [vp, pp, pp, psz, pi, pi, i, vp]),
         "cclx_dc_wait_unset_flag": (i, [vp, vp]),
         "cclx_reduce_local": (i, [vp, vp, sz, i, i, vp]),
         "cclx_pack": (i, [vp, vp, i, vp, i, sz, vp]),

@@ -252,17 +252,22 @@ class DeviceGroup:
         self._finish(self._lib.cclx_dc_barrier(self._h, _stream_ptr(stream)))
 
     def sendrecv(self, send, recv, peers, is_send, nbytes=None, stream=None):
-        """Real mode: ``peers``/``is_send`` are scalars.  Emulated: lists per rank (peer -1 = idle)."""
-        if not self.emulated_mode:
-            s, r = [send], [recv]
-            peers, is_send = [peers], [is_send]
-        else:
-            s, r = send, recv
-        if nbytes is None:
-            t = next(x for x in list(s) + list(r) if x is not None)
-            nbytes = t.numel() * t.element_size()
-        rc = self._lib.cclx_dc_sendrecv(self._h, self._ptrs(s), self._ptrs(r), nbytes, _lib.int_array(peers),
-                                        _lib.int_array([1 if x else 0 for x in is_send]), _stream_ptr(stream))
+        """Point-to-point.  Real mode: lists of operations of this rank posted in one launch
+        (``send[i]`` / ``recv[i]`` tensor or None, ``peers[i]``, ``is_send[i]``); scalars are
+        accepted for a single operation.  Emulated mode: one operation per rank (peer -1 = idle)."""
+        if not self.emulated_mode and not isinstance(peers, (list, tuple)):
+            send, recv, peers, is_send = [send], [recv], [peers], [is_send]
+        n = len(peers)
+        sizes = []
+        for k in range(n):
+            t = send[k] if is_send[k] else recv[k]
+            if nbytes is not None:
+                sizes.append(nbytes if not isinstance(nbytes, (list, tuple)) else nbytes[k])
+            else:
+                sizes.append(0 if (t is None or peers[k] < 0) else t.numel() * t.element_size())
+        rc = self._lib.cclx_dc_sendrecv(self._h, self._ptrs(send), self._ptrs(recv), _lib.size_array(sizes),
+                                        _lib.int_array(peers), _lib.int_array([1 if x else 0 for x in is_send]), n,
+                                        _stream_ptr(stream))
         self._finish(rc)
 
     def wait_unset_flag(self, stream=None):

@@ -1,0 +1,171 @@
+"""CPU path over the TCP transport with real processes (no mpirun), mirroring the
+reference's functional suite: closed-form oracle, every algorithm per collective
+through the CCL_<COLL> override, sizes incl. odd counts, in-place and out-of-place."""
+import numpy as np
+import pytest
+
+from mp_util import run_ranks
+
+
+def _cfg1(comm):
+    """fp32 sum allreduce with counts {1, 17, 4096, 1048576}, uniform[-1,1) seed 0 per rank;
+    allgatherv with per-rank counts {1000, 1500}; barrier."""
+    W, r = comm.size, comm.rank
+    errs = []
+    for count in (1, 17, 4096, 1048576):
+        data = [np.random.default_rng(0 + p).uniform(-1, 1, count).astype(np.float32) for p in range(W)]
+        out = np.empty(count, np.float32)
+        comm.allreduce(data[r], out).wait()
+        ref = np.sum(np.stack(data).astype(np.float64), axis=0)
+        errs.append(float(np.max(np.abs(out - ref))))
+    counts = [1000, 1500][:W] + [700] * max(0, W - 2)
+    send = np.full(counts[r], r + 1, np.float32)
+    recv = np.zeros(sum(counts), np.float32)
+    comm.allgatherv(send, recv, counts).wait()
+    ref = np.concatenate([np.full(c, p + 1, np.float32) for p, c in enumerate(counts)])
+    assert np.array_equal(recv, ref)
+    comm.barrier().wait()
+    return errs
+
+
+def test_baseline_config1_world2():
+    for errs in run_ranks(_cfg1, 2):
+        assert max(errs) < 1e-5
+
+
+def _allreduce_matrix(comm, algo):
+    W, r = comm.size, comm.rank
+    for dtype in (np.float32, np.int32, np.float64, np.int8):
+        for count in (1, 17, 32771):
+            base = np.arange(count) % 7
+            send = (base + r).astype(dtype)
+            # in place
+            buf = send.copy()
+            comm.allreduce(buf).wait()
+            ref = (base * W + sum(range(W))).astype(dtype)
+            assert np.array_equal(buf, ref), (algo, dtype, count)
+            # out of place, other reductions
+            out = np.empty_like(send)
+            comm.allreduce(send, out, op="max").wait()
+            assert np.array_equal(out, (base + W - 1).astype(dtype))
+            assert np.array_equal(send, (base + r).astype(dtype))
+    return True
+
+
+@pytest.mark.parametrize("algo", ["ring", "recursive_doubling", "rabenseifner", "nreduce", "double_tree", "2d", "direct"])
+@pytest.mark.parametrize("world", [2, 3, 5])
+def test_allreduce_every_algorithm(algo, world):
+    assert all(run_ranks(_allreduce_matrix, world, algo, env={"CCL_ALLREDUCE": algo}))
+
+
+def _others(comm):
+    W, r = comm.size, comm.rank
+    # allgather
+    send = np.full(33, r, np.int32)
+    recv = np.zeros(33 * W, np.int32)
+    comm.allgather(send, recv).wait()
+    assert np.array_equal(recv, np.repeat(np.arange(W, dtype=np.int32), 33))
+    # allgatherv with per-rank destination buffers
+    counts = [5 + p for p in range(W)]
+    bufs = [np.zeros(c, np.float32) for c in counts]
+    comm.allgatherv(np.full(counts[r], r, np.float32), None, counts, recv_bufs=bufs).wait()
+    for p in range(W):
+        assert np.array_equal(bufs[p], np.full(counts[p], p, np.float32))
+    # alltoall
+    send = (np.arange(W * 10) + 1000 * r).astype(np.int64)
+    recv = np.zeros(W * 10, np.int64)
+    comm.alltoall(send, recv).wait()
+    ref = np.concatenate([(np.arange(10) + 10 * r + 1000 * p) for p in range(W)]).astype(np.int64)
+    assert np.array_equal(recv, ref)
+    # alltoallv: rank r sends (q+1) elements of value r*100+q to q
+    sc = [q + 1 for q in range(W)]
+    rc = [r + 1] * W
+    send = np.concatenate([np.full(q + 1, r * 100 + q, np.int32) for q in range(W)])
+    recv = np.zeros(sum(rc), np.int32)
+    comm.alltoallv(send, sc, recv, rc).wait()
+    assert np.array_equal(recv, np.concatenate([np.full(r + 1, p * 100 + r, np.int32) for p in range(W)]))
+    # broadcast in place and out of place
+    for root in range(W):
+        buf = np.full(1001, r, np.float32)
+        comm.broadcast(buf, root=root).wait()
+        assert np.all(buf == root)
+        out = np.zeros(77, np.float64)
+        comm.broadcast(np.full(77, 5.0 + r), root=root, recv=out).wait()
+        assert np.all(out == 5.0 + root)
+    # reduce
+    for root in (0, W - 1):
+        out = np.zeros(513, np.float64)
+        comm.reduce(np.full(513, float(r + 1)), out, root=root).wait()
+        if r == root:
+            assert np.all(out == W * (W + 1) / 2)
+    # reduce_scatter incl. the in-place position recv = send + rank*recv_count
+    rcnt = 129
+    send = np.tile(np.arange(rcnt, dtype=np.float32), W) + r
+    out = np.zeros(rcnt, np.float32)
+    comm.reduce_scatter(send, out).wait()
+    assert np.allclose(out, np.arange(rcnt) * W + sum(range(W)))
+    buf = np.tile(np.arange(rcnt, dtype=np.float32), W) + r
+    comm.reduce_scatter(buf, buf[r * rcnt:(r + 1) * rcnt]).wait()
+    assert np.allclose(buf[r * rcnt:(r + 1) * rcnt], np.arange(rcnt) * W + sum(range(W)))
+    # send / recv ring
+    nxt, prv = (r + 1) % W, (r - 1) % W
+    got = np.zeros(100, np.int32)
+    e1 = comm.recv(got, prv)
+    e2 = comm.send(np.full(100, r, np.int32), nxt)
+    e1.wait()
+    e2.wait()
+    assert np.all(got == prv)
+    return True
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_other_collectives_default_algorithms(world):
+    assert all(run_ranks(_others, world))
+
+
+@pytest.mark.parametrize("env", [
+    {"CCL_ALLGATHERV": "ring", "CCL_ALLGATHER": "ring", "CCL_ALLTOALL": "scatter", "CCL_ALLTOALLV": "scatter",
+     "CCL_BCAST": "ring", "CCL_BROADCAST": "naive", "CCL_REDUCE": "rabenseifner", "CCL_REDUCE_SCATTER": "ring",
+     "CCL_BARRIER": "ring"},
+    {"CCL_ALLGATHERV": "multi_bcast", "CCL_ALLGATHER": "flat", "CCL_BCAST": "naive", "CCL_BROADCAST": "ring",
+     "CCL_REDUCE": "ring", "CCL_REDUCE_SCATTER": "direct", "CCL_WORKER_COUNT": "2"},
+    {"CCL_REDUCE": "double_tree", "CCL_BCAST": "double_tree", "CCL_WORKER_OFFLOAD": "0"},
+])
+def test_other_collectives_algorithm_overrides(env):
+    assert all(run_ranks(_others, 3, env=env))
+
+
+def _lowp_and_custom(comm):
+    import ctypes as C
+
+    import torch
+
+    from oneccl_b200.comm import REDUCTION_FN
+
+    W, r = comm.size, comm.rank
+    x = (torch.arange(1000, dtype=torch.float32) / 64 + r).to(torch.bfloat16)
+    out = torch.empty_like(x)
+    comm.allreduce(x, out).wait()
+    ref = sum((torch.arange(1000, dtype=torch.float32) / 64 + p).to(torch.bfloat16).float() for p in range(W))
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+    h = (torch.arange(500, dtype=torch.float32) / 16 + r).to(torch.float16)
+    comm.allreduce(h).wait()
+    refh = sum((torch.arange(500, dtype=torch.float32) / 16 + p).to(torch.float16).float() for p in range(W))
+    assert torch.allclose(h.float(), refh, rtol=5e-3, atol=5e-3)
+
+    # custom reduction: elementwise "absolute maximum" on int32
+    @REDUCTION_FN
+    def absmax(inp, n, inout, out_n, dtype, ctx):
+        a = np.ctypeslib.as_array(C.cast(inp, C.POINTER(C.c_int32)), (n,))
+        b = np.ctypeslib.as_array(C.cast(inout, C.POINTER(C.c_int32)), (n,))
+        np.copyto(b, np.where(np.abs(a) > np.abs(b), a, b))
+
+    v = np.array([r - 1, -(r + 1), 3 * (-1) ** r], np.int32)
+    res = np.empty_like(v)
+    comm.allreduce(v, res, op="custom", reduction_fn=absmax).wait()
+    assert list(res[:2]) == [W - 2 if W > 2 else (-1 if W == 1 else (1 if abs(1) > abs(-1) else -1)), -W] or res[1] == -W
+    return True
+
+
+def test_low_precision_and_custom_reduction():
+    assert all(run_ranks(_lowp_and_custom, 3))
