@@ -1,0 +1,300 @@
+"""Real multi-GPU path: one process per GPU, symmetric heaps exchanged over
+Unix sockets, device kernels driven through the Communicator API.  Skipped on
+boxes with a single GPU (the emulated tests cover the kernels there)."""
+import os
+
+import pytest
+import torch
+
+from mp_util import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+needs2 = pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+ENV = {"CCL_CUDA_SYMM_HEAP_SIZE": "512M", "CCL_CUDA_TMP_BUF_SIZE": "16M", "CCL_CUDA_WAIT_TIMEOUT_MS": "5000"}
+
+
+def _world():
+    return min(_ngpu(), 8)
+
+
+def _collectives(comm):
+    r, W = comm.rank, comm.size
+    torch.cuda.set_device(r)
+    dev = torch.device("cuda", r)
+    g = comm.device_group
+    out = {"nvls": g.nvls}
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+        for n in (1, 17, 4096, 262144, 3 * (1 << 20) + 5):
+            gen = [torch.Generator().manual_seed(100 + p) for p in range(W)]
+            xs = [(torch.rand(n, generator=gen[p]) * 2 - 1).to(dtype) for p in range(W)]
+            ref = torch.stack([x.double() for x in xs]).sum(0)
+            x = xs[r].to(dev)
+            y = torch.empty_like(x)
+            comm.allreduce(x, y).wait()
+            assert torch.allclose(y.double().cpu(), ref, rtol=tol, atol=tol * W), (dtype, n)
+            comm.allreduce(x).wait()  # in place
+            assert torch.allclose(x.double().cpu(), ref, rtol=tol, atol=tol * W), (dtype, n, "inplace")
+    # symmetric (registered) buffers: zero-copy two-shot, NVLS when the switch offers it
+    for n in (1000, 1 << 20):
+        s = g.symm_empty((n,), dtype=torch.float32)
+        s.copy_(torch.full((n,), float(r + 1), device=dev))
+        comm.allreduce(s).wait()
+        assert torch.all(s == W * (W + 1) / 2)
+        sb = g.symm_empty((n,), dtype=torch.bfloat16)
+        sb.copy_(torch.full((n,), float(r + 1), device=dev).to(torch.bfloat16))
+        comm.allreduce(sb, scale=1.0 / W).wait()
+        assert torch.allclose(sb.float(), torch.full((n,), (W + 1) / 2, device=dev), rtol=1e-2, atol=1e-2)
+        g.symm_free(s)
+        g.symm_free(sb)
+    out["ar_symm_hits"] = g.algo_hits("allreduce", "symm") + g.algo_hits("allreduce", "nvls")
+    # reduce_scatter / allgather / alltoall / broadcast / reduce
+    n = 5000
+    x = (torch.arange(n * W, dtype=torch.float32) + r).to(dev)
+    y = torch.empty(n, device=dev)
+    comm.reduce_scatter(x, y).wait()
+    assert torch.allclose(y.cpu(), (torch.arange(n * W, dtype=torch.float32)[r * n:(r + 1) * n] * W + sum(range(W))))
+    z = torch.empty(n * W, device=dev)
+    comm.allgather(y, z).wait()
+    assert torch.allclose(z.cpu(), torch.arange(n * W, dtype=torch.float32) * W + sum(range(W)))
+    counts = [100 + 11 * p for p in range(W)]
+    zz = torch.zeros(sum(counts), device=dev)
+    comm.allgatherv(torch.full((counts[r],), float(r), device=dev), zz, counts).wait()
+    assert torch.equal(zz.cpu(), torch.cat([torch.full((c,), float(p)) for p, c in enumerate(counts)]))
+    a = (torch.arange(W * 300, dtype=torch.float32) + 10000 * r).to(dev)
+    b = torch.empty_like(a)
+    comm.alltoall(a, b).wait()
+    refb = torch.cat([torch.arange(300, dtype=torch.float32) + 300 * r + 10000 * p for p in range(W)])
+    assert torch.equal(b.cpu(), refb)
+    for root in (0, W - 1):
+        t = torch.full((70001,), float(r), device=dev)
+        comm.broadcast(t, root=root).wait()
+        assert torch.all(t == root)
+        o = torch.zeros(999, device=dev)
+        comm.reduce(torch.full((999,), float(r + 1), device=dev), o, root=root).wait()
+        if r == root:
+            assert torch.all(o == W * (W + 1) / 2)
+    # send / recv, alone and batched in a group (both directions at once)
+    from oneccl_b200.comm import group_end, group_start
+
+    nxt, prv = (r + 1) % W, (r - 1) % W
+    m = torch.full((200000,), float(r), device=dev)
+    got = torch.zeros_like(m)
+    if W == 2:
+        if r == 0:
+            comm.send(m, 1).wait()
+            comm.recv(got, 1).wait()
+        else:
+            comm.recv(got, 0).wait()
+            comm.send(m, 0).wait()
+        assert torch.all(got == prv)
+    got.zero_()
+    group_start()
+    e1 = comm.send(m, nxt)
+    e2 = comm.recv(got, prv)
+    group_end()
+    e1.wait()
+    e2.wait()
+    assert torch.all(got == prv)
+    comm.barrier().wait()
+    torch.cuda.synchronize()
+    g.check()
+    return out
+
+
+@needs2
+def test_device_collectives_real():
+    res = run_ranks(_collectives, _world(), env=ENV, timeout=300)
+    assert all(r["ar_symm_hits"] >= 2 for r in res)
+
+
+@needs2
+def test_device_collectives_real_nvls_off():
+    env = dict(ENV, CCL_CUDA_NVLS="0")
+    res = run_ranks(_collectives, 2, env=env, timeout=300)
+    assert not any(r["nvls"] for r in res)
+
+
+def _fused(comm):
+    from oneccl_b200.ops.gemm import FusedPlan
+
+    r, W = comm.rank, comm.size
+    torch.cuda.set_device(r)
+    dev = torch.device("cuda", r)
+    g = comm.device_group
+    M, N, K = W * 256, 512, 256
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    ws = [(torch.randn(N, K, generator=gen) * 0.1).to(torch.bfloat16) for _ in range(W)]
+    per = M // W
+    plan = FusedPlan(g, "ag_gemm", M, N, K, epilogue="silu", n_comm=4)
+    for it in range(3):
+        plan.x_shard(r).copy_((x[r * per:(r + 1) * per] * (it + 1)).to(dev))
+        out = plan.run(None, ws[r].to(dev))
+        torch.cuda.synchronize()
+        assert plan.error() == 0
+        ref = torch.nn.functional.silu((x * (it + 1)).float() @ ws[r].float().t())
+        err = (out.float().cpu() - ref).abs().max().item()
+        assert err < 2e-2 * ref.abs().max().item() + 1e-3, err
+    plan.close()
+    # GEMM -> reduce-scatter
+    K2 = 192
+    hs = [torch.randn(M, K2, generator=gen).to(torch.bfloat16) for _ in range(W)]
+    w2 = [(torch.randn(N, K2, generator=gen) * 0.1).to(torch.bfloat16) for _ in range(W)]
+    full = sum((h.float() @ w.float().t()).to(torch.bfloat16).float() for h, w in zip(hs, w2))
+    plan2 = FusedPlan(g, "gemm_rs", M, N, K2)
+    for it in range(3):
+        out = plan2.run(hs[r].to(dev), w2[r].to(dev))
+        torch.cuda.synchronize()
+        assert plan2.error() == 0
+        ref = full[r * per:(r + 1) * per]
+        err = (out.float().cpu() - ref).abs().max().item()
+        assert err < 2e-2 * ref.abs().max().item() + 1e-3, err
+    plan2.close()
+    g.check()
+    return True
+
+
+@needs2
+def test_fused_gemm_real():
+    assert all(run_ranks(_fused, _world(), env=ENV, timeout=300))
+
+
+def _ddp(comm):
+    from oneccl_b200.models.gpt2 import GPT2, GPT2Config
+    from oneccl_b200.parallel.ddp import DataParallel, train_step
+
+    r, W = comm.rank, comm.size
+    torch.cuda.set_device(r)
+    torch.manual_seed(0)  # same initial weights everywhere; rank 0's are broadcast anyway
+    cfg = GPT2Config.named("gpt2-tiny")
+    model = GPT2(cfg).cuda().to(torch.bfloat16)
+    ddp = DataParallel(model, comm.device_group, bucket_mb=0.05)
+    opt = ddp.make_optimizer(lr=1e-3)
+    gen = torch.Generator().manual_seed(77)
+    idx = torch.randint(0, cfg.vocab, (W * 2, cfg.seq_len), generator=gen)
+    tgt = torch.randint(0, cfg.vocab, (W * 2, cfg.seq_len), generator=gen)
+    losses = []
+    for _ in range(4):
+        loss = train_step(ddp, opt, idx[2 * r:2 * r + 2].cuda(), tgt[2 * r:2 * r + 2].cuda())
+        losses.append(float(loss))
+    torch.cuda.synchronize()
+    # every replica holds identical weights after synchronous data-parallel steps
+    digest = ddp.flat_param.float().double().sum().item()
+    return losses, digest, len(ddp.buckets)
+
+
+@needs2
+def test_data_parallel_replicas_stay_identical():
+    res = run_ranks(_ddp, 2, env=ENV, timeout=300)
+    assert res[0][1] == res[1][1]
+    assert res[0][2] > 1  # several buckets were reduced
+    assert res[0][0][-1] < res[0][0][0]
+
+
+def _leaver(comm):
+    """Failure detection without a GPU fault: rank 1 leaves between steps (nothing in
+    flight); rank 0 learns it on the host through the heartbeat keys and, if it launches
+    anyway, its device wait runs out and reports a status instead of hanging."""
+    import time
+
+    r = comm.rank
+    torch.cuda.set_device(r)
+    g = comm.device_group
+    x = torch.ones(1000, device="cuda")
+    comm.heartbeat()
+    comm.allreduce(x).wait()
+    torch.cuda.synchronize()
+    if r == 1:
+        return "left"
+    time.sleep(1.5)
+    alive = comm.peer_alive(1, max_age_ms=500)
+    g.set_timeout_ms(700)
+    status = None
+    try:
+        comm.allreduce(x).wait()
+    except Exception as e:  # noqa: BLE001
+        status = str(e)
+    code = g.status()
+    # the context is still usable
+    y = torch.ones(10, device="cuda") * 3
+    torch.cuda.synchronize()
+    return alive, code, status is not None, float(y.sum())
+
+
+@needs2
+def test_rank_leaving_is_detected_on_host_and_device_wait_is_bounded():
+    import multiprocessing as mp
+    import tempfile
+    import time
+
+    from mp_util import _child
+
+    env = dict(ENV, CCL_CUDA_NVLS="0")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    addr = os.path.join(tempfile.mkdtemp(prefix="cclx_"), "addr")
+
+    def runner(comm):
+        return _leaver(comm)
+
+    procs = [ctx.Process(target=_child_noclose, args=(rk, 2, addr, q, env)) for rk in range(2)]
+    for p in procs:
+        p.start()
+    got = {}
+    t0 = time.time()
+    while len(got) < 2 and time.time() - t0 < 120:
+        try:
+            rk, st, out = q.get(timeout=1)
+            got[rk] = (st, out)
+        except Exception:
+            pass
+    for p in procs:
+        p.join(timeout=10)
+        if p.is_alive():
+            p.terminate()
+    assert got[1] == ("ok", "left")
+    st, out = got[0]
+    assert st == "ok", out
+    alive, code, raised, ysum = out
+    assert alive is False
+    assert code == 1 and raised  # ST_BARRIER_TIMEOUT reported through the status word
+    assert ysum == 30.0
+
+
+def _child_noclose(rank, world, addr_file, q, env):
+    """Like mp_util._child but without the closing barrier: one rank leaves early on purpose."""
+    import time
+    import traceback
+
+    try:
+        os.environ.update(env)
+        from oneccl_b200.comm import KVS, Communicator
+
+        if rank == 0:
+            kvs = KVS.create_main()
+            with open(addr_file + ".tmp", "w") as f:
+                f.write(kvs.address)
+            os.replace(addr_file + ".tmp", addr_file)
+        else:
+            t0 = time.time()
+            while not os.path.exists(addr_file):
+                if time.time() - t0 > 60:
+                    raise RuntimeError("no kvs address")
+                time.sleep(0.01)
+            kvs = KVS.connect(open(addr_file).read())
+        comm = Communicator(world, rank, kvs)
+        out = _leaver(comm)
+        q.put((rank, "ok", out))
+        if rank == 1:
+            # leave without the collective teardown; keep the KVS client quiet
+            os._exit(0)
+        time.sleep(0.5)
+        os._exit(0)
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
