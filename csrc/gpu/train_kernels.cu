@@ -42,9 +42,14 @@ __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, size
     return __bfloat162float(p[i]);
 }
 
-// out[0] += sum(g^2); 8 elements per thread per step, grid-stride
+// Squared L2 norm in two deterministic stages (every rank of a data-parallel job must get
+// the same bits, otherwise the clipping factor and then the replicas drift apart):
+// stage 1: block b writes sum of its grid-stride share of g^2 to partial[b];
+// stage 2: one block adds the partials in a fixed tree order and accumulates into out[0].
+constexpr int SQN_MAX_BLOCKS = 1024;
+
 template <class T>
-__global__ void __launch_bounds__(512) sq_norm_kernel(const T* g, size_t n, float* out) {
+__global__ void __launch_bounds__(512) sq_norm_partial_kernel(const T* g, size_t n, float* partial) {
     float acc = 0.f;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
@@ -60,8 +65,21 @@ __global__ void __launch_bounds__(512) sq_norm_kernel(const T* g, size_t n, floa
         float v = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.f;
         v = warp_sum(v);
         if (threadIdx.x == 0)
-            atomicAdd(out, v);
+            partial[blockIdx.x] = v;
     }
+}
+
+__global__ void __launch_bounds__(SQN_MAX_BLOCKS) sq_norm_final_kernel(const float* partial, int n, float* out) {
+    __shared__ float sh[SQN_MAX_BLOCKS];
+    sh[threadIdx.x] = (int)threadIdx.x < n ? partial[threadIdx.x] : 0.f;
+    __syncthreads();
+    for (int s = SQN_MAX_BLOCKS / 2; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s)
+            sh[threadIdx.x] += sh[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0)
+        out[0] += sh[0];
 }
 
 struct adamw_args {
@@ -226,18 +244,25 @@ int grid_for(size_t n, int threads) {
 
 } // namespace
 
-// dt: 9 = float32, 11 = bfloat16 (ccl datatype codes)
-CCLX_API int cclx_sq_norm(const void* g, size_t n, int dt, float* out, void* stream) {
+// dt: 9 = float32, 11 = bfloat16 (ccl datatype codes).  out[0] += sum(g^2).
+// `partials`: caller-provided scratch of at least 1024 floats.
+CCLX_API int cclx_sq_norm(const void* g, size_t n, int dt, float* out, float* partials, void* stream) {
     return cclx::capi::guard([&] {
         if (n == 0)
             return;
-        const int blocks = grid_for(n, 512);
+        CCL_THROW_IF_NOT(partials != nullptr, "sq_norm needs a partials buffer of 1024 floats");
+        // the grid depends on n only, so that every rank adds in the same order
+        size_t want = (n + 512 * 8 - 1) / (512 * 8);
+        const int blocks = (int)(want < 1 ? 1 : (want > (size_t)SQN_MAX_BLOCKS ? SQN_MAX_BLOCKS : want));
         if (dt == 11)
-            sq_norm_kernel<__nv_bfloat16><<<blocks, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)g, n, out);
+            sq_norm_partial_kernel<__nv_bfloat16><<<blocks, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)g, n,
+                                                                                           partials);
         else if (dt == 9)
-            sq_norm_kernel<float><<<blocks, 512, 0, (cudaStream_t)stream>>>((const float*)g, n, out);
+            sq_norm_partial_kernel<float><<<blocks, 512, 0, (cudaStream_t)stream>>>((const float*)g, n, partials);
         else
             CCL_THROW("sq_norm supports float32 and bfloat16 gradients");
+        CUDA_CHECK(cudaGetLastError());
+        sq_norm_final_kernel<<<1, SQN_MAX_BLOCKS, 0, (cudaStream_t)stream>>>(partials, blocks, out);
         CUDA_CHECK(cudaGetLastError());
     });
 }

@@ -461,7 +461,15 @@ void worker::loop() {
     }
     int idle_spins = 0;
     while (!stop_) {
-        size_t n = do_work();
+        size_t n = 0;
+        try {
+            n = do_work();
+        }
+        catch (const std::exception& e) {
+            if (!stop_)
+                LOG_ERROR("worker ", idx_, ": ", e.what());
+            std::this_thread::sleep_for(std::chrono::milliseconds(10));
+        }
         if (n > 0) {
             idle_spins = 0;
             continue;
@@ -509,6 +517,11 @@ void executor::ensure_started(std::shared_ptr<atl_transport> tr) {
         for (auto& w : workers_)
             w->start();
     LOG_DEBUG("executor started: ", env.worker_count, " worker(s), offload=", env.worker_offload);
+}
+
+executor::~executor() {
+    // workers poll the transport: stop them before the transport goes away
+    shutdown();
 }
 
 void executor::shutdown() {

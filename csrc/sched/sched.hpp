@@ -238,6 +238,8 @@ public:
     void lock_workers();
     void unlock_workers();
 
+    ~executor();
+
 private:
     friend class worker;
     executor() = default;

@@ -9,7 +9,7 @@ cs = C.c_char_p
 
 PROTOTYPES = {
     # csrc/gpu/train_kernels.cu
-    "cclx_sq_norm": (i, [vp, sz, i, vp, vp]),
+    "cclx_sq_norm": (i, [vp, sz, i, vp, vp, vp]),
     "cclx_adamw_flat": (i, [vp, vp, i, vp, vp, vp, sz, sz, f, f, f, f, f, i, f, f, vp, vp]),
     "cclx_softmax_xent": (i, [vp, vp, vp, sz, i, sz, f, i, vp]),
     # csrc/capi/capi_comm.cpp

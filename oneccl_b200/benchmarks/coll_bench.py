@@ -2,7 +2,7 @@
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         -m oneccl_b200.benchmarks.coll_bench [--colls allreduce,reduce_scatter,allgather,alltoall] \
-        [--dtypes bf16,fp32] [--min 8] [--max 1G] [--warmup 20] [--iters 100] [--out file.jsonl]
+        [--dtypes bf16,fp32] [--min-bytes 8] [--max-bytes 1G] [--warmup 20] [--iters 100] [--out file.jsonl]
 
 Method (the reference's benchmark tool measures start+wait on the host,
 examples/benchmark/src/benchmark.cpp:47-222; here timing is on the device):
@@ -54,8 +54,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--colls", default="allreduce,reduce_scatter,allgather,alltoall")
     ap.add_argument("--dtypes", default="bf16,fp32")
-    ap.add_argument("--min", default="8")
-    ap.add_argument("--max", default="1G")
+    ap.add_argument("--min-bytes", default="8")
+    ap.add_argument("--max-bytes", default="1G")
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--out", default="")
@@ -76,7 +76,7 @@ def main():
     arms = args.arms.split(",")
     if "nccl" in arms:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    lo, hi = parse_size(args.min), parse_size(args.max)
+    lo, hi = parse_size(args.min_bytes), parse_size(args.max_bytes)
     sizes = []
     s = lo
     while s <= hi:

@@ -55,12 +55,19 @@ def softmax_cross_entropy(logits: torch.Tensor, targets: torch.Tensor, vocab: in
     return _SoftmaxXent.apply(logits, targets.contiguous(), vocab)
 
 
+_partials = {}
+
+
 def sq_norm(flat_grad: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[0] += sum(flat_grad**2) (out: 1-element fp32 device tensor)."""
+    """out[0] += sum(flat_grad**2) (out: 1-element fp32 device tensor).  Two deterministic
+    stages (fixed summation order), so every data-parallel rank computes the same bits."""
     lib = _lib.load()
+    key = flat_grad.device
+    if key not in _partials:
+        _partials[key] = torch.empty(1024, dtype=torch.float32, device=flat_grad.device)
     _lib.check(lib.cclx_sq_norm(flat_grad.data_ptr(), flat_grad.numel(), torch_to_ccl(flat_grad.dtype),
-                                out.data_ptr(), _stream_ptr()))
-    _bump()
+                                out.data_ptr(), _partials[key].data_ptr(), _stream_ptr()))
+    _bump(2)
     return out
 
 
