@@ -438,6 +438,15 @@ event_ptr staged_device_coll(host_comm& comm, coll_param p, const coll_attr& att
 
 // ---- device path ----------------------------------------------------------------------------
 event_ptr device_coll(host_comm& comm, coll_param& p, const coll_attr& attr) {
+    if (!comm.has_device()) {
+        // first device operation: the heap is created on the device that owns the buffers
+        const void* probe = p.send_buf ? p.send_buf : (p.recv_buf ? p.recv_buf : (p.recv_bufs.empty() ? nullptr : p.recv_bufs[0]));
+        cudaPointerAttributes pa;
+        if (probe && cudaPointerGetAttributes(&pa, probe) == cudaSuccess && pa.type == cudaMemoryTypeDevice)
+            CUDA_CHECK(cudaSetDevice(pa.device));
+        else
+            (void)cudaGetLastError();
+    }
     gpu::device_comm* dc = comm.device();
     cudaStream_t st = (cudaStream_t)p.stream;
     CUDA_CHECK(cudaSetDevice(dc->device_id()));

@@ -258,6 +258,7 @@ void env_data::parse() {
     get_size("CCL_CUDA_SYMM_HEAP_SIZE", symm_heap_bytes);
     get_size("CCL_CUDA_TMP_BUF_SIZE", tmp_buf_bytes);
     get_int("CCL_CUDA_NVLS", nvls);
+    get_int("CCL_CUDA_NVLS_MIN_RANKS", nvls_min_ranks);
     get_size("CCL_CUDA_ALLREDUCE_SMALL_THRESHOLD", ar_oneshot_threshold);
     get_size("CCL_CUDA_ALLREDUCE_MEDIUM_THRESHOLD", ar_twoshot_threshold);
     get_size("CCL_CUDA_REDUCE_SCATTER_SMALL_THRESHOLD", rs_small_threshold);

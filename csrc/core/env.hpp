@@ -114,6 +114,7 @@ struct env_data {
     size_t symm_heap_bytes = 1ull << 30; // peer-mapped heap per rank
     size_t tmp_buf_bytes = 64ull << 20; // one staging generation; two generations are kept
     int nvls = -1; // -1 auto, 0 off, 1 force
+    int nvls_min_ranks = 3; // communicators smaller than this use peer loads even when NVLS exists
     size_t ar_oneshot_threshold = 256u << 10; // <= : one-shot
     size_t ar_twoshot_threshold = 16u << 20; // <= : two-shot single launch; above: chunked
     size_t rs_small_threshold = 2u << 20;

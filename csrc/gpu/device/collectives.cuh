@@ -256,44 +256,44 @@ __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* ta
             char* out = c.mc_heap + a.out_off;
             size_t i = mlo + lo + tid;
             const size_t end = mlo + hi;
-            // two packs in flight per thread
-            for (; i + nt < end; i += 2 * nt) {
-                uint4 v0 = multimem_ld_reduce_add16<T>(in + (i << 4));
-                uint4 v1 = multimem_ld_reduce_add16<T>(in + ((i + nt) << 4));
-                if (scale) {
-                    A t0[N], t1[N];
-                    unpack16<T, A>(v0, t0);
-                    unpack16<T, A>(v1, t1);
-                    T* o0 = reinterpret_cast<T*>(&v0);
-                    T* o1 = reinterpret_cast<T*>(&v1);
+            // four packs in flight per thread keep enough bytes on the wire for the switch round trip
+            constexpr int U = 4;
+            auto rescale = [&](uint4& v) {
+                A t0[N];
+                unpack16<T, A>(v, t0);
+                T* o0 = reinterpret_cast<T*>(&v);
 #pragma unroll
-                    for (int k = 0; k < N; k++) {
-                        o0[k] = from_acc<T, A>(apply_scale<A>(t0[k], a.scale));
-                        o1[k] = from_acc<T, A>(apply_scale<A>(t1[k], a.scale));
-                    }
+                for (int k = 0; k < N; k++)
+                    o0[k] = from_acc<T, A>(apply_scale<A>(t0[k], a.scale));
+            };
+            for (; i + (U - 1) * nt < end; i += U * nt) {
+                uint4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    v[u] = multimem_ld_reduce_add16<T>(in + ((i + u * nt) << 4));
+                if (scale) {
+#pragma unroll
+                    for (int u = 0; u < U; u++)
+                        rescale(v[u]);
                 }
-                multimem_st16(out + (i << 4), v0);
-                multimem_st16(out + ((i + nt) << 4), v1);
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    multimem_st16(out + ((i + u * nt) << 4), v[u]);
             }
             for (; i < end; i += nt) {
                 uint4 v0 = multimem_ld_reduce_add16<T>(in + (i << 4));
-                if (scale) {
-                    A t0[N];
-                    unpack16<T, A>(v0, t0);
-                    T* o0 = reinterpret_cast<T*>(&v0);
-#pragma unroll
-                    for (int k = 0; k < N; k++)
-                        o0[k] = from_acc<T, A>(apply_scale<A>(t0[k], a.scale));
-                }
+                if (scale)
+                    rescale(v0);
                 multimem_st16(out + (i << 4), v0);
             }
         }
         else {
-            for (size_t i = mlo + lo + tid; i < mlo + hi; i += nt) {
+            // two packs x world loads in flight per thread
+            auto reduce_one = [&](size_t i, const uint4 (&v)[MAX_RANKS]) {
                 A acc[N];
-                unpack16<T, A>(ld_cv16(c.heap[0] + a.in_off + (i << 4)), acc);
+                unpack16<T, A>(v[0], acc);
                 for (int p = 1; p < W; p++)
-                    accum16<T, A, Op>(ld_cv16(c.heap[p] + a.in_off + (i << 4)), acc);
+                    accum16<T, A, Op>(v[p], acc);
                 uint4 o;
                 T* t = reinterpret_cast<T*>(&o);
 #pragma unroll
@@ -303,6 +303,23 @@ __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* ta
                     const int p = (c.rank + k) % W;
                     st16(c.heap[p] + a.out_off + (i << 4), o);
                 }
+            };
+            size_t i = mlo + lo + tid;
+            const size_t end = mlo + hi;
+            for (; i + nt < end; i += 2 * nt) {
+                uint4 v0[MAX_RANKS], v1[MAX_RANKS];
+                for (int p = 0; p < W; p++) {
+                    v0[p] = ld_cv16(c.heap[p] + a.in_off + (i << 4));
+                    v1[p] = ld_cv16(c.heap[p] + a.in_off + ((i + nt) << 4));
+                }
+                reduce_one(i, v0);
+                reduce_one(i + nt, v1);
+            }
+            for (; i < end; i += nt) {
+                uint4 v0[MAX_RANKS];
+                for (int p = 0; p < W; p++)
+                    v0[p] = ld_cv16(c.heap[p] + a.in_off + (i << 4));
+                reduce_one(i, v0);
             }
         }
         if (blockIdx.x == 0 && tid < tail) {
@@ -753,7 +770,6 @@ static __global__ void __launch_bounds__(1024)
                               reinterpret_cast<const char*>(op.send) + round_off + l, h - l);
         __syncthreads();
         if (threadIdx.x == 0) {
-            __threadfence_system();
             st_release_sys(c.p2p_flags[peer] + c.rank * P2P_BLOCKS + b, seq_s);
             *seqw = seq_s;
         }
@@ -764,7 +780,6 @@ static __global__ void __launch_bounds__(1024)
                              L.data[c.rank] + (size_t)peer * L.slot_bytes + l, h - l);
         __syncthreads();
         if (threadIdx.x == 0) {
-            __threadfence_system();
             st_release_sys(c.p2p_flags[peer] + P2P_ACK_BASE + c.rank * P2P_BLOCKS + b, seq_s);
             *seqw = seq_s;
         }

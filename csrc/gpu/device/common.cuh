@@ -182,7 +182,8 @@ __device__ __forceinline__ bool peer_barrier(const comm_dev& c, block_sync& s) {
     const uint32_t target = s.epoch + s.used;
     if (s.ok && threadIdx.x < (unsigned)c.world) {
         const int p = threadIdx.x;
-        __threadfence_system();
+        // the release store is the only system-scope fence of the barrier: it orders the
+        // block's earlier writes (made visible to this thread by bar.sync) before the flag
         st_release_sys(c.flags[p] + blockIdx.x * MAX_RANKS + c.rank, target);
         if (!wait_flag_sys(c, c.flags[c.rank] + blockIdx.x * MAX_RANKS + p, target, p, ST_BARRIER_TIMEOUT))
             bar_fail = 1;

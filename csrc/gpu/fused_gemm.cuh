@@ -414,7 +414,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     // publish: this warp's quarter of tile (mb_local, ni) from `rank` has landed at `owner`
                     __syncwarp();
                     if (lane == 0) {
-                        __threadfence_system();
                         dev::red_release_sys_add(
                             cp->aux[owner] + P.flag_off + ((size_t)rank * tiles_m_per + mb_local) * tiles_n + ni, 1u);
                     }

@@ -33,10 +33,14 @@ int selected_allreduce_algo(const device_comm& dc, size_t bytes, bool symmetric,
     if (dc.world() == 1)
         return ga_copy;
     const bool fits_oneshot = (size_t)dc.world() * ((bytes + 15) & ~(size_t)15) <= dc.staging_bytes();
-    if (bytes <= env.ar_oneshot_threshold && fits_oneshot)
-        return (dc.nvls() && bytes >= 4096) ? ga_nvls_oneshot : ga_oneshot;
+    // one-shot sends (n-1) copies of the message: its break-even size shrinks with the rank
+    // count (the configured threshold is the 8-rank value)
+    const size_t oneshot_max = env.ar_oneshot_threshold * 8 / (size_t)std::max(dc.world(), 2);
+    if (bytes <= oneshot_max && fits_oneshot)
+        return (dc.nvls() && bytes >= 4096 && dc.world() >= env.nvls_min_ranks) ? ga_nvls_oneshot : ga_oneshot;
+    // in-switch reduction moves (1 + 1/n) S per direction, peer loads 2 (n-1)/n S: NVLS wins from 3 ranks on
     if (symmetric)
-        return (dc.nvls() && nvls_type_ok(dt, op)) ? ga_nvls : ga_symm;
+        return (dc.nvls() && nvls_type_ok(dt, op) && dc.world() >= env.nvls_min_ranks) ? ga_nvls : ga_symm;
     return ga_twoshot;
 }
 

@@ -85,7 +85,7 @@ rule nvcc
   description = NVCC $in
 
 rule link
-  command = $nvcc -shared -o $out $in -cudart static -Xlinker --no-undefined -lpthread -ldl -lrt
+  command = $nvcc -shared -o $out $in -cudart static -Xlinker --no-undefined -Xlinker -soname=libccl_b200.so -lpthread -ldl -lrt
   description = LINK $out
 """
     builds, objs = [], []
@@ -127,7 +127,7 @@ def build_torch_backend(verbose: bool = False) -> Path:
     tlib = Path(torch.__file__).parent / "lib"
     ext = LIBDIR / "_ccl_torch.so"
     ldflags = (
-        f"-shared -L{tlib} -L{LIBDIR} -Wl,-rpath,{tlib} -Wl,-rpath,$$ORIGIN "
+        f"-shared -L{tlib} -L{LIBDIR} -Wl,-rpath,{tlib} '-Wl,-rpath,$$ORIGIN' "
         f"-lc10 -lc10_cuda -ltorch_cpu -ltorch_cuda -ltorch -ltorch_python -lccl_b200"
     )
     rules = f"""

@@ -12,6 +12,9 @@ PROTOTYPES = {
     "cclx_sq_norm": (i, [vp, sz, i, vp, vp, vp]),
     "cclx_adamw_flat": (i, [vp, vp, i, vp, vp, vp, sz, sz, f, f, f, f, f, i, f, f, vp, vp]),
     "cclx_softmax_xent": (i, [vp, vp, vp, sz, i, sz, f, i, vp]),
+    # csrc/gpu/moe_kernels.cu
+    "cclx_moe_gather_rows": (i, [vp, vp, vp, sz, i, vp]),
+    "cclx_moe_combine": (i, [vp, vp, vp, vp, sz, i, i, vp]),
     # csrc/capi/capi_comm.cpp
     "cclx_kvs_create_main": (vp, [cs]),
     "cclx_kvs_create_peer": (vp, [cs]),

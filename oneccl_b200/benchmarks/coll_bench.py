@@ -50,8 +50,33 @@ def time_op(fn, warmup, iters, sync):
     return e0.elapsed_time(e1) / iters * 1e-3  # seconds
 
 
+def time_graph(fn, iters, sync):
+    """Device time of one launch with the host out of the loop: `iters` launches are
+    captured into a CUDA graph and replayed (one untimed replay, one timed)."""
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for _ in range(iters):
+            fn()
+    sync()
+    g.replay()
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--graph", action="store_true",
+                    help="time graph replays (device time without per-launch host overhead)")
     ap.add_argument("--colls", default="allreduce,reduce_scatter,allgather,alltoall")
     ap.add_argument("--dtypes", default="bf16,fp32")
     ap.add_argument("--min-bytes", default="8")
@@ -117,7 +142,8 @@ def main():
                 warm = args.warmup if Sb <= (64 << 20) else max(3, args.warmup // 5)
                 gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
                 factor = {"allreduce": 2.0 * (world - 1) / world}.get(coll, (world - 1) / world)
-                row = {"coll": coll, "dtype": dname, "bytes": Sb, "n_gpus": world, "iters": iters, "warmup": warm}
+                row = {"coll": coll, "dtype": dname, "bytes": Sb, "n_gpus": world, "iters": iters, "warmup": warm,
+                       "timing": "graph" if args.graph else "stream"}
                 for arm in arms:
                     symm = arm == "ours_symm"
                     if arm == "nccl":
@@ -147,7 +173,7 @@ def main():
                             fn = lambda: grp.allgatherv(a, b)  # noqa: E731
                         else:
                             fn = lambda: grp.alltoallv(a, b)  # noqa: E731
-                    t = maxr(time_op(fn, warm, iters, sync))
+                    t = maxr(time_graph(fn, iters, sync) if args.graph else time_op(fn, warm, iters, sync))
                     row[arm + "_us"] = t * 1e6
                     row[arm + "_busbw_gbs"] = factor * Sb / t / 1e9
                     if symm:

@@ -233,15 +233,10 @@ def test_rank_leaving_is_detected_on_host_and_device_wait_is_bounded():
     import tempfile
     import time
 
-    from mp_util import _child
-
     env = dict(ENV, CCL_CUDA_NVLS="0")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     addr = os.path.join(tempfile.mkdtemp(prefix="cclx_"), "addr")
-
-    def runner(comm):
-        return _leaver(comm)
 
     procs = [ctx.Process(target=_child_noclose, args=(rk, 2, addr, q, env)) for rk in range(2)]
     for p in procs:
@@ -291,10 +286,55 @@ def _child_noclose(rank, world, addr_file, q, env):
         comm = Communicator(world, rank, kvs)
         out = _leaver(comm)
         q.put((rank, "ok", out))
-        if rank == 1:
-            # leave without the collective teardown; keep the KVS client quiet
-            os._exit(0)
-        time.sleep(0.5)
+        q.close()
+        q.join_thread()  # the result must reach the parent before the hard exit below
+        # leave without the collective teardown (the peer is gone or about to go)
         os._exit(0)
     except Exception:
         q.put((rank, "error", traceback.format_exc()))
+        q.close()
+        q.join_thread()
+
+
+def _tp_and_moe(comm):
+    from oneccl_b200.parallel.ep import ExpertParallelMoE, reference_moe
+    from oneccl_b200.parallel.tp import TensorParallelMLP
+
+    r, W = comm.rank, comm.size
+    torch.cuda.set_device(r)
+    g = comm.device_group
+    # tensor-parallel MLP: fused kernels against separate collectives + cuBLAS
+    tokens, d_model, d_ff = W * 128, 256, W * 128
+    mlp = TensorParallelMLP(g, tokens, d_model, d_ff, n_comm=2)
+    gen = torch.Generator(device="cuda").manual_seed(100 + r)
+    x_local = torch.randn(tokens // W, d_model, generator=gen, device="cuda").to(torch.bfloat16)
+    for _ in range(2):
+        mlp.x_shard.copy_(x_local)
+        y = mlp.forward().float().clone()
+        y_ref = mlp.forward_unfused(x_local).float()
+        torch.cuda.synchronize()
+        assert (y - y_ref).abs().max().item() < 3e-2 * y_ref.abs().max().item() + 1e-3
+    mlp.close()
+    # expert-parallel MoE against the dense restatement (all experts gathered on every rank)
+    T, H, F = 96, 64, 128
+    moe = ExpertParallelMoE(g, H, F, topk=2)
+    x = torch.randn(T, H, generator=gen, device="cuda").to(torch.bfloat16)
+    logits = torch.randn(T, W, generator=gen, device="cuda")
+    out = moe(x, logits).float()
+    w1s = [torch.empty_like(moe.w1) for _ in range(W)]
+    w2s = [torch.empty_like(moe.w2) for _ in range(W)]
+    w1all = torch.empty((W,) + tuple(moe.w1.shape), dtype=torch.bfloat16, device="cuda")
+    w2all = torch.empty((W,) + tuple(moe.w2.shape), dtype=torch.bfloat16, device="cuda")
+    g.allgatherv(moe.w1, w1all)
+    g.allgatherv(moe.w2, w2all)
+    torch.cuda.synchronize()
+    ref = reference_moe(x, logits, list(w1all), list(w2all), topk=2)
+    assert (out - ref).abs().max().item() < 3e-2 * ref.abs().max().item() + 1e-3
+    assert sum(moe.stats["sent_rows"]) == T * 2
+    g.check()
+    return True
+
+
+@needs2
+def test_tensor_parallel_mlp_and_moe():
+    assert all(run_ranks(_tp_and_moe, _world(), env=ENV, timeout=300))

@@ -66,3 +66,22 @@ def test_reduce_local_and_pack():
     reduce_local(c, d, op="max")
     torch.cuda.synchronize()
     assert torch.equal(d, torch.clamp(torch.arange(1000, device="cuda", dtype=torch.int32), min=5))
+
+
+def test_moe_gather_and_combine_kernels():
+    from oneccl_b200.parallel.ep import combine_rows, gather_rows
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    T, H, k = 257, 136, 2
+    x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
+    order = torch.randperm(T * k, generator=g, device="cuda")
+    xs = gather_rows(x, order // k)
+    torch.cuda.synchronize()
+    assert torch.equal(xs, x[order // k])
+    pos = torch.empty_like(order)
+    pos[order] = torch.arange(T * k, device="cuda")
+    w = torch.rand(T, k, generator=g, device="cuda")
+    out = combine_rows(xs, pos.view(T, k), w)
+    ref = (xs[pos].view(T, k, H).float() * w.unsqueeze(-1)).sum(1)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)

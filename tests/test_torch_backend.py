@@ -1,0 +1,123 @@
+"""torch.distributed 'ccl' backend on CPU tensors with real processes; the CUDA
+variant runs when at least two GPUs are visible."""
+import multiprocessing as mp
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, device, q):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        os.environ["CCL_CUDA_SYMM_HEAP_SIZE"] = "256M"
+        os.environ["CCL_CUDA_TMP_BUF_SIZE"] = "16M"
+        import torch.distributed as dist
+
+        import oneccl_b200.torch_backend  # noqa: F401  registers "ccl"
+
+        if device == "cuda":
+            torch.cuda.set_device(rank)
+        dist.init_process_group("ccl", rank=rank, world_size=world)
+        dev = torch.device(device, rank) if device == "cuda" else torch.device("cpu")
+        W = world
+        x = torch.arange(1000, dtype=torch.float32, device=dev) + rank
+        dist.all_reduce(x)
+        assert torch.allclose(x.cpu(), torch.arange(1000, dtype=torch.float32) * W + sum(range(W)))
+        y = torch.full((7,), float(rank), device=dev)
+        dist.all_reduce(y, op=dist.ReduceOp.MAX)
+        assert torch.all(y == W - 1)
+        z = torch.full((5,), float(rank + 1), device=dev)
+        dist.all_reduce(z, op=dist.ReduceOp.AVG)
+        assert torch.allclose(z.cpu(), torch.full((5,), (W + 1) / 2))
+        b = torch.full((33,), float(rank), device=dev)
+        dist.broadcast(b, src=W - 1)
+        assert torch.all(b == W - 1)
+        outs = [torch.zeros(4, device=dev) for _ in range(W)]
+        dist.all_gather(outs, torch.full((4,), float(rank), device=dev))
+        for p in range(W):
+            assert torch.all(outs[p] == p)
+        flat = torch.zeros(4 * W, device=dev)
+        dist.all_gather_into_tensor(flat, torch.full((4,), float(rank), device=dev))
+        assert torch.equal(flat.cpu(), torch.repeat_interleave(torch.arange(W, dtype=torch.float32), 4))
+        rs = torch.zeros(3, device=dev)
+        dist.reduce_scatter_tensor(rs, torch.arange(3 * W, dtype=torch.float32, device=dev))
+        assert torch.allclose(rs.cpu(), torch.arange(3 * W, dtype=torch.float32)[3 * rank:3 * rank + 3] * W)
+        a2a = torch.zeros(2 * W, device=dev)
+        dist.all_to_all_single(a2a, torch.arange(2 * W, dtype=torch.float32, device=dev) + 100 * rank)
+        ref = torch.cat([torch.arange(2, dtype=torch.float32) + 2 * rank + 100 * p for p in range(W)])
+        assert torch.equal(a2a.cpu(), ref)
+        red = torch.full((9,), float(rank + 1), device=dev)
+        dist.reduce(red, dst=0)
+        if rank == 0:
+            assert torch.all(red == W * (W + 1) / 2)
+        if rank == 0:
+            dist.send(torch.full((6,), 42.0, device=dev), dst=1)
+        elif rank == 1:
+            got = torch.zeros(6, device=dev)
+            dist.recv(got, src=0)
+            assert torch.all(got == 42)
+        dist.barrier()
+        # DistributedDataParallel over the backend
+        torch.manual_seed(0)
+        model = torch.nn.Linear(16, 4).to(dev)
+        ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[rank] if device == "cuda" else None)
+        inp = torch.randn(8, 16, generator=torch.Generator().manual_seed(rank)).to(dev)
+        ddp(inp).sum().backward()
+        g = model.weight.grad.detach().cpu().clone()
+        gathered = [torch.zeros_like(g) for _ in range(W)]
+        dist.all_gather(gathered, g.to(dev) if device == "cuda" else g)
+        for t in gathered:
+            assert torch.allclose(t.cpu(), g, rtol=1e-5, atol=1e-6)
+        dist.barrier()
+        if device == "cuda":
+            torch.cuda.synchronize()
+        dist.destroy_process_group()
+        q.put((rank, "ok", ""))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def _run(world, device):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, device, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = []
+    try:
+        for _ in range(world):
+            res.append(q.get(timeout=240))
+    finally:
+        for p in procs:
+            p.join(timeout=20)
+            if p.is_alive():
+                p.terminate()
+    for rank, status, msg in res:
+        assert status == "ok", f"rank {rank}: {msg}"
+
+
+def test_process_group_cpu_world2():
+    _run(2, "cpu")
+
+
+def test_process_group_cpu_world3():
+    _run(3, "cpu")
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_process_group_cuda():
+    _run(2, "cuda")
