@@ -308,3 +308,78 @@ CCLX_API int cclx_softmax_xent(void* logits_bf16, const long long* targets, floa
         CUDA_CHECK(cudaGetLastError());
     });
 }
+
+// ---------------------------------------------------------------------------------------------
+// Mean cross-entropy without any allocation (declared and documented in gpu/xent_noalloc.h).
+// The per-row losses of the regular kernel go to a fixed device array that is part of this
+// library image; a one-block kernel then averages them into the caller's float.
+// ---------------------------------------------------------------------------------------------
+#include "gpu/xent_noalloc.h"
+
+#include <mutex>
+
+namespace {
+
+// scratch: one loss per row.  Lives in every device's copy of this module until the process ends.
+static __device__ __align__(256) float xent_row_scratch[CCLX_XENT_NOALLOC_MAX_ROWS];
+
+// out[0] = sum(rows[0..n)) / n, fixed summation order (one block, strided partials, tree in shared memory)
+__global__ void __launch_bounds__(1024) mean_rows_kernel(const float* rows, size_t n, float* out) {
+    __shared__ float part[1024];
+    float acc = 0.f;
+    for (size_t i = threadIdx.x; i < n; i += blockDim.x)
+        acc += rows[i];
+    part[threadIdx.x] = acc;
+    __syncthreads();
+    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+        if ((int)threadIdx.x < s)
+            part[threadIdx.x] += part[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0)
+        out[0] = part[0] / (float)n;
+}
+
+constexpr int XENT_MAX_DEVICES = 64;
+std::mutex xent_setup_mu;
+float* xent_scratch_addr[XENT_MAX_DEVICES] = {};
+
+// Device address of the scratch array on the current device.  In host code the array's name
+// is only a handle for the runtime, never an address a kernel may use: ask the runtime once
+// per device, with that device current.
+float* xent_scratch_for_current_device() {
+    int dev = -1;
+    CUDA_CHECK(cudaGetDevice(&dev));
+    CCL_THROW_IF_NOT(dev >= 0 && dev < XENT_MAX_DEVICES, "device index ", dev, " out of range");
+    std::lock_guard<std::mutex> lk(xent_setup_mu);
+    if (!xent_scratch_addr[dev]) {
+        float* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&p, xent_row_scratch);
+        CCL_THROW_IF_NOT(e == cudaSuccess && p != nullptr, "cudaGetSymbolAddress(xent_row_scratch) failed: ",
+                         cudaGetErrorString(e));
+        xent_scratch_addr[dev] = p;
+    }
+    return xent_scratch_addr[dev];
+}
+
+} // namespace
+
+CCLX_API int cclx_softmax_xent_mean_noalloc(void* logits_bf16, const long long* targets, float* mean_loss, size_t rows,
+                                            int vocab, size_t ld, float grad_scale, int pad_cols, void* stream) {
+    return cclx::capi::guard([&] {
+        CCL_THROW_IF_NOT(rows <= (size_t)CCLX_XENT_NOALLOC_MAX_ROWS, "softmax_xent_mean_noalloc: ", rows,
+                         " rows exceed the built-in scratch of ", CCLX_XENT_NOALLOC_MAX_ROWS,
+                         " rows; split the batch or use cclx_softmax_xent with a caller-provided buffer");
+        CCL_THROW_IF_NOT(logits_bf16 && targets && mean_loss, "softmax_xent_mean_noalloc: null pointer argument");
+        CCL_THROW_IF_NOT(vocab > 0 && (size_t)(vocab + pad_cols) <= ld, "softmax_xent_mean_noalloc: bad row layout");
+        if (rows == 0)
+            return;
+        float* scratch = xent_scratch_for_current_device();
+        cudaStream_t st = (cudaStream_t)stream;
+        softmax_xent_kernel<<<(unsigned)rows, 1024, 0, st>>>((__nv_bfloat16*)logits_bf16, targets, scratch, vocab, ld,
+                                                            grad_scale, pad_cols);
+        CUDA_CHECK(cudaGetLastError());
+        mean_rows_kernel<<<1, 1024, 0, st>>>(scratch, rows, mean_loss);
+        CUDA_CHECK(cudaGetLastError());
+    });
+}
