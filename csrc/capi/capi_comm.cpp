@@ -323,7 +323,7 @@ CCLX_API int cclx_parse_algo_spec(int ctype, const char* spec) {
         [&] { algorithm_selector::parse(spec, algorithm_selector::known_cpu_algos((coll_type)ctype)); });
 }
 
-// stats: which = 0 calls, 1 device calls, 2 fused ops, 3 fused batches, 4 cache hits
+// stats: which = 0 calls, 1 device calls, 2 fused ops, 3 fused batches, 4 cache hits, 5 postponed
 CCLX_API long long cclx_stats(int which, int ctype) {
     coll_stats& s = stats();
     switch (which) {
@@ -332,6 +332,7 @@ CCLX_API long long cclx_stats(int which, int ctype) {
         case 2: return (long long)s.fused_ops;
         case 3: return (long long)s.fused_batches;
         case 4: return (long long)s.cache_hits;
+        case 5: return (long long)s.postponed;
         default: return -1;
     }
 }

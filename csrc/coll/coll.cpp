@@ -3,7 +3,10 @@
 #include <cuda_runtime.h>
 
 #include <cstring>
+#include <deque>
 #include <list>
+#include <map>
+#include <mutex>
 #include <sstream>
 
 #include "coll/algorithms.hpp"
@@ -593,6 +596,204 @@ event_ptr staged_device_coll(host_comm& comm, coll_param p, const coll_attr& att
     return make_completed_event();
 }
 
+// ---- schedule: cached or new -----------------------------------------------------------------
+constexpr uint64_t NO_SCHED_ID = ~0ull;
+
+event_ptr start_sched(host_comm& comm, const coll_param& p, const coll_attr& attr, uint64_t fixed_id) {
+    const env_data& env = env_data::get();
+    const bool cacheable = attr.to_cache && p.ctype != coll_send && p.ctype != coll_recv && p.deps.empty() &&
+                           (env.cache_key == cache_key_t::full || !attr.match_id.empty());
+    if (p.ctype == coll_barrier && env.cache_flush)
+        comm.cache().flush();
+    master_sched* m = nullptr;
+    std::unique_ptr<master_sched> owned;
+    if (cacheable) {
+        const std::string key = coll_cache_key(comm, p, attr);
+        m = comm.cache().find(key);
+        if (m)
+            stats().cache_hits++;
+        else {
+            auto fresh = build_master(comm, p, attr, fixed_id != NO_SCHED_ID ? fixed_id : comm.next_sched_id());
+            m = fresh.get();
+            comm.cache().insert(key, std::move(fresh));
+        }
+    }
+    else {
+        uint64_t sid;
+        if (fixed_id != NO_SCHED_ID)
+            sid = fixed_id;
+        else if (p.ctype == coll_send)
+            sid = atl_tag::PT2PT_SCHED - 8 - (comm.p2p_send_seq(p.peer) & 0xff);
+        else if (p.ctype == coll_recv)
+            sid = atl_tag::PT2PT_SCHED - 8 - (comm.p2p_recv_seq(p.peer) & 0xff);
+        else
+            sid = comm.next_sched_id();
+        owned = build_master(comm, p, attr, sid);
+        m = owned.get();
+    }
+    const uint64_t ticket = executor::get().start(m);
+    return std::make_shared<host_event>(m, ticket, std::move(owned));
+}
+
+// ---- unordered collectives -------------------------------------------------------------------
+// With CCL_UNORDERED_COLL=1 operations that carry a match_id may be issued in a different order
+// on every rank.  Rank 0 of the communicator names them: the k-th match_id it meets gets the k-th
+// reserved schedule id, and coordination message k (a 256-byte record sent to every rank) tells
+// the others.  A rank that issues a match_id it cannot name yet parks the operation behind a
+// deferred event and posts a receive for the next coordination message; when the message arrives
+// (on a worker thread) the parked operations of that match_id start, and another receive is
+// posted while anything is still parked.  Messages that arrive for match_ids the rank has not
+// issued yet are simply remembered.  Same role as the reference's ccl_unordered_coll_manager
+// (src/unordered_coll/unordered_coll.cpp:96-300), which clones the communicator per match_id;
+// here a schedule id inside the same communicator is enough because messages match by tag.
+class deferred_event : public event_impl {
+public:
+    void bind(event_ptr e) {
+        std::lock_guard<std::mutex> lk(mu_);
+        real_ = std::move(e);
+    }
+    void fail(const std::string& why) {
+        std::lock_guard<std::mutex> lk(mu_);
+        error_ = why;
+    }
+    void wait() override {
+        for (;;) {
+            event_ptr r = current();
+            if (r) {
+                r->wait();
+                return;
+            }
+            executor::get().progress();
+        }
+    }
+    bool test() override {
+        event_ptr r = current();
+        if (r)
+            return r->test();
+        executor::get().progress();
+        return false;
+    }
+    void* native() override { return nullptr; }
+
+private:
+    event_ptr current() {
+        std::lock_guard<std::mutex> lk(mu_);
+        if (!error_.empty())
+            CCL_THROW("postponed operation failed: ", error_);
+        return real_;
+    }
+    std::mutex mu_;
+    event_ptr real_;
+    std::string error_;
+};
+
+constexpr size_t UNORDERED_MSG_BYTES = 256;
+
+struct unordered_state {
+    struct parked {
+        coll_param param;
+        coll_attr attr;
+        std::shared_ptr<deferred_event> ev;
+    };
+    struct round {
+        char msg[UNORDERED_MSG_BYTES];
+        std::unique_ptr<master_sched> m;
+    };
+    std::mutex mu;
+    std::map<std::string, uint64_t> ids;
+    std::map<std::string, std::vector<parked>> waiting;
+    uint64_t rounds = 0; // coordination messages posted by this rank
+    bool receiving = false;
+    std::deque<std::unique_ptr<round>> live;
+};
+
+unordered_state& unordered_of(host_comm& comm) {
+    static std::mutex create_mu;
+    std::lock_guard<std::mutex> lk(create_mu);
+    if (!comm.frontend_state)
+        comm.frontend_state = std::make_shared<unordered_state>();
+    return *static_cast<unordered_state*>(comm.frontend_state.get());
+}
+
+void unordered_post_round(host_comm& comm, unordered_state& st, const std::string* name);
+
+// runs on a worker thread when coordination message k has arrived
+void unordered_on_message(host_comm& comm, unordered_state& st, unordered_state::round* r, uint64_t k) {
+    std::lock_guard<std::mutex> lk(st.mu);
+    r->msg[UNORDERED_MSG_BYTES - 1] = 0;
+    const std::string name(r->msg);
+    const uint64_t sid = comm.unordered_sched_id(k);
+    st.ids[name] = sid;
+    st.receiving = false;
+    auto it = st.waiting.find(name);
+    if (it != st.waiting.end()) {
+        // under the lock: a later operation with this match_id must not overtake the parked ones
+        for (auto& w : it->second) {
+            try {
+                w.ev->bind(start_sched(comm, w.param, w.attr, sid));
+            }
+            catch (const std::exception& e) {
+                w.ev->fail(e.what());
+            }
+        }
+        st.waiting.erase(it);
+    }
+    if (!st.waiting.empty())
+        unordered_post_round(comm, st, nullptr);
+}
+
+// st.mu is held.  name != nullptr: rank 0 announces it; otherwise post the receive of the next message
+void unordered_post_round(host_comm& comm, unordered_state& st, const std::string* name) {
+    // schedules of finished rounds are released a few rounds later, never from their own callback
+    while (st.live.size() > 4 && st.live.front()->m->ticket_complete(1) && !st.live.front()->m->in_flight)
+        st.live.pop_front();
+    const uint64_t k = st.rounds++;
+    std::unique_ptr<unordered_state::round> r(new unordered_state::round());
+    std::memset(r->msg, 0, sizeof(r->msg));
+    r->m.reset(new master_sched(&comm, atl_tag::UNORDERED_SCHED));
+    r->m->priority = 1 << 29;
+    sched* s = r->m->add_partial(0);
+    if (name) {
+        CCL_THROW_IF_NOT(name->size() < UNORDERED_MSG_BYTES, "match_id longer than ", UNORDERED_MSG_BYTES - 1,
+                         " characters can not be used with unordered collectives");
+        std::memcpy(r->msg, name->data(), name->size());
+        for (int peer = 1; peer < comm.size(); peer++)
+            s->add<send_entry>(r->msg, UNORDERED_MSG_BYTES, peer, k);
+    }
+    else {
+        s->add<recv_entry>(r->msg, UNORDERED_MSG_BYTES, 0, k);
+        unordered_state::round* raw = r.get();
+        host_comm* c = &comm;
+        unordered_state* stp = &st;
+        r->m->user_complete = [c, stp, raw, k] { unordered_on_message(*c, *stp, raw, k); };
+        st.receiving = true;
+    }
+    master_sched* m = r->m.get();
+    st.live.push_back(std::move(r));
+    executor::get().start(m);
+}
+
+event_ptr unordered_submit(host_comm& comm, const coll_param& p, const coll_attr& attr) {
+    unordered_state& st = unordered_of(comm);
+    std::lock_guard<std::mutex> lk(st.mu);
+    auto it = st.ids.find(attr.match_id);
+    if (it != st.ids.end())
+        return start_sched(comm, p, attr, it->second);
+    if (comm.rank() == 0) {
+        const uint64_t sid = comm.unordered_sched_id(st.rounds);
+        st.ids[attr.match_id] = sid;
+        unordered_post_round(comm, st, &attr.match_id);
+        return start_sched(comm, p, attr, sid);
+    }
+    auto ev = std::make_shared<deferred_event>();
+    st.waiting[attr.match_id].push_back(unordered_state::parked{ p, attr, ev });
+    stats().postponed++;
+    if (!st.receiving)
+        unordered_post_round(comm, st, nullptr);
+    return ev;
+}
+
+
 } // namespace
 
 // ---- entry point ----------------------------------------------------------------------------
@@ -658,37 +859,15 @@ event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr) {
             fusion_manager::get().flush(&comm);
     }
 
-    // ---- schedule: cached or new
-    const bool cacheable = attr.to_cache && p.ctype != coll_send && p.ctype != coll_recv && p.deps.empty() &&
-                           (env.cache_key == cache_key_t::full || !attr.match_id.empty());
-    if (p.ctype == coll_barrier && env.cache_flush)
-        comm.cache().flush();
-    master_sched* m = nullptr;
-    std::unique_ptr<master_sched> owned;
-    if (cacheable) {
-        const std::string key = coll_cache_key(comm, p, attr);
-        m = comm.cache().find(key);
-        if (m)
-            stats().cache_hits++;
-        else {
-            auto fresh = build_master(comm, p, attr, comm.next_sched_id());
-            m = fresh.get();
-            comm.cache().insert(key, std::move(fresh));
-        }
+    // ---- operations named by match_id may arrive in any order
+    if (env.unordered_coll && !attr.match_id.empty() && p.ctype != coll_send && p.ctype != coll_recv) {
+        event_ptr ev = unordered_submit(comm, p, attr);
+        if (sync)
+            ev->wait();
+        return ev;
     }
-    else {
-        uint64_t sid;
-        if (p.ctype == coll_send)
-            sid = atl_tag::PT2PT_SCHED - 8 - (comm.p2p_send_seq(p.peer) & 0xff);
-        else if (p.ctype == coll_recv)
-            sid = atl_tag::PT2PT_SCHED - 8 - (comm.p2p_recv_seq(p.peer) & 0xff);
-        else
-            sid = comm.next_sched_id();
-        owned = build_master(comm, p, attr, sid);
-        m = owned.get();
-    }
-    const uint64_t ticket = executor::get().start(m);
-    auto ev = std::make_shared<host_event>(m, ticket, std::move(owned));
+
+    event_ptr ev = start_sched(comm, p, attr, NO_SCHED_ID);
     if (sync)
         ev->wait();
     return ev;

@@ -77,6 +77,7 @@ struct coll_stats {
     uint64_t device_calls[coll_last] = {};
     uint64_t fused_ops = 0, fused_batches = 0;
     uint64_t cache_hits = 0;
+    uint64_t postponed = 0; // operations parked until their match_id was named
 };
 coll_stats& stats();
 

@@ -69,7 +69,12 @@ uint64_t host_comm::next_sched_id(bool internal) {
     const uint64_t half = atl_tag::MAX_SCHED / 2;
     if (internal)
         return half + (int_sched_++ % (half - 8));
-    return ext_sched_++ % half;
+    return ext_sched_++ % (half - atl_tag::UNORDERED_SPAN);
+}
+
+uint64_t host_comm::unordered_sched_id(uint64_t k) const {
+    CCL_THROW_IF_NOT(k < atl_tag::UNORDERED_SPAN, "too many distinct match_ids on one communicator");
+    return atl_tag::MAX_SCHED / 2 - atl_tag::UNORDERED_SPAN + k;
 }
 
 std::shared_ptr<host_comm> host_comm::split(int color, int key) {

@@ -40,6 +40,10 @@ public:
     // schedule ids: external half for user operations, internal half for operations
     // the library issues itself (fusion, unordered coordination)
     uint64_t next_sched_id(bool internal = false);
+    // id of the k-th match_id named by the coordinator of unordered collectives
+    uint64_t unordered_sched_id(uint64_t k) const;
+    // state the collective front-end keeps per communicator (unordered coordination)
+    std::shared_ptr<void> frontend_state;
     std::shared_ptr<host_comm> split(int color, int key);
     std::shared_ptr<host_comm> node_comm();
     std::shared_ptr<host_comm> r2r_comm();

@@ -613,6 +613,14 @@ void executor::wait(master_sched* m, uint64_t ticket) {
         CCL_THROW("collective failed: ", m->req().error());
 }
 
+void executor::progress() {
+    if (!env_data::get().worker_offload)
+        for (auto& w : workers_)
+            w->do_work();
+    else
+        std::this_thread::yield();
+}
+
 void executor::lock_workers() {
     freeze_mu_.lock();
     frozen_.store(true, std::memory_order_release);

@@ -223,6 +223,8 @@ private:
 class executor {
 public:
     static executor& get();
+    // lets the calling thread drive the schedules when there are no worker threads
+    void progress();
     void ensure_started(std::shared_ptr<atl_transport> tr);
     void shutdown();
     int worker_count() const { return (int)workers_.size(); }

@@ -40,6 +40,10 @@ struct atl_tag {
     static constexpr uint64_t PT2PT_SCHED = MAX_SCHED;
     static constexpr uint64_t PT2PT_ACK_SCHED = MAX_SCHED - 1;
     static constexpr uint64_t INTERNAL_SCHED = MAX_SCHED - 2;
+    // coordination messages of unordered collectives (op_id = coordination round)
+    static constexpr uint64_t UNORDERED_SCHED = MAX_SCHED - 3;
+    // the top of the external half of the schedule ids names operations by match_id
+    static constexpr uint64_t UNORDERED_SPAN = 1u << 20;
 };
 
 // process-wide mesh of connections among the ranks of one "world" (one KVS rendezvous)

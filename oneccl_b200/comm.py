@@ -365,7 +365,7 @@ def group_end():
 
 
 def stats(which: str, coll: str = "allreduce") -> int:
-    idx = {"calls": 0, "device_calls": 1, "fused_ops": 2, "fused_batches": 3, "cache_hits": 4}[which]
+    idx = {"calls": 0, "device_calls": 1, "fused_ops": 2, "fused_batches": 3, "cache_hits": 4, "postponed": 5}[which]
     return int(_lib.load().cclx_stats(idx, COLL[coll]))
 
 

@@ -156,3 +156,43 @@ def _hang_child(rank, addr_file, q):
     q.close()
     q.join_thread()
     os._exit(0)
+
+
+def _unordered(comm):
+    from oneccl_b200.comm import stats
+
+    W, r = comm.size, comm.rank
+    names = [f"grad.{i}" for i in range(7)]
+    n = 3000
+    xs = {m: np.full(n + i, (r + 1.0) * (i + 1), np.float32) for i, m in enumerate(names)}
+    ys = {m: np.zeros_like(xs[m]) for m in names}
+    # every rank issues the operations in its own order, and waits in yet another one
+    order = np.random.RandomState(100 + r).permutation(len(names))
+    evs = {}
+    for i in order:
+        m = names[i]
+        evs[m] = comm.allreduce(xs[m], ys[m], match_id=m, to_cache=bool(i % 2))
+    for i in np.random.RandomState(200 + r).permutation(len(names)):
+        evs[names[i]].wait()
+    for i, m in enumerate(names):
+        assert np.all(ys[m] == (i + 1) * W * (W + 1) / 2), m
+    # a second pass reuses the names without coordination; allgatherv shares the mechanism
+    for i in reversed(order):
+        m = names[i]
+        ys[m][:] = 0
+        evs[m] = comm.allreduce(xs[m], ys[m], match_id=m, to_cache=bool(i % 2))
+    g = np.zeros(4 * W, np.int32)
+    ge = comm.allgatherv(np.full(4, r, np.int32), g, [4] * W, match_id="gather")
+    for m in names:
+        evs[m].wait()
+        assert np.all(ys[m] == (names.index(m) + 1) * W * (W + 1) / 2), m
+    ge.wait()
+    assert np.all(g == np.repeat(np.arange(W), 4))
+    return stats("postponed")
+
+
+@pytest.mark.parametrize("env", [{}, {"CCL_WORKER_OFFLOAD": "0"}, {"CCL_WORKER_COUNT": "2"}])
+def test_unordered_collectives_match_by_name(env):
+    env = dict(env, CCL_UNORDERED_COLL="1")
+    postponed = run_ranks(_unordered, 3, env=env)
+    assert postponed[0] == 0  # the coordinator never parks an operation
