@@ -7,15 +7,25 @@
 // address table is the list of "<ip>:<port>" strings published in the KVS, the
 // higher rank of a pair dials the lower one, and a 16-byte header (tag, length)
 // frames every message so that a receive posted later still matches.
+//
+// Pairs of ranks on one host talk through shared memory instead (the reference's
+// shm provider, src/atl/ofi/atl_ofi_helper.cpp:1040-1393 picks "shm" beside the
+// network provider): every rank owns a POSIX shared-memory segment with one
+// single-producer / single-consumer byte ring per (endpoint, sender).  A ring
+// carries the same framed byte stream as a socket, so the matching logic is
+// shared; only the two functions that move bytes differ.
 #include <arpa/inet.h>
 #include <fcntl.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
 #include <sys/epoll.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
 #include <sys/socket.h>
 #include <unistd.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <deque>
 #include <list>
@@ -56,8 +66,50 @@ struct unexpected_msg {
     bool complete = false;
 };
 
+// single-producer / single-consumer byte ring in shared memory
+struct shm_ring {
+    alignas(64) std::atomic<uint64_t> head; // bytes written so far (producer)
+    alignas(64) std::atomic<uint64_t> tail; // bytes read so far (consumer)
+    alignas(64) char data[1];
+
+    static size_t footprint(size_t cap) { return offsetof(shm_ring, data) + cap; }
+
+    size_t write(const void* src, size_t n, size_t cap) {
+        const uint64_t h = head.load(std::memory_order_relaxed);
+        const uint64_t t = tail.load(std::memory_order_acquire);
+        const size_t room = cap - (size_t)(h - t);
+        n = std::min(n, room);
+        if (n == 0)
+            return 0;
+        const size_t pos = (size_t)(h & (cap - 1));
+        const size_t first = std::min(n, cap - pos);
+        std::memcpy(data + pos, src, first);
+        std::memcpy(data, (const char*)src + first, n - first);
+        head.store(h + n, std::memory_order_release);
+        return n;
+    }
+    size_t read(void* dst, size_t n, size_t cap) {
+        const uint64_t t = tail.load(std::memory_order_relaxed);
+        const uint64_t h = head.load(std::memory_order_acquire);
+        n = std::min(n, (size_t)(h - t));
+        if (n == 0)
+            return 0;
+        const size_t pos = (size_t)(t & (cap - 1));
+        const size_t first = std::min(n, cap - pos);
+        std::memcpy(dst, data + pos, first);
+        std::memcpy((char*)dst + first, data, n - first);
+        tail.store(t + n, std::memory_order_release);
+        return n;
+    }
+    bool readable() const {
+        return head.load(std::memory_order_acquire) != tail.load(std::memory_order_relaxed);
+    }
+};
+
 struct peer_state {
     int fd = -1;
+    shm_ring* tx = nullptr; // ring in the peer's segment that this rank fills
+    shm_ring* rx = nullptr; // ring in this rank's segment that the peer fills
     std::deque<out_msg> outq;
     // incoming
     wire_header in_hdr{};
@@ -73,6 +125,7 @@ struct peer_state {
 
 struct endpoint {
     std::vector<peer_state> peers;
+    std::vector<int> shm_peers;
     std::mutex mu;
     int epfd = -1;
 };
@@ -156,9 +209,12 @@ public:
             ep.peers.resize(size_);
             ep.epfd = epoll_create1(EPOLL_CLOEXEC);
         }
-        // dial every lower rank, once per endpoint
+        setup_shm(pm, ep_count);
+        // dial every lower rank that is not reached through shared memory, once per endpoint
         for (int e = 0; e < ep_count; e++) {
             for (int p = 0; p < rank_; p++) {
+                if (eps_[e].peers[p].tx)
+                    continue;
                 int fd = ::socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
                 sockaddr_in d{};
                 d.sin_family = AF_INET;
@@ -177,7 +233,10 @@ public:
             }
         }
         // accept every higher rank
-        const int expect = (size_ - 1 - rank_) * ep_count;
+        int expect = 0;
+        for (int p = rank_ + 1; p < size_; p++)
+            if (!eps_[0].peers[p].tx)
+                expect += ep_count;
         for (int i = 0; i < expect; i++) {
             int fd = ::accept4(lfd, nullptr, nullptr, SOCK_CLOEXEC);
             CCL_THROW_IF_NOT(fd >= 0, "accept failed: ", std::strerror(errno));
@@ -190,7 +249,7 @@ public:
         ::close(lfd);
         for (auto& ep : eps_) {
             for (int p = 0; p < size_; p++) {
-                if (p == rank_)
+                if (p == rank_ || ep.peers[p].tx)
                     continue;
                 set_nonblock(ep.peers[p].fd);
                 epoll_event ev{};
@@ -200,7 +259,8 @@ public:
             }
         }
         pm.barrier();
-        LOG_DEBUG("tcp transport up: rank ", rank_, "/", size_, ", endpoints ", ep_count);
+        LOG_DEBUG("mesh transport up: rank ", rank_, "/", size_, ", endpoints ", ep_count, ", shared-memory peers ",
+                  eps_[0].shm_peers.size());
     }
 
     ~tcp_transport() override {
@@ -211,13 +271,15 @@ public:
             if (ep.epfd >= 0)
                 ::close(ep.epfd);
         }
+        for (auto& m : maps_)
+            ::munmap(m.first, m.second);
     }
 
     int world_rank() const override { return rank_; }
     int world_size() const override { return size_; }
     int ep_count() const override { return (int)eps_.size(); }
     bool same_host(int peer) const override { return same_host_[peer]; }
-    const char* name() const override { return "tcp"; }
+    const char* name() const override { return eps_[0].shm_peers.empty() ? "tcp" : "shm+tcp"; }
 
     void send(int e, const void* buf, size_t len, int dst, uint64_t tag, atl_req* req) override {
         endpoint& ep = eps_[e];
@@ -290,6 +352,122 @@ public:
     }
 
 private:
+    static size_t ring_stride(size_t cap) { return (shm_ring::footprint(cap) + 4095) & ~(size_t)4095; }
+    shm_ring* ring_at(void* seg, int e, int sender) const {
+        return (shm_ring*)((char*)seg + ((size_t)e * size_ + sender) * ring_stride(ring_cap_));
+    }
+
+    // Shared-memory links to the ranks of this host.  Every rank creates its own segment (the rings
+    // it reads from), all ranks agree that creation worked everywhere, then map one another's.
+    void setup_shm(pmi& pm, int ep_count) {
+        const env_data& env = env_data::get();
+        int local_peers = 0;
+        for (int r = 0; r < size_; r++)
+            local_peers += (r != rank_ && same_host_[r]) ? 1 : 0;
+        const bool want = (env.atl_shm || env.atl_transport == atl_transport_t::shm) && size_ > 1;
+        ring_cap_ = 64 * 1024;
+        while (ring_cap_ * 2 <= env.atl_shm_ring_bytes)
+            ring_cap_ *= 2;
+        const size_t seg_bytes = (size_t)ep_count * size_ * ring_stride(ring_cap_);
+        struct info {
+            int ok;
+            char name[60];
+        } mine{}, zero{};
+        void* my_seg = nullptr;
+        if (want && local_peers > 0) {
+            std::snprintf(mine.name, sizeof(mine.name), "/cclx-%d-%d-%llx", (int)getpid(), rank_,
+                          (unsigned long long)std::hash<std::string>()(pm.ns()) & 0xffffffffull);
+            int fd = ::shm_open(mine.name, O_CREAT | O_EXCL | O_RDWR | O_CLOEXEC, 0600);
+            if (fd >= 0) {
+                if (::ftruncate(fd, (off_t)seg_bytes) == 0) {
+                    my_seg = ::mmap(nullptr, seg_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+                    if (my_seg == MAP_FAILED)
+                        my_seg = nullptr;
+                }
+                ::close(fd);
+                if (!my_seg)
+                    ::shm_unlink(mine.name);
+            }
+            mine.ok = my_seg ? 1 : 0;
+            if (!my_seg)
+                LOG_WARN("shared-memory segment could not be created (", std::strerror(errno), "): sockets only");
+        }
+        else
+            mine.ok = want ? 1 : 0; // nothing to create, nothing against it
+        std::vector<info> all(size_, zero);
+        pm.allgather(&mine, all.data(), sizeof(info));
+        bool everyone = want;
+        for (auto& i : all)
+            everyone = everyone && i.ok;
+        if (my_seg)
+            maps_.push_back({ my_seg, seg_bytes });
+        if (everyone && my_seg) {
+            for (int p = 0; p < size_; p++) {
+                if (p == rank_ || !same_host_[p])
+                    continue;
+                int fd = ::shm_open(all[p].name, O_RDWR | O_CLOEXEC, 0600);
+                CCL_THROW_IF_NOT(fd >= 0, "can not open the shared-memory segment of rank ", p, ": ",
+                                 std::strerror(errno));
+                void* seg = ::mmap(nullptr, seg_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+                ::close(fd);
+                CCL_THROW_IF_NOT(seg != MAP_FAILED, "can not map the shared-memory segment of rank ", p);
+                maps_.push_back({ seg, seg_bytes });
+                for (int e = 0; e < ep_count; e++) {
+                    eps_[e].peers[p].tx = ring_at(seg, e, rank_);
+                    eps_[e].peers[p].rx = ring_at(my_seg, e, p);
+                    eps_[e].shm_peers.push_back(p);
+                }
+            }
+        }
+        pm.barrier(); // every mapping exists: the names can go, the memory stays until the last unmap
+        if (my_seg)
+            ::shm_unlink(mine.name);
+    }
+
+    // bytes moved (0 = would block); throws on a broken socket
+    size_t link_write(peer_state& ps, const void* a, size_t na, const void* b, size_t nb) {
+        if (ps.tx) {
+            size_t w = ps.tx->write(a, na, ring_cap_);
+            if (w == na && nb)
+                w += ps.tx->write(b, nb, ring_cap_);
+            return w;
+        }
+        for (;;) {
+            iovec iov[2];
+            iov[0].iov_base = const_cast<void*>(a);
+            iov[0].iov_len = na;
+            iov[1].iov_base = const_cast<void*>(b);
+            iov[1].iov_len = nb;
+            msghdr mh{};
+            mh.msg_iov = iov;
+            mh.msg_iovlen = nb ? 2 : 1;
+            ssize_t r = ::sendmsg(ps.fd, &mh, MSG_NOSIGNAL);
+            if (r >= 0)
+                return (size_t)r;
+            if (errno == EAGAIN || errno == EWOULDBLOCK)
+                return 0;
+            if (errno == EINTR)
+                continue;
+            CCL_THROW("tcp transport: send failed: ", std::strerror(errno));
+        }
+    }
+    size_t link_read(peer_state& ps, void* dst, size_t n) {
+        if (ps.rx)
+            return ps.rx->read(dst, n, ring_cap_);
+        for (;;) {
+            ssize_t r = ::recv(ps.fd, dst, n, 0);
+            if (r > 0)
+                return (size_t)r;
+            if (r == 0)
+                return 0; // peer closed; pending operations time out at a higher level
+            if (errno == EAGAIN || errno == EWOULDBLOCK)
+                return 0;
+            if (errno == EINTR)
+                continue;
+            CCL_THROW("tcp transport: recv failed: ", std::strerror(errno));
+        }
+    }
+
     void deliver_local(peer_state& ps, const char* buf, size_t len, uint64_t tag) {
         for (auto it = ps.posted.begin(); it != ps.posted.end(); ++it) {
             if (it->tag == tag) {
@@ -314,30 +492,16 @@ private:
             out_msg& m = ps.outq.front();
             const size_t total = sizeof(wire_header) + m.hdr.len;
             while (m.sent < total) {
-                ssize_t r;
-                if (m.sent < sizeof(wire_header)) {
-                    iovec iov[2];
-                    iov[0].iov_base = (char*)&m.hdr + m.sent;
-                    iov[0].iov_len = sizeof(wire_header) - m.sent;
-                    iov[1].iov_base = const_cast<char*>(m.payload);
-                    iov[1].iov_len = m.hdr.len;
-                    msghdr mh{};
-                    mh.msg_iov = iov;
-                    mh.msg_iovlen = m.hdr.len ? 2 : 1;
-                    r = ::sendmsg(ps.fd, &mh, MSG_NOSIGNAL);
-                }
+                size_t w;
+                if (m.sent < sizeof(wire_header))
+                    w = link_write(ps, (char*)&m.hdr + m.sent, sizeof(wire_header) - m.sent, m.payload, m.hdr.len);
                 else {
                     const size_t off = m.sent - sizeof(wire_header);
-                    r = ::send(ps.fd, m.payload + off, m.hdr.len - off, MSG_NOSIGNAL);
+                    w = link_write(ps, m.payload + off, m.hdr.len - off, nullptr, 0);
                 }
-                if (r < 0) {
-                    if (errno == EAGAIN || errno == EWOULDBLOCK)
-                        return;
-                    if (errno == EINTR)
-                        continue;
-                    CCL_THROW("tcp transport: send failed: ", std::strerror(errno));
-                }
-                m.sent += (size_t)r;
+                if (w == 0)
+                    return;
+                m.sent += w;
             }
             m.req->done.store(1, std::memory_order_release);
             ps.outq.pop_front();
@@ -362,17 +526,10 @@ private:
     void drain(peer_state& ps) {
         for (;;) {
             if (!ps.in_body) {
-                ssize_t r = ::recv(ps.fd, (char*)&ps.in_hdr + ps.hdr_got, sizeof(wire_header) - ps.hdr_got, 0);
-                if (r < 0) {
-                    if (errno == EAGAIN || errno == EWOULDBLOCK)
-                        return;
-                    if (errno == EINTR)
-                        continue;
-                    CCL_THROW("tcp transport: recv failed: ", std::strerror(errno));
-                }
+                const size_t r = link_read(ps, (char*)&ps.in_hdr + ps.hdr_got, sizeof(wire_header) - ps.hdr_got);
                 if (r == 0)
-                    return; // peer closed; pending operations will time out at a higher level
-                ps.hdr_got += (size_t)r;
+                    return;
+                ps.hdr_got += r;
                 if (ps.hdr_got < sizeof(wire_header))
                     continue;
                 // header complete: find where the body goes
@@ -407,17 +564,10 @@ private:
                     continue;
                 }
             }
-            ssize_t r = ::recv(ps.fd, ps.in_dst + ps.in_got, ps.in_hdr.len - ps.in_got, 0);
-            if (r < 0) {
-                if (errno == EAGAIN || errno == EWOULDBLOCK)
-                    return;
-                if (errno == EINTR)
-                    continue;
-                CCL_THROW("tcp transport: recv failed: ", std::strerror(errno));
-            }
+            const size_t r = link_read(ps, ps.in_dst + ps.in_got, ps.in_hdr.len - ps.in_got);
             if (r == 0)
                 return;
-            ps.in_got += (size_t)r;
+            ps.in_got += r;
             if (ps.in_got == ps.in_hdr.len)
                 finish_incoming(ps);
         }
@@ -427,6 +577,11 @@ private:
         for (auto& ps : ep.peers)
             if (!ps.outq.empty())
                 flush(ps);
+        for (int p : ep.shm_peers)
+            if (ep.peers[p].rx->readable())
+                drain(ep.peers[p]);
+        if (ep.shm_peers.size() + 1 == ep.peers.size())
+            return; // no socket on this endpoint
         epoll_event evs[64];
         int n = epoll_wait(ep.epfd, evs, 64, 0);
         for (int i = 0; i < n; i++)
@@ -436,6 +591,8 @@ private:
     int rank_, size_;
     std::vector<endpoint> eps_;
     std::vector<char> same_host_;
+    size_t ring_cap_ = 0;
+    std::vector<std::pair<void*, size_t>> maps_;
 };
 
 } // namespace

@@ -28,8 +28,12 @@ def _cfg1(comm):
     return errs
 
 
-def test_baseline_config1_world2():
-    for errs in run_ranks(_cfg1, 2):
+@pytest.mark.parametrize("env", [{}, {"CCL_ATL_SHM": "0"}, {"CCL_ATL_SHM_RING_BYTES": "65536"}],
+                         ids=["shm", "sockets", "small-rings"])
+def test_baseline_config1_world2(env):
+    """fp32 sum allreduce at 1 / 17 / 4096 / 1M elements, allgatherv with unequal counts, barrier:
+    over the shared-memory rings, over sockets only, and with rings smaller than the messages."""
+    for errs in run_ranks(_cfg1, 2, env=env):
         assert max(errs) < 1e-5
 
 
@@ -130,6 +134,7 @@ def test_other_collectives_default_algorithms(world):
     {"CCL_ALLGATHERV": "multi_bcast", "CCL_ALLGATHER": "flat", "CCL_BCAST": "naive", "CCL_BROADCAST": "ring",
      "CCL_REDUCE": "ring", "CCL_REDUCE_SCATTER": "direct", "CCL_WORKER_COUNT": "2"},
     {"CCL_REDUCE": "double_tree", "CCL_BCAST": "double_tree", "CCL_WORKER_OFFLOAD": "0"},
+    {"CCL_ATL_SHM": "0", "CCL_WORKER_COUNT": "2"},
 ])
 def test_other_collectives_algorithm_overrides(env):
     assert all(run_ranks(_others, 3, env=env))
