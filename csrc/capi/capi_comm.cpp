@@ -13,6 +13,7 @@
 #include "core/log.hpp"
 #include "fusion/fusion.hpp"
 #include "gpu/device_comm.hpp"
+#include "topo/numa.hpp"
 #include "topo/topo.hpp"
 
 using namespace cclx;
@@ -342,6 +343,52 @@ CCLX_API int cclx_topo_describe(char* out, size_t cap) {
         std::string s = topo_info::local().describe();
         CCL_THROW_IF_NOT(s.size() + 1 <= cap, "buffer too small");
         std::memcpy(out, s.c_str(), s.size() + 1);
+    });
+}
+
+// NUMA helpers.  `sys_root` empty = this machine's sysfs.  Lists are returned as int arrays; the
+// return value is the number of entries (or -1).
+CCLX_API int cclx_numa_query(const char* sys_root, int what, int arg, const char* text, int* out, int cap) {
+    int n = -1;
+    int rc = capi::guard([&] {
+        numa_info custom(sys_root && sys_root[0] ? sys_root : "/sys");
+        const numa_info& ni = custom;
+        std::vector<int> v;
+        switch (what) {
+            case 0: v = { ni.node_count() }; break;
+            case 1: v = ni.cpus_of_node(arg); break;
+            case 2: v = { ni.node_of_cpu(arg) }; break;
+            case 3: v = { ni.node_of_pci(text ? text : "") }; break;
+            case 4: v = numa_info::parse_cpulist(text ? text : ""); break;
+            case 5: v = ni.allowed_cpus(); break;
+            default: CCL_THROW("unknown numa query ", what);
+        }
+        n = (int)std::min<size_t>(v.size(), (size_t)cap);
+        for (int k = 0; k < n; k++)
+            out[k] = v[k];
+    });
+    return rc == 0 ? n : -1;
+}
+
+CCLX_API int cclx_numa_auto_worker_cpus(const int* cpus, int ncpus, int local_rank, int local_size, int workers,
+                                        int* out) {
+    std::vector<int> v = numa_info::auto_worker_cpus(std::vector<int>(cpus, cpus + ncpus), local_rank, local_size,
+                                                     workers);
+    for (size_t k = 0; k < v.size(); k++)
+        out[k] = v[k];
+    return (int)v.size();
+}
+
+// binds the calling thread's memory to `node`, allocates and touches a buffer there, restores the policy
+CCLX_API int cclx_numa_selftest(int node, size_t bytes) {
+    return capi::guard([&] {
+        const numa_info& ni = numa_info::get();
+        ni.bind_thread_memory(node);
+        void* p = ni.alloc_on_node(bytes, node);
+        CCL_THROW_IF_NOT(p, "allocation failed");
+        std::memset(p, 1, bytes);
+        ni.free_on_node(p, bytes);
+        ni.bind_thread_memory(-1);
     });
 }
 

@@ -206,6 +206,24 @@ CCLX_API int cclx_dc_alltoallv(void* h, const void* const* send, void* const* re
     });
 }
 
+// alltoall with one block size for every pair of ranks (bytes per peer)
+CCLX_API int cclx_dc_alltoall(void* h, const void* const* send, void* const* recv, size_t bytes_per_peer, int algo,
+                              int blocks, void* stream) {
+    return capi::guard([&] {
+        device_comm* dc = (device_comm*)h;
+        auto ra = make_ra(dc, send, recv);
+        const int W = dc->world();
+        for (size_t e = 0; e < ra.size(); e++)
+            for (int p = 0; p < W; p++) {
+                ra[e].scount[p] = ra[e].rcount[p] = bytes_per_peer;
+                ra[e].sdispl[p] = ra[e].rdispl[p] = (size_t)p * bytes_per_peer;
+            }
+        launch_opts o = make_opts(algo, blocks, 1.f, 0);
+        o.uniform = true;
+        launch_alltoallv(*dc, ra.data(), o, (cudaStream_t)stream);
+    });
+}
+
 CCLX_API int cclx_dc_broadcast(void* h, const void* const* send, void* const* recv, size_t bytes, int root, int blocks,
                                void* stream) {
     return capi::guard([&] {

@@ -14,6 +14,7 @@
 #include "core/datatype.hpp"
 #include "core/env.hpp"
 #include "core/log.hpp"
+#include "core/trace.hpp"
 #include "fusion/fusion.hpp"
 #include "gpu/cuda_driver.hpp"
 #include "gpu/device_comm.hpp"
@@ -509,6 +510,7 @@ event_ptr device_coll(host_comm& comm, coll_param& p, const coll_attr& attr) {
                 ra.rcount[q] = rc[q] * esz;
                 ra.rdispl[q] = ro[q] * esz;
             }
+            o.uniform = p.ctype == coll_alltoall;
             gpu::launch_alltoallv(*dc, &ra, o, st);
             break;
         }
@@ -800,6 +802,7 @@ event_ptr unordered_submit(host_comm& comm, const coll_param& p, const coll_attr
 event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr) {
     const env_data& env = env_data::get();
     coll_validate(comm, p, attr);
+    trace_range tr(1, coll_name(p.ctype), p.ctype == coll_barrier ? 0 : selection_bytes(comm, p));
     stats().calls[p.ctype]++;
     purge_recycle();
 

@@ -163,6 +163,27 @@ void env_data::parse() {
                            { "none", launcher_t::none } });
     get_int("CCL_LOCAL_RANK", local_rank);
     get_int("CCL_LOCAL_SIZE", local_size);
+    if (local_rank < 0 || local_size < 0) {
+        // what the launcher exports (reference src/common/global/global.cpp:182-220)
+        const char* lr = nullptr;
+        const char* ls = nullptr;
+        if (process_launcher == launcher_t::hydra) {
+            lr = std::getenv("MPI_LOCALRANKID");
+            ls = std::getenv("MPI_LOCALNRANKS");
+        }
+        else if (process_launcher == launcher_t::torchrun) {
+            lr = std::getenv("LOCAL_RANK");
+            ls = std::getenv("LOCAL_WORLD_SIZE");
+        }
+        else if (process_launcher == launcher_t::pmix) {
+            lr = std::getenv("PMIX_LOCAL_RANK");
+            ls = std::getenv("PMIX_LOCAL_SIZE");
+        }
+        if (lr && ls && local_rank < 0 && local_size < 0) {
+            local_rank = std::atoi(lr);
+            local_size = std::atoi(ls);
+        }
+    }
 
     get_int("CCL_WORKER_COUNT", worker_count);
     CCL_THROW_IF_NOT(worker_count >= 1 && worker_count <= 64, "CCL_WORKER_COUNT out of range");
@@ -171,6 +192,8 @@ void env_data::parse() {
     if (const char* s = std::getenv("CCL_WORKER_AFFINITY")) {
         if (lower(s) != "auto")
             worker_affinity = env_to_int_list(s);
+        else
+            worker_affinity_auto = true;
     }
     if (const char* s = std::getenv("CCL_WORKER_MEM_AFFINITY")) {
         if (lower(s) != "auto")
@@ -261,6 +284,8 @@ void env_data::parse() {
     get_int("CCL_CUDA_NVLS_MIN_RANKS", nvls_min_ranks);
     get_size("CCL_CUDA_ALLREDUCE_SMALL_THRESHOLD", ar_oneshot_threshold);
     get_size("CCL_CUDA_ALLREDUCE_MEDIUM_THRESHOLD", ar_twoshot_threshold);
+    get_size("CCL_CUDA_ALLREDUCE_PIPELINE_MIN", ar_pipelined_min);
+    get_int("CCL_CUDA_ALLREDUCE_PIPELINE_BLOCKS", ar_pipelined_blocks);
     get_size("CCL_CUDA_REDUCE_SCATTER_SMALL_THRESHOLD", rs_small_threshold);
     get_size("CCL_CUDA_ALLGATHERV_SMALL_THRESHOLD", ag_small_threshold);
     get_int("CCL_CUDA_MAX_BLOCKS", cuda_max_blocks);

@@ -46,7 +46,8 @@ struct env_data {
     int worker_count = 1;
     bool worker_offload = true;
     bool worker_wait = true;
-    std::vector<int> worker_affinity; // empty = auto (no pinning)
+    std::vector<int> worker_affinity; // explicit core per worker
+    bool worker_affinity_auto = false; // CCL_WORKER_AFFINITY=auto: cores from the end of the allowed set
     std::vector<int> worker_mem_affinity;
     int spin_count = 1000;
     yield_t yield = yield_t::pause;
@@ -112,13 +113,15 @@ struct env_data {
     bool cuda_kernels = true; // CCL_ENABLE_CUDA_KERNELS (reference CCL_ENABLE_SYCL_KERNELS)
     ipc_exchange_t ipc_exchange = ipc_exchange_t::sockets;
     size_t symm_heap_bytes = 1ull << 30; // peer-mapped heap per rank
-    size_t tmp_buf_bytes = 64ull << 20; // one staging generation; two generations are kept
+    size_t tmp_buf_bytes = 128ull << 20; // one staging generation; two generations are kept
     int nvls = -1; // -1 auto, 0 off, 1 force
     int nvls_min_ranks = 3; // communicators smaller than this use peer loads even when NVLS exists
     size_t ar_oneshot_threshold = 256u << 10; // <= : one-shot
     size_t ar_twoshot_threshold = 16u << 20; // <= : two-shot single launch; above: chunked
+    size_t ar_pipelined_min = 512u << 10; // >= : ordinary buffers take the chunk pipeline
+    int ar_pipelined_blocks = 64; // blocks of the chunk pipeline (few SMs: compute keeps the rest)
     size_t rs_small_threshold = 2u << 20;
-    size_t ag_small_threshold = 128u << 10;
+    size_t ag_small_threshold = 4u << 20; // per-rank block <= : push through staging; above: pull
     int cuda_max_blocks = 0; // 0 = auto (co-resident cap)
     int cuda_block_threads = 512;
     size_t wait_timeout_ms = 20000; // bound of every device-side wait

@@ -22,7 +22,8 @@ struct rank_args {
 enum : int {
     CF_SYMM_IN = 1, // send buffer lives in the symmetric heap (offset given in in_off)
     CF_SYMM_OUT = 2, // recv buffer lives in the symmetric heap (offset given in out_off)
-    CF_NVLS = 4 // use multimem instructions on the multicast window
+    CF_NVLS = 4, // use multimem instructions on the multicast window
+    CF_UNIFORM = 8 // equal 16-byte-multiple blocks at contiguous displacements, 16-byte aligned user buffers
 };
 
 struct coll_args {

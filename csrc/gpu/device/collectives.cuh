@@ -135,7 +135,10 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const comm_dev*
     CCLX_KERNEL_PROLOGUE();
     typedef typename acc_of<T>::type A;
     constexpr int N = pack_traits<T>::N;
-    constexpr size_t OUTP = (size_t)N * sizeof(Tout); // bytes of one reduced pack
+    constexpr size_t RAWP = (size_t)N * sizeof(Tout); // bytes of one reduced pack
+    constexpr size_t OUTP = RAWP < 16 ? 16 : RAWP; // staged in whole 16-byte units
+    constexpr int ON = (int)(OUTP / sizeof(Tout));
+    static_assert(RAWP >= 16 || RAWP == 8, "unexpected output pack size");
     const T* send = reinterpret_cast<const T*>(ra.send);
     Tout* recv = reinterpret_cast<Tout*>(ra.recv);
     const size_t count = a.count;
@@ -180,7 +183,7 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const comm_dev*
             }
             store_pack<Tout, A, N>(recv, mlo + i, count, vout, acc, a.scale, a.do_scale != 0);
             // reduced pack in output precision, pushed to the peers' OUT region
-            alignas(16) Tout o[N];
+            alignas(16) Tout o[ON] = {};
 #pragma unroll
             for (int k = 0; k < N; k++)
                 o[k] = from_acc<Tout, A>(a.do_scale ? apply_scale<A>(acc[k], a.scale) : acc[k]);
@@ -205,16 +208,20 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const comm_dev*
             for (size_t i = l2 + tid; i < h2; i += nt) {
                 const size_t e0 = (qlo + i) * N;
                 const char* src = outr + (qlo + i) * OUTP;
-                if (vout && e0 + N <= count) {
+                alignas(16) Tout o[ON];
 #pragma unroll
-                    for (int q2 = 0; q2 < (int)(OUTP / 16); q2++)
-                        reinterpret_cast<uint4*>(recv + e0)[q2] = ld_cv16(src + q2 * 16);
+                for (int q2 = 0; q2 < (int)(OUTP / 16); q2++)
+                    reinterpret_cast<uint4*>(o)[q2] = ld_cv16(src + q2 * 16);
+                if (vout && e0 + N <= count) {
+                    if constexpr (RAWP >= 16) {
+#pragma unroll
+                        for (int q2 = 0; q2 < (int)(OUTP / 16); q2++)
+                            reinterpret_cast<uint4*>(recv + e0)[q2] = reinterpret_cast<const uint4*>(o)[q2];
+                    }
+                    else
+                        *reinterpret_cast<uint2*>(recv + e0) = *reinterpret_cast<const uint2*>(o);
                 }
                 else {
-                    alignas(16) Tout o[N];
-#pragma unroll
-                    for (int q2 = 0; q2 < (int)(OUTP / 16); q2++)
-                        reinterpret_cast<uint4*>(o)[q2] = ld_cv16(src + q2 * 16);
 #pragma unroll
                     for (int k2 = 0; k2 < N; k2++)
                         if (e0 + k2 < count)
@@ -224,6 +231,150 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const comm_dev*
         }
     }
     sync_end(c, gridDim.x, 2, true);
+}
+
+// ---------------------------------------------------------------------------
+// pipelined allreduce through staging for large messages in ordinary (not
+// registered) buffers.  The message is cut into chunks; one staging generation
+// holds IN[2] and OUT[2] chunk buffers.  Iteration j of every block does
+//   A: copy its piece of chunk j   from send   into this rank's IN[j&1]
+//   B: reduce its share of chunk j-1 across the ranks (multimem.ld_reduce on
+//      the multicast window, or loads from every peer) and write the result
+//      into every rank's OUT[(j-1)&1] (multimem.st, or stores to every peer)
+//   C: copy its piece of chunk j-2 from OUT[(j-2)&1] into recv
+// and ends with one cross-GPU barrier, so the local copies of the neighbouring
+// chunks run under the NVLink traffic of the current one.  A chunk is divided
+// first among the blocks and then, inside a block's piece, among the ranks, so
+// that all data dependencies stay between blocks of equal index and the
+// per-block barrier is enough.  Same role as the three-stage pipeline of the
+// reference's allreduce_large_impl
+// (src/coll/algorithms/allreduce/sycl/allreduce_large_sycl_impl.hpp:234-684).
+// a.stride = packs per chunk (a multiple of gridDim.x * world).
+// staging need: 2*chunk*16 + 2*chunk*N*sizeof(Tout) <= staging_bytes
+// ---------------------------------------------------------------------------
+template <class T, class Tout, class Op, bool NVLS>
+__global__ void __launch_bounds__(1024) allreduce_pipelined_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    typedef typename acc_of<T>::type A;
+    constexpr int N = pack_traits<T>::N;
+    constexpr size_t RAWP = (size_t)N * sizeof(Tout); // bytes of one reduced pack
+    constexpr size_t OUTP = RAWP < 16 ? 16 : RAWP; // staged in whole 16-byte units
+    constexpr int OQ = (int)(OUTP / 16);
+    constexpr int ON = (int)(OUTP / sizeof(Tout));
+    static_assert(RAWP >= 16 || RAWP == 8, "unexpected output pack size");
+    const T* send = reinterpret_cast<const T*>(ra.send);
+    Tout* recv = reinterpret_cast<Tout*>(ra.recv);
+    const size_t count = a.count;
+    const size_t npacks = round_up16(count * sizeof(T)) >> 4;
+    const int W = c.world;
+    const size_t cp = a.stride;
+    const size_t nchunks = (npacks + cp - 1) / cp;
+    const size_t piece = cp / gridDim.x;
+    const size_t sub = piece / W;
+    const size_t gbase = (size_t)s.gen * c.staging_bytes;
+    const size_t out_base = gbase + 2 * cp * 16;
+    const bool vin = (((uintptr_t)send) & 15) == 0;
+    const bool vout = out_vec_ok<Tout, N>(recv);
+    const bool scale = a.do_scale != 0;
+    char* my_stage = c.staging[c.rank];
+    bool ok = true;
+
+    for (size_t j = 0; j < nchunks + 2; j++) {
+        if (j < nchunks) { // A
+            const size_t p0 = j * cp + blockIdx.x * piece;
+            char* dst = my_stage + gbase + (j & 1) * cp * 16 + blockIdx.x * piece * 16;
+            const size_t n = p0 < npacks ? min(piece, npacks - p0) : 0;
+            for (size_t i = tid; i < n; i += nt)
+                st16(dst + (i << 4), load_pack<T>(send, p0 + i, count, vin));
+        }
+        if (j >= 1 && j <= nchunks && ok) { // B
+            const size_t jj = j - 1;
+            const size_t q0 = blockIdx.x * piece + (size_t)c.rank * sub; // first pack of my share inside the chunk
+            const size_t p0 = jj * cp + q0;
+            const size_t n = p0 < npacks ? min(sub, npacks - p0) : 0;
+            const size_t in_off = gbase + (jj & 1) * cp * 16 + q0 * 16;
+            const size_t o_off = out_base + (jj & 1) * cp * OUTP + q0 * OUTP;
+            auto finish = [&](size_t i, A(&acc)[N]) {
+                alignas(16) Tout o[ON] = {};
+#pragma unroll
+                for (int k = 0; k < N; k++)
+                    o[k] = from_acc<Tout, A>(scale ? apply_scale<A>(acc[k], a.scale) : acc[k]);
+                if (NVLS) {
+#pragma unroll
+                    for (int q = 0; q < OQ; q++)
+                        multimem_st16(c.mc_staging + o_off + i * OUTP + q * 16, reinterpret_cast<const uint4*>(o)[q]);
+                }
+                else {
+                    for (int k = 0; k < W; k++) {
+                        char* dst = c.staging[(c.rank + k) % W] + o_off + i * OUTP;
+#pragma unroll
+                        for (int q = 0; q < OQ; q++)
+                            st16(dst + q * 16, reinterpret_cast<const uint4*>(o)[q]);
+                    }
+                }
+            };
+            if constexpr (NVLS) {
+                size_t i = tid;
+                for (; i + nt < n; i += 2 * nt) { // two switch round trips in flight per thread
+                    uint4 v0 = multimem_ld_reduce_add16<T>(c.mc_staging + in_off + (i << 4));
+                    uint4 v1 = multimem_ld_reduce_add16<T>(c.mc_staging + in_off + ((i + nt) << 4));
+                    A a0[N], a1[N];
+                    unpack16<T, A>(v0, a0);
+                    unpack16<T, A>(v1, a1);
+                    finish(i, a0);
+                    finish(i + nt, a1);
+                }
+                for (; i < n; i += nt) {
+                    A a0[N];
+                    unpack16<T, A>(multimem_ld_reduce_add16<T>(c.mc_staging + in_off + (i << 4)), a0);
+                    finish(i, a0);
+                }
+            }
+            else {
+                for (size_t i = tid; i < n; i += nt) {
+                    uint4 v[MAX_RANKS];
+                    for (int p = 0; p < W; p++) // fixed rank order: reproducible rounding
+                        v[p] = ld_cv16(c.staging[p] + in_off + (i << 4));
+                    A acc[N];
+                    unpack16<T, A>(v[0], acc);
+                    for (int p = 1; p < W; p++)
+                        accum16<T, A, Op>(v[p], acc);
+                    finish(i, acc);
+                }
+            }
+        }
+        if (j >= 2 && ok) { // C
+            const size_t jj = j - 2;
+            const size_t p0 = jj * cp + blockIdx.x * piece;
+            const size_t n = p0 < npacks ? min(piece, npacks - p0) : 0;
+            const char* src = my_stage + out_base + (jj & 1) * cp * OUTP + blockIdx.x * piece * OUTP;
+            for (size_t i = tid; i < n; i += nt) {
+                const size_t e0 = (p0 + i) * N;
+                alignas(16) Tout o[ON];
+#pragma unroll
+                for (int q = 0; q < OQ; q++)
+                    reinterpret_cast<uint4*>(o)[q] = ld_cv16(src + i * OUTP + q * 16);
+                if (vout && e0 + N <= count) {
+                    if constexpr (RAWP >= 16) {
+#pragma unroll
+                        for (int q = 0; q < OQ; q++)
+                            reinterpret_cast<uint4*>(recv + e0)[q] = reinterpret_cast<const uint4*>(o)[q];
+                    }
+                    else
+                        *reinterpret_cast<uint2*>(recv + e0) = *reinterpret_cast<const uint2*>(o);
+                }
+                else {
+#pragma unroll
+                    for (int k = 0; k < N; k++)
+                        if (e0 + k < count)
+                            recv[e0 + k] = o[k];
+                }
+            }
+        }
+        if (j <= nchunks)
+            ok = peer_barrier(c, s);
+    }
+    sync_end(c, gridDim.x, (uint32_t)(nchunks + 1), true);
 }
 
 // ---------------------------------------------------------------------------
@@ -458,25 +609,47 @@ __global__ void __launch_bounds__(1024) allgatherv_kernel(const comm_dev* tab, c
             myoff += round_up16(ra.scount[p]);
         split_range((mybytes + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
         const size_t blo = lo << 4, bhi = (hi << 4) < mybytes ? (hi << 4) : mybytes;
+        const bool nvls = (a.flags & CF_NVLS) != 0;
+        const bool uniform = (a.flags & CF_UNIFORM) != 0;
         if (bhi > blo) {
-            for (int k = 1; k < W; k++) {
-                const int p = (c.rank + k) % W;
-                block_copy<false>(c.staging[p] + gbase + myoff + blo, send + blo, bhi - blo);
+            // read once, store to every peer (one multimem.st reaches all of them)
+            const unsigned char* sb = reinterpret_cast<const unsigned char*>(send);
+            const bool vin = (((uintptr_t)send) & 15) == 0;
+            for (size_t i = lo + tid; i < hi; i += nt) {
+                const uint4 v = load_pack<unsigned char>(sb, i, mybytes, vin);
+                if (nvls)
+                    multimem_st16(c.mc_staging + gbase + myoff + (i << 4), v);
+                else
+                    for (int k = 1; k < W; k++)
+                        st16(c.staging[(c.rank + k) % W] + gbase + myoff + (i << 4), v);
             }
             if (send != recv + ra.sdispl[c.rank])
                 block_copy<false>(recv + ra.sdispl[c.rank] + blo, send + blo, bhi - blo);
         }
         if (peer_barrier(c, s)) {
-            size_t off = 0;
-            for (int p = 0; p < W; p++) {
-                const size_t pb = ra.scount[p];
-                if (p != c.rank) {
-                    split_range((pb + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
-                    const size_t l = lo << 4, h = (hi << 4) < pb ? (hi << 4) : pb;
-                    if (h > l)
-                        block_copy<true>(recv + ra.sdispl[p] + l, c.staging[c.rank] + gbase + off + l, h - l);
+            if (uniform) {
+                // equal aligned blocks: one pass with the loads of all peers in flight together
+                const char* st = c.staging[c.rank] + gbase;
+                for (size_t i = lo + tid; i < hi; i += nt) {
+                    uint4 v[MAX_RANKS];
+                    for (int k = 1; k < W; k++)
+                        v[k] = ld_cv16(st + (size_t)((c.rank + k) % W) * mybytes + (i << 4));
+                    for (int k = 1; k < W; k++)
+                        *reinterpret_cast<uint4*>(recv + (size_t)((c.rank + k) % W) * mybytes + (i << 4)) = v[k];
                 }
-                off += round_up16(pb);
+            }
+            else {
+                size_t off = 0;
+                for (int p = 0; p < W; p++) {
+                    const size_t pb = ra.scount[p];
+                    if (p != c.rank) {
+                        split_range((pb + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+                        const size_t l = lo << 4, h = (hi << 4) < pb ? (hi << 4) : pb;
+                        if (h > l)
+                            block_copy<true>(recv + ra.sdispl[p] + l, c.staging[c.rank] + gbase + off + l, h - l);
+                    }
+                    off += round_up16(pb);
+                }
             }
         }
         sync_end(c, gridDim.x, 1, true);
@@ -559,25 +732,45 @@ static __global__ void __launch_bounds__(1024) alltoallv_kernel(const comm_dev* 
         const uint32_t g = (s.gen + rounds) & 1u;
         const size_t gbase = (size_t)g * c.staging_bytes;
         bool more = false;
-        for (int k = 0; k < W; k++) {
-            const int q = (c.rank + k) % W;
-            size_t b = ra.scount[q] > round_off ? ra.scount[q] - round_off : 0;
-            if (b > slot) {
-                b = slot;
+        const bool uniform = (a.flags & CF_UNIFORM) != 0;
+        if (uniform) {
+            // equal aligned blocks: the loads for all peers are in flight together
+            const size_t b = ra.scount[0];
+            size_t rb = b > round_off ? b - round_off : 0;
+            if (rb > slot) {
+                rb = slot;
                 more = true;
             }
-            if (ra.rcount[q] > round_off + slot)
-                more = true;
-            split_range((b + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
-            const size_t l = lo << 4, h = (hi << 4) < b ? (hi << 4) : b;
-            if (h > l) {
-                const char* src = send + ra.sdispl[q] + round_off + l;
-                if (q == c.rank)
-                    block_copy<false>(recv + ra.rdispl[q] + round_off + l, src, h - l);
-                else
-                    block_copy<false>(c.staging[q] + gbase + (size_t)c.rank * slot + l, src, h - l);
+            split_range(rb >> 4, gridDim.x, blockIdx.x, lo, hi);
+            for (size_t i = lo + tid; i < hi; i += nt) {
+                uint4 v[MAX_RANKS];
+                for (int k = 0; k < W; k++)
+                    v[k] = *reinterpret_cast<const uint4*>(send + (size_t)((c.rank + k) % W) * b + round_off + (i << 4));
+                *reinterpret_cast<uint4*>(recv + (size_t)c.rank * b + round_off + (i << 4)) = v[0];
+                for (int k = 1; k < W; k++)
+                    st16(c.staging[(c.rank + k) % W] + gbase + (size_t)c.rank * slot + (i << 4), v[k]);
             }
         }
+        else
+            for (int k = 0; k < W; k++) {
+                const int q = (c.rank + k) % W;
+                size_t b = ra.scount[q] > round_off ? ra.scount[q] - round_off : 0;
+                if (b > slot) {
+                    b = slot;
+                    more = true;
+                }
+                if (ra.rcount[q] > round_off + slot)
+                    more = true;
+                split_range((b + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+                const size_t l = lo << 4, h = (hi << 4) < b ? (hi << 4) : b;
+                if (h > l) {
+                    const char* src = send + ra.sdispl[q] + round_off + l;
+                    if (q == c.rank)
+                        block_copy<false>(recv + ra.rdispl[q] + round_off + l, src, h - l);
+                    else
+                        block_copy<false>(c.staging[q] + gbase + (size_t)c.rank * slot + l, src, h - l);
+                }
+            }
         const size_t hdr = ((size_t)g * MAX_BLOCKS + blockIdx.x) * MAX_RANKS;
         if (tid < (size_t)W)
             c.aux[tid][hdr + c.rank] = more ? 1u : 0u;
@@ -585,17 +778,32 @@ static __global__ void __launch_bounds__(1024) alltoallv_kernel(const comm_dev* 
             rounds++;
             break;
         }
-        for (int k = 1; k < W; k++) {
-            const int p = (c.rank + k) % W;
-            size_t b = ra.rcount[p] > round_off ? ra.rcount[p] - round_off : 0;
-            if (b > slot)
-                b = slot;
-            split_range((b + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
-            const size_t l = lo << 4, h = (hi << 4) < b ? (hi << 4) : b;
-            if (h > l)
-                block_copy<true>(recv + ra.rdispl[p] + round_off + l,
-                                 c.staging[c.rank] + gbase + (size_t)p * slot + l, h - l);
+        if (uniform) {
+            const size_t b = ra.scount[0];
+            size_t rb = b > round_off ? b - round_off : 0;
+            rb = rb > slot ? slot : rb;
+            split_range(rb >> 4, gridDim.x, blockIdx.x, lo, hi);
+            const char* st = c.staging[c.rank] + gbase;
+            for (size_t i = lo + tid; i < hi; i += nt) {
+                uint4 v[MAX_RANKS];
+                for (int k = 1; k < W; k++)
+                    v[k] = ld_cv16(st + (size_t)((c.rank + k) % W) * slot + (i << 4));
+                for (int k = 1; k < W; k++)
+                    *reinterpret_cast<uint4*>(recv + (size_t)((c.rank + k) % W) * b + round_off + (i << 4)) = v[k];
+            }
         }
+        else
+            for (int k = 1; k < W; k++) {
+                const int p = (c.rank + k) % W;
+                size_t b = ra.rcount[p] > round_off ? ra.rcount[p] - round_off : 0;
+                if (b > slot)
+                    b = slot;
+                split_range((b + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
+                const size_t l = lo << 4, h = (hi << 4) < b ? (hi << 4) : b;
+                if (h > l)
+                    block_copy<true>(recv + ra.rdispl[p] + round_off + l,
+                                     c.staging[c.rank] + gbase + (size_t)p * slot + l, h - l);
+            }
         if (tid == 0) {
             uint32_t m = 0;
             for (int p = 0; p < W; p++)
@@ -610,6 +818,32 @@ static __global__ void __launch_bounds__(1024) alltoallv_kernel(const comm_dev* 
             break;
     }
     sync_end(c, gridDim.x, rounds, rounds);
+}
+
+// alltoall with equal blocks into a symmetric recv buffer: every rank stores block q of its send
+// buffer straight into rank q's recv (at the place of the sender), no staging and no second copy.
+// a.count = bytes per peer (multiple of 16); send is 16-byte aligned and distinct from recv.
+static __global__ void __launch_bounds__(1024) alltoall_symm_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    const int W = c.world;
+    const size_t b = a.count;
+    const char* send = reinterpret_cast<const char*>(ra.send);
+    size_t lo, hi;
+    split_range(b >> 4, gridDim.x, blockIdx.x, lo, hi);
+    // peers must have finished reading the previous contents of recv
+    bool ok = peer_barrier(c, s);
+    if (ok) {
+        const size_t doff = a.out_off + (size_t)c.rank * b;
+        for (size_t i = lo + tid; i < hi; i += nt) {
+            uint4 v[MAX_RANKS];
+            for (int k = 0; k < W; k++)
+                v[k] = *reinterpret_cast<const uint4*>(send + (size_t)((c.rank + k) % W) * b + (i << 4));
+            for (int k = 0; k < W; k++)
+                st16(c.heap[(c.rank + k) % W] + doff + (i << 4), v[k]);
+        }
+    }
+    peer_barrier(c, s);
+    sync_end(c, gridDim.x, 2, false);
 }
 
 // ---------------------------------------------------------------------------

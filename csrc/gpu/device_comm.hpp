@@ -33,6 +33,7 @@ enum gpu_algo : int {
     ga_push, // allgather: push into peers' staging
     ga_pull, // allgather: pull from peers' staging
     ga_copy, // single rank / local copy
+    ga_pipelined, // allreduce: chunk pipeline through staging (copy in | reduce + broadcast | copy out)
     ga_last
 };
 const char* gpu_algo_name(int a);
@@ -109,6 +110,9 @@ struct launch_opts {
     int blocks = 0; // 0 = automatic
     float scale = 1.0f;
     bool do_scale = false;
+    // alltoall: every rank passes the same single block size (lets the grid follow the size and
+    // enables the direct path into symmetric buffers)
+    bool uniform = false;
 };
 
 void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, int dt_in, int dt_out, int op,

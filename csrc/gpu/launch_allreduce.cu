@@ -41,7 +41,8 @@ int selected_allreduce_algo(const device_comm& dc, size_t bytes, bool symmetric,
     // in-switch reduction moves (1 + 1/n) S per direction, peer loads 2 (n-1)/n S: NVLS wins from 3 ranks on
     if (symmetric)
         return (dc.nvls() && nvls_type_ok(dt, op) && dc.world() >= env.nvls_min_ranks) ? ga_nvls : ga_symm;
-    return ga_twoshot;
+    // ordinary buffers: the chunk pipeline hides the staging copies under the NVLink traffic
+    return bytes >= env.ar_pipelined_min ? ga_pipelined : ga_twoshot;
 }
 
 void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, int dt_in, int dt_out, int op,
@@ -142,11 +143,47 @@ void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, i
         }
     }
 
-    // two-shot, chunked so that IN slots + OUT region fit one staging generation
-    CCL_THROW_IF_NOT(algo == ga_twoshot, "unknown allreduce algorithm ", algo);
     const size_t osz = predefined_dtype_size(dt_out);
     const size_t N = 16 / esz;
-    const size_t out_pack = N * osz;
+    const size_t out_pack = std::max<size_t>(N * osz, 16); // reduced packs are staged in whole 16-byte units
+
+    if (algo == ga_pipelined) {
+        const env_data& env = env_data::get();
+        const size_t npacks = (bytes + 15) / 16;
+        int blocks = o.blocks > 0 ? o.blocks : env.ar_pipelined_blocks;
+        blocks = std::max(1, std::min(blocks, dc.max_blocks()));
+        // a few hundred packs per block and rank at least, so that small messages do not pay for idle blocks
+        while (blocks > 1 && npacks < (size_t)blocks * W * 256)
+            blocks /= 2;
+        const size_t unit = (size_t)blocks * W; // a chunk divides evenly among blocks, then ranks
+        size_t cp = dc.staging_bytes() / (2 * 16 + 2 * out_pack) / unit * unit;
+        CCL_THROW_IF_NOT(cp >= unit, "staging buffer too small for the pipelined allreduce");
+        cp = std::min(cp, (npacks + unit - 1) / unit * unit);
+        a.count = count;
+        a.stride = cp;
+        const bool nvls = dc.nvls() && nvls_type_ok(dt_in, op) && W >= env.nvls_min_ranks;
+        prepare_args(dc, a, ra, st);
+        dispatch_reduce_types(dt_in, dt_out, op, [&](auto tin, auto tout, auto opv) {
+            typedef decltype(tin) T;
+            typedef decltype(tout) Tout;
+            typedef decltype(opv) OP;
+            if constexpr (std::is_same<OP, dev::op_sum>::value &&
+                          (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value ||
+                           std::is_same<T, __half>::value)) {
+                if (nvls) {
+                    launch_kernel(dc, dev::allreduce_pipelined_kernel<T, Tout, OP, true>, blocks, threads, st,
+                                  dc.table(), a);
+                    return;
+                }
+            }
+            launch_kernel(dc, dev::allreduce_pipelined_kernel<T, Tout, OP, false>, blocks, threads, st, dc.table(),
+                          a);
+        });
+        return;
+    }
+
+    // two-shot, chunked so that IN slots + OUT region fit one staging generation
+    CCL_THROW_IF_NOT(algo == ga_twoshot, "unknown allreduce algorithm ", algo);
     size_t max_packs = (dc.staging_bytes() - 16 * (size_t)W) / (16 + out_pack);
     max_packs = max_packs / W * W; // whole slices
     CCL_THROW_IF_NOT(max_packs >= (size_t)W, "staging buffer too small for a two-shot allreduce");

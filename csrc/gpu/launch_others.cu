@@ -202,8 +202,15 @@ void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_o
     if (algo == ga_push && rounded > dc.staging_bytes())
         algo = ga_pull;
     if (algo == ga_push) {
+        bool uniform = (maxb & 15) == 0;
+        for (int p = 0; p < W && uniform; p++)
+            uniform = ra[0].scount[p] == maxb && ra[0].sdispl[p] == (size_t)p * maxb;
+        for (int e = 0; e < entries && uniform; e++)
+            uniform = (((uintptr_t)ra[e].recv) & 15) == 0;
+        a.flags = (dc.nvls() && W >= env_data::get().nvls_min_ranks ? dev::CF_NVLS : 0) |
+                  (uniform ? dev::CF_UNIFORM : 0);
         prepare_args(dc, a, ra, st);
-        const int blocks = pick_blocks(dc, r16(maxb) / 16, 2048, o.blocks);
+        const int blocks = pick_blocks(dc, r16(maxb) / 16, 1024, o.blocks);
         launch_kernel(dc, dev::allgatherv_kernel<true>, blocks, threads, st, dc.table(), a);
         return;
     }
@@ -235,14 +242,50 @@ void launch_alltoallv(device_comm& dc, const dev::rank_args* ra, const launch_op
     for (int e = 0; e < entries; e++)
         for (int p = 0; p < W; p++)
             lmax = std::max(lmax, std::max(ra[e].scount[p], ra[e].rcount[p]));
-    dc.algo_hits[coll_alltoallv * ga_last + ga_push]++;
     const size_t slot = (dc.staging_bytes() / W) & ~(size_t)15;
     CCL_THROW_IF_NOT(slot >= 16, "staging buffer too small for alltoallv");
     dev::coll_args a{};
+    // equal blocks (alltoall): the block size is the same on every rank, so it may size the grid
+    const size_t b = ra[0].scount[0];
+    bool uniform = o.uniform && W > 1 && b > 0 && (b & 15) == 0;
+    bool symm = uniform && o.algo != ga_push;
+    size_t out_off = 0;
+    for (int e = 0; e < entries && uniform; e++) {
+        for (int p = 0; p < W; p++)
+            uniform = uniform && ra[e].scount[p] == b && ra[e].rcount[p] == b && ra[e].sdispl[p] == (size_t)p * b &&
+                      ra[e].rdispl[p] == (size_t)p * b;
+        const bool aligned = ((((uintptr_t)ra[e].send) | ((uintptr_t)ra[e].recv)) & 15) == 0;
+        const size_t oo = dc.symm_offset(ra[e].recv, dc.emulated() ? e : dc.rank());
+        // the direct path must be chosen by every rank or by none: it depends only on the block size
+        // and on recv being a symmetric allocation, which is a collective property
+        if (symm && (oo == (size_t)-1 || (oo & 15) || (e > 0 && oo != out_off) || !aligned || ra[e].send == ra[e].recv))
+            symm = false;
+        out_off = oo;
+        uniform = uniform && aligned;
+    }
+    symm = symm && uniform;
+    if (symm) {
+        dc.algo_hits[coll_alltoallv * ga_last + ga_symm]++;
+        a.count = b;
+        a.out_off = out_off;
+        prepare_args(dc, a, ra, st);
+        const int blocks = pick_blocks(dc, b / 16, 512, o.blocks);
+        launch_kernel(dc, dev::alltoall_symm_kernel, blocks, dc.threads(), st, dc.table(), a);
+        return;
+    }
+    dc.algo_hits[coll_alltoallv * ga_last + ga_push]++;
+    a.flags = uniform ? dev::CF_UNIFORM : 0;
     prepare_args(dc, a, ra, st);
-    // every rank must use the same grid: derive it from the slot size, not from local counts
+    // every rank must use the same grid: derive it from what all ranks know (the common block size
+    // of an alltoall, else a fixed size), never from local counts
     (void)lmax;
-    const int blocks = o.blocks > 0 ? pick_blocks(dc, 1, 1, o.blocks) : std::min(dc.max_blocks(), 32);
+    int blocks;
+    if (o.blocks > 0)
+        blocks = pick_blocks(dc, 1, 1, o.blocks);
+    else if (o.uniform)
+        blocks = pick_blocks(dc, std::min(b, slot) / 16 + 1, 512, 0);
+    else
+        blocks = std::min(dc.max_blocks(), 32);
     launch_kernel(dc, dev::alltoallv_kernel, blocks, dc.threads(), st, dc.table(), a);
 }
 

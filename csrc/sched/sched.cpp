@@ -1,4 +1,5 @@
 #include "sched/sched.hpp"
+#include "topo/numa.hpp"
 
 #include <pthread.h>
 #include <sched.h>
@@ -10,6 +11,7 @@
 #include "comm/host_comm.hpp"
 #include "core/datatype.hpp"
 #include "core/env.hpp"
+#include "core/trace.hpp"
 #include "core/log.hpp"
 #include "sched/entries.hpp"
 
@@ -96,11 +98,14 @@ void sched_entry::do_progress() {
         if (status_ == entry_status::not_started && timed)
             started_at_ns_ = t0;
         status_ = entry_status::started;
+        trace_range tr(2, name()); // entries are state machines: the range covers the start call, marks the end
         start();
     }
     else if (status_ == entry_status::started) {
         update_calls++;
         update();
+        if (status_ == entry_status::complete && trace_level() >= 2)
+            trace_mark(name());
     }
     if (timed) {
         uint64_t t1 = now_ns();
@@ -451,14 +456,32 @@ void worker::loop() {
     {
         std::string nm = "ccl_worker_" + std::to_string(idx_);
         pthread_setname_np(pthread_self(), nm.c_str());
+        trace_name_thread(nm.c_str());
     }
-    if ((size_t)idx_ < env.worker_affinity.size()) {
+    int cpu = -1;
+    if ((size_t)idx_ < env.worker_affinity.size())
+        cpu = env.worker_affinity[idx_];
+    else if (env.worker_affinity_auto) {
+        const numa_info& numa = numa_info::get();
+        const auto cpus = numa_info::auto_worker_cpus(numa.allowed_cpus(), env.local_rank, env.local_size,
+                                                      env.worker_count);
+        if ((size_t)idx_ < cpus.size())
+            cpu = cpus[idx_];
+    }
+    if (cpu >= 0) {
         cpu_set_t set;
         CPU_ZERO(&set);
-        CPU_SET(env.worker_affinity[idx_], &set);
+        CPU_SET(cpu, &set);
         if (pthread_setaffinity_np(pthread_self(), sizeof(set), &set) != 0)
-            LOG_WARN("can not pin worker ", idx_, " to core ", env.worker_affinity[idx_]);
+            LOG_WARN("can not pin worker ", idx_, " to core ", cpu);
+        else
+            LOG_DEBUG("worker ", idx_, " pinned to core ", cpu);
     }
+    // staging memory the worker touches first lands on its own NUMA node
+    int node = (size_t)idx_ < env.worker_mem_affinity.size() ? env.worker_mem_affinity[idx_]
+                                                              : (cpu >= 0 ? numa_info::get().node_of_cpu(cpu) : -1);
+    if (node >= 0 && numa_info::get().node_count() > 1 && !numa_info::get().bind_thread_memory(node))
+        LOG_DEBUG("worker ", idx_, ": memory policy for node ", node, " not applied");
     int idle_spins = 0;
     while (!stop_) {
         size_t n = 0;

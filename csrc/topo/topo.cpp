@@ -1,4 +1,5 @@
 #include "topo/topo.hpp"
+#include "topo/numa.hpp"
 
 #include <cuda_runtime.h>
 #include <dlfcn.h>
@@ -66,6 +67,7 @@ topo_info discover() {
         char bus[32] = { 0 };
         if (cudaDeviceGetPCIBusId(bus, sizeof(bus), i) == cudaSuccess)
             g.pci_bus_id = bus;
+            g.numa_node = numa_info::get().node_of_pci(bus);
         if (d.loaded) {
             CUdevice cd;
             int mc = 0;
@@ -146,7 +148,7 @@ std::string topo_info::describe() const {
     const int n = gpu_count();
     ss << n << " GPU(s)";
     for (auto& g : gpus)
-        ss << "\n  [" << g.index << "] " << g.name << " " << g.pci_bus_id << " sm_" << g.cc_major << g.cc_minor << " "
+        ss << "\n  [" << g.index << "] " << g.name << " " << g.pci_bus_id << " numa " << g.numa_node << " sm_" << g.cc_major << g.cc_minor << " "
            << g.sm_count << " SMs " << (g.mem_bytes >> 30) << " GiB L2 " << (g.l2_bytes >> 20)
            << " MiB nvlink_active=" << g.nvlink_active << " multicast=" << g.multicast;
     if (n > 1) {

@@ -20,6 +20,7 @@ struct gpu_info {
     int index = -1;
     std::string name;
     std::string pci_bus_id;
+    int numa_node = -1; // home NUMA node of the device (sysfs), -1 when unknown
     int sm_count = 0;
     size_t mem_bytes = 0;
     int cc_major = 0, cc_minor = 0;

@@ -60,5 +60,8 @@ PROTOTYPES = {
     "cclx_parse_algo_spec": (i, [i, cs]),
     "cclx_stats": (ll, [i, i]),
     "cclx_topo_describe": (i, [vp, sz]),
+    "cclx_numa_query": (i, [C.c_char_p, i, i, C.c_char_p, C.POINTER(C.c_int), i]),
+    "cclx_numa_auto_worker_cpus": (i, [C.POINTER(C.c_int), i, i, i, i, C.POINTER(C.c_int)]),
+    "cclx_numa_selftest": (i, [i, sz]),
     "cclx_env_size": (i, [cs, C.POINTER(sz)]),
 }

@@ -213,17 +213,25 @@ class DeviceGroup:
         self._finish(rc)
         return recv
 
+    def alltoall(self, send, recv, algo="auto", blocks=0, stream=None):
+        """Equal blocks: block q of `send` goes to rank q.  With `recv` from the symmetric heap the
+        blocks are stored straight into the peers' buffers (algo="push" forces the staged kernel)."""
+        s, r = self._lists(send, recv)
+        per = s[0].numel() // self.world * s[0].element_size()
+        rc = self._lib.cclx_dc_alltoall(self._h, self._ptrs(s), self._ptrs(r), per, GPU_ALGO[algo], blocks,
+                                        _stream_ptr(stream))
+        self._finish(rc)
+        return recv
+
     def alltoallv(self, send, recv, send_counts=None, recv_counts=None, blocks=0, stream=None):
         """Counts are in elements; emulated mode takes one row of counts per rank."""
+        if send_counts is None:
+            return self.alltoall(send, recv, blocks=blocks, stream=stream)
         s, r = self._lists(send, recv)
         W = self.world
         esz = s[0].element_size()
         n = self.n_entries
-        if send_counts is None:
-            per = s[0].numel() // W
-            send_counts = [[per] * W for _ in range(n)]
-            recv_counts = [[per] * W for _ in range(n)]
-        elif not self.emulated_mode:
+        if not self.emulated_mode:
             send_counts, recv_counts = [list(send_counts)], [list(recv_counts)]
         table = []
         for e in range(n):

@@ -60,7 +60,7 @@ def _tol(dtype, world):
 
 @pytest.mark.parametrize("n", SIZES)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.int32])
-@pytest.mark.parametrize("algo", ["oneshot", "twoshot"])
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "pipelined"])
 def test_allreduce_sum(group, n, dtype, algo):
     W = group.world
     xs = _inputs(W, n, dtype)
@@ -97,7 +97,7 @@ def test_allreduce_inplace_unaligned_and_repeat(group):
     times in a row so that both staging generations and the epoch flags are reused."""
     W, n = group.world, 5003
     for it in range(5):
-        for algo in ("oneshot", "twoshot"):
+        for algo in ("oneshot", "twoshot", "pipelined"):
             base = [torch.zeros(n + 1, dtype=torch.float32, device="cuda") for _ in range(W)]
             xs = [b[1:] for b in base]
             src = _inputs(W, n, torch.float32, seed=10 + it)
@@ -116,13 +116,48 @@ def test_allreduce_scale_and_cast(group):
     W, n = group.world, 70001
     xs = _inputs(W, n, torch.bfloat16, seed=5)
     ref = torch.stack([x.float() for x in xs]).sum(0) / W
-    for algo in ("oneshot", "twoshot"):
+    for algo in ("oneshot", "twoshot", "pipelined"):
         outs = [torch.empty(n, dtype=torch.float32, device="cuda") for _ in range(W)]
         group.allreduce(xs, outs, algo=algo, scale=1.0 / W)
         torch.cuda.synchronize()
         group.check()
         for o in outs:
             torch.testing.assert_close(o, ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("algo", ["twoshot", "pipelined"])
+def test_allreduce_narrowing_cast(group, algo):
+    """fp32 in, bf16 out: a reduced pack is 8 bytes, staged in 16-byte units."""
+    W, n = group.world, 9001
+    xs = _inputs(W, n, torch.float32, seed=6)
+    ref = torch.stack(xs).sum(0)
+    bufs = [_padded(n, torch.bfloat16) for _ in range(W)]
+    group.allreduce(xs, [b[1] for b in bufs], algo=algo)
+    torch.cuda.synchronize()
+    group.check()
+    for buf, o in bufs:
+        torch.testing.assert_close(o.float(), ref, rtol=1e-2, atol=1e-2)
+        assert _canary_ok(buf, n)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("blocks", [0, 3])
+def test_allreduce_pipelined_many_chunks(group, dtype, blocks):
+    """Message of several chunks (8 MiB staging holds 2 MiB chunks): the copy-in, reduce and
+    copy-out stages of neighbouring chunks overlap; odd length, run twice for the generation flip."""
+    W = group.world
+    n = (11 << 20) // torch.empty((), dtype=dtype).element_size() + 13
+    xs = _inputs(W, n, dtype, seed=8)
+    ref = torch.stack([x.double() for x in xs]).sum(0)
+    for _ in range(2):
+        bufs = [_padded(n, dtype) for _ in range(W)]
+        group.allreduce(xs, [b[1] for b in bufs], algo="pipelined", blocks=blocks)
+        torch.cuda.synchronize()
+        group.check()
+        for buf, o in bufs:
+            torch.testing.assert_close(o.double(), ref, **_tol(dtype, W))
+            assert _canary_ok(buf, n)
+        assert group.algo_hits("allreduce", "pipelined") > 0
 
 
 def test_allreduce_twoshot_chunked(group):
@@ -274,6 +309,42 @@ def test_alltoall_multi_round(group):
     for r in range(W):
         ref = torch.cat([send[p][r * per:(r + 1) * per] for p in range(W)])
         assert torch.equal(recv[r], ref)
+
+
+@pytest.mark.parametrize("per", [4, 2052, ((8 << 20) // 8 // 4) * 3 + 8])
+@pytest.mark.parametrize("symmetric", [False, True])
+def test_alltoall_equal_blocks(group, per, symmetric):
+    """Equal 16-byte-multiple blocks: batched staged kernel (one or several rounds) and the
+    direct stores into a symmetric recv buffer; run twice to cover buffer reuse."""
+    W = group.world
+    send = [torch.arange(per * W, device="cuda", dtype=torch.float32) + r * 1e6 for r in range(W)]
+    recv = group.symm_empty((per * W,), dtype=torch.float32) if symmetric else \
+        [torch.zeros(per * W, device="cuda") for _ in range(W)]
+    for it in range(2):
+        for x in send:
+            x += it
+        group.alltoall(send, recv)
+        torch.cuda.synchronize()
+        group.check()
+        for r in range(W):
+            ref = torch.cat([send[p][r * per:(r + 1) * per] for p in range(W)])
+            assert torch.equal(recv[r], ref)
+    assert group.algo_hits("alltoallv", "symm" if symmetric else "push") > 0
+    if symmetric:
+        group.symm_free(recv)
+
+
+def test_allgather_push_uniform_and_nvls_flags(group):
+    """Equal aligned blocks take the batched copy-out; unequal ones the per-peer copies."""
+    W, per = group.world, 4100
+    src = [torch.arange(per, device="cuda", dtype=torch.float32) + r * 10000 for r in range(W)]
+    bufs = [_padded(per * W, torch.float32) for _ in range(W)]
+    group.allgatherv(src, [b[1] for b in bufs], algo="push")
+    torch.cuda.synchronize()
+    group.check()
+    ref = torch.cat(src)
+    for buf, o in bufs:
+        assert torch.equal(o, ref) and _canary_ok(buf, per * W)
 
 
 def test_barrier_and_sendrecv(group):
