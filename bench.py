@@ -171,6 +171,11 @@ def main():
     dev_idx = [t.cuda() for t in host_idx[: args.steps]]
     dev_tgt = [t.cuda() for t in host_tgt[: args.steps]]
 
+    # the clock sampler starts before the warm-up (nvidia-smi needs a moment to come up); only the
+    # samples that arrive inside the two timed regions are summarised
+    clocks = ClockSampler(local_rank)
+    clocks.__enter__()
+
     # ---- warm-up
     for w in range(args.warmup):
         loss = step(dev_idx[w % len(dev_idx)], dev_tgt[w % len(dev_tgt)])
@@ -179,13 +184,14 @@ def main():
     # ---- device-timed region: exactly K steps
     l0 = my_launches()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        barrier()
-        ev0.record()
-        for k in range(args.steps):
-            loss = step(dev_idx[k], dev_tgt[k])
-        ev1.record()
-        barrier()
+    barrier()
+    clocks.begin()
+    ev0.record()
+    for k in range(args.steps):
+        loss = step(dev_idx[k], dev_tgt[k])
+    ev1.record()
+    barrier()
+    clocks.end()
     ms_dev = max_over_ranks(ev0.elapsed_time(ev1))
     launches = my_launches() - l0
     final_loss = float(loss.item())
@@ -193,6 +199,7 @@ def main():
     # ---- end-to-end region: batch from pinned host memory every step, loss read back every step
     h2d = host_idx[0].numel() * host_idx[0].element_size() + host_tgt[0].numel() * host_tgt[0].element_size()
     barrier()
+    clocks.begin()
     t0 = time.perf_counter()
     ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev2.record()
@@ -203,6 +210,8 @@ def main():
         _ = float(loss.item())  # 4-byte device->host read of the step's result
     ev3.record()
     barrier()
+    clocks.end()
+    clocks.__exit__(None, None, None)
     ms_e2e = max_over_ranks(ev2.elapsed_time(ev3))
     wall_e2e = time.perf_counter() - t0
 

@@ -5,6 +5,7 @@ import shutil
 import statistics
 import subprocess
 import threading
+import time
 
 _QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
           "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -14,10 +15,11 @@ _QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,
 class ClockSampler:
     """Context manager: starts ``nvidia-smi -lms`` for one GPU index, parses the rows on exit."""
 
-    def __init__(self, gpu_index: int = 0, period_ms: int = 200):
+    def __init__(self, gpu_index: int = 0, period_ms: int = 100):
         self.gpu_index = gpu_index
         self.period_ms = period_ms
-        self.rows = []
+        self.rows = []  # (arrival time, csv line)
+        self._windows = []  # [begin, end] pairs of time.monotonic(); empty = everything counts
         self._proc = None
         self._thread = None
 
@@ -35,7 +37,7 @@ class ClockSampler:
 
         def pump():
             for line in self._proc.stdout:
-                self.rows.append(line.strip())
+                self.rows.append((time.monotonic(), line.strip()))
 
         self._thread = threading.Thread(target=pump, daemon=True)
         self._thread.start()
@@ -52,11 +54,27 @@ class ClockSampler:
                 self._thread.join(timeout=2)
         return False
 
+    def begin(self):
+        """Opens a window: only samples that arrive inside windows are summarised (the tool takes a
+        few hundred ms to start, so it is launched well before the region of interest)."""
+        self._windows.append([time.monotonic(), None])
+
+    def end(self):
+        if self._windows and self._windows[-1][1] is None:
+            self._windows[-1][1] = time.monotonic()
+
+    def _inside(self, t: float) -> bool:
+        if not self._windows:
+            return True
+        return any(b <= t <= (e if e is not None else float("inf")) for b, e in self._windows)
+
     def summary(self) -> dict:
         sm, mx, power = [], [], []
         reasons = set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for row in self.rows:
+        for t, row in self.rows:
+            if not self._inside(t):
+                continue
             parts = [p.strip() for p in row.split(",")]
             if len(parts) < 9:
                 continue
