@@ -10,6 +10,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
+#include <vector>
+
 #include "capi/capi_common.hpp"
 #include "core/log.hpp"
 #include "gpu/cuda_driver.hpp"
@@ -89,5 +92,251 @@ CCLX_API int cclx_moe_combine(const void* y, const long long* pos, const float* 
         combine_rows_kernel<<<blocks_for(n_tokens), 256, 0, (cudaStream_t)stream>>>(
             (const __nv_bfloat16*)y, pos, w, (__nv_bfloat16*)out, n_tokens, topk, hidden);
         CUDA_CHECK(cudaGetLastError());
+    });
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused dispatch and combine over peer memory: the all-to-all of an expert-parallel layer without
+// staging buffers, send-side row gather or receive-side copies.
+//
+//   dispatch: every rank tells every peer how many rows it sends to each expert (a W x W table in
+//             symmetric memory, written redundantly per block so that the per-block barrier is
+//             enough), derives where its rows start inside each expert's receive buffer (ranks in
+//             order), and stores row `order[i] / topk` of x straight into the owner's buffer.
+//   combine : after the expert FFN wrote its output rows (same layout as the receive buffer) every
+//             rank pulls the rows of its tokens from the owners with peer loads and forms the
+//             weighted sum in fp32.
+//
+// The reference leaves both steps to alltoallv (src/coll/algorithms/alltoallv.cpp:112-751) around
+// user kernels; on NVSwitch the rows can go directly where they are needed.
+// ---------------------------------------------------------------------------------------------
+#include "gpu/device/common.cuh"
+#include "gpu/device_comm.hpp"
+
+namespace {
+
+using namespace cclx;
+using namespace cclx::dev;
+
+struct moe_rank_args {
+    const __nv_bfloat16* x; // dispatch: [tokens, hidden] input rows | combine: unused
+    const long long* order; // dispatch: (token, slot) pairs sorted by expert, as token * topk + slot
+    const long long* send_counts; // dispatch: rows for every expert [world]
+    const long long* expert; // combine: expert of every (token, slot) [tokens * topk]
+    const long long* pos; // combine: place of (token, slot) in `order`
+    const float* weight; // combine: routing weights [tokens * topk]
+    __nv_bfloat16* out; // combine: [tokens, hidden]
+    int* meta; // [0, W) first row of my block inside expert e's buffer, [W, 2W) prefix of send_counts,
+               // [2W] rows this rank's expert received, [2W+1] 1 if some buffer overflowed
+};
+
+struct moe_args {
+    moe_rank_args r0;
+    const moe_rank_args* emu_tab;
+    int emu;
+    int topk;
+    int hidden;
+    size_t n_items; // tokens * topk
+    size_t cap_rows; // rows of the receive / output buffers
+    size_t buf_off; // heap offset of the receive buffer (dispatch) or of the expert output (combine)
+    size_t cnt_off; // heap offset of the int32 table [blocks][W][W]
+};
+
+__global__ void __launch_bounds__(512) moe_dispatch_kernel(const comm_dev* tab, moe_args a) {
+    const int er = a.emu ? (int)blockIdx.y : 0;
+    const comm_dev& c = tab[er];
+    const moe_rank_args& ra = a.emu ? a.emu_tab[er] : a.r0;
+    block_sync s;
+    sync_begin(c, s);
+    const int W = c.world;
+    __shared__ int s_dst[MAX_RANKS], s_pre[MAX_RANKS + 1], s_over;
+    // my counts into every rank's table, slot of this block
+    const size_t blk_words = (size_t)blockIdx.x * W * W;
+    for (int i = threadIdx.x; i < W * W; i += blockDim.x) {
+        const int p = i / W, e = i % W;
+        int* t = reinterpret_cast<int*>(c.heap[p] + a.cnt_off) + blk_words;
+        t[c.rank * W + e] = (int)ra.send_counts[e];
+    }
+    bool ok = peer_barrier(c, s);
+    if (threadIdx.x == 0) {
+        const int* t = reinterpret_cast<const int*>(c.heap[c.rank] + a.cnt_off) + blk_words;
+        int over = 0, pre = 0, recv = 0;
+        for (int e = 0; e < W; e++) {
+            int off = 0, tot = 0;
+            for (int q = 0; q < W; q++) {
+                const int v = __ldcv(t + q * W + e);
+                if (q < c.rank)
+                    off += v;
+                tot += v;
+            }
+            s_dst[e] = off;
+            s_pre[e] = pre;
+            pre += (int)ra.send_counts[e];
+            over |= tot > (long long)a.cap_rows ? 1 : 0;
+            if (e == c.rank)
+                recv = tot;
+        }
+        s_pre[W] = pre;
+        s_over = over;
+        if (blockIdx.x == 0) {
+            for (int e = 0; e < W; e++) {
+                ra.meta[e] = s_dst[e];
+                ra.meta[W + e] = s_pre[e];
+            }
+            ra.meta[2 * W] = recv;
+            ra.meta[2 * W + 1] = over;
+        }
+    }
+    __syncthreads();
+    if (ok && !s_over) {
+        // one warp per row
+        const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+        const size_t warp = (size_t)blockIdx.x * wpb + (threadIdx.x >> 5), nwarps = (size_t)gridDim.x * wpb;
+        const int packs = a.hidden / 8;
+        for (size_t i = warp; i < a.n_items; i += nwarps) {
+            int e = 0;
+            while (e + 1 < W && (long long)i >= s_pre[e + 1])
+                e++;
+            const size_t row = (size_t)s_dst[e] + (i - (size_t)s_pre[e]);
+            const uint4* src = reinterpret_cast<const uint4*>(ra.x + (size_t)(ra.order[i] / a.topk) * a.hidden);
+            char* dst = c.heap[e] + a.buf_off + row * (size_t)a.hidden * 2;
+            for (int k = lane; k < packs; k += 32)
+                st16(dst + (size_t)k * 16, src[k]);
+        }
+    }
+    peer_barrier(c, s);
+    sync_end(c, gridDim.x, 2, false);
+}
+
+__global__ void __launch_bounds__(512) moe_combine_kernel(const comm_dev* tab, moe_args a) {
+    const int er = a.emu ? (int)blockIdx.y : 0;
+    const comm_dev& c = tab[er];
+    const moe_rank_args& ra = a.emu ? a.emu_tab[er] : a.r0;
+    block_sync s;
+    sync_begin(c, s);
+    const int W = c.world;
+    // every owner has finished its expert FFN (this launch is ordered after it on each rank's stream)
+    bool ok = peer_barrier(c, s);
+    if (ok) {
+        const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+        const size_t warp = (size_t)blockIdx.x * wpb + (threadIdx.x >> 5), nwarps = (size_t)gridDim.x * wpb;
+        const int packs = a.hidden / 8;
+        const size_t tokens = a.n_items / a.topk;
+        for (size_t t = warp; t < tokens; t += nwarps) {
+            for (int k0 = lane; k0 < packs; k0 += 32) {
+                float acc[8] = { 0, 0, 0, 0, 0, 0, 0, 0 };
+                for (int sl = 0; sl < a.topk; sl++) {
+                    const size_t f = t * a.topk + sl;
+                    const int e = (int)ra.expert[f];
+                    const size_t row = (size_t)ra.meta[e] + ((size_t)ra.pos[f] - (size_t)ra.meta[W + e]);
+                    const float w = ra.weight[f];
+                    const uint4 v = ld_cv16(c.heap[e] + a.buf_off + row * (size_t)a.hidden * 2 + (size_t)k0 * 16);
+                    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+                    for (int q = 0; q < 8; q++)
+                        acc[q] = fmaf(w, __bfloat162float(h[q]), acc[q]);
+                }
+                uint4 o;
+                __nv_bfloat16* oh = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+                for (int q = 0; q < 8; q++)
+                    oh[q] = __float2bfloat16_rn(acc[q]);
+                reinterpret_cast<uint4*>(ra.out + t * a.hidden)[k0] = o;
+            }
+        }
+    }
+    // nobody may overwrite its output rows (the next layer's FFN) before every reader is done
+    peer_barrier(c, s);
+    sync_end(c, gridDim.x, 2, false);
+}
+
+void launch_moe(gpu::device_comm& dc, bool dispatch, moe_args& a, const moe_rank_args* ra, int blocks,
+                cudaStream_t st) {
+    dc.check_status();
+    blocks = blocks > 0 ? std::min(blocks, dc.max_blocks()) : std::min(dc.max_blocks(), 128);
+    a.r0 = ra[0];
+    if (dc.emulated()) {
+        static_assert(sizeof(moe_rank_args) <= sizeof(dev::rank_args), "argument block too large");
+        CUDA_CHECK(cudaStreamSynchronize(st));
+        CUDA_CHECK(cudaMemcpy(dc.emu_args_dev(), ra, dc.world() * sizeof(moe_rank_args), cudaMemcpyHostToDevice));
+        a.emu = 1;
+        a.emu_tab = reinterpret_cast<const moe_rank_args*>(dc.emu_args_dev());
+        const comm_dev* tab = dc.table();
+        void* argv[] = { (void*)&tab, (void*)&a };
+        dim3 grid(blocks, dc.world());
+        CUDA_CHECK(cudaLaunchCooperativeKernel(dispatch ? (const void*)moe_dispatch_kernel : (const void*)moe_combine_kernel,
+                                               grid, dim3(512), argv, 0, st));
+    }
+    else {
+        a.emu = 0;
+        a.emu_tab = nullptr;
+        if (dispatch)
+            moe_dispatch_kernel<<<blocks, 512, 0, st>>>(dc.table(), a);
+        else
+            moe_combine_kernel<<<blocks, 512, 0, st>>>(dc.table(), a);
+        CUDA_CHECK(cudaGetLastError());
+    }
+}
+
+} // namespace
+
+// Arrays hold one pointer per entry: one entry in real mode, `world` entries in emulation mode.
+// `recv_buf` / `cnt_table` are this rank's (entry 0's) symmetric allocations: [cap_rows, hidden] bf16 and
+// at least 256 * world * world int32.  meta: 2 * world + 2 int32 per entry.
+CCLX_API int cclx_moe_dispatch(void* h, const void* const* x, const long long* const* order,
+                               const long long* const* send_counts, int* const* meta, size_t n_items, int topk,
+                               int hidden, const void* recv_buf, size_t cap_rows, const void* cnt_table, int blocks,
+                               void* stream) {
+    return cclx::capi::guard([&] {
+        gpu::device_comm* dc = (gpu::device_comm*)h;
+        CCL_THROW_IF_NOT(hidden % 8 == 0 && topk >= 1, "hidden size must be a multiple of 8");
+        const int entries = dc->emulated() ? dc->world() : 1;
+        const int owner = dc->emulated() ? 0 : dc->rank();
+        moe_args a{};
+        a.topk = topk;
+        a.hidden = hidden;
+        a.n_items = n_items;
+        a.cap_rows = cap_rows;
+        a.buf_off = dc->symm_offset(recv_buf, owner);
+        a.cnt_off = dc->symm_offset(cnt_table, owner);
+        CCL_THROW_IF_NOT(a.buf_off != (size_t)-1 && a.cnt_off != (size_t)-1 && (a.buf_off & 15) == 0,
+                         "the receive buffer and the count table must come from the symmetric heap");
+        std::vector<moe_rank_args> ra(entries);
+        for (int e = 0; e < entries; e++) {
+            ra[e] = moe_rank_args{};
+            ra[e].x = (const __nv_bfloat16*)x[e];
+            ra[e].order = order[e];
+            ra[e].send_counts = send_counts[e];
+            ra[e].meta = meta[e];
+        }
+        launch_moe(*dc, true, a, ra.data(), blocks, (cudaStream_t)stream);
+    });
+}
+
+CCLX_API int cclx_moe_combine_peer(void* h, const long long* const* expert, const long long* const* pos,
+                                   const float* const* weight, void* const* out, int* const* meta, size_t n_items,
+                                   int topk, int hidden, const void* expert_out, int blocks, void* stream) {
+    return cclx::capi::guard([&] {
+        gpu::device_comm* dc = (gpu::device_comm*)h;
+        CCL_THROW_IF_NOT(hidden % 8 == 0 && topk >= 1, "hidden size must be a multiple of 8");
+        const int entries = dc->emulated() ? dc->world() : 1;
+        const int owner = dc->emulated() ? 0 : dc->rank();
+        moe_args a{};
+        a.topk = topk;
+        a.hidden = hidden;
+        a.n_items = n_items;
+        a.buf_off = dc->symm_offset(expert_out, owner);
+        CCL_THROW_IF_NOT(a.buf_off != (size_t)-1 && (a.buf_off & 15) == 0,
+                         "the expert output must come from the symmetric heap");
+        std::vector<moe_rank_args> ra(entries);
+        for (int e = 0; e < entries; e++) {
+            ra[e] = moe_rank_args{};
+            ra[e].expert = expert[e];
+            ra[e].pos = pos[e];
+            ra[e].weight = weight[e];
+            ra[e].out = (__nv_bfloat16*)out[e];
+            ra[e].meta = meta[e];
+        }
+        launch_moe(*dc, false, a, ra.data(), blocks, (cudaStream_t)stream);
     });
 }

@@ -49,12 +49,37 @@ __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, size
 constexpr int SQN_MAX_BLOCKS = 1024;
 
 template <class T>
+__device__ __forceinline__ float sq_pack(const uint4& u) {
+    const T* h = reinterpret_cast<const T*>(&u);
+    float a = 0.f;
+#pragma unroll
+    for (int k = 0; k < (int)(16 / sizeof(T)); k++) {
+        const float v = ldf<T>(h, k);
+        a = fmaf(v, v, a);
+    }
+    return a;
+}
+
+template <class T>
 __global__ void __launch_bounds__(512) sq_norm_partial_kernel(const T* g, size_t n, float* partial) {
+    constexpr size_t N = 16 / sizeof(T);
     float acc = 0.f;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        float v = ldf<T>(g, i);
-        acc += v * v;
+    const size_t gtid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    // 16-byte loads, four of them in flight per thread; the order of the additions depends on n,
+    // the grid and the alignment of g only
+    const size_t nv = ((((uintptr_t)g) & 15) == 0) ? n / N : 0;
+    const uint4* gv = reinterpret_cast<const uint4*>(g);
+    size_t i = gtid;
+    for (; i + 3 * stride < nv; i += 4 * stride) {
+        const uint4 a = gv[i], b = gv[i + stride], c = gv[i + 2 * stride], d = gv[i + 3 * stride];
+        acc += (sq_pack<T>(a) + sq_pack<T>(b)) + (sq_pack<T>(c) + sq_pack<T>(d));
+    }
+    for (; i < nv; i += stride)
+        acc += sq_pack<T>(gv[i]);
+    for (size_t e = nv * N + gtid; e < n; e += stride) {
+        const float v = ldf<T>(g, e);
+        acc = fmaf(v, v, acc);
     }
     __shared__ float part[16];
     acc = warp_sum(acc);
@@ -233,6 +258,126 @@ __global__ void __launch_bounds__(1024)
     }
 }
 
+// Same contract as softmax_xent_kernel for rows that fit the register file: every thread keeps up
+// to PPT 16-byte packs of the row in registers, so the row is read from memory once.  The exponentials
+// are computed once (fp32, summed in fp32) and parked in the same registers as bf16 until the
+// normaliser is known; the gradient is bf16 anyway, the second rounding costs at most one more ulp.
+// Needs vocab % 8 == 0 columns handled as packs plus a scalar tail, ld % 8 == 0 and a 16-byte aligned base.
+template <int PPT>
+__global__ void __launch_bounds__(1024)
+    softmax_xent_regs_kernel(__nv_bfloat16* logits, const long long* targets, float* loss_rows, int vocab, size_t ld,
+                             float grad_scale, int pad_cols) {
+    constexpr float LOG2E = 1.4426950408889634f;
+    const size_t row = blockIdx.x;
+    __nv_bfloat16* x = logits + row * ld;
+    const long long tgt = targets[row];
+    __shared__ float red[32];
+    __shared__ float s_max, s_sum, s_tgt;
+    const int nv = vocab / 8;
+    uint4* xv = reinterpret_cast<uint4*>(x);
+    const int tail = nv * 8 + (int)threadIdx.x; // at most 7 leftover columns, one per thread
+    const bool has_tail = tail < vocab;
+
+    uint4 u[PPT];
+#pragma unroll
+    for (int j = 0; j < PPT; j++) {
+        const int i = (int)threadIdx.x + j * 1024;
+        u[j] = i < nv ? xv[i] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u); // -inf pairs
+    }
+    float xt = has_tail ? __bfloat162float(x[tail]) : -INFINITY;
+    if (threadIdx.x == 0)
+        s_tgt = (tgt >= 0 && tgt < vocab) ? __bfloat162float(x[tgt]) : 0.f;
+
+    float mx = xt;
+#pragma unroll
+    for (int j = 0; j < PPT; j++) {
+        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&u[j]);
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+            mx = fmaxf(mx, __bfloat162float(h[k]));
+    }
+    mx = warp_max(mx);
+    if ((threadIdx.x & 31) == 0)
+        red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = warp_max(red[threadIdx.x]);
+        if (threadIdx.x == 0)
+            s_max = v;
+    }
+    __syncthreads();
+    mx = s_max;
+    const float ms = mx * LOG2E;
+
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < PPT; j++) {
+        __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(&u[j]);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const float e = exp2f(fmaf(__bfloat162float(h[k]), LOG2E, -ms)); // exp2(-inf) = 0 for the filler
+            sum += e;
+            h[k] = __float2bfloat16_rn(e);
+        }
+    }
+    const float et = has_tail ? exp2f(fmaf(xt, LOG2E, -ms)) : 0.f;
+    sum += et;
+    sum = warp_sum(sum);
+    if ((threadIdx.x & 31) == 0)
+        red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float v = warp_sum(red[threadIdx.x]);
+        if (threadIdx.x == 0)
+            s_sum = v;
+    }
+    __syncthreads();
+    sum = s_sum;
+    const bool ignore = tgt < 0 || tgt >= vocab;
+    if (threadIdx.x == 0)
+        loss_rows[row] = ignore ? 0.f : (logf(sum) + mx - s_tgt);
+    const float inv = ignore ? 0.f : grad_scale / sum;
+    for (int i = vocab + threadIdx.x; i < vocab + pad_cols; i += blockDim.x)
+        x[i] = __float2bfloat16_rn(0.f);
+#pragma unroll
+    for (int j = 0; j < PPT; j++) {
+        const int i = (int)threadIdx.x + j * 1024;
+        if (i < nv) {
+            __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(&u[j]);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                float p = __bfloat162float(h[k]) * inv;
+                if (!ignore && (long long)i * 8 + k == tgt)
+                    p -= grad_scale;
+                h[k] = __float2bfloat16_rn(p);
+            }
+            xv[i] = u[j];
+        }
+    }
+    if (has_tail) {
+        float p = et * inv;
+        if (!ignore && tail == tgt)
+            p -= grad_scale;
+        x[tail] = __float2bfloat16_rn(p);
+    }
+}
+
+void launch_softmax_xent(__nv_bfloat16* logits, const long long* targets, float* loss_rows, size_t rows, int vocab,
+                         size_t ld, float grad_scale, int pad_cols, cudaStream_t st) {
+    const bool vec = (ld % 8 == 0) && ((((uintptr_t)logits) & 15) == 0);
+    const int nv = vocab / 8;
+    if (vec && nv <= 4 * 1024)
+        softmax_xent_regs_kernel<4><<<(unsigned)rows, 1024, 0, st>>>(logits, targets, loss_rows, vocab, ld, grad_scale,
+                                                                    pad_cols);
+    else if (vec && nv <= 7 * 1024)
+        softmax_xent_regs_kernel<7><<<(unsigned)rows, 1024, 0, st>>>(logits, targets, loss_rows, vocab, ld, grad_scale,
+                                                                    pad_cols);
+    else
+        softmax_xent_kernel<<<(unsigned)rows, 1024, 0, st>>>(logits, targets, loss_rows, vocab, ld, grad_scale,
+                                                            pad_cols);
+    CUDA_CHECK(cudaGetLastError());
+}
+
 int grid_for(size_t n, int threads) {
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
@@ -252,7 +397,7 @@ CCLX_API int cclx_sq_norm(const void* g, size_t n, int dt, float* out, float* pa
             return;
         CCL_THROW_IF_NOT(partials != nullptr, "sq_norm needs a partials buffer of 1024 floats");
         // the grid depends on n only, so that every rank adds in the same order
-        size_t want = (n + 512 * 8 - 1) / (512 * 8);
+        size_t want = (n + 512 * 32 - 1) / (512 * 32);
         const int blocks = (int)(want < 1 ? 1 : (want > (size_t)SQN_MAX_BLOCKS ? SQN_MAX_BLOCKS : want));
         if (dt == 11)
             sq_norm_partial_kernel<__nv_bfloat16><<<blocks, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)g, n,
@@ -303,9 +448,8 @@ CCLX_API int cclx_softmax_xent(void* logits_bf16, const long long* targets, floa
     return cclx::capi::guard([&] {
         if (rows == 0)
             return;
-        softmax_xent_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits_bf16, targets,
-                                                                              loss_rows, vocab, ld, grad_scale, pad_cols);
-        CUDA_CHECK(cudaGetLastError());
+        launch_softmax_xent((__nv_bfloat16*)logits_bf16, targets, loss_rows, rows, vocab, ld, grad_scale, pad_cols,
+                            (cudaStream_t)stream);
     });
 }
 
@@ -376,9 +520,7 @@ CCLX_API int cclx_softmax_xent_mean_noalloc(void* logits_bf16, const long long* 
             return;
         float* scratch = xent_scratch_for_current_device();
         cudaStream_t st = (cudaStream_t)stream;
-        softmax_xent_kernel<<<(unsigned)rows, 1024, 0, st>>>((__nv_bfloat16*)logits_bf16, targets, scratch, vocab, ld,
-                                                            grad_scale, pad_cols);
-        CUDA_CHECK(cudaGetLastError());
+        launch_softmax_xent((__nv_bfloat16*)logits_bf16, targets, scratch, rows, vocab, ld, grad_scale, pad_cols, st);
         mean_rows_kernel<<<1, 1024, 0, st>>>(scratch, rows, mean_loss);
         CUDA_CHECK(cudaGetLastError());
     });

@@ -15,6 +15,8 @@ PROTOTYPES = {
     # csrc/gpu/moe_kernels.cu
     "cclx_moe_gather_rows": (i, [vp, vp, vp, sz, i, vp]),
     "cclx_moe_combine": (i, [vp, vp, vp, vp, sz, i, i, vp]),
+    "cclx_moe_dispatch": (i, [vp, vp, vp, vp, vp, sz, i, i, vp, sz, vp, i, vp]),
+    "cclx_moe_combine_peer": (i, [vp, vp, vp, vp, vp, vp, sz, i, i, vp, i, vp]),
     # csrc/capi/capi_comm.cpp
     "cclx_kvs_create_main": (vp, [cs]),
     "cclx_kvs_create_peer": (vp, [cs]),

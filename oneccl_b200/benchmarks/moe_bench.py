@@ -88,8 +88,11 @@ def main():
     res = {"config": {"experts": world, "topk": args.topk, "hidden": args.hidden, "ffn": args.ffn,
                       "tokens_per_gpu": args.tokens, "dtype": "bf16"},
            "max_abs_diff_vs_nccl_cublas": (a - b).abs().max().item(), "ref_abs_max": b.abs().max().item(),
-           "rows_received": sum(moe.stats["recv_rows"])}
+           "rows_received": moe.stats["recv_rows"]}
+    c = moe.forward_alltoall(x, logits).float()
+    res["max_abs_diff_alltoall_path"] = (c - b).abs().max().item()
     res["ours_ms"] = timeit(ours)
+    res["ours_alltoall_path_ms"] = timeit(lambda: moe.forward_alltoall(x, logits))
     res["nccl_cublas_ms"] = timeit(nccl_cublas)
     res["speedup_vs_nccl_cublas"] = res["nccl_cublas_ms"] / res["ours_ms"]
     if rank == 0:

@@ -2,9 +2,13 @@
 tcgen05 GEMM, combine all-to-all with the weighted sum fused into the
 un-permute kernel.
 
-One expert per rank (``world`` experts).  The exchange is the library's
-``alltoallv`` kernel (variable per-destination counts; rounds are agreed on
-the device), the gather / combine passes are ``csrc/gpu/moe_kernels.cu``.
+One expert per rank (``world`` experts).  Default path: ``fused_dispatch`` stores
+every routed row straight into the owning expert's symmetric receive buffer and
+``fused_combine`` pulls the expert outputs back with peer loads while forming the
+weighted sum (no staging, no gather or un-permute pass).  ``forward_alltoall`` is
+the same layer on the library's ``alltoallv`` kernel (variable per-destination
+counts; rounds are agreed on the device) with separate gather / combine kernels;
+all kernels are in ``csrc/gpu/moe_kernels.cu``.
 """
 from __future__ import annotations
 
@@ -40,11 +44,43 @@ def combine_rows(y: torch.Tensor, pos: torch.Tensor, w: torch.Tensor, out: torch
     return out
 
 
+def _per_entry(group: DeviceGroup, t):
+    """Real mode takes one tensor, emulation a list with one tensor per rank."""
+    return list(t) if group.emulated_mode else [t]
+
+
+def fused_dispatch(group: DeviceGroup, x, order, send_counts, meta, recv_buf, cnt_table, topk: int, blocks: int = 0):
+    """Stores row ``order[i] // topk`` of ``x`` into the receive buffer of the expert that owns item i
+    (items sorted by expert), straight over NVLink.  ``recv_buf`` ([cap, hidden] bf16) and ``cnt_table``
+    (int32, >= 256 * world**2) are symmetric allocations; ``meta`` (int32 [2 * world + 2]) receives the row
+    offsets, the number of rows this rank's expert got (``meta[2 * world]``) and an overflow flag."""
+    global launches
+    xs, orders, counts, metas = (_per_entry(group, v) for v in (x, order, send_counts, meta))
+    rb, ct = _per_entry(group, recv_buf)[0], _per_entry(group, cnt_table)[0]
+    _lib.check(_lib.load().cclx_moe_dispatch(
+        group.handle, group._ptrs(xs), group._ptrs(orders), group._ptrs(counts), group._ptrs(metas),
+        orders[0].numel(), topk, xs[0].shape[1], rb.data_ptr(), rb.shape[0], ct.data_ptr(), blocks, _stream_ptr()))
+    launches += 1
+
+
+def fused_combine(group: DeviceGroup, expert, pos, weight, out, meta, expert_out, topk: int, blocks: int = 0):
+    """out[t] = sum_s weight[t, s] * (row of item (t, s) in the output buffer of its expert), read with
+    peer loads.  ``expert_out`` is the symmetric [cap, hidden] bf16 buffer every expert wrote its rows to,
+    in the order ``fused_dispatch`` delivered them."""
+    global launches
+    es, ps, ws, outs, metas = (_per_entry(group, v) for v in (expert, pos, weight, out, meta))
+    eo = _per_entry(group, expert_out)[0]
+    _lib.check(_lib.load().cclx_moe_combine_peer(
+        group.handle, group._ptrs(es), group._ptrs(ps), group._ptrs(ws), group._ptrs(outs), group._ptrs(metas),
+        es[0].numel(), topk, outs[0].shape[1], eo.data_ptr(), blocks, _stream_ptr()))
+    launches += 1
+
+
 class ExpertParallelMoE:
     """x [T, H] bf16 on every rank -> y [T, H]: every token visits its top-k experts."""
 
     def __init__(self, group: DeviceGroup, hidden: int, ffn: int, topk: int = 2, seed: int = 0,
-                 use_native_gemm: bool = True):
+                 use_native_gemm: bool = True, fused: bool = True, max_tokens: int = 0):
         self.group = group
         self.world = group.world
         self.rank = group.rank
@@ -55,6 +91,53 @@ class ExpertParallelMoE:
         self.w1 = (torch.randn(ffn, hidden, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
         self.w2 = (torch.randn(hidden, ffn, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
         self.stats = {}
+        # fused path: rows travel straight into / out of symmetric buffers sized for the worst case
+        # (every token of every rank choosing this expert); set up lazily for the first batch size
+        self.fused = fused
+        self._cap = 0
+        self._max_tokens = max_tokens
+        self._xrecv = self._yout = self._cnt = self._meta = None
+
+    def _buffers(self, tokens: int):
+        cap = max(tokens, self._max_tokens) * self.topk * self.world
+        if cap > self._cap:  # collective: every rank sees the same token count
+            for t in (self._xrecv, self._yout):
+                if t is not None:
+                    self.group.symm_free(t)
+            self._xrecv = self.group.symm_empty((cap, self.hidden), dtype=torch.bfloat16)
+            self._yout = self.group.symm_empty((cap, self.hidden), dtype=torch.bfloat16)
+            if self._cnt is None:
+                self._cnt = self.group.symm_empty((256 * self.world * self.world,), dtype=torch.int32)
+                self._meta = torch.zeros(2 * self.world + 2, dtype=torch.int32, device="cuda")
+            self._cap = cap
+
+    def forward_fused(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        global launches
+        T, H = x.shape
+        W, k = self.world, self.topk
+        self._buffers(T)
+        idx, wts = self.route(logits)
+        flat_e = idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        send_counts = torch.bincount(flat_e, minlength=W)
+        fused_dispatch(self.group, x, order, send_counts, self._meta, self._xrecv, self._cnt, k)
+        n_recv, over = self._meta[2 * W:2 * W + 2].tolist()  # the only host read: the GEMM needs its row count
+        if over:
+            raise RuntimeError("expert receive buffer overflow")
+        if n_recv > 0:
+            if self.use_native_gemm:
+                h = gemm_bf16(self._xrecv[:n_recv], self.w1, epilogue="silu")
+                gemm_bf16(h, self.w2, out=self._yout[:n_recv])
+                launches += 2
+            else:
+                torch.matmul(torch.nn.functional.silu(self._xrecv[:n_recv] @ self.w1.t()), self.w2.t(),
+                             out=self._yout[:n_recv])
+        pos = torch.empty_like(order)
+        pos[order] = torch.arange(order.numel(), device=order.device)
+        out = torch.empty_like(x)
+        fused_combine(self.group, flat_e, pos, wts.contiguous().view(-1), out, self._meta, self._yout, k)
+        self.stats = {"recv_rows": n_recv}
+        return out
 
     def route(self, logits: torch.Tensor):
         """Returns expert ids [T, k] and normalised weights [T, k] (fp32)."""
@@ -72,6 +155,11 @@ class ExpertParallelMoE:
         return torch.nn.functional.silu(rows @ self.w1.t()) @ self.w2.t()
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        if self.fused:
+            return self.forward_fused(x, logits)
+        return self.forward_alltoall(x, logits)
+
+    def forward_alltoall(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         T, H = x.shape
         W, k = self.world, self.topk
         idx, wts = self.route(logits)

@@ -330,7 +330,11 @@ def _tp_and_moe(comm):
     torch.cuda.synchronize()
     ref = reference_moe(x, logits, list(w1all), list(w2all), topk=2)
     assert (out - ref).abs().max().item() < 3e-2 * ref.abs().max().item() + 1e-3
+    out2 = moe.forward_alltoall(x, logits).float()
+    assert (out2 - ref).abs().max().item() < 3e-2 * ref.abs().max().item() + 1e-3
     assert sum(moe.stats["sent_rows"]) == T * 2
+    out3 = moe(x, logits).float()  # buffers and count table are reused
+    assert torch.equal(out3, out)
     g.check()
     return True
 

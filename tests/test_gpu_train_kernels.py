@@ -5,7 +5,8 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("rows,vocab,pad", [(64, 1000, 24), (33, 50257, 47), (8, 257, 0)])
+@pytest.mark.parametrize("rows,vocab,pad", [(64, 1000, 24), (33, 50257, 47), (8, 257, 0), (5, 70000, 0),
+                                            (16, 32768, 0), (3, 57347, 5)])
 def test_softmax_xent(rows, vocab, pad):
     from oneccl_b200.ops.train import softmax_cross_entropy
 
