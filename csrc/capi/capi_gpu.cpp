@@ -285,6 +285,12 @@ CCLX_API int cclx_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
         [&] { gemm_bf16_plain(A, B, C, M, N, K, epilogue, ctas, (uint32_t*)err_words, (cudaStream_t)stream); });
 }
 
+CCLX_API int cclx_gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int clusters,
+                                void* err_words, void* stream) {
+    return capi::guard(
+        [&] { gemm_bf16_2sm(A, B, C, M, N, K, epilogue, clusters, (uint32_t*)err_words, (cudaStream_t)stream); });
+}
+
 CCLX_API void* cclx_fused_plan_create(void* dc, int mode, int M, int N, int K, int epilogue, int n_comm, int ctas) {
     fused_plan* p = nullptr;
     capi::guard([&] { p = fused_plan_create(*(device_comm*)dc, mode, M, N, K, epilogue, n_comm, ctas); });

@@ -33,6 +33,14 @@ CUtensorMap make_map(const void* base, uint64_t rows, uint64_t cols, uint32_t bo
     return m;
 }
 
+} // namespace
+
+CUtensorMap make_bf16_kmajor_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    return make_map(base, rows, cols, box_rows);
+}
+
+namespace {
+
 int pick_bn(int N) {
     return (N % 256 == 0 || N % 128 != 0) ? 256 : 128;
 }
@@ -81,6 +89,14 @@ int sm_count() {
 void gemm_bf16_plain(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int ctas,
                      uint32_t* err, cudaStream_t st) {
     CCL_THROW_IF_NOT(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "unsupported GEMM shape ", M, "x", N, "x", K);
+    // CTA pairs (two-SM MMA) when the problem has at least one 256-row tile per pair; a negative `ctas` forces
+    // the single-CTA kernel, CCL_CUDA_GEMM_2SM=0 turns the pairs off
+    if (ctas >= 0 && env_data::get().gemm_2sm && M >= 256 && N >= 128) {
+        gemm_bf16_2sm(A, B, C, M, N, K, epilogue, ctas / 2, err, st);
+        return;
+    }
+    if (ctas < 0)
+        ctas = -ctas - 1; // -(n + 1) asks for the single-CTA kernel on n CTAs (0 = all SMs)
     const int bn = pick_bn(N);
     fused_params P;
     std::memset(&P, 0, sizeof(P));

@@ -60,6 +60,7 @@ def _proto(lib):
         "cclx_reduce_local": (i, [vp, vp, sz, i, i, vp]),
         "cclx_pack": (i, [vp, vp, i, vp, i, sz, vp]),
         "cclx_gemm_bf16": (i, [vp, vp, vp, i, i, i, i, i, vp, vp]),
+        "cclx_gemm_bf16_2sm": (i, [vp, vp, vp, i, i, i, i, i, vp, vp]),
         "cclx_fused_plan_create": (vp, [vp, i, i, i, i, i, i, i]),
         "cclx_fused_plan_destroy": (i, [vp]),
         "cclx_fused_plan_x_shard": (vp, [vp, i]),
