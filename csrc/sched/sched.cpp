@@ -437,8 +437,10 @@ size_t worker::do_work() {
         std::lock_guard<std::mutex> lk(ex_->freeze_mu_); // parked while the executor is locked
     }
     iteration_++;
-    if (ex_->transport_)
-        ex_->transport_->poll(idx_);
+    if (auto list = std::atomic_load(&ex_->transports_))
+        for (auto& w : *list)
+            if (auto tr = w.lock())
+                tr->poll(idx_);
     if (idx_ == 0 && ex_->service_hook)
         ex_->service_hook();
     size_t n = queue_.progress(iteration_, env_data::get().strict_order);
@@ -527,12 +529,22 @@ executor& executor::get() {
 
 void executor::ensure_started(std::shared_ptr<atl_transport> tr) {
     std::lock_guard<std::mutex> lk(mu_);
-    if (!workers_.empty()) {
-        if (tr && !transport_)
-            transport_ = tr;
-        return;
+    if (tr) {
+        // copy-on-write list: workers read a snapshot without taking a lock; dead entries are dropped here
+        auto next = std::make_shared<transport_list>();
+        bool known = false;
+        if (auto cur = std::atomic_load(&transports_))
+            for (auto& w : *cur)
+                if (auto live = w.lock()) {
+                    next->push_back(w);
+                    known = known || live == tr;
+                }
+        if (!known)
+            next->push_back(tr);
+        std::atomic_store(&transports_, std::shared_ptr<const transport_list>(next));
     }
-    transport_ = tr;
+    if (!workers_.empty())
+        return;
     const env_data& env = env_data::get();
     for (int i = 0; i < env.worker_count; i++)
         workers_.emplace_back(new worker(this, i));
@@ -552,7 +564,7 @@ void executor::shutdown() {
     for (auto& w : workers_)
         w->stop();
     workers_.clear();
-    transport_.reset();
+    std::atomic_store(&transports_, std::shared_ptr<const transport_list>());
     service_hook = nullptr;
 }
 

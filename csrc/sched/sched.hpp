@@ -233,7 +233,6 @@ public:
     void wait(master_sched* m, uint64_t ticket);
     bool test(master_sched* m, uint64_t ticket);
     void launch_now(master_sched* m); // arm + enqueue (internal)
-    std::shared_ptr<atl_transport> transport() { return transport_; }
     // service hook run by worker 0 every iteration (fusion flush)
     std::function<void()> service_hook;
     // hold every worker outside its progress loop (datatype table changes, resize)
@@ -246,7 +245,9 @@ private:
     friend class worker;
     executor() = default;
     std::vector<std::unique_ptr<worker>> workers_;
-    std::shared_ptr<atl_transport> transport_;
+    // every transport with a live communicator is polled; the executor does not keep them alive
+    typedef std::vector<std::weak_ptr<atl_transport>> transport_list;
+    std::shared_ptr<const transport_list> transports_;
     std::atomic<unsigned> rr_{ 0 };
     std::mutex mu_;
     std::mutex freeze_mu_;

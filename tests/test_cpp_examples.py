@@ -74,3 +74,36 @@ def test_benchmark_tool(bindir):
         assert rc == 0, err[-2000:]
     lines = [l for l in outs[0][1].splitlines() if l.startswith("allreduce,")]
     assert len(lines) == 13 and lines[-1].split(",")[1] == "4096"
+
+
+def test_external_launcher_reforms_the_communicator(bindir):
+    """No process manager: rank / size / address file on the command line, five incarnations."""
+    exe = bindir / "external_launcher"
+    _build(ROOT / "examples" / "external_launcher" / "external_launcher.cpp", exe)
+    d = tempfile.mkdtemp(prefix="cclx_el_")
+    world = 3
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, CCL_PROCESS_LAUNCHER="none", CCL_LOCAL_RANK=str(r), CCL_LOCAL_SIZE=str(world))
+        procs.append(subprocess.Popen([str(exe), str(world), str(r), os.path.join(d, "addr"), "5"],
+                                      stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env))
+    outs = [p.communicate(timeout=180) + (p.returncode,) for p in procs]
+    for o, err, rc in outs:
+        assert rc == 0, err[-2000:]
+    assert "PASSED after 5" in outs[0][0]
+
+
+def test_point_to_point_latency_and_bandwidth_tools(bindir):
+    lat, bw = bindir / "ccl_latency", bindir / "ccl_bw"
+    _build(ROOT / "examples" / "pt2pt" / "ccl_latency.cpp", lat)
+    _build(ROOT / "examples" / "pt2pt" / "ccl_bw.cpp", bw)
+    outs = _run_ranks(lat, 2, extra_args=("1", "4096", "20"))
+    for rc, o, err in outs:
+        assert rc == 0, err[-2000:]
+    rows = [l for l in outs[0][1].splitlines() if l and l[0].isdigit()]
+    assert len(rows) == 13 and all(float(r.split(",")[1]) > 0 for r in rows) and "PASSED" in outs[0][1]
+    outs = _run_ranks(bw, 2, extra_args=("1024", "262144", "4", "4"))
+    for rc, o, err in outs:
+        assert rc == 0, err[-2000:]
+    rows = [l for l in outs[0][1].splitlines() if l and l[0].isdigit()]
+    assert len(rows) == 9 and all(float(r.split(",")[1]) > 0 for r in rows) and "PASSED" in outs[0][1]
