@@ -90,6 +90,13 @@ def main():
     res = {"config": {"tokens": args.tokens, "d_model": args.d_model, "d_ff": args.d_ff, "tp": world, "dtype": "bf16"},
            "max_abs_diff_vs_nccl_cublas": err, "ref_abs_max": scale}
     res["fused_ms"] = timeit(fused)
+    # the two fused stages on their own, and the bare GEMMs they contain (no communication)
+    res["fused_up_ms"] = timeit(lambda: mlp.up.run(None, mlp.w_up, out=mlp.h))
+    res["fused_down_ms"] = timeit(lambda: mlp.down.run(mlp.h, mlp.w_down, out=mlp.y))
+    from oneccl_b200.ops.gemm import gemm_bf16
+    tmp = torch.empty((args.tokens, args.d_model), dtype=torch.bfloat16, device="cuda")
+    res["gemm_up_only_ms"] = timeit(lambda: gemm_bf16(xf, mlp.w_up, out=mlp.h, epilogue="silu"))
+    res["gemm_down_only_ms"] = timeit(lambda: gemm_bf16(mlp.h, mlp.w_down, out=tmp))
     res["unfused_ours_ms"] = timeit(unfused_ours)
     res["nccl_cublas_ms"] = timeit(nccl_cublas)
     flops = 2.0 * args.tokens * args.d_model * (args.d_ff // world) * 2

@@ -21,19 +21,22 @@ def _check(out, ref, K):
 
 @pytest.mark.parametrize("shape", [(128, 256, 64), (128, 256, 256), (256, 512, 512), (1024, 1792, 1024),
                                    (384, 128, 192), (200, 264, 136)])
-def test_gemm_plain(shape):
+@pytest.mark.parametrize("kernel", ["1sm", "2sm", "auto"])
+def test_gemm_plain(shape, kernel):
+    """One CTA per 128 x 256 tile, CTA pairs on 256 x 256 tiles (cta_group::2), and the library's choice."""
     from oneccl_b200.ops.gemm import gemm_bf16
 
     M, N, K = shape
     g = torch.Generator(device="cuda").manual_seed(0)
     a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g, device="cuda") * 0.1).to(torch.bfloat16)
-    out = gemm_bf16(a, w, check=True)
+    out = gemm_bf16(a, w, check=True, kernel=kernel)
     torch.cuda.synchronize()
     _check(out, _ref(a, w), K)
 
 
-def test_gemm_silu_and_persistence():
+@pytest.mark.parametrize("kernel", ["1sm", "2sm"])
+def test_gemm_silu_and_persistence(kernel):
     """More tiles than CTAs (each CTA loops, both TMEM accumulators are reused) + SiLU epilogue."""
     from oneccl_b200.ops.gemm import gemm_bf16
 
@@ -41,7 +44,7 @@ def test_gemm_silu_and_persistence():
     g = torch.Generator(device="cuda").manual_seed(1)
     a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
     w = (torch.randn(N, K, generator=g, device="cuda") * 0.05).to(torch.bfloat16)
-    out = gemm_bf16(a, w, epilogue="silu", ctas=8, check=True)
+    out = gemm_bf16(a, w, epilogue="silu", ctas=8, check=True, kernel=kernel)
     torch.cuda.synchronize()
     _check(out, _ref(a, w, silu=True), K)
 
