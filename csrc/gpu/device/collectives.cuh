@@ -278,16 +278,33 @@ __global__ void __launch_bounds__(1024) allreduce_pipelined_kernel(const comm_de
     const bool scale = a.do_scale != 0;
     char* my_stage = c.staging[c.rank];
     bool ok = true;
+    // with several chunks in flight the block splits into a reducing half and a copying half, so that
+    // the local copies of chunks j and j-2 really run while chunk j-1 is on the wire
+    const bool split = nchunks >= 2 && nt >= 64;
+    const size_t half = nt / 2;
+    const bool do_red = !split || tid < half, do_copy = !split || tid >= half;
+    const size_t rt = tid, rnt = split ? half : nt;
+    const size_t ct = split ? tid - half : tid, cnt = split ? nt - half : nt;
 
     for (size_t j = 0; j < nchunks + 2; j++) {
-        if (j < nchunks) { // A
+        if (j < nchunks && do_copy) { // A
             const size_t p0 = j * cp + blockIdx.x * piece;
             char* dst = my_stage + gbase + (j & 1) * cp * 16 + blockIdx.x * piece * 16;
             const size_t n = p0 < npacks ? min(piece, npacks - p0) : 0;
-            for (size_t i = tid; i < n; i += nt)
+            size_t i = ct;
+            for (; i + 3 * cnt < n; i += 4 * cnt) {
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    v[u] = load_pack<T>(send, p0 + i + u * cnt, count, vin);
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    st16(dst + ((i + u * cnt) << 4), v[u]);
+            }
+            for (; i < n; i += cnt)
                 st16(dst + (i << 4), load_pack<T>(send, p0 + i, count, vin));
         }
-        if (j >= 1 && j <= nchunks && ok) { // B
+        if (j >= 1 && j <= nchunks && ok && do_red) { // B
             const size_t jj = j - 1;
             const size_t q0 = blockIdx.x * piece + (size_t)c.rank * sub; // first pack of my share inside the chunk
             const size_t p0 = jj * cp + q0;
@@ -314,24 +331,27 @@ __global__ void __launch_bounds__(1024) allreduce_pipelined_kernel(const comm_de
                 }
             };
             if constexpr (NVLS) {
-                size_t i = tid;
-                for (; i + nt < n; i += 2 * nt) { // two switch round trips in flight per thread
-                    uint4 v0 = multimem_ld_reduce_add16<T>(c.mc_staging + in_off + (i << 4));
-                    uint4 v1 = multimem_ld_reduce_add16<T>(c.mc_staging + in_off + ((i + nt) << 4));
-                    A a0[N], a1[N];
-                    unpack16<T, A>(v0, a0);
-                    unpack16<T, A>(v1, a1);
-                    finish(i, a0);
-                    finish(i + nt, a1);
+                size_t i = rt;
+                for (; i + 3 * rnt < n; i += 4 * rnt) { // four switch round trips in flight per thread
+                    uint4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        v[u] = multimem_ld_reduce_add16<T>(c.mc_staging + in_off + ((i + u * rnt) << 4));
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        A au[N];
+                        unpack16<T, A>(v[u], au);
+                        finish(i + u * rnt, au);
+                    }
                 }
-                for (; i < n; i += nt) {
+                for (; i < n; i += rnt) {
                     A a0[N];
                     unpack16<T, A>(multimem_ld_reduce_add16<T>(c.mc_staging + in_off + (i << 4)), a0);
                     finish(i, a0);
                 }
             }
             else {
-                for (size_t i = tid; i < n; i += nt) {
+                for (size_t i = rt; i < n; i += rnt) {
                     uint4 v[MAX_RANKS];
                     for (int p = 0; p < W; p++) // fixed rank order: reproducible rounding
                         v[p] = ld_cv16(c.staging[p] + in_off + (i << 4));
@@ -343,32 +363,48 @@ __global__ void __launch_bounds__(1024) allreduce_pipelined_kernel(const comm_de
                 }
             }
         }
-        if (j >= 2 && ok) { // C
+        if (j >= 2 && ok && do_copy) { // C
             const size_t jj = j - 2;
             const size_t p0 = jj * cp + blockIdx.x * piece;
             const size_t n = p0 < npacks ? min(piece, npacks - p0) : 0;
             const char* src = my_stage + out_base + (jj & 1) * cp * OUTP + blockIdx.x * piece * OUTP;
-            for (size_t i = tid; i < n; i += nt) {
+            auto put = [&](size_t i, const uint4(&raw)[OQ]) {
                 const size_t e0 = (p0 + i) * N;
-                alignas(16) Tout o[ON];
-#pragma unroll
-                for (int q = 0; q < OQ; q++)
-                    reinterpret_cast<uint4*>(o)[q] = ld_cv16(src + i * OUTP + q * 16);
+                const Tout* o = reinterpret_cast<const Tout*>(raw);
                 if (vout && e0 + N <= count) {
                     if constexpr (RAWP >= 16) {
 #pragma unroll
                         for (int q = 0; q < OQ; q++)
-                            reinterpret_cast<uint4*>(recv + e0)[q] = reinterpret_cast<const uint4*>(o)[q];
+                            reinterpret_cast<uint4*>(recv + e0)[q] = raw[q];
                     }
                     else
-                        *reinterpret_cast<uint2*>(recv + e0) = *reinterpret_cast<const uint2*>(o);
+                        *reinterpret_cast<uint2*>(recv + e0) = *reinterpret_cast<const uint2*>(raw);
                 }
                 else {
 #pragma unroll
-                    for (int k = 0; k < N; k++)
-                        if (e0 + k < count)
-                            recv[e0 + k] = o[k];
+                    for (int k2 = 0; k2 < N; k2++)
+                        if (e0 + k2 < count)
+                            recv[e0 + k2] = o[k2];
                 }
+            };
+            size_t i = ct;
+            for (; i + 3 * cnt < n; i += 4 * cnt) { // four loads in flight per thread
+                uint4 raw[4][OQ];
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+#pragma unroll
+                    for (int q = 0; q < OQ; q++)
+                        raw[u][q] = ld_cv16(src + (i + u * cnt) * OUTP + q * 16);
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    put(i + u * cnt, raw[u]);
+            }
+            for (; i < n; i += cnt) {
+                uint4 raw[OQ];
+#pragma unroll
+                for (int q = 0; q < OQ; q++)
+                    raw[q] = ld_cv16(src + i * OUTP + q * 16);
+                put(i, raw);
             }
         }
         if (j <= nchunks)
