@@ -13,6 +13,7 @@
 #include "core/log.hpp"
 #include "fusion/fusion.hpp"
 #include "gpu/device_comm.hpp"
+#include "bootstrap/elastic.hpp"
 #include "topo/numa.hpp"
 #include "topo/topo.hpp"
 
@@ -100,6 +101,64 @@ CCLX_API int cclx_kvs_barrier(void* h, const char* name, int participants, int t
 
 CCLX_API int cclx_kvs_destroy(void* h) {
     return capi::guard([&] { delete (kvs_handle*)h; });
+}
+
+// ---- elastic membership ------------------------------------------------------------------------
+struct elastic_handle {
+    std::unique_ptr<elastic_group> g;
+};
+
+CCLX_API void* cclx_elastic_create(void* kvs_h, const char* pod_id, int heartbeat_ms, int dead_after_ms, int min_size) {
+    elastic_handle* h = nullptr;
+    capi::guard([&] {
+        h = new elastic_handle{ std::unique_ptr<elastic_group>(
+            new elastic_group(((kvs_handle*)kvs_h)->k, pod_id, heartbeat_ms, dead_after_ms)) };
+        h->g->set_min_size((size_t)std::max(min_size, 1));
+    });
+    return h;
+}
+// callback: int (*fn)(size_t live_pods) returning 0 wait, 1 run, 2 finalize (nullptr restores the default)
+CCLX_API int cclx_elastic_set_resize_fn(void* h, int (*fn)(size_t)) {
+    return capi::guard([&] {
+        if (fn)
+            ((elastic_handle*)h)->g->set_resize_fn([fn](size_t n) { return (resize_action)fn(n); });
+        else
+            ((elastic_handle*)h)->g->set_resize_fn(nullptr);
+    });
+}
+// out: rank, size, generation; members as a comma separated list in `members` (cap bytes)
+CCLX_API int cclx_elastic_form(void* h, int timeout_ms, long long* out3, char* members, size_t cap) {
+    return capi::guard([&] {
+        elastic_group::view v = ((elastic_handle*)h)->g->form(timeout_ms);
+        out3[0] = v.rank;
+        out3[1] = v.size;
+        out3[2] = (long long)v.generation;
+        std::string list;
+        for (auto& m : v.members)
+            list += (list.empty() ? "" : ",") + m;
+        CCL_THROW_IF_NOT(list.size() + 1 <= cap, "member list buffer too small");
+        std::memcpy(members, list.c_str(), list.size() + 1);
+    });
+}
+CCLX_API int cclx_elastic_changed(void* h) {
+    int r = -1;
+    capi::guard([&] { r = ((elastic_handle*)h)->g->changed() ? 1 : 0; });
+    return r;
+}
+CCLX_API int cclx_elastic_leave(void* h) {
+    return capi::guard([&] { ((elastic_handle*)h)->g->leave(); });
+}
+CCLX_API int cclx_elastic_destroy(void* h) {
+    return capi::guard([&] { delete (elastic_handle*)h; });
+}
+// communicator of the current generation (bootstraps through the generation's key prefix)
+CCLX_API void* cclx_elastic_comm_create(void* h) {
+    comm_handle* c = nullptr;
+    capi::guard([&] {
+        elastic_group& g = *((elastic_handle*)h)->g;
+        c = new comm_handle{ host_comm::create(g.current().size, g.current().rank, g.generation_store()) };
+    });
+    return c;
 }
 
 // ---- communicator ------------------------------------------------------------------------------

@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import ctypes as C
 import os
-from typing import Optional, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 
@@ -394,3 +394,71 @@ def init_from_env(port_offset: Optional[int] = None) -> Communicator:
     ip_port = f"{addr}_{port + port_offset}"
     kvs = KVS.create_main(ip_port) if rank == 0 else KVS.connect(ip_port)
     return Communicator(world, rank, kvs)
+
+
+class ElasticGroup:
+    """Membership that survives pods leaving and joining (the reference's resizable process
+    manager, ``CCL_PM_TYPE=resizable``): every pod heart-beats into the KVS, the live pods agree
+    on a member list ("generation") and re-form their communicator over it.
+
+        eg = ElasticGroup(kvs, pod_id="worker-3", min_size=2)
+        rank, size, gen = eg.form()            # blocks until the live pods agree
+        comm = eg.communicator()
+        ...
+        if eg.changed():                        # somebody died, left or joined
+            comm.close(); eg.form(); comm = eg.communicator()
+
+    ``resize_fn(n)`` may veto a size: return "wait", "run" or "finalize"."""
+
+    _ACTIONS = {"wait": 0, "run": 1, "finalize": 2}
+
+    def __init__(self, kvs: "KVS", pod_id: Optional[str] = None, heartbeat_ms: int = 100, dead_after_ms: int = 1000,
+                 min_size: int = 1, resize_fn=None):
+        import os
+        import socket
+
+        self._lib = _lib.load()
+        self._kvs = kvs
+        pod_id = pod_id or f"{socket.gethostname()}-{os.getpid()}"
+        h = self._lib.cclx_elastic_create(kvs._h, pod_id.encode(), heartbeat_ms, dead_after_ms, min_size)
+        if not h:
+            raise _lib.CclError(self._lib.cclx_last_error().decode())
+        self._h = C.c_void_p(h)
+        self.pod_id = pod_id
+        self.rank = self.size = -1
+        self.generation = 0
+        self.members: List[str] = []
+        self._cb = None
+        if resize_fn is not None:
+            proto = C.CFUNCTYPE(C.c_int, C.c_size_t)
+            self._cb = proto(lambda n: self._ACTIONS[resize_fn(int(n))])
+            _lib.check(self._lib.cclx_elastic_set_resize_fn(self._h, C.cast(self._cb, C.c_void_p)))
+
+    def form(self, timeout_ms: int = 60000):
+        out = (C.c_longlong * 3)()
+        buf = C.create_string_buffer(1 << 16)
+        _lib.check(self._lib.cclx_elastic_form(self._h, timeout_ms, out, buf, len(buf)))
+        self.rank, self.size, self.generation = int(out[0]), int(out[1]), int(out[2])
+        self.members = buf.value.decode().split(",") if buf.value else []
+        return self.rank, self.size, self.generation
+
+    def changed(self) -> bool:
+        r = self._lib.cclx_elastic_changed(self._h)
+        if r < 0:
+            raise _lib.CclError(self._lib.cclx_last_error().decode())
+        return bool(r)
+
+    def communicator(self) -> "Communicator":
+        h = self._lib.cclx_elastic_comm_create(self._h)
+        if not h:
+            raise _lib.CclError(self._lib.cclx_last_error().decode())
+        return Communicator(_handle=h, kvs=self._kvs)
+
+    def leave(self):
+        if self._h:
+            _lib.check(self._lib.cclx_elastic_leave(self._h))
+
+    def close(self):
+        if self._h:
+            self._lib.cclx_elastic_destroy(self._h)
+            self._h = None
