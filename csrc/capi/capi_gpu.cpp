@@ -92,6 +92,17 @@ CCLX_API int cclx_dc_abort(void* h) {
 CCLX_API int cclx_dc_set_timeout_ms(void* h, size_t ms) {
     return capi::guard([&] { ((device_comm*)h)->set_timeout_ms(ms); });
 }
+// registration of ordinary device allocations for zero-copy peer access (collective; arrays hold one
+// entry in real mode and `world` entries in emulation mode); returns the registration id or -1
+CCLX_API int cclx_dc_register(void* h, void* const* ptrs, const size_t* bytes) {
+    int id = -1;
+    capi::guard([&] { id = ((device_comm*)h)->register_user(ptrs, bytes); });
+    return id;
+}
+CCLX_API int cclx_dc_deregister(void* h, int id) {
+    return capi::guard([&] { ((device_comm*)h)->deregister_user(id); });
+}
+
 CCLX_API unsigned long long cclx_dc_algo_hits(void* h, int coll, int algo) {
     return ((device_comm*)h)->algo_hits[coll * ga_last + algo];
 }

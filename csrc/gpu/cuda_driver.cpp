@@ -41,6 +41,7 @@ const driver_api& driver() {
         LOAD(DeviceGet);
         LOAD(DeviceGetAttribute);
         LOAD(CtxGetCurrent);
+        LOAD(MemGetAddressRange);
         LOAD(MemCreate);
         LOAD(MemRelease);
         LOAD(MemAddressReserve);

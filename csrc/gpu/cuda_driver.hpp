@@ -22,6 +22,7 @@ struct driver_api {
     decltype(&cuDeviceGet) DeviceGet = nullptr;
     decltype(&cuDeviceGetAttribute) DeviceGetAttribute = nullptr;
     decltype(&cuCtxGetCurrent) CtxGetCurrent = nullptr;
+    decltype(&cuMemGetAddressRange) MemGetAddressRange = nullptr;
     decltype(&cuMemCreate) MemCreate = nullptr;
     decltype(&cuMemRelease) MemRelease = nullptr;
     decltype(&cuMemAddressReserve) MemAddressReserve = nullptr;

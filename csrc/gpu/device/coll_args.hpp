@@ -23,6 +23,8 @@ enum : int {
     CF_SYMM_IN = 1, // send buffer lives in the symmetric heap (offset given in in_off)
     CF_SYMM_OUT = 2, // recv buffer lives in the symmetric heap (offset given in out_off)
     CF_NVLS = 4, // use multimem instructions on the multicast window
+    CF_REG_IN = 16, // the send buffers are registered allocations: peers' addresses in reg_in
+    CF_REG_OUT = 32, // the recv buffers are registered allocations: peers' addresses in reg_out
     CF_UNIFORM = 8 // equal 16-byte-multiple blocks at contiguous displacements, 16-byte aligned user buffers
 };
 
@@ -39,6 +41,8 @@ struct coll_args {
     int emu;
     int flags;
     int peer; // point-to-point partner
+    const char* reg_in[ARG_MAX_RANKS]; // CF_REG_IN: rank p's send buffer as mapped here
+    char* reg_out[ARG_MAX_RANKS]; // CF_REG_OUT: rank p's recv buffer as mapped here
 };
 
 } // namespace dev

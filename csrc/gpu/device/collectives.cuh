@@ -78,6 +78,15 @@ __device__ __forceinline__ bool out_vec_ok(const Tout* p) {
     (void)nt;                                                    \
     (void)ra
 
+// rank p's send / recv buffer of a zero-copy operation: an offset into the symmetric heap, or the
+// address of p's registered allocation as mapped in this process
+__device__ __forceinline__ const char* peer_in(const comm_dev& c, const coll_args& a, int p) {
+    return (a.flags & CF_REG_IN) ? a.reg_in[p] : c.heap[p] + a.in_off;
+}
+__device__ __forceinline__ char* peer_out(const comm_dev& c, const coll_args& a, int p) {
+    return (a.flags & CF_REG_OUT) ? a.reg_out[p] : c.heap[p] + a.out_off;
+}
+
 // ---------------------------------------------------------------------------
 // one-shot allreduce: push my data into slot[rank] of everybody's staging,
 // one barrier, reduce the `world` slots locally.
@@ -488,7 +497,7 @@ __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* ta
                     t[k] = from_acc<T, A>(scale ? apply_scale<A>(acc[k], a.scale) : acc[k]);
                 for (int k = 0; k < W; k++) {
                     const int p = (c.rank + k) % W;
-                    st16(c.heap[p] + a.out_off + (i << 4), o);
+                    st16(peer_out(c, a, p) + (i << 4), o);
                 }
             };
             size_t i = mlo + lo + tid;
@@ -496,8 +505,8 @@ __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* ta
             for (; i + nt < end; i += 2 * nt) {
                 uint4 v0[MAX_RANKS], v1[MAX_RANKS];
                 for (int p = 0; p < W; p++) {
-                    v0[p] = ld_cv16(c.heap[p] + a.in_off + (i << 4));
-                    v1[p] = ld_cv16(c.heap[p] + a.in_off + ((i + nt) << 4));
+                    v0[p] = ld_cv16(peer_in(c, a, p) + (i << 4));
+                    v1[p] = ld_cv16(peer_in(c, a, p) + ((i + nt) << 4));
                 }
                 reduce_one(i, v0);
                 reduce_one(i + nt, v1);
@@ -505,22 +514,22 @@ __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* ta
             for (; i < end; i += nt) {
                 uint4 v0[MAX_RANKS];
                 for (int p = 0; p < W; p++)
-                    v0[p] = ld_cv16(c.heap[p] + a.in_off + (i << 4));
+                    v0[p] = ld_cv16(peer_in(c, a, p) + (i << 4));
                 reduce_one(i, v0);
             }
         }
         if (blockIdx.x == 0 && tid < tail) {
             const size_t e = full * N + tid;
-            tail_acc = to_acc<A, T>(reinterpret_cast<const T*>(c.heap[0] + a.in_off)[e]);
+            tail_acc = to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(peer_in(c, a, 0)) + e));
             for (int p = 1; p < W; p++)
                 tail_acc = Op::apply(tail_acc,
-                                     to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(c.heap[p] + a.in_off) + e)));
+                                     to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(peer_in(c, a, p)) + e)));
         }
     }
     ok = peer_barrier(c, s);
     if (ok && blockIdx.x == 0 && tid < tail) {
         const size_t e = full * N + tid;
-        reinterpret_cast<T*>(c.heap[c.rank] + a.out_off)[e] =
+        reinterpret_cast<T*>(peer_out(c, a, c.rank))[e] =
             from_acc<T, A>(scale ? apply_scale<A>(tail_acc, a.scale) : tail_acc);
     }
     // nobody reads a peer's input after the second barrier, so the next
@@ -589,8 +598,8 @@ __global__ void __launch_bounds__(1024) reduce_scatter_symm_kernel(const comm_de
     T* recv = reinterpret_cast<T*>(ra.recv);
     const size_t rc = a.count;
     const int W = c.world;
-    const size_t boff = a.in_off + (size_t)c.rank * rc * sizeof(T); // my block inside every peer's send
-    const bool aligned = (boff & 15) == 0;
+    const size_t blk = (size_t)c.rank * rc * sizeof(T); // my block inside every peer's send
+    const bool aligned = ((((uintptr_t)peer_in(c, a, 0)) + blk) & 15) == 0;
     const size_t full = aligned ? rc / N : 0;
     const bool vout = (((uintptr_t)recv) & 15) == 0;
     size_t lo, hi;
@@ -600,20 +609,20 @@ __global__ void __launch_bounds__(1024) reduce_scatter_symm_kernel(const comm_de
         for (size_t i = lo + tid; i < hi; i += nt) {
             A acc[N];
             if (NVLS) {
-                unpack16<T, A>(multimem_ld_reduce_add16<T>(c.mc_heap + boff + (i << 4)), acc);
+                unpack16<T, A>(multimem_ld_reduce_add16<T>(c.mc_heap + a.in_off + blk + (i << 4)), acc);
             }
             else {
-                unpack16<T, A>(ld_cv16(c.heap[0] + boff + (i << 4)), acc);
+                unpack16<T, A>(ld_cv16(peer_in(c, a, 0) + blk + (i << 4)), acc);
                 for (int p = 1; p < W; p++)
-                    accum16<T, A, Op>(ld_cv16(c.heap[p] + boff + (i << 4)), acc);
+                    accum16<T, A, Op>(ld_cv16(peer_in(c, a, p) + blk + (i << 4)), acc);
             }
             store_pack<T, A, N>(recv, i, rc, vout, acc, a.scale, a.do_scale != 0);
         }
         // elements outside whole aligned packs
         for (size_t e = full * N + (size_t)blockIdx.x * nt + tid; e < rc; e += (size_t)gridDim.x * nt) {
-            A acc = to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(c.heap[0] + boff) + e));
+            A acc = to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(peer_in(c, a, 0) + blk) + e));
             for (int p = 1; p < W; p++)
-                acc = Op::apply(acc, to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(c.heap[p] + boff) + e)));
+                acc = Op::apply(acc, to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(peer_in(c, a, p) + blk) + e)));
             recv[e] = from_acc<T, A>(a.do_scale ? apply_scale<A>(acc, a.scale) : acc);
         }
     }
@@ -720,8 +729,8 @@ __global__ void __launch_bounds__(1024) allgather_symm_kernel(const comm_dev* ta
     const int W = c.world;
     const size_t bytes = a.count; // bytes per rank, multiple of 16, 16-byte aligned offsets
     const char* send = ra.send ? reinterpret_cast<const char*>(ra.send)
-                               : c.heap[c.rank] + a.out_off + (size_t)c.rank * bytes;
-    const size_t doff = a.out_off + (size_t)c.rank * bytes;
+                               : peer_out(c, a, c.rank) + (size_t)c.rank * bytes;
+    const size_t doff = (size_t)c.rank * bytes; // place of my block inside every recv buffer
     size_t lo, hi;
     split_range(bytes >> 4, gridDim.x, blockIdx.x, lo, hi);
     // peers must have finished reading the previous contents of recv
@@ -731,12 +740,12 @@ __global__ void __launch_bounds__(1024) allgather_symm_kernel(const comm_dev* ta
         for (size_t i = lo + tid; i < hi; i += nt) {
             uint4 v = load_pack<unsigned char>(reinterpret_cast<const unsigned char*>(send), i, bytes, vin);
             if (NVLS) {
-                multimem_st16(c.mc_heap + doff + (i << 4), v);
+                multimem_st16(c.mc_heap + a.out_off + doff + (i << 4), v);
             }
             else {
                 for (int k = 0; k < W; k++) {
                     const int p = (c.rank + k) % W;
-                    st16(c.heap[p] + doff + (i << 4), v);
+                    st16(peer_out(c, a, p) + doff + (i << 4), v);
                 }
             }
         }
@@ -869,13 +878,13 @@ static __global__ void __launch_bounds__(1024) alltoall_symm_kernel(const comm_d
     // peers must have finished reading the previous contents of recv
     bool ok = peer_barrier(c, s);
     if (ok) {
-        const size_t doff = a.out_off + (size_t)c.rank * b;
+        const size_t doff = (size_t)c.rank * b;
         for (size_t i = lo + tid; i < hi; i += nt) {
             uint4 v[MAX_RANKS];
             for (int k = 0; k < W; k++)
                 v[k] = *reinterpret_cast<const uint4*>(send + (size_t)((c.rank + k) % W) * b + (i << 4));
             for (int k = 0; k < W; k++)
-                st16(c.heap[(c.rank + k) % W] + doff + (i << 4), v[k]);
+                st16(peer_out(c, a, (c.rank + k) % W) + doff + (i << 4), v[k]);
         }
     }
     peer_barrier(c, s);

@@ -33,6 +33,7 @@ device_comm::~device_comm() {
 
 void device_comm::init(bootstrap_if& bs) {
     const env_data& env = env_data::get();
+    bs_ = &bs;
     rank_ = bs.rank();
     world_ = bs.size();
     emulated_ = false;
@@ -118,6 +119,10 @@ void device_comm::destroy() {
     if (!table_dev_)
         return;
     cudaDeviceSynchronize();
+    for (auto& r : regs_)
+        for (void* m : r.opened)
+            cudaIpcCloseMemHandle(m);
+    regs_.clear();
     cudaFree(table_dev_);
     table_dev_ = nullptr;
     cudaFree(state_dev_);
@@ -179,6 +184,86 @@ void device_comm::symm_free(void* p, int emu_rank) {
     size_t off = heap_.offset_of(p, emulated_ ? emu_rank : rank_);
     CCL_THROW_IF_NOT(off != (size_t)-1, "pointer is not in the symmetric heap");
     heap_.free(off);
+}
+
+// ---- registration of ordinary allocations ---------------------------------------------------
+// Reference counterpart: ze_handle_exchange_entry + ipc_handle_manager (src/sched/entry/ze/
+// ze_handle_exchange_entry.cpp:95-257, src/sched/ze/ze_handle_manager.cpp:292-335): the handle of the
+// allocation's BASE plus the offset of the buffer inside it travel to the peers, which open the
+// handle once.  Here the exchange happens at registration, not per operation.
+int device_comm::register_user(void* const* ptrs, const size_t* bytes) {
+    user_reg r;
+    r.live = true;
+    r.base.assign(world_, nullptr);
+    r.bytes.assign(world_, 0);
+    if (emulated_) {
+        for (int q = 0; q < world_; q++) {
+            r.base[q] = (char*)ptrs[q];
+            r.bytes[q] = bytes[q];
+        }
+    }
+    else {
+        CCL_THROW_IF_NOT(bs_ != nullptr, "communicator has no bootstrap for the handle exchange");
+        struct wire {
+            cudaIpcMemHandle_t handle;
+            unsigned long long offset, bytes;
+        } mine{}, zero{};
+        const driver_api& d = driver();
+        CUdeviceptr abase = 0;
+        size_t asize = 0;
+        CU_CHECK(d.MemGetAddressRange(&abase, &asize, (CUdeviceptr)ptrs[0]));
+        CUDA_CHECK(cudaIpcGetMemHandle(&mine.handle, (void*)abase));
+        mine.offset = (unsigned long long)((char*)ptrs[0] - (char*)abase);
+        mine.bytes = bytes[0];
+        std::vector<wire> all(world_, zero);
+        bs_->allgather(&mine, all.data(), sizeof(wire));
+        for (int q = 0; q < world_; q++) {
+            r.bytes[q] = (size_t)all[q].bytes;
+            if (q == rank_) {
+                r.base[q] = (char*)ptrs[0];
+                continue;
+            }
+            void* mapped = nullptr;
+            CUDA_CHECK(cudaIpcOpenMemHandle(&mapped, all[q].handle, cudaIpcMemLazyEnablePeerAccess));
+            r.opened.push_back(mapped);
+            r.base[q] = (char*)mapped + all[q].offset;
+        }
+        bs_->barrier();
+    }
+    for (size_t i = 0; i < regs_.size(); i++)
+        if (!regs_[i].live) {
+            regs_[i] = std::move(r);
+            return (int)i;
+        }
+    regs_.push_back(std::move(r));
+    return (int)regs_.size() - 1;
+}
+
+void device_comm::deregister_user(int id) {
+    CCL_THROW_IF_NOT(id >= 0 && id < (int)regs_.size() && regs_[id].live, "unknown registration ", id);
+    if (!emulated_ && bs_) {
+        CUDA_CHECK(cudaDeviceSynchronize());
+        bs_->barrier(); // nobody still reads this rank's buffer
+    }
+    for (void* m : regs_[id].opened)
+        cudaIpcCloseMemHandle(m);
+    regs_[id] = user_reg();
+}
+
+bool device_comm::find_user(const void* p, size_t len, int owner, int& id, size_t& off) const {
+    const int q = owner < 0 ? (emulated_ ? 0 : rank_) : owner;
+    for (size_t i = 0; i < regs_.size(); i++) {
+        const user_reg& r = regs_[i];
+        if (!r.live)
+            continue;
+        const char* b = r.base[q];
+        if ((const char*)p >= b && (const char*)p + len <= b + r.bytes[q]) {
+            id = (int)i;
+            off = (size_t)((const char*)p - b);
+            return true;
+        }
+    }
+    return false;
 }
 
 size_t device_comm::symm_offset(const void* p, int owner) const {

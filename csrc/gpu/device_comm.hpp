@@ -79,11 +79,31 @@ public:
     // offset of p inside the heap of `owner` (emulated rank or my rank), -1 if not symmetric
     size_t symm_offset(const void* p, int owner = -1) const;
 
+    // Registration of ordinary device allocations (not from the symmetric heap) for zero-copy peer
+    // access: collective; every rank passes its own buffer (emulation: one per emulated rank).  The
+    // owners' allocations are exported with the CUDA IPC handle of their base allocation and mapped
+    // by every peer once; collectives on a registered buffer must use the same offset inside it on
+    // every rank.  Returns the registration id.
+    int register_user(void* const* ptrs, const size_t* bytes);
+    void deregister_user(int id);
+    // registration that contains [p, p + len) of `owner` (emulated rank, or this rank when -1)
+    bool find_user(const void* p, size_t len, int owner, int& id, size_t& off) const;
+    // pointer of rank q's buffer of registration `id`, as mapped in this process
+    char* user_base(int id, int q) const { return regs_[id].base[q]; }
+
     // per-algorithm launch counters (observability)
     std::vector<unsigned long long> algo_hits = std::vector<unsigned long long>(ga_last * (int)coll_last, 0);
 
 private:
     void build_tables();
+    struct user_reg {
+        bool live = false;
+        std::vector<char*> base; // per rank, as seen from this process
+        std::vector<size_t> bytes;
+        std::vector<void*> opened; // IPC mappings this registration holds (closed on deregistration)
+    };
+    std::vector<user_reg> regs_;
+    bootstrap_if* bs_ = nullptr;
     int rank_ = 0, world_ = 0;
     bool emulated_ = false;
     symm_heap heap_;

@@ -54,23 +54,26 @@ void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, i
     const size_t bytes = count * esz;
     const int entries = dc.emulated() ? W : 1;
 
-    // are both buffers of every (emulated) rank inside the symmetric heap at equal offsets?
-    bool symmetric = dt_in == dt_out;
-    size_t in_off = 0, out_off = 0;
-    for (int e = 0; e < entries && symmetric; e++) {
-        const int owner = dc.emulated() ? e : dc.rank();
-        size_t io = dc.symm_offset(ra[e].send, owner), oo = dc.symm_offset(ra[e].recv, owner);
-        if (io == (size_t)-1 || oo == (size_t)-1 || (io & 15) || (oo & 15) || (e > 0 && (io != in_off || oo != out_off)))
-            symmetric = false;
-        in_off = io;
-        out_off = oo;
+    // zero-copy needs both buffers of every rank in the symmetric heap or in a registered allocation,
+    // at equal offsets; the in-switch reduction needs both in the heap (the multicast window covers only it)
+    zc_view vin, vout;
+    if (dt_in == dt_out) {
+        vin = zero_copy_view(dc, ra, false, bytes);
+        vout = zero_copy_view(dc, ra, true, bytes);
     }
+    const bool symmetric = vin.ok && vout.ok;
+    const bool in_heap = symmetric && !vin.registered && !vout.registered;
+    const size_t in_off = vin.off, out_off = vout.off;
+    (void)entries;
 
     int algo = o.algo;
     if (algo == ga_auto)
         algo = selected_allreduce_algo(dc, bytes, symmetric, dt_in, op);
     if ((algo == ga_symm || algo == ga_nvls) && !symmetric)
-        CCL_THROW("allreduce algorithm ", gpu_algo_name(algo), " needs buffers from the symmetric heap");
+        CCL_THROW("allreduce algorithm ", gpu_algo_name(algo),
+                  " needs buffers from the symmetric heap or from a registered allocation");
+    if (algo == ga_nvls && !in_heap)
+        algo = ga_symm;
     if ((algo == ga_nvls || algo == ga_nvls_oneshot) && !dc.nvls())
         algo = algo == ga_nvls ? ga_symm : ga_oneshot;
     if (algo == ga_nvls && !nvls_type_ok(dt_in, op))
@@ -107,6 +110,10 @@ void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, i
         a.in_off = in_off;
         a.out_off = out_off;
         a.flags = dev::CF_SYMM_IN | dev::CF_SYMM_OUT | (algo == ga_nvls ? dev::CF_NVLS : 0);
+        if (vin.registered)
+            fill_registered(dc, a, vin, false);
+        if (vout.registered)
+            fill_registered(dc, a, vout, true);
         prepare_args(dc, a, ra, st);
         // per-rank slice, 16 KiB of it per block
         const int blocks = pick_blocks(dc, bytes / 16 / W + 1, 1024, o.blocks);

@@ -70,6 +70,65 @@ inline int pick_blocks(const device_comm& dc, size_t units, size_t units_per_blo
     return (int)std::max<size_t>(1, std::min<size_t>(want, (size_t)cap));
 }
 
+// Where the send (or recv) buffers of a collective live, for the zero-copy kernels: the same offset of
+// the symmetric heap on every rank, or the same offset of one registered allocation on every rank.
+struct zc_view {
+    bool ok = false;
+    bool registered = false;
+    size_t off = 0; // heap offset, or offset inside the registration
+    int id = -1;
+};
+
+inline zc_view zero_copy_view(const device_comm& dc, const dev::rank_args* ra, bool recv_side, size_t bytes) {
+    zc_view v;
+    const int entries = dc.emulated() ? dc.world() : 1;
+    bool heap = true, reg = true;
+    size_t hoff = 0, roff = 0;
+    int rid = -1;
+    for (int e = 0; e < entries; e++) {
+        const void* p = recv_side ? (const void*)ra[e].recv : ra[e].send;
+        const int owner = dc.emulated() ? e : dc.rank();
+        if (!p)
+            return v;
+        if (heap) {
+            const size_t o = dc.symm_offset(p, owner);
+            if (o == (size_t)-1 || (o & 15) || (e > 0 && o != hoff))
+                heap = false;
+            hoff = o;
+        }
+        if (reg) {
+            int id = -1;
+            size_t o = 0;
+            if (!dc.find_user(p, bytes, owner, id, o) || (((uintptr_t)p) & 15) || (e > 0 && (id != rid || o != roff)))
+                reg = false;
+            rid = id;
+            roff = o;
+        }
+    }
+    if (heap) {
+        v.ok = true;
+        v.off = hoff;
+    }
+    else if (reg) {
+        v.ok = true;
+        v.registered = true;
+        v.off = roff;
+        v.id = rid;
+    }
+    return v;
+}
+
+// peers' addresses of a registered buffer into the argument block
+inline void fill_registered(const device_comm& dc, dev::coll_args& a, const zc_view& v, bool recv_side) {
+    for (int q = 0; q < dc.world(); q++) {
+        if (recv_side)
+            a.reg_out[q] = dc.user_base(v.id, q) + v.off;
+        else
+            a.reg_in[q] = dc.user_base(v.id, q) + v.off;
+    }
+    a.flags |= recv_side ? dev::CF_REG_OUT : dev::CF_REG_IN;
+}
+
 // Fill the mode-dependent part of coll_args.  In emulation mode the per-rank
 // table is uploaded to the device (the stream is drained first because an
 // earlier launch may still read the previous table).

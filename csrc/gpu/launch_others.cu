@@ -26,29 +26,29 @@ void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t rc,
     a.scale = o.scale;
     a.do_scale = o.do_scale ? 1 : 0;
 
-    // registered send buffers: pull (or NVLS) without staging
-    bool symmetric = dt_in == dt_out;
-    size_t in_off = 0;
-    for (int e = 0; e < entries && symmetric; e++) {
-        size_t io = dc.symm_offset(ra[e].send, dc.emulated() ? e : dc.rank());
-        if (io == (size_t)-1 || (e > 0 && io != in_off))
-            symmetric = false;
-        in_off = io;
-    }
+    // send buffers in the symmetric heap or in a registered allocation: pull (or NVLS) without staging
+    zc_view vin;
+    if (dt_in == dt_out)
+        vin = zero_copy_view(dc, ra, false, rc * esz * W);
+    const bool symmetric = vin.ok;
+    const size_t in_off = vin.off;
+    (void)entries;
     int algo = o.algo;
     if (algo == ga_auto)
         algo = (symmetric && W > 1 && rc * esz > env_data::get().rs_small_threshold)
-                   ? ((dc.nvls() && nvls_type_ok(dt_in, op)) ? ga_nvls : ga_symm)
+                   ? ((dc.nvls() && nvls_type_ok(dt_in, op) && !vin.registered) ? ga_nvls : ga_symm)
                    : ga_push;
     if ((algo == ga_symm || algo == ga_nvls) && !symmetric)
         CCL_THROW("reduce_scatter algorithm ", gpu_algo_name(algo), " needs a send buffer from the symmetric heap");
-    if (algo == ga_nvls && (!dc.nvls() || !nvls_type_ok(dt_in, op)))
+    if (algo == ga_nvls && (!dc.nvls() || !nvls_type_ok(dt_in, op) || vin.registered))
         algo = ga_symm;
     dc.algo_hits[coll_reduce_scatter * ga_last + algo]++;
 
     if (algo == ga_symm || algo == ga_nvls) {
         a.count = rc;
         a.in_off = in_off;
+        if (vin.registered)
+            fill_registered(dc, a, vin, false);
         prepare_args(dc, a, ra, st);
         const int blocks = pick_blocks(dc, rc * esz / 16 + 1, 1024, o.blocks);
         CCLX_DISPATCH_DTYPE(dt_in, T, {
@@ -148,15 +148,12 @@ void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_o
     const int threads = dc.threads();
     dev::coll_args a{};
 
-    // equal 16-byte-multiple blocks into a symmetric recv buffer: direct stores
-    bool symm = W > 1;
-    size_t out_off = 0;
-    for (int e = 0; e < entries && symm; e++) {
-        size_t oo = dc.symm_offset(ra[e].recv, dc.emulated() ? e : dc.rank());
-        if (oo == (size_t)-1 || (oo & 15) || (e > 0 && oo != out_off))
-            symm = false;
-        out_off = oo;
-    }
+    // equal 16-byte-multiple blocks into a symmetric or registered recv buffer: direct stores
+    zc_view vout;
+    if (W > 1)
+        vout = zero_copy_view(dc, ra, true, total);
+    bool symm = vout.ok;
+    const size_t out_off = vout.off;
     for (int p = 0; p < W && symm; p++)
         if (ra[0].scount[p] != maxb || (maxb & 15) || ra[0].sdispl[p] != (size_t)p * maxb)
             symm = false;
@@ -165,8 +162,8 @@ void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_o
     if (algo == ga_auto) {
         if (W == 1)
             algo = ga_copy;
-        else if (symm && maxb > env_data::get().ag_small_threshold)
-            algo = dc.nvls() ? ga_nvls : ga_symm;
+        else if (symm && (maxb > env_data::get().ag_small_threshold || vout.registered))
+            algo = (dc.nvls() && !vout.registered) ? ga_nvls : ga_symm;
         else if (maxb <= env_data::get().ag_small_threshold && rounded <= dc.staging_bytes())
             algo = ga_push;
         else
@@ -175,7 +172,7 @@ void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_o
     if ((algo == ga_symm || algo == ga_nvls) && !symm)
         CCL_THROW("allgather algorithm ", gpu_algo_name(algo),
                   " needs equal 16-byte-multiple blocks and a recv buffer from the symmetric heap");
-    if (algo == ga_nvls && !dc.nvls())
+    if (algo == ga_nvls && (!dc.nvls() || vout.registered))
         algo = ga_symm;
     dc.algo_hits[coll_allgatherv * ga_last + algo]++;
 
@@ -191,6 +188,8 @@ void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_o
     if (algo == ga_symm || algo == ga_nvls) {
         a.count = maxb;
         a.out_off = out_off;
+        if (vout.registered)
+            fill_registered(dc, a, vout, true);
         prepare_args(dc, a, ra, st);
         const int blocks = pick_blocks(dc, maxb / 16, 2048, o.blocks);
         if (algo == ga_nvls)
@@ -249,25 +248,29 @@ void launch_alltoallv(device_comm& dc, const dev::rank_args* ra, const launch_op
     const size_t b = ra[0].scount[0];
     bool uniform = o.uniform && W > 1 && b > 0 && (b & 15) == 0;
     bool symm = uniform && o.algo != ga_push;
-    size_t out_off = 0;
     for (int e = 0; e < entries && uniform; e++) {
         for (int p = 0; p < W; p++)
             uniform = uniform && ra[e].scount[p] == b && ra[e].rcount[p] == b && ra[e].sdispl[p] == (size_t)p * b &&
                       ra[e].rdispl[p] == (size_t)p * b;
         const bool aligned = ((((uintptr_t)ra[e].send) | ((uintptr_t)ra[e].recv)) & 15) == 0;
-        const size_t oo = dc.symm_offset(ra[e].recv, dc.emulated() ? e : dc.rank());
-        // the direct path must be chosen by every rank or by none: it depends only on the block size
-        // and on recv being a symmetric allocation, which is a collective property
-        if (symm && (oo == (size_t)-1 || (oo & 15) || (e > 0 && oo != out_off) || !aligned || ra[e].send == ra[e].recv))
+        if (!aligned || ra[e].send == ra[e].recv)
             symm = false;
-        out_off = oo;
         uniform = uniform && aligned;
     }
+    // the direct path must be chosen by every rank or by none: it depends only on the block size and
+    // on recv being a symmetric or registered allocation, which is a collective property
+    zc_view vout;
+    if (symm && uniform)
+        vout = zero_copy_view(dc, ra, true, b * W);
+    symm = symm && vout.ok;
+    const size_t out_off = vout.off;
     symm = symm && uniform;
     if (symm) {
         dc.algo_hits[coll_alltoallv * ga_last + ga_symm]++;
         a.count = b;
         a.out_off = out_off;
+        if (vout.registered)
+            fill_registered(dc, a, vout, true);
         prepare_args(dc, a, ra, st);
         const int blocks = pick_blocks(dc, b / 16, 512, o.blocks);
         launch_kernel(dc, dev::alltoall_symm_kernel, blocks, dc.threads(), st, dc.table(), a);

@@ -52,6 +52,8 @@ def _proto(lib):
         "cclx_dc_reduce": (i, [vp, pp, pp, sz, i, i, i, i, i, f, i, vp]),
         "cclx_dc_allgatherv": (i, [vp, pp, pp, psz, psz, i, i, vp]),
         "cclx_dc_alltoallv": (i, [vp, pp, pp, psz, i, vp]),
+        "cclx_dc_register": (i, [vp, pp, psz]),
+        "cclx_dc_deregister": (i, [vp, i]),
         "cclx_dc_alltoall": (i, [vp, pp, pp, sz, i, i, vp]),
         "cclx_dc_broadcast": (i, [vp, pp, pp, sz, i, i, vp]),
         "cclx_dc_barrier": (i, [vp, vp]),

@@ -141,6 +141,25 @@ class DeviceGroup:
             self._symm.pop(x.data_ptr(), None)
         _lib.check(self._lib.cclx_dc_symm_free(self._h, off))
 
+    # ---- registration of ordinary tensors ---------------------------------------------
+    def register(self, t) -> int:
+        """Makes an ordinary CUDA tensor (not from the symmetric heap) directly readable and writable by
+        the peers' kernels: collective; every rank passes its own tensor (emulation: one per rank).  The
+        whole allocation is exported once through a CUDA IPC handle; afterwards collectives whose buffers
+        lie inside the registered tensors (same offset on every rank) run without staging copies."""
+        ts = list(t) if self.emulated_mode else [t]
+        rid = self._lib.cclx_dc_register(self._h, self._ptrs(ts),
+                                         _lib.size_array([x.numel() * x.element_size() for x in ts]))
+        if rid < 0:
+            raise _lib.CclError(self._lib.cclx_last_error().decode())
+        self._registered = getattr(self, "_registered", {})
+        self._registered[rid] = ts  # keeps the tensors alive while peers may touch them
+        return rid
+
+    def deregister(self, rid: int):
+        _lib.check(self._lib.cclx_dc_deregister(self._h, rid))
+        getattr(self, "_registered", {}).pop(rid, None)
+
     # ---- helpers ------------------------------------------------------------------
     def _lists(self, send, recv):
         if self.emulated_mode:

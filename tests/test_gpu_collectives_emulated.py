@@ -440,3 +440,62 @@ def test_moe_fused_dispatch_and_combine(group, topk):
             torch.testing.assert_close(outs[r].float(), ref, rtol=2e-2, atol=2e-2)
     for t in (xrecv, yout, cnt):
         group.symm_free(t)
+
+
+def test_registered_buffers_zero_copy(group):
+    """Ordinary tensors made peer-accessible by registration take the zero-copy kernels: allreduce
+    (views at an inner offset, odd length), reduce_scatter, allgather and alltoall."""
+    W = group.world
+    n = 300_000
+    base = [torch.zeros(n + 64, dtype=torch.float32, device="cuda") for _ in range(W)]
+    rid = group.register(base)
+    xs = [b[32:32 + n - 3] for b in base]  # same offset on every rank, 128-byte aligned, odd length
+    src = _inputs(W, n - 3, torch.float32, seed=21)
+    for x, s in zip(xs, src):
+        x.copy_(s)
+    ref = torch.stack(src).sum(0)
+    before = group.algo_hits("allreduce", "symm")
+    group.allreduce(xs, xs)  # in place, large enough for the zero-copy path
+    torch.cuda.synchronize()
+    group.check()
+    assert group.algo_hits("allreduce", "symm") == before + 1
+    for x, b in zip(xs, base):
+        torch.testing.assert_close(x, ref, rtol=1e-5, atol=1e-5)
+        assert torch.count_nonzero(b[:32]) == 0 and torch.count_nonzero(b[32 + n - 3:]) == 0
+
+    # reduce_scatter out of a registered send buffer
+    per = 70_000
+    sends = [torch.randn(per * W, device="cuda") for _ in range(W)]
+    rid2 = group.register(sends)
+    outs = [torch.empty(per, device="cuda") for _ in range(W)]
+    group.reduce_scatter(sends, outs, algo="symm")
+    torch.cuda.synchronize()
+    group.check()
+    tot = torch.stack(sends).sum(0)
+    for r, o in enumerate(outs):
+        torch.testing.assert_close(o, tot[r * per:(r + 1) * per], rtol=1e-5, atol=1e-5)
+
+    # allgather and alltoall into registered recv buffers
+    recvs = [torch.zeros(per * W, device="cuda") for _ in range(W)]
+    rid3 = group.register(recvs)
+    parts = [torch.randn(per, device="cuda") for _ in range(W)]
+    group.allgatherv(parts, recvs, algo="symm")
+    torch.cuda.synchronize()
+    group.check()
+    for o in recvs:
+        assert torch.equal(o, torch.cat(parts))
+    a2a_before = group.algo_hits("alltoallv", "symm")
+    group.alltoall(sends, recvs)
+    torch.cuda.synchronize()
+    group.check()
+    assert group.algo_hits("alltoallv", "symm") == a2a_before + 1
+    for r in range(W):
+        assert torch.equal(recvs[r], torch.cat([sends[p][r * per:(r + 1) * per] for p in range(W)]))
+    for i in (rid, rid2, rid3):
+        group.deregister(i)
+    # after deregistration the same buffers go through staging again
+    before = group.algo_hits("allreduce", "symm")
+    group.allreduce(xs, xs)
+    torch.cuda.synchronize()
+    group.check()
+    assert group.algo_hits("allreduce", "symm") == before

@@ -53,6 +53,23 @@ def _collectives(comm):
         g.symm_free(s)
         g.symm_free(sb)
     out["ar_symm_hits"] = g.algo_hits("allreduce", "symm") + g.algo_hits("allreduce", "nvls")
+    # an ordinary torch allocation registered through CUDA IPC: peers read and write it directly
+    n = 1 << 20
+    plain = torch.full((n + 128,), float(r + 1), device=dev)
+    rid = g.register(plain)
+    view = plain[64:64 + n]
+    before = g.algo_hits("allreduce", "symm")
+    comm.allreduce(view).wait()
+    torch.cuda.synchronize()
+    assert g.algo_hits("allreduce", "symm") == before + 1
+    assert torch.all(view == W * (W + 1) / 2) and torch.all(plain[:64] == r + 1) and torch.all(plain[64 + n:] == r + 1)
+    gathered = torch.zeros(W * 4096, device=dev)
+    rid2 = g.register(gathered)
+    g.allgatherv(torch.full((4096,), float(r), device=dev), gathered, algo="symm")
+    torch.cuda.synchronize()
+    assert torch.equal(gathered, torch.arange(W, device=dev, dtype=torch.float32).repeat_interleave(4096))
+    g.deregister(rid)
+    g.deregister(rid2)
     # reduce_scatter / allgather / alltoall / broadcast / reduce
     n = 5000
     x = (torch.arange(n * W, dtype=torch.float32) + r).to(dev)
