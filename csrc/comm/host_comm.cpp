@@ -184,9 +184,9 @@ void host_comm::init_device() {
         CCL_THROW_IF_NOT(host_idx_[r] == host_idx_[rank()],
                          "the device communicator needs every rank on one node (NVLink domain); use the node "
                          "sub-communicator for multi-node jobs");
-    atl_bootstrap bs(*atl_, pm_);
+    dev_bs_.reset(new atl_bootstrap(*atl_, pm_));
     dev_.reset(new gpu::device_comm());
-    dev_->init(bs);
+    dev_->init(*dev_bs_);
 }
 
 gpu::device_comm* host_comm::device() {

@@ -21,6 +21,7 @@ namespace cclx {
 
 namespace gpu {
 class device_comm;
+class bootstrap_if;
 }
 class topo_info;
 
@@ -76,6 +77,7 @@ private:
     std::shared_ptr<host_comm> node_, r2r_;
     std::vector<int> host_idx_;
     sched_cache cache_;
+    std::unique_ptr<gpu::bootstrap_if> dev_bs_; // outlives dev_: later handle exchanges (buffer registration) use it
     std::unique_ptr<gpu::device_comm> dev_;
     std::unique_ptr<pmi> dev_pm_;
     bool aborted_ = false;
