@@ -33,7 +33,7 @@ const std::vector<std::string>& algorithm_selector::known_cpu_algos(coll_type c)
 
 static const std::vector<std::string>& known_gpu_algos() {
     static const std::vector<std::string> v = { "auto", "oneshot", "twoshot", "symm", "nvls", "nvls_oneshot",
-                                                "push", "pull",    "copy", "pipelined" };
+                                                "push", "pull",    "copy", "pipelined", "ce" };
     return v;
 }
 

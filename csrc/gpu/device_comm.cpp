@@ -10,7 +10,7 @@ namespace cclx {
 namespace gpu {
 
 static const char* algo_names[] = { "auto", "oneshot", "twoshot", "symm", "nvls", "nvls_oneshot",
-                                    "push", "pull",    "copy", "pipelined" };
+                                    "push", "pull",    "copy", "pipelined", "ce" };
 
 const char* gpu_algo_name(int a) {
     return (a >= 0 && a < ga_last) ? algo_names[a] : "unknown";

@@ -34,6 +34,7 @@ enum gpu_algo : int {
     ga_pull, // allgather: pull from peers' staging
     ga_copy, // single rank / local copy
     ga_pipelined, // allreduce: chunk pipeline through staging (copy in | reduce + broadcast | copy out)
+    ga_ce, // allgather on symmetric / registered buffers by the copy engines (no SM time between two barriers)
     ga_last
 };
 const char* gpu_algo_name(int a);

@@ -134,6 +134,8 @@ void launch_reduce(device_comm& dc, const dev::rank_args* ra, size_t count, int 
     }
 }
 
+void launch_barrier(device_comm& dc, cudaStream_t st);
+
 void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_opts& o, cudaStream_t st) {
     const int W = dc.world();
     const int entries = dc.emulated() ? W : 1;
@@ -168,6 +170,33 @@ void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_o
             algo = ga_push;
         else
             algo = ga_pull;
+    }
+    if (algo == ga_ce) {
+        // Copy engines instead of SMs (the reference's copy-engine allgather, src/coll/algorithms/allgatherv/
+        // sycl/allgatherv_large_sycl_impl.hpp:77-200): barrier, every rank pulls the peers' blocks out of
+        // their recv buffers with asynchronous copies, barrier.  Between the two tiny barrier kernels no
+        // SM is busy, so a concurrent GEMM keeps the whole GPU.
+        CCL_THROW_IF_NOT(symm, "allgather algorithm ce needs equal 16-byte-multiple blocks and a recv buffer from the "
+                               "symmetric heap or a registered allocation");
+        dc.algo_hits[coll_allgatherv * ga_last + ga_ce]++;
+        for (int e = 0; e < entries; e++) {
+            const int r = dc.emulated() ? e : dc.rank();
+            char* mine = (char*)ra[e].recv + (size_t)r * maxb;
+            if (ra[e].send && ra[e].send != mine)
+                CUDA_CHECK(cudaMemcpyAsync(mine, ra[e].send, maxb, cudaMemcpyDeviceToDevice, st));
+        }
+        launch_barrier(dc, st); // every block sits in its owner's recv buffer
+        for (int e = 0; e < entries; e++) {
+            const int r = dc.emulated() ? e : dc.rank();
+            for (int k = 1; k < W; k++) {
+                const int p = (r + k) % W;
+                const char* peer = vout.registered ? dc.user_base(vout.id, p) + vout.off : dc.heap().base(p) + out_off;
+                CUDA_CHECK(cudaMemcpyAsync((char*)ra[e].recv + (size_t)p * maxb, peer + (size_t)p * maxb, maxb,
+                                           cudaMemcpyDeviceToDevice, st));
+            }
+        }
+        launch_barrier(dc, st); // nobody overwrites its block while a peer still reads it
+        return;
     }
     if ((algo == ga_symm || algo == ga_nvls) && !symm)
         CCL_THROW("allgather algorithm ", gpu_algo_name(algo),

@@ -11,7 +11,7 @@ COLL = {
     "bcast": 6, "broadcast": 7, "reduce": 8, "reduce_scatter": 9, "recv": 10, "send": 11,
 }
 GPU_ALGO = {"auto": 0, "oneshot": 1, "twoshot": 2, "symm": 3, "nvls": 4, "nvls_oneshot": 5,
-            "push": 6, "pull": 7, "copy": 8, "pipelined": 9}
+            "push": 6, "pull": 7, "copy": 8, "pipelined": 9, "ce": 10}
 
 
 def torch_to_ccl(dtype) -> int:

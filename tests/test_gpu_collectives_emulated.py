@@ -272,11 +272,15 @@ def test_allgather_inplace_and_symmetric(group):
         assert torch.equal(o, ref)
     sym = group.symm_empty((per * W,), dtype=torch.float32)
     src = [ref[r * per:(r + 1) * per].clone() for r in range(W)]
-    group.allgatherv(src, sym, algo="symm")
-    torch.cuda.synchronize()
-    group.check()
-    for s in sym:
-        assert torch.equal(s, ref)
+    for algo in ("symm", "ce"):  # stores by SMs / pulls by the copy engines between two barriers
+        for s in sym:
+            s.zero_()
+        group.allgatherv(src, sym, algo=algo)
+        torch.cuda.synchronize()
+        group.check()
+        for s in sym:
+            assert torch.equal(s, ref)
+        assert group.algo_hits("allgatherv", algo) > 0
     group.symm_free(sym)
 
 
