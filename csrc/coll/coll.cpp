@@ -533,6 +533,9 @@ event_ptr device_coll(host_comm& comm, coll_param& p, const coll_attr& attr) {
         }
         default: CCL_THROW("unsupported device collective ", (int)p.ctype);
     }
+    if (env_data::get().cuda_check_nan && p.recv_buf &&
+        (p.ctype == coll_allreduce || p.ctype == coll_reduce_scatter || (p.ctype == coll_reduce && r == p.root)))
+        gpu::launch_check_finite(*dc, p.recv_buf, p.count, out_dt, st);
     return std::make_shared<cuda_event_impl>(dc, st);
 }
 

@@ -17,7 +17,8 @@ enum : uint32_t {
     ST_ABORTED = 2,
     ST_FLAG_TIMEOUT = 3,
     ST_MBAR_TIMEOUT = 4,
-    ST_BAD_ARGS = 5
+    ST_BAD_ARGS = 5,
+    ST_NOT_FINITE = 6 // debug scan found NaN / Inf in a reduction result (CCL_CUDA_CHECK_NAN)
 };
 
 // words of comm_dev::state

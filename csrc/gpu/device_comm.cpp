@@ -154,8 +154,9 @@ void device_comm::check_status() const {
         volatile uint32_t* s = (volatile uint32_t*)status_host_ + e * 8;
         if (s[0] != dev::ST_OK) {
             static const char* what[] = { "ok",           "barrier timeout", "aborted",
-                                          "flag timeout", "mbarrier timeout", "bad arguments" };
-            const char* w = s[0] < 6 ? what[s[0]] : "unknown";
+                                          "flag timeout", "mbarrier timeout", "bad arguments",
+                                          "NaN or Inf in a reduction result (detail = element index)" };
+            const char* w = s[0] < 7 ? what[s[0]] : "unknown";
             CCL_THROW("device communicator error on rank ", table_host_[e].rank, ": ", w, " (block ", s[1],
                       ", peer ", s[2], ", detail ", s[3], ")");
         }

@@ -144,6 +144,8 @@ void launch_reduce(device_comm& dc, const dev::rank_args* ra, size_t count, int 
                    int root, const launch_opts& o, cudaStream_t st);
 // scount/sdispl of ra[*] in BYTES: block sizes / offsets inside recv (identical on every rank)
 void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_opts& o, cudaStream_t st);
+// debug: scans a floating-point result for NaN / Inf and records ST_NOT_FINITE in the status words
+void launch_check_finite(device_comm& dc, const void* buf, size_t count, int dt, cudaStream_t st);
 // scount/sdispl/rcount/rdispl of ra[*] in BYTES
 void launch_alltoallv(device_comm& dc, const dev::rank_args* ra, const launch_opts& o, cudaStream_t st);
 void launch_broadcast(device_comm& dc, const dev::rank_args* ra, size_t bytes, int root, const launch_opts& o,

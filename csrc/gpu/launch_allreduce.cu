@@ -26,7 +26,40 @@ __global__ void __launch_bounds__(1024) scale_cast_kernel(const T* in, Tout* out
     }
 }
 
+// debug scan of a result buffer (the reference's sycl_check_nan,
+// src/coll/algorithms/utils/sycl_coll_base.hpp:516-549)
+template <class T>
+__global__ void __launch_bounds__(256) check_finite_kernel(const T* p, size_t count, volatile uint32_t* status) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = (float)p[i];
+        if (!isfinite(v) && status[0] == dev::ST_OK) {
+            status[1] = blockIdx.x;
+            status[3] = (uint32_t)i;
+            __threadfence_system();
+            status[0] = dev::ST_NOT_FINITE;
+        }
+    }
+}
+
 } // namespace
+
+void launch_check_finite(device_comm& dc, const void* buf, size_t count, int dt, cudaStream_t st) {
+    if (count == 0 || dc.emulated())
+        return;
+    volatile uint32_t* status = dc.host_entry(0).status;
+    const int blocks = (int)std::min<size_t>((count + 255) / 256, (size_t)dc.sm_count() * 4);
+    if (dt == dt_float32)
+        check_finite_kernel<float><<<blocks, 256, 0, st>>>((const float*)buf, count, status);
+    else if (dt == dt_bfloat16)
+        check_finite_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)buf, count, status);
+    else if (dt == dt_float16)
+        check_finite_kernel<__half><<<blocks, 256, 0, st>>>((const __half*)buf, count, status);
+    else if (dt == dt_float64)
+        check_finite_kernel<double><<<blocks, 256, 0, st>>>((const double*)buf, count, status);
+    else
+        return;
+    CUDA_CHECK(cudaGetLastError());
+}
 
 int selected_allreduce_algo(const device_comm& dc, size_t bytes, bool symmetric, int dt, int op) {
     const env_data& env = env_data::get();

@@ -359,3 +359,32 @@ def _tp_and_moe(comm):
 @needs2
 def test_tensor_parallel_mlp_and_moe():
     assert all(run_ranks(_tp_and_moe, _world(), env=ENV, timeout=300))
+
+
+def _nan_check(comm):
+    r = comm.rank
+    torch.cuda.set_device(r)
+    dev = torch.device("cuda", r)
+    g = comm.device_group
+    x = torch.ones(5000, device=dev)
+    comm.allreduce(x).wait()
+    torch.cuda.synchronize()
+    g.check()  # finite result: nothing recorded
+    x[1234] = float("inf") if r == 0 else 1.0
+    comm.allreduce(x).wait()
+    torch.cuda.synchronize()
+    try:
+        g.check()
+        found = False
+    except Exception as e:  # noqa: BLE001
+        found = "NaN or Inf" in str(e) and "1234" in str(e)
+    g.clear_status()
+    comm.allreduce(torch.ones(8, device=dev)).wait()  # the communicator stays usable
+    torch.cuda.synchronize()
+    g.check()
+    return found
+
+
+@needs2
+def test_debug_scan_reports_non_finite_results():
+    assert all(run_ranks(_nan_check, 2, env=dict(ENV, CCL_CUDA_CHECK_NAN="1"), timeout=200))
