@@ -289,6 +289,7 @@ void env_data::parse() {
     get_bool("CCL_CUDA_GEMM_2SM", gemm_2sm);
     get_bool("CCL_CUDA_CHECK_NAN", cuda_check_nan);
     get_size("CCL_CUDA_REDUCE_SCATTER_SMALL_THRESHOLD", rs_small_threshold);
+    get_size("CCL_CUDA_REDUCE_SCATTER_PIPELINE_MIN", rs_pipelined_min);
     get_size("CCL_CUDA_ALLGATHERV_SMALL_THRESHOLD", ag_small_threshold);
     get_int("CCL_CUDA_MAX_BLOCKS", cuda_max_blocks);
     get_int("CCL_CUDA_BLOCK_THREADS", cuda_block_threads);

@@ -123,6 +123,7 @@ struct env_data {
     bool cuda_check_nan = false; // debug: scan reduction results for NaN / Inf
     bool gemm_2sm = true; // plain GEMMs run on CTA pairs (tcgen05 cta_group::2) when they have a 256-row tile
     size_t rs_small_threshold = 2u << 20;
+    size_t rs_pipelined_min = 16u << 20; // total bytes >= : ordinary send buffers take the chunk pipeline
     size_t ag_small_threshold = 4u << 20; // per-rank block <= : push through staging; above: pull
     int cuda_max_blocks = 0; // 0 = auto (co-resident cap)
     int cuda_block_threads = 512;

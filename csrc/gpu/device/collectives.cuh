@@ -557,13 +557,15 @@ __global__ void __launch_bounds__(1024) reduce_scatter_kernel(const comm_dev* ta
     const size_t gbase = (size_t)s.gen * c.staging_bytes;
     const bool vout = out_vec_ok<Tout, N>(recv);
 
-    for (int k = 1; k < W; k++) {
-        const int q = (c.rank + k) % W;
-        const T* blk = send + (size_t)q * a.stride;
-        const bool vin = (((uintptr_t)blk) & 15) == 0;
-        char* dst = c.staging[q] + gbase + (size_t)c.rank * slot;
-        for (size_t i = lo + tid; i < hi; i += nt)
-            st16(dst + (i << 4), load_pack<T>(blk, i, rc, vin));
+    // the loads for all peers are in flight together, then the stores
+    for (size_t i = lo + tid; i < hi; i += nt) {
+        uint4 v[MAX_RANKS];
+        for (int k = 1; k < W; k++) {
+            const T* blk = send + (size_t)((c.rank + k) % W) * a.stride;
+            v[k] = load_pack<T>(blk, i, rc, (((uintptr_t)blk) & 15) == 0);
+        }
+        for (int k = 1; k < W; k++)
+            st16(c.staging[(c.rank + k) % W] + gbase + (size_t)c.rank * slot + (i << 4), v[k]);
     }
     if (peer_barrier(c, s)) {
         const char* mine = c.staging[c.rank] + gbase;
@@ -586,6 +588,106 @@ __global__ void __launch_bounds__(1024) reduce_scatter_kernel(const comm_dev* ta
         }
     }
     sync_end(c, gridDim.x, 1, true);
+}
+
+// ---------------------------------------------------------------------------
+// pipelined reduce_scatter through staging for large ordinary send buffers: chunk j holds, for every
+// destination rank q, packs [j*cs, (j+1)*cs) of block q.  Iteration j of every block
+//   A: copies its piece of every slab of chunk j from send into this rank's IN[j&1]   (copying half)
+//   B: reduces its piece of MY slab of chunk j-1 across the ranks (multimem.ld_reduce, or loads from
+//      every peer) straight into recv                                                  (reducing half)
+// followed by one cross-GPU barrier; pieces are cut by block index first, so the per-block barrier
+// covers every dependency.  a.stride = elements between blocks of send, a.in_off = cs (packs per slab).
+// staging need: 2 * world * cs * 16 <= staging_bytes
+// ---------------------------------------------------------------------------
+template <class T, class Tout, class Op, bool NVLS>
+__global__ void __launch_bounds__(1024) reduce_scatter_pipelined_kernel(const comm_dev* tab, coll_args a) {
+    CCLX_KERNEL_PROLOGUE();
+    typedef typename acc_of<T>::type A;
+    constexpr int N = pack_traits<T>::N;
+    const T* send = reinterpret_cast<const T*>(ra.send);
+    Tout* recv = reinterpret_cast<Tout*>(ra.recv);
+    const size_t rc = a.count;
+    const int W = c.world;
+    const size_t rpacks = round_up16(rc * sizeof(T)) >> 4;
+    const size_t cs = a.in_off;
+    const size_t nchunks = (rpacks + cs - 1) / cs;
+    const size_t piece = cs / gridDim.x;
+    const size_t gbase = (size_t)s.gen * c.staging_bytes;
+    const bool vout = out_vec_ok<Tout, N>(recv);
+    char* my_stage = c.staging[c.rank];
+    bool ok = true;
+    const bool split = nchunks >= 2 && nt >= 64;
+    const size_t half = nt / 2;
+    const bool do_red = !split || tid < half, do_copy = !split || tid >= half;
+    const size_t rt = tid, rnt = split ? half : nt;
+    const size_t ct = split ? tid - half : tid, cnt = split ? nt - half : nt;
+
+    for (size_t j = 0; j <= nchunks; j++) {
+        if (j < nchunks && do_copy) { // A
+            const size_t p0 = j * cs + blockIdx.x * piece;
+            const size_t n = p0 < rpacks ? min(piece, rpacks - p0) : 0;
+            char* dst0 = my_stage + gbase + (j & 1) * (size_t)W * cs * 16 + blockIdx.x * piece * 16;
+            for (int q = 0; q < W; q++) {
+                const T* blk = send + (size_t)q * a.stride;
+                const bool vin = (((uintptr_t)blk) & 15) == 0;
+                char* dst = dst0 + (size_t)q * cs * 16;
+                size_t i = ct;
+                for (; i + 3 * cnt < n; i += 4 * cnt) {
+                    uint4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        v[u] = load_pack<T>(blk, p0 + i + u * cnt, rc, vin);
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        st16(dst + ((i + u * cnt) << 4), v[u]);
+                }
+                for (; i < n; i += cnt)
+                    st16(dst + (i << 4), load_pack<T>(blk, p0 + i, rc, vin));
+            }
+        }
+        if (j >= 1 && ok && do_red) { // B
+            const size_t jj = j - 1;
+            const size_t p0 = jj * cs + blockIdx.x * piece;
+            const size_t n = p0 < rpacks ? min(piece, rpacks - p0) : 0;
+            const size_t off = gbase + (jj & 1) * (size_t)W * cs * 16 + ((size_t)c.rank * cs + blockIdx.x * piece) * 16;
+            if constexpr (NVLS) {
+                size_t i = rt;
+                for (; i + 3 * rnt < n; i += 4 * rnt) {
+                    uint4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        v[u] = multimem_ld_reduce_add16<T>(c.mc_staging + off + ((i + u * rnt) << 4));
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        A acc[N];
+                        unpack16<T, A>(v[u], acc);
+                        store_pack<Tout, A, N>(recv, p0 + i + u * rnt, rc, vout, acc, a.scale, a.do_scale != 0);
+                    }
+                }
+                for (; i < n; i += rnt) {
+                    A acc[N];
+                    unpack16<T, A>(multimem_ld_reduce_add16<T>(c.mc_staging + off + (i << 4)), acc);
+                    store_pack<Tout, A, N>(recv, p0 + i, rc, vout, acc, a.scale, a.do_scale != 0);
+                }
+            }
+            else {
+                for (size_t i = rt; i < n; i += rnt) {
+                    uint4 v[MAX_RANKS];
+                    for (int p = 0; p < W; p++) // fixed rank order: reproducible rounding
+                        v[p] = ld_cv16(c.staging[p] + off + (i << 4));
+                    A acc[N];
+                    unpack16<T, A>(v[0], acc);
+                    for (int p = 1; p < W; p++)
+                        accum16<T, A, Op>(v[p], acc);
+                    store_pack<Tout, A, N>(recv, p0 + i, rc, vout, acc, a.scale, a.do_scale != 0);
+                }
+            }
+        }
+        if (j < nchunks)
+            ok = peer_barrier(c, s);
+    }
+    sync_end(c, gridDim.x, (uint32_t)nchunks, true);
 }
 
 // reduce_scatter on symmetric send buffers: pull my block from every peer

@@ -174,7 +174,7 @@ void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, i
             a.count = count;
             a.flags = algo == ga_nvls_oneshot ? dev::CF_NVLS : 0;
             prepare_args(dc, a, ra, st);
-            const int blocks = pick_blocks(dc, slot / 16, 2048, o.blocks);
+            const int blocks = pick_blocks(dc, slot / 16, 512, o.blocks); // one pack per thread: latency, not throughput, counts here
             dispatch_reduce_types(dt_in, dt_out, op, [&](auto tin, auto tout, auto opv) {
                 launch_kernel(dc, dev::allreduce_oneshot_kernel<decltype(tin), decltype(tout), decltype(opv)>, blocks,
                               threads, st, dc.table(), a);

@@ -39,9 +39,12 @@ void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t rc,
                    ? ((dc.nvls() && nvls_type_ok(dt_in, op) && !vin.registered) ? ga_nvls : ga_symm)
                    : ga_push;
     if ((algo == ga_symm || algo == ga_nvls) && !symmetric)
-        CCL_THROW("reduce_scatter algorithm ", gpu_algo_name(algo), " needs a send buffer from the symmetric heap");
+        CCL_THROW("reduce_scatter algorithm ", gpu_algo_name(algo),
+                  " needs a send buffer from the symmetric heap or from a registered allocation");
     if (algo == ga_nvls && (!dc.nvls() || !nvls_type_ok(dt_in, op) || vin.registered))
         algo = ga_symm;
+    if (algo == ga_push && o.algo == ga_auto && W > 1 && rc * esz * W >= env_data::get().rs_pipelined_min)
+        algo = ga_pipelined;
     dc.algo_hits[coll_reduce_scatter * ga_last + algo]++;
 
     if (algo == ga_symm || algo == ga_nvls) {
@@ -67,6 +70,41 @@ void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t rc,
         return;
     }
 
+    // large ordinary buffers: chunk pipeline (staging copy of chunk j under the reduction of chunk j-1)
+    const env_data& env = env_data::get();
+    if (algo == ga_pipelined && W > 1) {
+        const size_t rpacks = r16(rc * esz) / 16;
+        int blocks = o.blocks > 0 ? o.blocks : env.ar_pipelined_blocks;
+        blocks = std::max(1, std::min(blocks, dc.max_blocks()));
+        while (blocks > 1 && rpacks < (size_t)blocks * 256)
+            blocks /= 2;
+        size_t cs = dc.staging_bytes() / (2 * 16 * (size_t)W) / blocks * blocks;
+        CCL_THROW_IF_NOT(cs >= (size_t)blocks, "staging buffer too small for the pipelined reduce_scatter");
+        cs = std::min(cs, (rpacks + blocks - 1) / blocks * blocks);
+        a.count = rc;
+        a.stride = rc;
+        a.in_off = cs;
+        const bool nvls = dc.nvls() && nvls_type_ok(dt_in, op) && W >= env.nvls_min_ranks;
+        prepare_args(dc, a, ra, st);
+        dispatch_reduce_types(dt_in, dt_out, op, [&](auto tin, auto tout, auto opv) {
+            typedef decltype(tin) T;
+            typedef decltype(tout) Tout;
+            typedef decltype(opv) OP;
+            if constexpr (std::is_same<OP, dev::op_sum>::value &&
+                          (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value ||
+                           std::is_same<T, __half>::value)) {
+                if (nvls) {
+                    launch_kernel(dc, dev::reduce_scatter_pipelined_kernel<T, Tout, OP, true>, blocks, threads, st,
+                                  dc.table(), a);
+                    return;
+                }
+            }
+            launch_kernel(dc, dev::reduce_scatter_pipelined_kernel<T, Tout, OP, false>, blocks, threads, st,
+                          dc.table(), a);
+        });
+        return;
+    }
+
     // staged push, chunked over the per-rank block so that world slots fit
     const size_t N = 16 / esz;
     size_t max_packs = dc.staging_bytes() / 16 / W;
@@ -77,7 +115,7 @@ void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t rc,
         a.count = rc;
         a.stride = rc;
         prepare_args(dc, a, ra, st);
-        const int blocks = pick_blocks(dc, r16(rc * esz) / 16, 1024, o.blocks);
+        const int blocks = pick_blocks(dc, r16(rc * esz) / 16, 512, o.blocks);
         dispatch_reduce_types(dt_in, dt_out, op, [&](auto tin, auto tout, auto opv) {
             launch_kernel(dc, dev::reduce_scatter_kernel<decltype(tin), decltype(tout), decltype(opv)>, blocks,
                           threads, st, dc.table(), a);

@@ -207,6 +207,26 @@ def test_reduce_scatter(group, n, dtype):
         assert _canary_ok(buf, n)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_reduce_scatter_pipelined_many_chunks(group, dtype):
+    """Blocks larger than a staging slab (8 MiB staging): several chunks, copy and reduction overlap;
+    odd block length, twice for the generation flip, with a fused scale."""
+    W = group.world
+    esz = torch.empty((), dtype=dtype).element_size()
+    n = (3 << 20) // esz // W * 2 + 7
+    xs = _inputs(W, n * W, dtype, seed=12)
+    full = torch.stack([x.double() for x in xs]).sum(0) / W
+    for _ in range(2):
+        bufs = [_padded(n, dtype) for _ in range(W)]
+        group.reduce_scatter(xs, [b[1] for b in bufs], algo="pipelined", scale=1.0 / W)
+        torch.cuda.synchronize()
+        group.check()
+        for r, (buf, out) in enumerate(bufs):
+            torch.testing.assert_close(out.double(), full[r * n:(r + 1) * n], **_tol(dtype, W))
+            assert _canary_ok(buf, n)
+    assert group.algo_hits("reduce_scatter", "pipelined") >= 2
+
+
 def test_reduce_scatter_symmetric(group):
     W, n = group.world, 4099
     send = group.symm_empty((n * W,), dtype=torch.float32)

@@ -371,9 +371,9 @@ def _nan_check(comm):
     torch.cuda.synchronize()
     g.check()  # finite result: nothing recorded
     x[1234] = float("inf") if r == 0 else 1.0
-    comm.allreduce(x).wait()
-    torch.cuda.synchronize()
-    try:
+    try:  # the scan's record surfaces at the first status check: the event wait or an explicit check
+        comm.allreduce(x).wait()
+        torch.cuda.synchronize()
         g.check()
         found = False
     except Exception as e:  # noqa: BLE001
