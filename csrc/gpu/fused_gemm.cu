@@ -128,7 +128,22 @@ struct fused_plan {
     // cached maps, rebuilt when the operand pointers change
     std::vector<const void*> lastA, lastB;
     fused_params P;
+    // all-gather by the copy engines (n_comm == 0): a side stream carries the peer copies and the
+    // flag kernels while every SM runs GEMM tiles
+    bool ce_gather = false;
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
+
+namespace {
+// flags of one gathered shard: its 128-row blocks may be loaded (sequence number of the running call)
+__global__ void publish_shard_kernel(uint32_t* flags, int n, const uint32_t* plan_state) {
+    const uint32_t seq = dev::ld_volatile_u32(plan_state + PLAN_SEQ) + 1;
+    __threadfence();
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        dev::st_release_gpu(flags + i, seq);
+}
+} // namespace
 
 // auxiliary flag words are handed out linearly per communicator
 static uint32_t take_flag_words(device_comm& dc, uint32_t n) {
@@ -162,9 +177,17 @@ fused_plan* fused_plan_create(device_comm& dc, int mode, int M, int N, int K, in
     int per_rank = dc.emulated() ? sms / W : sms;
     if (ctas > 0)
         per_rank = std::min(per_rank, ctas);
+    // n_comm < 0 (or CCL_CUDA_AG_GEMM_CE=1 with n_comm == 0): the copy engines gather, no copy CTAs
+    p->ce_gather = mode == GM_AG && W > 1 && (n_comm < 0 || (n_comm == 0 && env_data::get().ag_gemm_ce));
     p->n_comm = mode == GM_AG ? (n_comm > 0 ? n_comm : std::max(1, per_rank / 8)) : 0;
     if (W == 1)
         p->n_comm = mode == GM_AG ? 1 : 0;
+    if (p->ce_gather) {
+        p->n_comm = 0;
+        CUDA_CHECK(cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking));
+        CUDA_CHECK(cudaEventCreateWithFlags(&p->ev_fork, cudaEventDisableTiming));
+        CUDA_CHECK(cudaEventCreateWithFlags(&p->ev_join, cudaEventDisableTiming));
+    }
     CCL_THROW_IF_NOT(per_rank - p->n_comm >= 1, "not enough CTAs");
     CCL_THROW_IF_NOT(per_rank <= dev::MAX_BLOCKS, "too many CTAs for the barrier slots");
     p->ctas = per_rank;
@@ -212,6 +235,11 @@ void fused_plan_destroy(fused_plan* p) {
     else
         p->dc->heap().free(p->part_off);
     cudaFree(p->state_dev);
+    if (p->side) {
+        cudaStreamDestroy(p->side);
+        cudaEventDestroy(p->ev_fork);
+        cudaEventDestroy(p->ev_join);
+    }
     delete p;
 }
 
@@ -241,7 +269,35 @@ void fused_plan_run(fused_plan* p, const void* const* A, const void* const* B, v
         }
         p->P.r[e].C = (__nv_bfloat16*)C[e];
     }
+    if (!p->ce_gather) {
+        launch(dc.table(), p->P, p->bn, p->ctas, p->entries, dc.emulated(), st);
+        return;
+    }
+    // every rank has written its shard once it passed this barrier
+    launch_barrier(dc, st);
+    CUDA_CHECK(cudaEventRecord(p->ev_fork, st));
+    CUDA_CHECK(cudaStreamWaitEvent(p->side, p->ev_fork, 0));
+    const int W = dc.world();
+    const int tiles_m_per = p->M / GEMM_BM / W;
+    const size_t shard = (size_t)(p->M / W) * p->K * 2;
+    for (int k = 1; k < W; k++) {
+        for (int e = 0; e < p->entries; e++) {
+            const int r = dc.emulated() ? e : dc.rank();
+            const int src = (r + k) % W;
+            const size_t off = p->x_off + (size_t)src * shard;
+            CUDA_CHECK(cudaMemcpyAsync(dc.heap().base(r) + off, dc.heap().base(src) + off, shard, cudaMemcpyDeviceToDevice,
+                                       p->side));
+            uint32_t* flags = dc.host_entry(e).aux[dc.emulated() ? e : dc.rank()] + p->flag_off + (size_t)src * tiles_m_per;
+            publish_shard_kernel<<<1, 32, 0, p->side>>>(flags, tiles_m_per, p->P.r[e].plan_state);
+            CUDA_CHECK(cudaGetLastError());
+        }
+    }
+    CUDA_CHECK(cudaEventRecord(p->ev_join, p->side));
+    // the GEMM starts on the local shard at once and waits per 128-row block for the others
     launch(dc.table(), p->P, p->bn, p->ctas, p->entries, dc.emulated(), st);
+    CUDA_CHECK(cudaStreamWaitEvent(st, p->ev_join, 0));
+    // peers may overwrite their shard (next call) only after everybody has copied it
+    launch_barrier(dc, st);
 }
 
 uint32_t fused_plan_error(fused_plan* p, int r) {

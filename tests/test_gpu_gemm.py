@@ -50,13 +50,16 @@ def test_gemm_silu_and_persistence(kernel):
 
 
 @pytest.mark.parametrize("world", [2, 4])
-def test_ag_gemm_emulated(world):
+@pytest.mark.parametrize("n_comm", [2, -1], ids=["copy-ctas", "copy-engines"])
+def test_ag_gemm_emulated(world, n_comm):
+    """The gather runs on dedicated copy CTAs of the kernel, or on the copy engines of a side stream
+    with one flag kernel per shard while every CTA computes."""
     from oneccl_b200.ops.device_group import DeviceGroup
     from oneccl_b200.ops.gemm import FusedPlan
 
     M, N, K = world * 256, 512, 256
     grp = DeviceGroup.emulated(world, heap_bytes=64 << 20, staging_bytes=1 << 20)
-    plan = FusedPlan(grp, "ag_gemm", M, N, K, epilogue="silu", n_comm=2)
+    plan = FusedPlan(grp, "ag_gemm", M, N, K, epilogue="silu", n_comm=n_comm)
     g = torch.Generator(device="cuda").manual_seed(2)
     x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
     ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(world)]
