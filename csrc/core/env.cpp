@@ -287,6 +287,7 @@ void env_data::parse() {
     get_size("CCL_CUDA_ALLREDUCE_PIPELINE_MIN", ar_pipelined_min);
     get_int("CCL_CUDA_ALLREDUCE_PIPELINE_BLOCKS", ar_pipelined_blocks);
     get_bool("CCL_CUDA_GEMM_2SM", gemm_2sm);
+    get_bool("CCL_CUDA_GEMM_RS_RING", gemm_rs_ring);
     get_bool("CCL_CUDA_AG_GEMM_CE", ag_gemm_ce);
     get_bool("CCL_CUDA_CHECK_NAN", cuda_check_nan);
     get_size("CCL_CUDA_REDUCE_SCATTER_SMALL_THRESHOLD", rs_small_threshold);

@@ -122,6 +122,7 @@ struct env_data {
     int ar_pipelined_blocks = 128; // blocks of the chunk pipeline (few SMs: compute keeps the rest)
     bool cuda_check_nan = false; // debug: scan reduction results for NaN / Inf
     bool ag_gemm_ce = true; // all-gather -> GEMM: the copy engines gather, every SM computes
+    bool gemm_rs_ring = true; // GEMM -> reduce-scatter: partial sums ride a ring through the epilogues
     bool gemm_2sm = true; // plain GEMMs run on CTA pairs (tcgen05 cta_group::2) when they have a 256-row tile
     size_t rs_small_threshold = 2u << 20;
     size_t rs_pipelined_min = 16u << 20; // total bytes >= : ordinary send buffers take the chunk pipeline

@@ -212,6 +212,8 @@ fused_plan* fused_plan_create(device_comm& dc, int mode, int M, int N, int K, in
     p->P.emu = dc.emulated() ? 1 : 0;
     p->P.world = W;
     p->P.n_comm = p->n_comm;
+    // GEMM -> reduce-scatter: ring of partial sums inside the epilogue unless n_comm == -1 or the knob is off
+    p->P.rs_ring = (mode == GM_RS && W > 1 && n_comm != -1 && env_data::get().gemm_rs_ring) ? 1 : 0;
     p->P.x_off = p->x_off;
     p->P.part_off = p->part_off;
     p->P.flag_off = p->flag_off;

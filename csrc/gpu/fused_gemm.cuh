@@ -11,6 +11,10 @@
 //              stores), bumps a per-tile counter there, and after its GEMM
 //              tiles every CTA reduces the tiles it owns (fp32 sum of `world`
 //              partials) as soon as their counters are complete.
+//              Ring form (rs_ring): every rank visits the owners in the order r+1, r+2, ..., r; the
+//              epilogue adds the partial sum that rank r+1 produced for the same tile one step
+//              earlier and passes the result on to rank r-1, so the last step writes the finished
+//              rows and nothing is left to reduce after the GEMM.
 //
 // Mainloop: TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) fills a
 // 4-stage shared-memory ring; one elected thread issues tcgen05.mma
@@ -64,6 +68,7 @@ struct fused_params {
     int M, N, K;
     int mode, epilogue, emu, world;
     int n_comm; // GM_AG: number of copy CTAs (the last n_comm blocks of the grid)
+    int rs_ring; // GM_RS: partial sums travel rank r -> r-1 inside the epilogue (no reduction pass at the end)
     size_t x_off; // GM_AG: heap offset of the gathered X [M,K]
     size_t part_off; // GM_RS: heap offset of the partial slots [world][M/world][N]
     uint32_t flag_off; // first auxiliary flag word of this plan
@@ -353,12 +358,37 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 int row0 = mi * GEMM_BM + q * 32; // first row handled by this warp
                 int row_limit = P.M;
                 int owner = 0, mb_local = 0;
+                const __nv_bfloat16* incoming = nullptr; // ring: partial sum of the previous rank for this tile
+                bool ring_final = false;
                 if (P.mode == GM_RS) {
                     owner = mi / tiles_m_per;
                     mb_local = mi % tiles_m_per;
-                    cbase = (__nv_bfloat16*)(cp->heap[owner] + P.part_off) + (size_t)rank * M_per * P.N;
                     row0 = mb_local * GEMM_BM + q * 32;
                     row_limit = M_per;
+                    if (P.rs_ring) {
+                        const int step = (owner - rank - 1 + W) % W; // 0 .. W-1, my own rows come last
+                        const size_t slot = (size_t)owner * M_per * P.N; // inbox region of this owner's rows
+                        if (step > 0) {
+                            const uint32_t* f = cp->aux[rank] + P.flag_off + ((size_t)owner * tiles_m_per + mb_local) * tiles_n + ni;
+                            bool got = true;
+                            if (lane == 0)
+                                got = wait_word<true>(f, seq * 4u, abort_flag, limit);
+                            got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+                            if (!got) {
+                                if (lane == 0)
+                                    gemm_fail(fr, abort_flag, GE_FLAG_TIMEOUT, (uint32_t)mi);
+                                break;
+                            }
+                            incoming = (const __nv_bfloat16*)(cp->heap[rank] + P.part_off) + slot;
+                        }
+                        ring_final = step == W - 1;
+                        if (ring_final)
+                            cbase = fr.C;
+                        else
+                            cbase = (__nv_bfloat16*)(cp->heap[(rank + W - 1) % W] + P.part_off) + slot;
+                    }
+                    else
+                        cbase = (__nv_bfloat16*)(cp->heap[owner] + P.part_off) + (size_t)rank * M_per * P.N;
                 }
                 else
                     cbase = fr.C;
@@ -375,6 +405,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         __syncwarp();
                         if (lane == 0)
                             mbar_arrive(&tempty[acc]);
+                    }
+                    if (incoming) {
+                        // my row of the incoming partial tile: 64 bf16 = eight 16-byte loads
+                        const int irow = row0 + lane;
+                        const int icol = ni * BN + c * GEMM_EPI_COLS;
+                        const __nv_bfloat16* src = incoming + (size_t)irow * P.N + icol;
+                        uint4 inc[8];
+#pragma unroll
+                        for (int v = 0; v < 8; v++)
+                            inc[v] = (irow < row_limit && icol + v * 8 < P.N) ? dev::ld_cv16(src + v * 8) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                        for (int v = 0; v < 4; v++) {
+                            const __nv_bfloat16* h0 = reinterpret_cast<const __nv_bfloat16*>(&inc[v]);
+                            const __nv_bfloat16* h1 = reinterpret_cast<const __nv_bfloat16*>(&inc[4 + v]);
+#pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                r0[v * 8 + e] = __float_as_uint(__uint_as_float(r0[v * 8 + e]) + __bfloat162float(h0[e]));
+                                r1[v * 8 + e] = __float_as_uint(__uint_as_float(r1[v * 8 + e]) + __bfloat162float(h1[e]));
+                            }
+                        }
                     }
                     uint32_t packed[32];
 #pragma unroll
@@ -410,12 +460,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     }
                     __syncwarp();
                 }
-                if (P.mode == GM_RS) {
-                    // publish: this warp's quarter of tile (mb_local, ni) from `rank` has landed at `owner`
+                if (P.mode == GM_RS && !(P.rs_ring && ring_final)) {
+                    // publish: this warp's quarter of the tile has landed (ring: at the next rank down, in
+                    // the inbox region of the tile's owner; otherwise at the owner, in my slot)
                     __syncwarp();
                     if (lane == 0) {
-                        dev::red_release_sys_add(
-                            cp->aux[owner] + P.flag_off + ((size_t)rank * tiles_m_per + mb_local) * tiles_n + ni, 1u);
+                        if (P.rs_ring)
+                            dev::red_release_sys_add(cp->aux[(rank + W - 1) % W] + P.flag_off +
+                                                         ((size_t)owner * tiles_m_per + mb_local) * tiles_n + ni,
+                                                     1u);
+                        else
+                            dev::red_release_sys_add(
+                                cp->aux[owner] + P.flag_off + ((size_t)rank * tiles_m_per + mb_local) * tiles_n + ni, 1u);
                     }
                 }
             }
@@ -433,7 +489,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (P.mode == GM_RS) {
             const int M_per = P.M / W;
             const __nv_bfloat16* part = (const __nv_bfloat16*)(cp->heap[rank] + P.part_off);
-            const int items = tiles_m_per * tiles_n;
+            const int items = P.rs_ring ? 0 : tiles_m_per * tiles_n; // ring: the last step wrote the result
             __shared__ int item_fail;
             for (int item = g; item < items; item += G) {
                 const int mb = item / tiles_n, ni = item % tiles_n;

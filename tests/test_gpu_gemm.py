@@ -79,18 +79,21 @@ def test_ag_gemm_emulated(world, n_comm):
 
 
 @pytest.mark.parametrize("world", [2, 4])
-def test_gemm_rs_emulated(world):
+@pytest.mark.parametrize("variant", ["ring", "owner-reduce"])
+@pytest.mark.parametrize("rows_per_rank", [128, 256])
+def test_gemm_rs_emulated(world, variant, rows_per_rank):
+    """GEMM -> reduce-scatter: partial sums passed down a ring inside the epilogues (bf16 on the wire,
+    one rounding per hop), or stored at the owner and summed in fp32 after the GEMM."""
     from oneccl_b200.ops.device_group import DeviceGroup
     from oneccl_b200.ops.gemm import FusedPlan
 
-    M, N, K = world * 128, 512, 192
+    M, N, K = world * rows_per_rank, 768, 192
     grp = DeviceGroup.emulated(world, heap_bytes=64 << 20, staging_bytes=1 << 20)
-    plan = FusedPlan(grp, "gemm_rs", M, N, K)
+    plan = FusedPlan(grp, "gemm_rs", M, N, K, n_comm=0 if variant == "ring" else -1)
     g = torch.Generator(device="cuda").manual_seed(3)
     hs = [torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
     ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(world)]
-    # every partial is rounded to bf16 before the fp32 reduction
-    full = sum(_ref(h, w).to(torch.bfloat16).float() for h, w in zip(hs, ws))
+    full = sum(_ref(h, w) for h, w in zip(hs, ws))
     per = M // world
     for it in range(2):
         outs = plan.run(hs, ws)
@@ -98,6 +101,9 @@ def test_gemm_rs_emulated(world):
         grp.check()
         for r in range(world):
             assert plan.error(r) == 0
-            _check(outs[r], full[r * per:(r + 1) * per], K)
+            ref = full[r * per:(r + 1) * per]
+            err = (outs[r].float() - ref).abs().max().item()
+            # one bf16 rounding per contribution (owner-reduce) or per hop (ring)
+            assert err <= 2.0e-2 * ref.abs().max().item() + 1e-3, (variant, err)
     plan.close()
     grp.close()
