@@ -90,7 +90,8 @@ def main():
 
     cfg = GPT2Config.named(args.model)
     B, S = args.batch, cfg.seq_len
-    model = GPT2(cfg).cuda().to(torch.bfloat16)
+    # ours: the library's fused layer kernels; nccl arm: the same network on stock PyTorch modules
+    model = GPT2(cfg, fused_ops=args.impl == "ours").cuda().to(torch.bfloat16)
 
     # ---- communicator + data-parallel wrapper
     comm = None

@@ -1,7 +1,10 @@
 """GPT-2 (124M ... 1.5B) decoder used by the data-parallel benchmark.
 
-Plain PyTorch modules (cuBLAS GEMMs, fused SDPA attention); the loss goes
-through the fused softmax cross-entropy kernel.  The vocabulary dimension of
+cuBLAS GEMMs and fused SDPA attention; with ``fused_ops`` (the default on CUDA bf16) the
+LayerNorms (with the residual addition in front of them), the bias gradients and the
+packed QKV gradient use the kernels of ``oneccl_b200.ops.nn``; the loss goes through the
+fused softmax cross-entropy kernel.  ``fused_ops=False`` is the same network on stock
+PyTorch modules.  The vocabulary dimension of
 the tied embedding / output matrix is padded to a multiple of 64 so that the
 logit rows are 16-byte aligned; the padding columns take no part in the
 softmax."""
@@ -60,11 +63,27 @@ class Block(nn.Module):
         x = x + self.fc2(F.gelu(self.fc(h), approximate="tanh"))
         return x
 
+    def forward_fused(self, x, delta):
+        """``x`` is the residual stream without the previous block's MLP output ``delta`` (None for
+        the first block): the addition happens inside the LayerNorm kernel.  Returns (x, delta)."""
+        from ..ops import nn as K
+
+        B, S, D = x.shape
+        h, x = K.add_layer_norm(x, delta, self.ln1.weight, self.ln1.bias, self.ln1.eps)
+        q, k, v = K.split_qkv(K.linear(h, self.qkv.weight, self.qkv.bias), self.n_head)
+        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        attn = K.linear(a.transpose(1, 2).reshape(B, S, D), self.proj.weight, self.proj.bias)
+        h, x = K.add_layer_norm(x, attn, self.ln2.weight, self.ln2.bias, self.ln2.eps)
+        delta = K.linear(F.gelu(K.linear(h, self.fc.weight, self.fc.bias), approximate="tanh"), self.fc2.weight,
+                         self.fc2.bias)
+        return x, delta
+
 
 class GPT2(nn.Module):
-    def __init__(self, c: GPT2Config):
+    def __init__(self, c: GPT2Config, fused_ops: bool = True):
         super().__init__()
         self.cfg = c
+        self.fused_ops = fused_ops
         self.wte = nn.Embedding(c.vocab_padded, c.d_model)
         self.wpe = nn.Embedding(c.seq_len, c.d_model)
         self.blocks = nn.ModuleList([Block(c) for _ in range(c.n_layer)])
@@ -87,6 +106,14 @@ class GPT2(nn.Module):
         B, S = idx.shape
         pos = torch.arange(S, device=idx.device)
         x = self.wte(idx) + self.wpe(pos)
+        if self.fused_ops and x.is_cuda and x.dtype == torch.bfloat16:
+            from ..ops import nn as K
+
+            delta = None
+            for b in self.blocks:
+                x, delta = b.forward_fused(x, delta)
+            h, _ = K.add_layer_norm(x, delta, self.ln_f.weight, self.ln_f.bias, self.ln_f.eps)
+            return h
         for b in self.blocks:
             x = b(x)
         return self.ln_f(x)
