@@ -111,7 +111,7 @@ def test_gpt2_fused_ops_match_stock_modules():
         m.zero_grad(set_to_none=True)
         loss = m(idx, tgt)
         loss.backward()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
         grads.append(torch.cat([p.grad.float().flatten() for p in m.parameters()]))
     assert abs(losses[0] - losses[1]) < 2e-2
     cos = torch.nn.functional.cosine_similarity(grads[0], grads[1], dim=0).item()
