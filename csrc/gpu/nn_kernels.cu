@@ -162,29 +162,38 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(const __nv_bfloat16* __rest
     }
 }
 
-// out[c] = sum over `n` partial rows (fixed order); two outputs interleaved as in ln_bwd_kernel
+// out[c] = sum over `n` partial rows (fixed order per column); two outputs interleaved as in ln_bwd_kernel.
+// A block owns 32 columns of one output: 8 row groups add their share of the partial rows, a fixed tree
+// in shared memory joins them.  grid = (D / 32, 2).
 __global__ void __launch_bounds__(256) ln_bwd_final_kernel(const float* __restrict__ partial, int n, int D,
                                                            __nv_bfloat16* __restrict__ dgamma, __nv_bfloat16* __restrict__ dbeta) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= D)
-        return;
-    float a = 0.f, b = 0.f;
-    for (int k = 0; k < n; k++) {
-        a += partial[((size_t)k * 2 + 0) * D + c];
-        b += partial[((size_t)k * 2 + 1) * D + c];
+    const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane, which = blockIdx.y;
+    float a = 0.f;
+    if (c < D)
+        for (int k = grp; k < n; k += 8)
+            a += partial[((size_t)k * 2 + which) * D + c];
+    __shared__ float sh[8][32];
+    sh[grp][lane] = a;
+    __syncthreads();
+    if (grp == 0 && c < D) {
+        float s = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; g++)
+            s += sh[g][lane];
+        (which == 0 ? dgamma : dbeta)[c] = __float2bfloat16_rn(s);
     }
-    dgamma[c] = __float2bfloat16_rn(a);
-    dbeta[c] = __float2bfloat16_rn(b);
 }
 
 } // namespace
 
 namespace {
 
-// column sums of a [rows, N] bf16 matrix (bias gradient): partial[chunk][N] then a fixed-order final sum.
+// column sums of a [rows, N] bf16 matrix (bias gradient): partial[chunk][N], then a fixed-order sum by the last block.
 // One warp covers 256 columns (a 16-byte pack per lane); grid = (N / 256, chunks).
-__global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16* __restrict__ dy, size_t rows, int N,
-                                                             float* __restrict__ partial) {
+__global__ void __launch_bounds__(256) colsum_kernel(const __nv_bfloat16* __restrict__ dy, size_t rows, int N,
+                                                     float* __restrict__ partial, unsigned* __restrict__ counters,
+                                                     __nv_bfloat16* __restrict__ out) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
     const int col = (blockIdx.x * 32 + lane) * 8;
     float acc[8] = { 0, 0, 0, 0, 0, 0, 0, 0 };
@@ -214,28 +223,36 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const __nv_bfloat16
         }
     }
     __shared__ float sh[8][256];
+    __shared__ int last;
 #pragma unroll
     for (int e = 0; e < 8; e++)
         sh[warp][lane * 8 + e] = acc[e];
     __syncthreads();
     const int c = blockIdx.x * 256 + threadIdx.x;
-    if (threadIdx.x < 256 && c < N) {
+    if (c < N) {
         float s = 0.f;
         for (int k = 0; k < wpb; k++)
             s += sh[k][threadIdx.x];
         partial[(size_t)blockIdx.y * N + c] = s;
     }
-}
-
-__global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ partial, int chunks, int N,
-                                                           __nv_bfloat16* __restrict__ out) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= N)
-        return;
-    float s = 0.f;
-    for (int k = 0; k < chunks; k++)
-        s += partial[(size_t)k * N + c];
-    out[c] = __float2bfloat16_rn(s);
+    // the block that finishes last for this column tile adds the chunks in index order (the result does
+    // not depend on which block that is) and re-arms the counter for the next call
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0)
+        last = atomicAdd(counters + blockIdx.x, 1u) == gridDim.y - 1 ? 1 : 0;
+    __syncthreads();
+    if (last) {
+        __threadfence();
+        if (c < N) {
+            float s = 0.f;
+            for (unsigned k = 0; k < gridDim.y; k++)
+                s += __ldcg(partial + (size_t)k * N + c);
+            out[c] = __float2bfloat16_rn(s);
+        }
+        if (threadIdx.x == 0)
+            counters[blockIdx.x] = 0;
+    }
 }
 
 // dst[b, s, h, :] = src[b, s, h, :] for head rows of `dh` elements (dh % 8 == 0) with arbitrary element
@@ -302,7 +319,7 @@ CCLX_API int cclx_layer_norm_fwd(const void* x, const void* res, const void* w, 
 
 // workspace: fp32 [cclx_layer_norm_bwd_blocks(rows) * 2 * D].  dres may be null.
 CCLX_API int cclx_layer_norm_bwd_blocks(size_t rows) {
-    return (int)std::min<size_t>((rows + 7) / 8, (size_t)sm_count_now() * 2);
+    return (int)std::min<size_t>((rows + 7) / 8, (size_t)sm_count_now());
 }
 
 CCLX_API int cclx_layer_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
@@ -325,23 +342,22 @@ CCLX_API int cclx_layer_norm_bwd(const void* dy, const void* x, const void* w, c
         }
 #undef LN_BWD
         CUDA_CHECK(cudaGetLastError());
-        ln_bwd_final_kernel<<<(D + 255) / 256, 256, 0, st>>>(workspace, blocks, D, (__nv_bfloat16*)dgamma,
-                                                            (__nv_bfloat16*)dbeta);
+        ln_bwd_final_kernel<<<dim3((D + 31) / 32, 2), 256, 0, st>>>(workspace, blocks, D, (__nv_bfloat16*)dgamma,
+                                                                   (__nv_bfloat16*)dbeta);
         CUDA_CHECK(cudaGetLastError());
     });
 }
 
-// workspace: fp32 [64 * N]
-CCLX_API int cclx_colsum_bf16(const void* dy, size_t rows, int N, void* out, float* workspace, void* stream) {
+// workspace: fp32 [64 * N]; counters: (N + 255) / 256 zero-initialised words that the kernel leaves zero
+CCLX_API int cclx_colsum_bf16(const void* dy, size_t rows, int N, void* out, float* workspace, unsigned* counters,
+                              void* stream) {
     return cclx::capi::guard([&] {
         CCL_THROW_IF_NOT(N % 8 == 0, "column count must be a multiple of 8");
         if (rows == 0 || N == 0)
             return;
         const int chunks = (int)std::min<size_t>(64, (rows + 31) / 32);
-        cudaStream_t st = (cudaStream_t)stream;
-        colsum_partial_kernel<<<dim3((N + 255) / 256, chunks), 256, 0, st>>>((const __nv_bfloat16*)dy, rows, N, workspace);
-        CUDA_CHECK(cudaGetLastError());
-        colsum_final_kernel<<<(N + 255) / 256, 256, 0, st>>>(workspace, chunks, N, (__nv_bfloat16*)out);
+        colsum_kernel<<<dim3((N + 255) / 256, chunks), 256, 0, (cudaStream_t)stream>>>(
+            (const __nv_bfloat16*)dy, rows, N, workspace, counters, (__nv_bfloat16*)out);
         CUDA_CHECK(cudaGetLastError());
     });
 }

@@ -103,9 +103,17 @@ def colsum(dy2: torch.Tensor) -> torch.Tensor:
     rows, N = dy2.shape
     out = torch.empty(N, dtype=dy2.dtype, device=dy2.device)
     ws = torch.empty(64 * N, dtype=torch.float32, device=dy2.device)
-    _lib.check(_lib.load().cclx_colsum_bf16(dy2.data_ptr(), rows, N, out.data_ptr(), ws.data_ptr(), _stream_ptr()))
-    _train._bump(2)
+    key = (dy2.device, torch.cuda.current_stream())
+    if key not in _colsum_counters:  # arrival counters per column tile; the kernel leaves them zero
+        _colsum_counters[key] = torch.zeros(1024, dtype=torch.int32, device=dy2.device)
+    assert N <= 1024 * 256
+    _lib.check(_lib.load().cclx_colsum_bf16(dy2.data_ptr(), rows, N, out.data_ptr(), ws.data_ptr(),
+                                            _colsum_counters[key].data_ptr(), _stream_ptr()))
+    _train._bump()
     return out
+
+
+_colsum_counters = {}
 
 
 class _Linear(torch.autograd.Function):
