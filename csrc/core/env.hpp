@@ -121,7 +121,7 @@ struct env_data {
     size_t ar_pipelined_min = 512u << 10; // >= : ordinary buffers take the chunk pipeline
     int ar_pipelined_blocks = 128; // blocks of the chunk pipeline (few SMs: compute keeps the rest)
     bool cuda_check_nan = false; // debug: scan reduction results for NaN / Inf
-    bool ag_gemm_ce = true; // all-gather -> GEMM: the copy engines gather, every SM computes
+    bool ag_gemm_ce = false; // all-gather -> GEMM: the copy engines gather, every SM computes (serial peer copies: pays only when the shards are large)
     bool gemm_rs_ring = true; // GEMM -> reduce-scatter: partial sums ride a ring through the epilogues
     bool gemm_2sm = true; // plain GEMMs run on CTA pairs (tcgen05 cta_group::2) when they have a 256-row tile
     size_t rs_small_threshold = 2u << 20;

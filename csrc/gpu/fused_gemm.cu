@@ -213,7 +213,12 @@ fused_plan* fused_plan_create(device_comm& dc, int mode, int M, int N, int K, in
     p->P.world = W;
     p->P.n_comm = p->n_comm;
     // GEMM -> reduce-scatter: ring of partial sums inside the epilogue unless n_comm == -1 or the knob is off
-    p->P.rs_ring = (mode == GM_RS && W > 1 && n_comm != -1 && env_data::get().gemm_rs_ring) ? 1 : 0;
+    // The ring needs the neighbour's tile of the previous step to be finished well before this rank reaches
+    // the same tile: with fewer than about one and a half waves of tiles per step the epilogues would wait on one another
+    // (measured: faster at 4 ranks with 256 tiles per step, slower at 8 ranks with 128), so the owner-side
+    // reduction stays the default there.  n_comm == -2 forces the ring.
+    const bool ring_pays = 2 * (size_t)(tiles_m / W) * tiles_n >= 3 * (size_t)per_rank;
+    p->P.rs_ring = (mode == GM_RS && W > 1 && n_comm != -1 && env_data::get().gemm_rs_ring && (ring_pays || n_comm == -2)) ? 1 : 0;
     p->P.x_off = p->x_off;
     p->P.part_off = p->part_off;
     p->P.flag_off = p->flag_off;

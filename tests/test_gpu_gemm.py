@@ -89,7 +89,7 @@ def test_gemm_rs_emulated(world, variant, rows_per_rank):
 
     M, N, K = world * rows_per_rank, 768, 192
     grp = DeviceGroup.emulated(world, heap_bytes=64 << 20, staging_bytes=1 << 20)
-    plan = FusedPlan(grp, "gemm_rs", M, N, K, n_comm=0 if variant == "ring" else -1)
+    plan = FusedPlan(grp, "gemm_rs", M, N, K, n_comm=-2 if variant == "ring" else -1)
     g = torch.Generator(device="cuda").manual_seed(3)
     hs = [torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
     ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(world)]
