@@ -47,11 +47,14 @@ int pick_bn(int N) {
 
 template <int BN>
 void set_smem_attr() {
-    static bool done = false;
-    if (!done) {
+    int dev_now = 0;
+    CUDA_CHECK(cudaGetDevice(&dev_now));
+    static bool done[64] = {}; // the attribute is per device
+    if (dev_now >= 64 || !done[dev_now]) {
         CUDA_CHECK(cudaFuncSetAttribute(fused_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         gemm_smem<BN>::TOTAL));
-        done = true;
+        if (dev_now < 64)
+            done[dev_now] = true;
     }
 }
 

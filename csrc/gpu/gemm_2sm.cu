@@ -258,10 +258,13 @@ CUtensorMap make_bf16_kmajor_map(const void* base, uint64_t rows, uint64_t cols,
 void gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int clusters,
                    uint32_t* err, cudaStream_t st) {
     CCL_THROW_IF_NOT(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "unsupported GEMM shape ", M, "x", N, "x", K);
-    static bool attr_done = false;
-    if (!attr_done) {
+    int dev_now = 0;
+    CUDA_CHECK(cudaGetDevice(&dev_now));
+    static bool attr_done[64] = {}; // the attribute is per device
+    if (dev_now >= 64 || !attr_done[dev_now]) {
         CUDA_CHECK(cudaFuncSetAttribute(gemm2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM));
-        attr_done = true;
+        if (dev_now < 64)
+            attr_done[dev_now] = true;
     }
     gemm2_params P;
     std::memset(&P, 0, sizeof(P));

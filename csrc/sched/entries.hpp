@@ -21,6 +21,7 @@ public:
     send_entry(sched* s, const void* buf, size_t bytes, int dst, uint64_t step)
             : sched_entry(s), buf_(buf), bytes_(bytes), dst_(dst), step_(step) {}
     const char* name() const override { return "SEND"; }
+    bool uses_credit() const override { return true; }
     void start() override;
     void update() override;
     // the buffer may be bound late (address known only when an earlier entry ran)

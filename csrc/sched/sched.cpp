@@ -247,10 +247,21 @@ bool sched::do_progress() {
     const size_t n = entries_.size();
     while (first_incomplete_ < n && entries_[first_incomplete_]->is_complete())
         first_incomplete_++;
+    // flow control (reference src/sched/queue/flow_control.cpp:21-65): at most CCL_MAX_FLOW_CREDITS
+    // sends of one schedule are in flight; the others start as credits come back.  Receives never
+    // wait for a credit: a rank that posted only receives could otherwise starve every sender.
+    const size_t credits = (size_t)std::max(1, env_data::get().max_flow_credits);
+    size_t in_flight = 0;
     for (size_t i = first_incomplete_; i < n; i++) {
         sched_entry& e = *entries_[i];
-        if (!e.is_complete())
-            e.do_progress();
+        if (!e.is_complete()) {
+            if (!e.uses_credit() || e.status() != entry_status::not_started || in_flight < credits)
+                e.do_progress();
+            if (e.uses_credit() && !e.is_complete() && e.status() != entry_status::not_started)
+                in_flight++;
+        }
+        if (in_flight > flow_high_water)
+            flow_high_water = in_flight;
         if (e.is_barrier()) {
             bool all_done = true;
             for (size_t k = first_incomplete_; k <= i; k++)

@@ -93,6 +93,8 @@ public:
     void do_progress();
     entry_status status() const { return status_; }
     bool is_complete() const { return status_ == entry_status::complete; }
+    // entries that inject data into the transport take a flow-control credit while in flight
+    virtual bool uses_credit() const { return false; }
     void make_barrier() { barrier_ = true; }
     bool is_barrier() const { return barrier_; }
     // profile (CCL_SCHED_PROFILE)
@@ -132,6 +134,7 @@ public:
     void reset(); // re-arm for another launch (cached schedules)
     void dump(std::string& out) const;
     void profile(std::string& out) const;
+    size_t flow_high_water = 0; // most entries of this schedule ever in flight together
 
     int priority = 0;
     request* req = nullptr; // request of the master schedule this partial belongs to

@@ -135,6 +135,7 @@ def test_other_collectives_default_algorithms(world):
      "CCL_REDUCE": "ring", "CCL_REDUCE_SCATTER": "direct", "CCL_WORKER_COUNT": "2"},
     {"CCL_REDUCE": "double_tree", "CCL_BCAST": "double_tree", "CCL_WORKER_OFFLOAD": "0"},
     {"CCL_ATL_SHM": "0", "CCL_WORKER_COUNT": "2"},
+    {"CCL_MAX_FLOW_CREDITS": "1", "CCL_ALLTOALL": "naive", "CCL_ALLTOALLV": "naive"},  # one entry in flight at a time
 ])
 def test_other_collectives_algorithm_overrides(env):
     assert all(run_ranks(_others, 3, env=env))
