@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--model", default=MODEL)
     ap.add_argument("--batch", type=int, default=PER_GPU_BATCH)
     ap.add_argument("--bucket-mb", type=float, default=25.0)
+    ap.add_argument("--comm-blocks", type=int, default=0,
+                    help="thread blocks of the gradient allreduce kernel (0 = the kernel's own choice)")
     return ap.parse_args()
 
 
@@ -107,7 +109,7 @@ def main():
 
             comm = init_from_env()
             group = comm.device_group
-        ddp = DataParallel(model, group, bucket_mb=args.bucket_mb)
+        ddp = DataParallel(model, group, bucket_mb=args.bucket_mb, comm_blocks=args.comm_blocks)
         opt = ddp.make_optimizer(lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, max_norm=1.0)
 
         def step(idx, tgt):
