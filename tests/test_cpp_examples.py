@@ -107,3 +107,17 @@ def test_point_to_point_latency_and_bandwidth_tools(bindir):
         assert rc == 0, err[-2000:]
     rows = [l for l in outs[0][1].splitlines() if l and l[0].isdigit()]
     assert len(rows) == 9 and all(float(r.split(",")[1]) > 0 for r in rows) and "PASSED" in outs[0][1]
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_all_operations_through_the_typed_api(bindir, world):
+    exe = bindir / "cpu_all_ops_test"
+    if not exe.exists():
+        _build(ROOT / "examples" / "cpu" / "cpu_all_ops_test.cpp", exe)
+    outs = _run_ranks(exe, world, timeout=240)
+    for rc, o, err in outs:
+        assert rc == 0, (o[-3000:], err[-2000:])
+    text = outs[0][1]
+    assert "FAILED" not in text
+    # 5 datatypes x 2 iterations x 7 operation groups + the final line
+    assert text.count("PASSED") == 5 * 2 * 7 + 1
