@@ -120,18 +120,35 @@ class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
         x2 = x.reshape(-1, x.shape[-1])
-        ctx.save_for_backward(x2, weight)
+        ctx.save_for_backward(x2, weight, bias)
         ctx.in_shape = x.shape
         return torch.addmm(bias, x2, weight.t()).view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
-        x2, weight = ctx.saved_tensors
+        x2, weight, bias = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1])
         dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
         dx = (dy2 @ weight).view(ctx.in_shape) if ctx.needs_input_grad[0] else None
-        dw = dy2.t() @ x2
-        return dx, dw, colsum(dy2)
+        # A parameter may carry a gradient sink (a view of a flat gradient buffer plus a callback, set by
+        # DataParallel): the weight gradient is then accumulated by the GEMM itself (beta = 1) instead of
+        # being materialised and added by a separate kernel, and autograd gets no gradient to accumulate.
+        wsink = getattr(weight, "_grad_sink", None)
+        if wsink is not None:
+            wsink[0].addmm_(dy2.t(), x2)
+            dw = None
+        else:
+            dw = dy2.t() @ x2
+        bsink = getattr(bias, "_grad_sink", None)
+        db = colsum(dy2)
+        if bsink is not None:
+            bsink[0].add_(db)
+            db = None
+        if wsink is not None:
+            wsink[1](weight)
+        if bsink is not None:
+            bsink[1](bias)
+        return dx, dw, db
 
 
 def linear(x, weight, bias):

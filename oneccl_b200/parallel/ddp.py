@@ -77,6 +77,9 @@ class DataParallel:
             self.flat_param[o:o + p.numel()].copy_(p.data.reshape(-1))
             p.data = self.flat_param[o:o + p.numel()].view_as(p.data)
             p.grad = self.flat_grad[o:o + p.numel()].view_as(p.data)
+            # layers that can accumulate straight into the flat buffer (oneccl_b200.ops.nn.linear) use this
+            # instead of handing autograd a gradient to add; the callback does the bucket accounting
+            p._grad_sink = (p.grad, self._on_grad)
 
         # ---- buckets over the flat gradient
         cap = max(1, int(bucket_mb * (1 << 20) / self.flat_grad.element_size()))
