@@ -100,6 +100,7 @@ class DataParallel:
         self.comm_stream = torch.cuda.Stream()
         self._hooks = [p.register_post_accumulate_grad_hook(self._on_grad) for p in order]
         self._armed = False
+        self._seen = set()
         if broadcast_from is not None and self.world > 1:
             group.broadcast(self.flat_param, root=broadcast_from)
             torch.cuda.synchronize()
@@ -109,6 +110,7 @@ class DataParallel:
         self.flat_grad.zero_()
         for b in self.buckets:
             b.pending = len(b.params)
+        self._seen = set()
         self._armed = True
 
     def _launch_bucket(self, b: _Bucket):
@@ -124,8 +126,9 @@ class DataParallel:
             self.launches += 1
 
     def _on_grad(self, p):
-        if not self._armed:
-            return
+        if not self._armed or id(p) in self._seen:
+            return  # a parameter counts once per step, whether its layer or autograd reports it
+        self._seen.add(id(p))
         b = self.buckets[self._bucket_of[id(p)]]
         b.pending -= 1
         if b.pending == 0:
