@@ -539,6 +539,101 @@ event_ptr device_coll(host_comm& comm, coll_param& p, const coll_attr& attr) {
     return std::make_shared<cuda_event_impl>(dc, st);
 }
 
+// Allreduce of device buffers across nodes, in three steps: reduce_scatter inside the node (device
+// kernels over NVLink), allreduce of this rank's slice across the nodes (host path on the sub-communicator
+// of equal local ranks, through pinned memory), all-gather inside the node.  The scheme of the reference's
+// scale-out allreduce (src/coll/algorithms/allreduce/sycl/allreduce_sycl.cpp:170-384 with
+// coll_util.cpp:553-642 for the host hop).  Needs the same number of ranks on every node and a count that
+// splits evenly among them; otherwise the whole buffer takes the host path.
+bool hier_allreduce_possible(host_comm& comm, const coll_param& p, const coll_attr& attr) {
+    if (p.ctype != coll_allreduce || !env_data::get().cuda_kernels || attr.reduction_fn || attr.out_dtype >= 0 ||
+        attr.do_scale)
+        return false;
+    const int L = comm.local_size();
+    if (L <= 0 || comm.size() % L != 0 || p.count % (size_t)L != 0 || p.count == 0)
+        return false;
+    const std::vector<int>& h = comm.host_index();
+    std::vector<int> per_host;
+    for (int v : h) {
+        if ((size_t)v >= per_host.size())
+            per_host.resize(v + 1, 0);
+        per_host[v]++;
+    }
+    for (int c : per_host)
+        if (c != L)
+            return false;
+    return true;
+}
+
+event_ptr hier_device_allreduce(host_comm& comm, coll_param& p, const coll_attr& attr) {
+    auto node = comm.node_comm();
+    auto r2r = comm.r2r_comm();
+    const int L = node->size();
+    const size_t esz = dtype_size(p.dtype);
+    const size_t rc = p.count / (size_t)L, slice_bytes = rc * esz;
+    cudaStream_t st = (cudaStream_t)p.stream;
+    stats().device_calls[coll_allreduce]++;
+
+    // scratch: this rank's slice on the device, its mirror in pinned host memory (kept per thread, grown on demand)
+    struct scratch {
+        void* dev = nullptr;
+        void* host = nullptr;
+        size_t cap = 0;
+        ~scratch() {
+            if (dev)
+                cudaFree(dev);
+            if (host)
+                cudaFreeHost(host);
+        }
+    };
+    static thread_local scratch sc;
+    if (sc.cap < slice_bytes) {
+        if (sc.dev)
+            CUDA_CHECK(cudaFree(sc.dev));
+        if (sc.host)
+            CUDA_CHECK(cudaFreeHost(sc.host));
+        sc.dev = sc.host = nullptr;
+        sc.cap = 0;
+        CUDA_CHECK(cudaMalloc(&sc.dev, slice_bytes));
+        CUDA_CHECK(cudaMallocHost(&sc.host, slice_bytes));
+        sc.cap = slice_bytes;
+    }
+
+    // 1. inside the node: my slice of the node-wide sum
+    coll_param rs = p;
+    rs.ctype = coll_reduce_scatter;
+    rs.count = rc;
+    rs.recv_buf = sc.dev;
+    rs.deps.clear();
+    coll_attr plain;
+    device_coll(*node, rs, plain)->wait();
+    // 2. across the nodes: same slice on the ranks with my local index
+    CUDA_CHECK(cudaMemcpyAsync(sc.host, sc.dev, slice_bytes, cudaMemcpyDeviceToHost, st));
+    CUDA_CHECK(cudaStreamSynchronize(st));
+    if (r2r->size() > 1) {
+        coll_param ar;
+        ar.ctype = coll_allreduce;
+        ar.send_buf = sc.host;
+        ar.recv_buf = sc.host;
+        ar.count = rc;
+        ar.dtype = p.dtype;
+        ar.reduction = p.reduction;
+        ar.device = false;
+        coll_attr host_attr;
+        coll_create(*r2r, ar, host_attr)->wait();
+    }
+    CUDA_CHECK(cudaMemcpyAsync(sc.dev, sc.host, slice_bytes, cudaMemcpyHostToDevice, st));
+    // 3. inside the node: everybody gets every slice
+    coll_param ag = p;
+    ag.ctype = coll_allgather;
+    ag.send_buf = sc.dev;
+    ag.recv_buf = p.recv_buf;
+    ag.count = rc;
+    ag.deps.clear();
+    coll_attr none;
+    return device_coll(*node, ag, none);
+}
+
 bool same_node(host_comm& comm) {
     const std::vector<int>& h = comm.host_index();
     for (int v : h)
@@ -829,6 +924,8 @@ event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr) {
         event_ptr ev;
         if (env.cuda_kernels && same_node(comm))
             ev = device_coll(comm, p, attr);
+        else if (hier_allreduce_possible(comm, p, attr))
+            ev = hier_device_allreduce(comm, p, attr);
         else
             ev = staged_device_coll(comm, p, attr);
         if (sync)

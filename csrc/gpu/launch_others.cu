@@ -19,6 +19,10 @@ void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t rc,
     if (rc == 0)
         return;
     const int W = dc.world();
+    if (W == 1) { // a single rank keeps its only block: the copy / cast / scale path of allreduce
+        launch_allreduce(dc, ra, rc, dt_in, dt_out, op, o, st);
+        return;
+    }
     const int entries = dc.emulated() ? W : 1;
     const size_t esz = predefined_dtype_size(dt_in), osz = predefined_dtype_size(dt_out);
     const int threads = dc.threads();

@@ -388,3 +388,67 @@ def _nan_check(comm):
 @needs2
 def test_debug_scan_reports_non_finite_results():
     assert all(run_ranks(_nan_check, 2, env=dict(ENV, CCL_CUDA_CHECK_NAN="1"), timeout=200))
+
+
+def _fake_nodes(rank, world, addr_file, q):
+    """Two ranks that pretend to sit on different hosts and share GPU 0: the node communicators have one
+    rank each (their kernels wait on nobody), the slice crosses the 'nodes' on the host path."""
+    try:
+        os.environ["CCL_TOPO_FAKE_HOST"] = f"node{rank}"
+        os.environ["CCL_CUDA_NVLS"] = "0"
+        os.environ["CCL_CUDA_SYMM_HEAP_SIZE"] = "64M"
+        os.environ["CCL_CUDA_TMP_BUF_SIZE"] = "8M"
+        import time
+
+        from oneccl_b200.comm import KVS, Communicator
+
+        if rank == 0:
+            kvs = KVS.create_main()
+            with open(addr_file + ".tmp", "w") as f:
+                f.write(kvs.address)
+            os.replace(addr_file + ".tmp", addr_file)
+        else:
+            t0 = time.time()
+            while not os.path.exists(addr_file):
+                assert time.time() - t0 < 60
+                time.sleep(0.01)
+            kvs = KVS.connect(open(addr_file).read())
+        comm = Communicator(world, rank, kvs)
+        torch.cuda.set_device(0)
+        x = torch.full((4096,), float(rank + 1), device="cuda")
+        y = torch.zeros_like(x)
+        comm.allreduce(x, y).wait()
+        torch.cuda.synchronize()
+        ok = bool(torch.all(y == world * (world + 1) / 2)) and comm.local_size == 1
+        z = torch.arange(1000, device="cuda", dtype=torch.float32) + rank
+        comm.allreduce(z).wait()  # in place
+        torch.cuda.synchronize()
+        ok = ok and bool(torch.all(z == 2 * torch.arange(1000, device="cuda") + 1))
+        comm.barrier().wait()
+        comm.close()
+        q.put((rank, "ok", ok))
+    except Exception:
+        import traceback
+
+        q.put((rank, "error", traceback.format_exc()))
+
+
+@pytest.mark.skipif(_ngpu() < 1, reason="needs a GPU")
+def test_allreduce_across_fake_nodes_takes_the_hierarchical_path():
+    import multiprocessing as mp
+    import tempfile
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    addr = os.path.join(tempfile.mkdtemp(prefix="cclx_fn_"), "addr")
+    procs = [ctx.Process(target=_fake_nodes, args=(r, 2, addr, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = {}
+    for _ in range(2):
+        rank, status, out = q.get(timeout=180)
+        assert status == "ok", out
+        res[rank] = out
+    for p in procs:
+        p.join(timeout=30)
+    assert res == {0: True, 1: True}
