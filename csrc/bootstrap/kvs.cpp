@@ -220,7 +220,9 @@ void server::stop() {
     if (listen_fd_ < 0)
         return;
     stopping_ = true;
-    ::shutdown(listen_fd_, SHUT_RDWR);
+    ::shutdown(listen_fd_, SHUT_RDWR); // wakes the accept loop; the descriptor stays valid until it has left
+    if (accept_thread_.joinable())
+        accept_thread_.join();
     ::close(listen_fd_);
     listen_fd_ = -1;
     {
@@ -229,8 +231,6 @@ void server::stop() {
             ::shutdown(fd, SHUT_RDWR);
     }
     cv_.notify_all();
-    if (accept_thread_.joinable())
-        accept_thread_.join();
     for (auto& t : workers_)
         if (t.joinable())
             t.join();

@@ -39,8 +39,9 @@ std::string request::error() const {
 
 // ---- buffer cache ---------------------------------------------------------------------
 buffer_cache& buffer_cache::get() {
-    static buffer_cache inst;
-    return inst;
+    // never destroyed: schedules that outlive static destruction still hand their buffers back
+    static buffer_cache* inst = new buffer_cache();
+    return *inst;
 }
 
 static size_t bucket_of(size_t bytes) {

@@ -51,16 +51,24 @@ def _write_ninja(path: Path, rules: str, builds: list[str]):
     path.write_text(rules + "\n" + "\n".join(builds) + "\n")
 
 
-def build_native(verbose: bool = False) -> Path:
-    """Compile csrc/{core,bootstrap,transport,sched,coll,gpu,api,capi} into libccl_b200.so."""
-    LIBDIR.mkdir(parents=True, exist_ok=True)
-    bdir = BUILD / "native"
+def build_native(verbose: bool = False, sanitize: str = "") -> Path:
+    """Compile csrc/{core,bootstrap,transport,sched,coll,gpu,api,capi} into libccl_b200.so.
+
+    ``sanitize`` = "address" or "thread" builds an instrumented copy of the host code into
+    ``build/lib-<sanitizer>/`` (the CUDA translation units stay uninstrumented); the C++ examples can be
+    linked against it to run the host runtime under ASan / TSan."""
+    assert sanitize in ("", "address", "thread")
+    libdir = BUILD / f"lib-{sanitize}" if sanitize else LIBDIR
+    libdir.mkdir(parents=True, exist_ok=True)
+    bdir = BUILD / (f"native-{sanitize}" if sanitize else "native")
     bdir.mkdir(parents=True, exist_ok=True)
+    san_cxx = f" -fsanitize={sanitize} -fno-omit-frame-pointer" if sanitize else ""
+    san_link = f" -Xcompiler -fsanitize={sanitize}" if sanitize else ""
     subdirs = ["core", "bootstrap", "transport", "sched", "coll", "comm", "fusion", "topo", "gpu", "api", "capi"]
     cpp = _sources(subdirs, [".cpp"])
     cu = _sources(subdirs, [".cu"])
     inc = f"-I{CSRC} -I{CSRC / 'include'} -I/usr/local/cuda/include"
-    cxxflags = f"-std=c++17 -O2 -g1 -fPIC -Wall -Wno-unused-function -pthread {inc}"
+    cxxflags = f"-std=c++17 -O2 -g1 -fPIC -Wall -Wno-unused-function -pthread {inc}{san_cxx}"
     nvflags = (
         f"-std=c++17 -O3 -lineinfo {' '.join(ARCH_FLAGS)} --expt-relaxed-constexpr --extended-lambda "
         f"-Xcompiler -fPIC -Xcompiler -Wno-unused-function {inc}"
@@ -85,7 +93,7 @@ rule nvcc
   description = NVCC $in
 
 rule link
-  command = $nvcc -shared -o $out $in -cudart static -Xlinker --no-undefined -Xlinker -soname=libccl_b200.so -lpthread -ldl -lrt
+  command = $nvcc -shared -o $out $in -cudart static {'' if sanitize else '-Xlinker --no-undefined '}-Xlinker -soname=libccl_b200.so -lpthread -ldl -lrt{san_link}
   description = LINK $out
 """
     builds, objs = [], []
@@ -97,7 +105,7 @@ rule link
         o = bdir / (str(s.relative_to(CSRC)).replace("/", "_") + ".o")
         builds.append(f"build {_ninja_escape(o)}: nvcc {_ninja_escape(s)}")
         objs.append(o)
-    lib = LIBDIR / "libccl_b200.so"
+    lib = libdir / "libccl_b200.so"
     builds.append(f"build {_ninja_escape(lib)}: link {' '.join(_ninja_escape(o) for o in objs)}")
     builds.append(f"default {_ninja_escape(lib)}")
     _write_ninja(bdir / "build.ninja", rules, builds)

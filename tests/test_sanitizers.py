@@ -1,0 +1,40 @@
+"""Host runtime under AddressSanitizer / ThreadSanitizer: an instrumented copy of the library is built
+into build/lib-<sanitizer>/ and the all-operations C++ example runs against it as three ranks, in several
+runtime modes.  Two extra full builds: opt-in with CCLX_RUN_SANITIZERS=1."""
+import os
+import subprocess
+import tempfile
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+pytestmark = pytest.mark.skipif(os.environ.get("CCLX_RUN_SANITIZERS") != "1",
+                                reason="set CCLX_RUN_SANITIZERS=1 (builds two instrumented copies of the library)")
+
+MODES = [{}, {"CCL_FUSION": "1"}, {"CCL_WORKER_COUNT": "2"}, {"CCL_WORKER_OFFLOAD": "0"},
+         {"CCL_ATL_SHM": "0", "CCL_PRIORITY": "lifo"}]
+
+
+@pytest.mark.parametrize("sanitizer", ["address", "thread"])
+def test_all_operations_under_sanitizer(sanitizer):
+    from oneccl_b200._build import build_native
+
+    lib = build_native(sanitize=sanitizer)
+    exe = Path(tempfile.mkdtemp(prefix="cclx_san_")) / f"all_ops_{sanitizer}"
+    cmd = ["g++", "-std=c++17", "-O1", "-g", f"-fsanitize={sanitizer}", "-fno-omit-frame-pointer",
+           str(ROOT / "examples" / "cpu" / "cpu_all_ops_test.cpp"), "-o", str(exe), f"-I{ROOT / 'csrc' / 'include'}",
+           f"-I{ROOT / 'examples' / 'include'}", f"-L{lib.parent}", "-lccl_b200", f"-Wl,-rpath,{lib.parent}", "-pthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    marker = "ERROR: AddressSanitizer" if sanitizer == "address" else "WARNING: ThreadSanitizer"
+    for mode in MODES:
+        addr = os.path.join(tempfile.mkdtemp(prefix="cclx_san_addr_"), "addr")
+        env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1", TSAN_OPTIONS="halt_on_error=0 report_signal_unsafe=0", **mode)
+        procs = [subprocess.Popen([str(exe), str(rk), "3", addr], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                                  text=True, env=env) for rk in range(3)]
+        outs = [p.communicate(timeout=300)[0] for p in procs]
+        for o in outs:
+            assert marker not in o and "LeakSanitizer" not in o, (mode, o[-4000:])
+        assert outs[0].count("PASSED") == 71, (mode, outs[0][-2000:])
