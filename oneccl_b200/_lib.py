@@ -92,6 +92,13 @@ def load():
     global _LIB
     if _LIB is not None:
         return _LIB
+    override = os.environ.get("CCL_B200_LIBRARY")  # e.g. an instrumented build (see _build.build_native)
+    if override:
+        _LIB = _proto(C.CDLL(override, mode=C.RTLD_GLOBAL))
+        from . import _capi_extra
+
+        _declare_optional(_LIB, _capi_extra.PROTOTYPES)
+        return _LIB
     if not LIBPATH.exists():
         if os.environ.get("CCL_B200_AUTOBUILD", "1") == "1":
             from . import _build
