@@ -118,11 +118,15 @@ def check(rc: int):
         raise CclError(load().cclx_last_error().decode(errors="replace"))
 
 
+_VOIDP_ARRAYS = {}
+
+
 def ptr_array(ptrs):
-    arr = (C.c_void_p * len(ptrs))()
-    for k, p in enumerate(ptrs):
-        arr[k] = p
-    return arr
+    n = len(ptrs)
+    t = _VOIDP_ARRAYS.get(n)
+    if t is None:  # ctypes array types are costly to create: one per length
+        t = _VOIDP_ARRAYS[n] = C.c_void_p * n
+    return t(*ptrs)
 
 
 def size_array(vals):

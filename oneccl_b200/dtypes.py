@@ -14,27 +14,39 @@ GPU_ALGO = {"auto": 0, "oneshot": 1, "twoshot": 2, "symm": 3, "nvls": 4, "nvls_o
             "push": 6, "pull": 7, "copy": 8, "pipelined": 9, "ce": 10}
 
 
-def torch_to_ccl(dtype) -> int:
-    import torch
+_TORCH_TABLE = None
 
-    table = {
-        torch.int8: INT8, torch.uint8: UINT8, torch.int16: INT16, torch.int32: INT32, torch.int64: INT64,
-        torch.float16: FLOAT16, torch.float32: FLOAT32, torch.float64: FLOAT64, torch.bfloat16: BFLOAT16,
-        torch.bool: UINT8,
-    }
-    for name, code in (("uint16", UINT16), ("uint32", UINT32), ("uint64", UINT64)):
-        if hasattr(torch, name):
-            table[getattr(torch, name)] = code
-    if dtype not in table:
-        raise TypeError(f"{dtype} has no ccl datatype")
-    return table[dtype]
+
+def torch_to_ccl(dtype) -> int:
+    global _TORCH_TABLE
+    if _TORCH_TABLE is None:  # built once: this sits on the launch path of every collective
+        import torch
+
+        table = {
+            torch.int8: INT8, torch.uint8: UINT8, torch.int16: INT16, torch.int32: INT32, torch.int64: INT64,
+            torch.float16: FLOAT16, torch.float32: FLOAT32, torch.float64: FLOAT64, torch.bfloat16: BFLOAT16,
+            torch.bool: UINT8,
+        }
+        for name, code in (("uint16", UINT16), ("uint32", UINT32), ("uint64", UINT64)):
+            if hasattr(torch, name):
+                table[getattr(torch, name)] = code
+        _TORCH_TABLE = table
+    try:
+        return _TORCH_TABLE[dtype]
+    except KeyError:
+        raise TypeError(f"{dtype} has no ccl datatype") from None
+
+
+_OPS = {"sum": SUM, "prod": PROD, "product": PROD, "min": MIN, "max": MAX, "avg": SUM}
 
 
 def reduce_op_code(op) -> int:
     if isinstance(op, int):
         return op
+    code = _OPS.get(op) if isinstance(op, str) else None
+    if code is not None:
+        return code
     name = str(op).lower().split(".")[-1]
-    table = {"sum": SUM, "prod": PROD, "product": PROD, "min": MIN, "max": MAX, "avg": SUM}
-    if name not in table:
+    if name not in _OPS:
         raise ValueError(f"unsupported reduction {op}")
-    return table[name]
+    return _OPS[name]

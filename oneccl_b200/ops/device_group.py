@@ -14,6 +14,7 @@ flavours that share every kernel:
 from __future__ import annotations
 
 import ctypes as C
+import threading
 from typing import Optional, Sequence
 
 import torch
@@ -26,8 +27,14 @@ def _stream_ptr(stream=None) -> int:
     """Raw handle of the launch stream; also points the library's own CUDA runtime
     (per-thread current device) at the caller's device."""
     s = stream if stream is not None else torch.cuda.current_stream()
-    _lib.load().cclx_set_device(s.device.index if s.device.index is not None else torch.cuda.current_device())
+    idx = s.device.index if s.device.index is not None else torch.cuda.current_device()
+    if getattr(_tls, "device", None) != idx:  # the library's runtime keeps the device per thread too
+        _lib.load().cclx_set_device(idx)
+        _tls.device = idx
     return s.cuda_stream
+
+
+_tls = threading.local()
 
 
 class _SymmStorage:
