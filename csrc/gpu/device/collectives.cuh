@@ -7,10 +7,12 @@
 //                          allreduce_kernel (src/kernels/kernels.cl:190-217)
 //   allreduce_twoshot   <- reduce_sum_general + copy (allreduce_small_sycl_rw_kernel.hpp:43-94),
 //                          allreduce_large_read_write_* (allreduce_large_sycl_impl.hpp:23-230)
+//   allreduce_pipelined <- allreduce_large_impl, the chunk pipeline (allreduce_large_sycl_impl.hpp:234-684)
 //   allreduce_symm      <- same two-shot on registered (IPC) user buffers, no tmp copy
+//   reduce_scatter_pipelined <- reduce_scatter_large_impl (reduce_scatter_large_sycl_impl.hpp:76-304)
 //   reduce_scatter      <- reduce_scatter_small/large_impl, reduce_monolithic_* (kernels.cl:269-421)
 //   allgatherv          <- gather / read_write, write_monolithic_* (kernels.cl:424-560)
-//   alltoallv           <- alltoallv_kernel_* (kernels.cl:110-116)
+//   alltoallv, alltoall_symm <- alltoallv_kernel_* (kernels.cl:110-116)
 //   broadcast / reduce  <- ze_copy_entry fan-out, ze_onesided_reduce
 // Design differences: push-style (remote stores, local reduction) so that a
 // collective costs one NVLink one-way trip plus one flag; two staging

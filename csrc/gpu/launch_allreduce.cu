@@ -1,8 +1,10 @@
 // Allreduce on GPU buffers: selection by size / registration and launch.
 // Counterpart of allreduce_sycl_single_node (reference
 // src/coll/algorithms/allreduce/sycl/allreduce_sycl.cpp:27-168): world==1 is a
-// copy, small messages take the one-shot kernel, larger ones the two-shot
-// kernel (chunked to the staging size), registered buffers skip staging.
+// copy, small messages take the one-shot kernel, larger ordinary buffers the
+// chunk-pipelined kernel (two-shot below its threshold), buffers from the
+// symmetric heap or from a registered allocation skip staging (NVLS when both
+// lie in the heap).
 #include "gpu/launch_common.cuh"
 
 namespace cclx {
