@@ -121,3 +121,81 @@ def test_process_group_cpu_world3():
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_process_group_cuda():
     _run(2, "cuda")
+
+
+def _worker_more(rank, world, port, q):
+    """Remaining operations on CPU tensors: gather / scatter, list forms of all_to_all and
+    reduce_scatter, coalesced and object collectives, sub-groups, uneven all_to_all splits."""
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        import torch.distributed as dist
+
+        import oneccl_b200.torch_backend  # noqa: F401
+
+        dist.init_process_group("ccl", rank=rank, world_size=world)
+        W = world
+        # gather / scatter
+        got = [torch.zeros(3) for _ in range(W)] if rank == 1 else None
+        dist.gather(torch.full((3,), float(rank)), got, dst=1)
+        if rank == 1:
+            assert all(torch.all(got[p] == p) for p in range(W))
+        out = torch.zeros(2)
+        dist.scatter(out, [torch.full((2,), float(10 + p)) for p in range(W)] if rank == 0 else None, src=0)
+        assert torch.all(out == 10 + rank)
+        # list forms
+        outs = [torch.zeros(2) for _ in range(W)]
+        dist.all_to_all(outs, [torch.full((2,), float(rank * 10 + p)) for p in range(W)])
+        assert all(torch.all(outs[p] == p * 10 + rank) for p in range(W))
+        rs = torch.zeros(4)
+        dist.reduce_scatter(rs, [torch.full((4,), float(p + 1)) for p in range(W)])
+        assert torch.all(rs == (rank + 1) * W)
+        # uneven all_to_all_single: rank r sends r + 1 elements to everybody
+        send = torch.full(((rank + 1) * W,), float(rank))
+        recv = torch.zeros(sum(p + 1 for p in range(W)))
+        dist.all_to_all_single(recv, send, output_split_sizes=[p + 1 for p in range(W)],
+                               input_split_sizes=[rank + 1] * W)
+        assert torch.equal(recv, torch.cat([torch.full((p + 1,), float(p)) for p in range(W)]))
+        # object collectives ride on byte tensors
+        objs = [None] * W
+        dist.all_gather_object(objs, {"rank": rank, "name": "r%d" % rank})
+        assert [o["rank"] for o in objs] == list(range(W))
+        box = [{"lr": 3e-4} if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        assert box[0] == {"lr": 3e-4}
+        # sub-group of the even ranks plus a reduce to its first member
+        evens = list(range(0, W, 2))
+        sub = dist.new_group(evens)
+        if rank in evens:
+            t = torch.full((5,), float(rank + 1))
+            dist.all_reduce(t, group=sub)
+            assert torch.all(t == sum(e + 1 for e in evens))
+            r = torch.full((2,), 1.0)
+            dist.reduce(r, dst=evens[0], group=sub)
+            if rank == evens[0]:
+                assert torch.all(r == len(evens))
+        # asynchronous work objects
+        w1 = dist.all_reduce(torch.ones(10), async_op=True)
+        w2 = dist.broadcast(torch.ones(3), src=0, async_op=True)
+        w1.wait()
+        w2.wait()
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok", ""))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def test_ccl_backend_cpu_remaining_operations():
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_more, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, status, msg in res:
+        assert status == "ok", f"rank {rank}:\n{msg}"
