@@ -360,13 +360,14 @@ CCLX_API const char* cclx_comp_impl(int which) {
 }
 
 // name of the CPU algorithm the selector picks
-CCLX_API int cclx_select_cpu_algo(int ctype, size_t bytes, int comm_size, char* out, size_t cap) {
+CCLX_API int cclx_select_cpu_algo(int ctype, size_t bytes, int comm_size, int scaleout, char* out, size_t cap) {
     return capi::guard([&] {
         selector_param sp;
         sp.ctype = (coll_type)ctype;
         sp.bytes = bytes;
         sp.count = bytes;
         sp.comm_size = comm_size;
+        sp.scaleout = scaleout != 0;
         std::string a = algorithm_selector::get().select_cpu(sp);
         CCL_THROW_IF_NOT(a.size() + 1 <= cap, "buffer too small");
         std::memcpy(out, a.c_str(), a.size() + 1);

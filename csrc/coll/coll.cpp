@@ -277,6 +277,7 @@ void build_cpu(sched& s, host_comm& comm, const coll_param& p, const coll_attr& 
     sp.comm_size = N;
     sp.vector_buf = !p.recv_bufs.empty();
     sp.custom_fn = attr.reduction_fn != nullptr;
+    sp.scaleout = attr.scaleout;
     const char* sbuf = p.send_buf ? (const char*)p.send_buf + off_elems * esz : nullptr;
     char* rbuf = p.recv_buf ? (char*)p.recv_buf + off_elems * esz : nullptr;
     switch (p.ctype) {
@@ -620,6 +621,7 @@ event_ptr hier_device_allreduce(host_comm& comm, coll_param& p, const coll_attr&
         ar.reduction = p.reduction;
         ar.device = false;
         coll_attr host_attr;
+        host_attr.scaleout = true; // CCL_ALLREDUCE_SCALEOUT chooses the inter-node algorithm
         coll_create(*r2r, ar, host_attr)->wait();
     }
     CUDA_CHECK(cudaMemcpyAsync(sc.dev, sc.host, slice_bytes, cudaMemcpyHostToDevice, st));

@@ -28,6 +28,9 @@ struct coll_attr {
     float scale = 1.0f;
     int out_dtype = -1; // -1: same as the input datatype
     std::string gpu_algo; // "" = automatic
+    // the inter-node stage of a hierarchical device collective: CCL_<COLL>_SCALEOUT applies (reference
+    // ccl_coll_param::is_scaleout, src/coll/coll_param.hpp:52-130)
+    bool scaleout = false;
 };
 
 class event_impl {

@@ -100,6 +100,8 @@ void algorithm_selector::reload() {
     const env_data& env = env_data::get();
     for (auto& kv : env.algo_raw)
         forced_[kv.first] = parse(kv.second, known_cpu_algos((coll_type)kv.first));
+    for (auto& kv : env.algo_scaleout_raw)
+        forced_scaleout_[kv.first] = parse(kv.second, known_cpu_algos((coll_type)kv.first));
     for (auto& kv : env.algo_gpu_raw)
         forced_gpu_[kv.first] = parse(kv.second, known_gpu_algos());
 }
@@ -113,8 +115,14 @@ static const std::string* lookup(const std::vector<algo_range>& t, size_t bytes)
 
 std::string algorithm_selector::select_cpu(const selector_param& p) const {
     std::string algo;
+    if (p.scaleout) {
+        auto so = forced_scaleout_.find(p.ctype);
+        if (so != forced_scaleout_.end())
+            if (const std::string* a = lookup(so->second, p.bytes))
+                algo = *a;
+    }
     auto f = forced_.find(p.ctype);
-    if (f != forced_.end())
+    if (algo.empty() && f != forced_.end())
         if (const std::string* a = lookup(f->second, p.bytes))
             algo = *a;
     if (algo.empty()) {

@@ -22,6 +22,7 @@ struct selector_param {
     bool vector_buf = false;
     bool custom_fn = false;
     bool pof2 = false;
+    bool scaleout = false; // consult the CCL_<COLL>_SCALEOUT table first
 };
 
 struct algo_range {
@@ -43,7 +44,7 @@ public:
 
 private:
     algorithm_selector();
-    std::map<int, std::vector<algo_range>> main_, forced_, forced_gpu_;
+    std::map<int, std::vector<algo_range>> main_, forced_, forced_scaleout_, forced_gpu_;
 };
 
 } // namespace cclx

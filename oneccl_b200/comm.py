@@ -369,9 +369,11 @@ def stats(which: str, coll: str = "allreduce") -> int:
     return int(_lib.load().cclx_stats(idx, COLL[coll]))
 
 
-def select_cpu_algo(coll: str, nbytes: int, comm_size: int = 2) -> str:
+def select_cpu_algo(coll: str, nbytes: int, comm_size: int = 2, scaleout: bool = False) -> str:
+    """Name of the host algorithm the selector picks; ``scaleout`` asks for the inter-node stage of a
+    hierarchical device collective (``CCL_<COLL>_SCALEOUT`` is consulted first)."""
     buf = C.create_string_buffer(64)
-    _lib.check(_lib.load().cclx_select_cpu_algo(COLL[coll], nbytes, comm_size, buf, 64))
+    _lib.check(_lib.load().cclx_select_cpu_algo(COLL[coll], nbytes, comm_size, 1 if scaleout else 0, buf, 64))
     return buf.value.decode()
 
 

@@ -130,6 +130,20 @@ def test_selector_env_override_in_child_process():
     assert out.stdout.split() == ["ring", "rabenseifner", "rabenseifner", "double_tree"]
 
 
+def test_scaleout_table_applies_to_the_inter_node_stage_only():
+    code = (
+        "from oneccl_b200.comm import select_cpu_algo as s;"
+        "print(s('allreduce', 1 << 20), s('allreduce', 1 << 20, scaleout=True), s('allreduce', 100, scaleout=True),"
+        " s('allgatherv', 1 << 20, scaleout=True))"
+    )
+    env = dict(os.environ, CCL_ALLREDUCE="ring", CCL_ALLREDUCE_SCALEOUT="rabenseifner:65536-max",
+               PYTHONPATH=str(_lib.LIBDIR.parent.parent))
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env)
+    assert out.returncode == 0, out.stderr
+    # ordinary operation: CCL_ALLREDUCE; scale-out stage: its own table where it has a range, else CCL_ALLREDUCE
+    assert out.stdout.split() == ["ring", "rabenseifner", "ring", "ring"]
+
+
 def test_datatype_table_and_cpu_reductions():
     import numpy as np
 
