@@ -383,16 +383,44 @@ def topo_describe() -> str:
     return buf.value.decode()
 
 
+_init_calls = 0
+
+
 def init_from_env(port_offset: Optional[int] = None) -> Communicator:
-    """World communicator under torchrun-style environment variables."""
+    """World communicator under torchrun-style environment variables.
+
+    Under a torchrun agent (``TORCHELASTIC_USE_AGENT_STORE=True``) rank 0 starts the KVS on a free port
+    and publishes its address through the agent's store at MASTER_ADDR:MASTER_PORT, so no second
+    well-known port is needed.  Otherwise the KVS listens on MASTER_PORT + 1 (+ ``CCL_KVS_PORT_OFFSET``)."""
+    global _init_calls
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
     if addr in ("localhost",):
         addr = "127.0.0.1"
     port = int(os.environ.get("MASTER_PORT", "29500"))
-    if port_offset is None:
-        port_offset = 1 + int(os.environ.get("CCL_KVS_PORT_OFFSET", "0"))
+    call = _init_calls
+    _init_calls += 1
+    if port_offset is None and os.environ.get("TORCHELASTIC_USE_AGENT_STORE", "").lower() == "true" \
+            and os.environ.get("CCL_KVS_USE_AGENT_STORE", "1") == "1":
+        try:
+            from datetime import timedelta
+
+            from torch.distributed import TCPStore
+
+            store = TCPStore(addr, port, world, False, timeout=timedelta(seconds=60))
+            key = f"ccl_b200/kvs/{os.environ.get('TORCHELASTIC_RESTART_COUNT', '0')}/{call}"
+            if rank == 0:
+                kvs = KVS.create_main(f"{addr}_0" if addr[0].isdigit() else "")
+                store.set(key, kvs.address)
+            else:
+                kvs = KVS.connect(store.get(key).decode())
+            return Communicator(world, rank, kvs)
+        except Exception as e:  # noqa: BLE001  fall back to the fixed port
+            if rank == 0:
+                print(f"oneccl_b200: agent store not usable ({e}); using MASTER_PORT + 1", flush=True)
+    if port_offset is None:  # a further communicator of the same job takes the next port
+        port_offset = 1 + int(os.environ.get("CCL_KVS_PORT_OFFSET", "0")) + call
     ip_port = f"{addr}_{port + port_offset}"
     kvs = KVS.create_main(ip_port) if rank == 0 else KVS.connect(ip_port)
     return Communicator(world, rank, kvs)

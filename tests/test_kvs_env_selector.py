@@ -174,3 +174,29 @@ def test_datatype_table_and_cpu_reductions():
     assert lib.cclx_comp_reduce(x.ctypes.data, 100, y.ctypes.data, 6, 1) == 0
     assert np.array_equal(y, x * 3)
     assert lib.cclx_comp_impl(0).decode() in ("avx512f", "scalar")
+
+
+def test_init_from_env_under_torchrun_uses_the_agent_store(tmp_path):
+    """Three ranks under torchrun: the KVS address travels through the agent's store (no second fixed port),
+    two communicators in one job."""
+    script = tmp_path / "job.py"
+    script.write_text(
+        "import numpy as np\\n"
+        "from oneccl_b200.comm import init_from_env\\n"
+        "c = init_from_env(); c2 = init_from_env()\\n"
+        "x = np.full(10, c.rank + 1.0, np.float32); c.allreduce(x).wait()\\n"
+        "assert np.all(x == c.size * (c.size + 1) / 2)\\n"
+        "y = np.ones(3, np.float32); c2.allreduce(y).wait(); assert np.all(y == c2.size)\\n"
+        "c.barrier().wait(); print('rank-ok', c.rank, flush=True); c2.close(); c.close()\\n")
+    import socket
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, PYTHONPATH=str(_lib.LIBDIR.parent.parent))
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "3",
+                          "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+                         capture_output=True, text=True, env=env, timeout=240)
+    assert out.returncode == 0, out.stderr[-3000:]
+    assert out.stdout.count("rank-ok") == 3
