@@ -181,12 +181,12 @@ def test_init_from_env_under_torchrun_uses_the_agent_store(tmp_path):
     two communicators in one job."""
     script = tmp_path / "job.py"
     script.write_text(
-        "import numpy as np\\n"
-        "from oneccl_b200.comm import init_from_env\\n"
-        "c = init_from_env(); c2 = init_from_env()\\n"
-        "x = np.full(10, c.rank + 1.0, np.float32); c.allreduce(x).wait()\\n"
-        "assert np.all(x == c.size * (c.size + 1) / 2)\\n"
-        "y = np.ones(3, np.float32); c2.allreduce(y).wait(); assert np.all(y == c2.size)\\n"
+        "import numpy as np\n"
+        "from oneccl_b200.comm import init_from_env\n"
+        "c = init_from_env(); c2 = init_from_env()\n"
+        "x = np.full(10, c.rank + 1.0, np.float32); c.allreduce(x).wait()\n"
+        "assert np.all(x == c.size * (c.size + 1) / 2)\n"
+        "y = np.ones(3, np.float32); c2.allreduce(y).wait(); assert np.all(y == c2.size)\n"
         "c.barrier().wait(); print('rank-ok', c.rank, flush=True); c2.close(); c.close()\\n")
     import socket
 
