@@ -187,7 +187,7 @@ def test_init_from_env_under_torchrun_uses_the_agent_store(tmp_path):
         "x = np.full(10, c.rank + 1.0, np.float32); c.allreduce(x).wait()\n"
         "assert np.all(x == c.size * (c.size + 1) / 2)\n"
         "y = np.ones(3, np.float32); c2.allreduce(y).wait(); assert np.all(y == c2.size)\n"
-        "c.barrier().wait(); print('rank-ok', c.rank, flush=True); c2.close(); c.close()\\n")
+        "c.barrier().wait(); print('rank-ok', c.rank, flush=True); c2.close(); c.close()\n")
     import socket
 
     s = socket.socket()
