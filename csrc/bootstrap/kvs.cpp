@@ -180,6 +180,9 @@ void server::start(const std::string& ip_port_in) {
     std::string ip;
     int port = 0;
     std::string want = ip_port_in.empty() ? env.kvs_ip_port : ip_port_in;
+    // CCL_KVS_IP_EXCHANGE=env: the address is agreed outside the program, so it must be given
+    CCL_THROW_IF_NOT(!want.empty() || env.kvs_ip_exchange != "env",
+                     "CCL_KVS_IP_EXCHANGE=env needs the address of the main key-value store in CCL_KVS_IP_PORT");
     if (!want.empty())
         split_ip_port(want, ip, port);
     else

@@ -36,6 +36,52 @@ void copy_in(sched& s, const void* send, void* recv, size_t bytes) {
     }
 }
 
+// A message may travel as several chunks so that the receiver starts working on
+// the first while the rest is still on the wire.  Chunk k of step s uses tag
+// s + k * CHUNK_TAG_STRIDE; steps stay below the stride, chunks below MAX_CHUNKS,
+// and the product fits the 16 bits of step space that one partial schedule owns.
+constexpr uint64_t CHUNK_TAG_STRIDE = 2048;
+constexpr size_t MAX_CHUNKS = 16;
+
+// number of chunks for `bytes` (`count` elements): `want`, lowered until every
+// chunk has `min_bytes` and at least one element.  Both sides of a message call
+// this with the same arguments (reference
+// src/sched/entry/factory/chunked_entry_factory.hpp:24-41,
+// src/coll/algorithms/reduce_scatter/reduce_scatter.cpp:226-240).
+size_t chunks_for(size_t bytes, size_t count, size_t want, size_t min_bytes) {
+    size_t c = std::min(std::max<size_t>(want, 1), MAX_CHUNKS);
+    while (c > 1 && (bytes / c < min_bytes || count < c))
+        c--;
+    return c;
+}
+
+// element range of chunk k: equal shares, the last takes the remainder
+inline void chunk_range(size_t count, size_t chunks, size_t k, size_t& off, size_t& n) {
+    const size_t main = count / chunks;
+    off = k * main;
+    n = (k == chunks - 1) ? count - off : main;
+}
+
+// CCL_CHUNK_COUNT / CCL_MIN_CHUNK_SIZE: point-to-point transfers of the alltoall family
+void chunked_send(sched& s, const void* buf, size_t count, size_t esz, int dst, uint64_t step) {
+    const auto& e = env_data::get();
+    const size_t chunks = chunks_for(count * esz, count, e.chunk_count, e.min_chunk_size);
+    for (size_t k = 0; k < chunks; k++) {
+        size_t off, n;
+        chunk_range(count, chunks, k, off, n);
+        s.add<send_entry>(at(buf, off, esz), n * esz, dst, step + k * CHUNK_TAG_STRIDE);
+    }
+}
+void chunked_recv(sched& s, void* buf, size_t count, size_t esz, int src, uint64_t step) {
+    const auto& e = env_data::get();
+    const size_t chunks = chunks_for(count * esz, count, e.chunk_count, e.min_chunk_size);
+    for (size_t k = 0; k < chunks; k++) {
+        size_t off, n;
+        chunk_range(count, chunks, k, off, n);
+        s.add<recv_entry>(at(buf, off, esz), n * esz, src, step + k * CHUNK_TAG_STRIDE);
+    }
+}
+
 // Non-power-of-two fold used by recursive doubling / halving: the first 2*rem
 // ranks pair up, even ones hand their data to the odd neighbour and sit out.
 struct fold {
@@ -134,10 +180,26 @@ void reduce_scatter_ring_v(sched& s, void* inout, const std::vector<size_t>& cou
     size_t maxc = *std::max_element(counts.begin(), counts.end());
     void* tmp = s.alloc_tmp(maxc * esz + 64);
     const int next = (r + 1) % N, prev = (r - 1 + N) % N;
+    const auto& e = env_data::get();
     for (int st = 0; st < N - 1; st++) {
         const int sb = (r - st - 1 + 2 * N) % N, rb = (r - st - 2 + 2 * N) % N;
-        s.add<send_entry>(at(inout, offs[sb], esz), counts[sb] * esz, next, step_base + st);
-        s.add<recv_reduce_entry>(at(inout, offs[rb], esz), counts[rb], dtype, op, prev, step_base + st, fn, tmp);
+        // CCL_RS_CHUNK_COUNT > 1: the block travels in chunks, each reduced on arrival while
+        // the next is still in flight (reference reduce_scatter.cpp:289-390 delays the
+        // reduction by one chunk for the same overlap)
+        const size_t want = N < 1000 ? e.rs_chunk_count : 1; // steps must stay below the chunk tag stride
+        const size_t sc = chunks_for(counts[sb] * esz, counts[sb], want, e.rs_min_chunk_size);
+        const size_t rc = chunks_for(counts[rb] * esz, counts[rb], want, e.rs_min_chunk_size);
+        for (size_t k = 0; k < sc; k++) {
+            size_t off, n;
+            chunk_range(counts[sb], sc, k, off, n);
+            s.add<send_entry>(at(inout, offs[sb] + off, esz), n * esz, next, step_base + st + k * CHUNK_TAG_STRIDE);
+        }
+        for (size_t k = 0; k < rc; k++) {
+            size_t off, n;
+            chunk_range(counts[rb], rc, k, off, n);
+            s.add<recv_reduce_entry>(at(inout, offs[rb] + off, esz), n, dtype, op, prev,
+                                     step_base + st + k * CHUNK_TAG_STRIDE, fn, at(tmp, off, esz));
+        }
         s.add_barrier();
     }
 }
@@ -358,32 +420,53 @@ void allreduce_nreduce(sched& s, const buf_desc& b) {
         copy_in(s, b.send, b.recv, b.count * esz);
         return;
     }
+    const auto& e = env_data::get();
     const void* src = b.send ? b.send : b.recv;
-    std::vector<size_t> cnt, off;
-    block_partition(b.count, N, cnt, off);
-    // every rank owns one block: gather the N-1 foreign contributions, reduce in rank order
+    // The vector is processed in segments of CCL_ALLREDUCE_NREDUCE_SEGMENT_SIZE bytes, so the
+    // scratch memory is bounded by one segment whatever the message size (reference
+    // src/coll/algorithms/allreduce/allreduce.cpp:324-345).  With CCL_ALLREDUCE_NREDUCE_BUFFERING
+    // the owned block is reduced in scratch and copied to recv afterwards, which keeps recv
+    // untouched until the segment's result is final.
+    size_t seg_elems = std::max<size_t>(e.nreduce_segment_size / esz, (size_t)N);
+    seg_elems = std::min(seg_elems, b.count);
+    const size_t max_block = seg_elems / N + 1;
     std::vector<void*> tmps(N, nullptr);
-    for (int k = 1; k < N; k++) {
-        const int p = (r + k) % N;
-        tmps[p] = s.alloc_tmp(cnt[r] * esz + 64);
-        s.add<recv_entry>(tmps[p], cnt[r] * esz, p, 0);
-        s.add<send_entry>(at(src, off[p], esz), cnt[p] * esz, p, 0);
-    }
-    s.add_barrier();
-    if (src != b.recv)
-        s.add<copy_entry>(at(src, off[r], esz), at(b.recv, off[r], esz), cnt[r] * esz);
-    s.add_barrier();
     for (int p = 0; p < N; p++)
-        if (p != r) {
-            s.add<reduce_local_entry>(tmps[p], at(b.recv, off[r], esz), cnt[r], b.dtype, b.op, b.fn);
+        if (p != r || e.nreduce_buffering)
+            tmps[p] = s.alloc_tmp(max_block * esz + 64);
+    for (size_t seg = 0; seg < b.count; seg += seg_elems) {
+        const size_t n = std::min(seg_elems, b.count - seg);
+        const char* sseg = at(src, seg, esz);
+        char* rseg = at(b.recv, seg, esz);
+        std::vector<size_t> cnt, off;
+        block_partition(n, N, cnt, off);
+        // every rank owns one block: gather the N-1 foreign contributions, reduce in rank order
+        for (int k = 1; k < N; k++) {
+            const int p = (r + k) % N;
+            s.add<recv_entry>(tmps[p], cnt[r] * esz, p, 0);
+            s.add<send_entry>(sseg + off[p] * esz, cnt[p] * esz, p, 0);
+        }
+        char* acc = e.nreduce_buffering ? (char*)tmps[r] : rseg + off[r] * esz;
+        if ((const char*)acc != sseg + off[r] * esz)
+            s.add<copy_entry>(sseg + off[r] * esz, acc, cnt[r] * esz);
+        s.add_barrier();
+        for (int p = 0; p < N; p++)
+            if (p != r) {
+                s.add<reduce_local_entry>(tmps[p], acc, cnt[r], b.dtype, b.op, b.fn);
+                s.add_barrier();
+            }
+        if (e.nreduce_buffering) {
+            s.add<copy_entry>(acc, rseg + off[r] * esz, cnt[r] * esz);
             s.add_barrier();
         }
-    allgatherv_naive(s, nullptr, b.recv, cnt, off, b.dtype, 1);
+        allgatherv_naive(s, nullptr, rseg, cnt, off, b.dtype, 1);
+    }
 }
 
 void allreduce_2d(sched& s, const buf_desc& b) {
     host_comm* c = s.comm();
     const size_t esz = dtype_size(b.dtype);
+    const auto& e = env_data::get();
     auto node = c->node_comm();
     auto r2r = c->r2r_comm();
     if (!node || !r2r || r2r->size() == 1 || node->size() == 1 || node->size() * r2r->size() != c->size()) {
@@ -391,27 +474,55 @@ void allreduce_2d(sched& s, const buf_desc& b) {
         return;
     }
     copy_in(s, b.send, b.recv, b.count * esz);
-    // reduce-scatter inside the node, allreduce of my block across nodes, allgather inside the node
-    std::vector<size_t> cnt, off;
-    block_partition(b.count, node->size(), cnt, off);
-    const int lr = node->rank();
-    void* recv = b.recv;
+    // reduce-scatter in the first dimension, allreduce of my block in the second, allgather in
+    // the first.  CCL_ALLREDUCE_2D_SWITCH_DIMS makes the cross-node communicator the first one
+    // (reference src/coll/algorithms/allreduce/allreduce.cpp:811-817).
+    host_comm* first = e.ar2d_switch_dims ? r2r.get() : node.get();
+    host_comm* second = e.ar2d_switch_dims ? node.get() : r2r.get();
+    const int F = first->size(), fr = first->rank();
     const int dtype = b.dtype, op = b.op;
     reduction_fn_t fn = b.fn;
-    host_comm* node_p = node.get();
-    host_comm* r2r_p = r2r.get();
-    s.add<subsched_entry>(
-        [=](sched& sub) { reduce_scatter_ring_v(sub, recv, cnt, off, dtype, op, fn, 0); }, "2D_RS", node_p);
-    s.add_barrier();
-    s.add<subsched_entry>(
-        [=](sched& sub) {
-            allreduce_ring(sub, buf_desc{ nullptr, at(recv, off[lr], dtype_size(dtype)), cnt[lr], dtype, op, fn });
-        },
-        "2D_AR", r2r_p);
-    s.add_barrier();
-    s.add<subsched_entry>([=](sched& sub) { allgatherv_ring(sub, nullptr, recv, cnt, off, dtype, 0); }, "2D_AG",
-                          node_p);
-    s.add_barrier();
+    // CCL_ALLREDUCE_2D_CHUNK_COUNT > 1: the vector is cut into chunks that move through the
+    // three phases as a pipeline, so chunk t is scattered inside the first dimension while
+    // chunk t-1 crosses the second and chunk t-2 is gathered.  The two phases that share a
+    // communicator use disjoint steps (0.. and 1000..).
+    size_t chunks = std::min(std::max<size_t>(e.ar2d_chunk_count, 1), MAX_CHUNKS);
+    while (chunks > 1 && (b.count * esz / chunks < e.ar2d_min_chunk_size || b.count / chunks < (size_t)F))
+        chunks--;
+    struct piece {
+        void* base;
+        std::vector<size_t> cnt, off;
+    };
+    std::vector<piece> pieces(chunks);
+    for (size_t k = 0; k < chunks; k++) {
+        size_t o, n;
+        chunk_range(b.count, chunks, k, o, n);
+        pieces[k].base = at(b.recv, o, esz);
+        block_partition(n, F, pieces[k].cnt, pieces[k].off);
+    }
+    for (size_t t = 0; t < chunks + 2; t++) {
+        if (t < chunks) {
+            const piece pc = pieces[t];
+            s.add<subsched_entry>(
+                [=](sched& sub) { reduce_scatter_ring_v(sub, pc.base, pc.cnt, pc.off, dtype, op, fn, 0); }, "2D_RS",
+                first);
+        }
+        if (t >= 1 && t - 1 < chunks) {
+            const piece pc = pieces[t - 1];
+            s.add<subsched_entry>(
+                [=](sched& sub) {
+                    allreduce_ring(sub,
+                                   buf_desc{ nullptr, at(pc.base, pc.off[fr], dtype_size(dtype)), pc.cnt[fr], dtype, op, fn });
+                },
+                "2D_AR", second);
+        }
+        if (t >= 2) {
+            const piece pc = pieces[t - 2];
+            s.add<subsched_entry>(
+                [=](sched& sub) { allgatherv_ring(sub, nullptr, pc.base, pc.cnt, pc.off, dtype, 1000); }, "2D_AG", first);
+        }
+        s.add_barrier();
+    }
 }
 
 void allreduce_double_tree(sched& s, const buf_desc& b) {
@@ -425,23 +536,41 @@ void allreduce_double_tree(sched& s, const buf_desc& b) {
     // that is an inner node of one tree is a leaf (or near-leaf) of the other
     const size_t h0 = b.count / 2, h1 = b.count - h0;
     const int root0 = 0, root1 = N / 2;
-    void* recv = b.recv;
     const int dtype = b.dtype, op = b.op;
     reduction_fn_t fn = b.fn;
+    // CCL_DTREE_PARTITION_COUNT > 1: each half is cut into parts that follow one another down
+    // the tree, the broadcast of part k running beside the reduction of part k+1 (reference
+    // src/coll/algorithms/double_tree_ops.cpp:146-151)
+    const size_t want = std::min(std::max<size_t>(env_data::get().dtree_partition_count, 1), MAX_CHUNKS);
+    auto tree = [=](sched& sub, void* base, size_t count, int root, uint64_t tag0) {
+        const size_t parts = std::min(want, std::max<size_t>(count, 1));
+        if (parts == 1) {
+            reduce_tree(sub, buf_desc{ nullptr, base, count, dtype, op, fn }, root, tag0);
+            bcast_tree(sub, base, count * dtype_size(dtype), root, tag0 + 500);
+            return;
+        }
+        for (size_t t = 0; t <= parts; t++) {
+            if (t < parts) {
+                size_t o, n;
+                chunk_range(count, parts, t, o, n);
+                void* p = at(base, o, dtype_size(dtype));
+                sub.add<subsched_entry>(
+                    [=](sched& ss) { reduce_tree(ss, buf_desc{ nullptr, p, n, dtype, op, fn }, root, tag0); }, "DTREE_R");
+            }
+            if (t >= 1) {
+                size_t o, n;
+                chunk_range(count, parts, t - 1, o, n);
+                void* p = at(base, o, dtype_size(dtype));
+                sub.add<subsched_entry>(
+                    [=](sched& ss) { bcast_tree(ss, p, n * dtype_size(dtype), root, tag0 + 500); }, "DTREE_B");
+            }
+            sub.add_barrier();
+        }
+    };
+    void* recv = b.recv;
     if (h0)
-        s.add<subsched_entry>(
-            [=](sched& sub) {
-                reduce_tree(sub, buf_desc{ nullptr, recv, h0, dtype, op, fn }, root0, 0);
-                bcast_tree(sub, recv, h0 * dtype_size(dtype), root0, 500);
-            },
-            "DTREE_A");
-    s.add<subsched_entry>(
-        [=](sched& sub) {
-            void* p = at(recv, h0, dtype_size(dtype));
-            reduce_tree(sub, buf_desc{ nullptr, p, h1, dtype, op, fn }, root1, 1000);
-            bcast_tree(sub, p, h1 * dtype_size(dtype), root1, 1500);
-        },
-        "DTREE_B");
+        s.add<subsched_entry>([=](sched& sub) { tree(sub, recv, h0, root0, 0); }, "DTREE_A");
+    s.add<subsched_entry>([=](sched& sub) { tree(sub, at(recv, h0, dtype_size(dtype)), h1, root1, 1000); }, "DTREE_B");
     s.add_barrier();
 }
 
@@ -454,8 +583,8 @@ void alltoallv_naive(sched& s, const void* send, const std::vector<size_t>& scou
     s.add<copy_entry>(at(send, soffs[r], esz), at(recv, roffs[r], esz), std::min(scounts[r], rcounts[r]) * esz);
     for (int k = 1; k < N; k++) {
         const int src = (r - k + N) % N, dst = (r + k) % N;
-        s.add<recv_entry>(at(recv, roffs[src], esz), rcounts[src] * esz, src, 0);
-        s.add<send_entry>(at(send, soffs[dst], esz), scounts[dst] * esz, dst, 0);
+        chunked_recv(s, at(recv, roffs[src], esz), rcounts[src], esz, src, 0);
+        chunked_send(s, at(send, soffs[dst], esz), scounts[dst], esz, dst, 0);
     }
     s.add_barrier();
 }
@@ -473,8 +602,8 @@ void alltoallv_scatter(sched& s, const void* send, const std::vector<size_t>& sc
     size_t in_batch = 0;
     for (int k = 1; k < N; k++) {
         const int src = (r - k + N) % N, dst = (r + k) % N;
-        s.add<recv_entry>(at(recv, roffs[src], esz), rcounts[src] * esz, src, (uint64_t)k);
-        s.add<send_entry>(at(send, soffs[dst], esz), scounts[dst] * esz, dst, (uint64_t)k);
+        chunked_recv(s, at(recv, roffs[src], esz), rcounts[src], esz, src, (uint64_t)k);
+        chunked_send(s, at(send, soffs[dst], esz), scounts[dst], esz, dst, (uint64_t)k);
         if (++in_batch == max_ops) {
             s.add_barrier();
             in_batch = 0;

@@ -393,9 +393,16 @@ int part_count(const host_comm& comm, const coll_param& p, size_t bytes) {
     const int workers = executor::get().worker_count();
     if (workers <= 1)
         return 1;
-    const bool splittable = p.ctype == coll_allreduce || p.ctype == coll_reduce || p.ctype == coll_bcast ||
-                            p.ctype == coll_broadcast;
-    if (!splittable || bytes < (size_t)workers * env_data::get().min_chunk_size || p.count < (size_t)workers * 64)
+    const env_data& env = env_data::get();
+    const bool is_bcast = p.ctype == coll_bcast || p.ctype == coll_broadcast;
+    const bool splittable = p.ctype == coll_allreduce || p.ctype == coll_reduce || is_bcast;
+    if (!splittable || p.count < (size_t)workers * 64)
+        return 1;
+    // CCL_BCAST_PART_COUNT fixes the split of a broadcast; CCL_MAX_SHORT_SIZE keeps messages up to
+    // that size whole (reference parallelizer.cpp:224-235)
+    if (is_bcast && env.bcast_part_count > 0)
+        return (int)std::min<size_t>(std::min<size_t>(env.bcast_part_count, 64), p.count);
+    if (bytes <= env.max_short_size || bytes < (size_t)workers * env.min_chunk_size)
         return 1;
     return workers;
 }
@@ -419,7 +426,7 @@ std::unique_ptr<master_sched> build_master(host_comm& comm, const coll_param& p,
         if (d)
             deps.push_back([d] { return d->test(); });
     for (int i = 0; i < parts; i++) {
-        sched* s = m->add_partial(i);
+        sched* s = m->add_partial(i % executor::get().worker_count()); // more parts than workers: round robin
         if (!deps.empty()) {
             s->add<deps_entry>(deps);
             s->add_barrier();
@@ -547,8 +554,9 @@ event_ptr device_coll(host_comm& comm, coll_param& p, const coll_attr& attr) {
 // coll_util.cpp:553-642 for the host hop).  Needs the same number of ranks on every node and a count that
 // splits evenly among them; otherwise the whole buffer takes the host path.
 bool hier_allreduce_possible(host_comm& comm, const coll_param& p, const coll_attr& attr) {
-    if (p.ctype != coll_allreduce || !env_data::get().cuda_kernels || attr.reduction_fn || attr.out_dtype >= 0 ||
-        attr.do_scale)
+    // CCL_TOPO_ALGO=0 switches the topology-aware (node / cross-node) composition off
+    if (p.ctype != coll_allreduce || !env_data::get().cuda_kernels || !env_data::get().topo_algo ||
+        attr.reduction_fn || attr.out_dtype >= 0 || attr.do_scale)
         return false;
     const int L = comm.local_size();
     if (L <= 0 || comm.size() % L != 0 || p.count % (size_t)L != 0 || p.count == 0)

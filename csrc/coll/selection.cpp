@@ -125,6 +125,13 @@ std::string algorithm_selector::select_cpu(const selector_param& p) const {
     if (algo.empty() && f != forced_.end())
         if (const std::string* a = lookup(f->second, p.bytes))
             algo = *a;
+    const bool forced = !algo.empty();
+    // CCL_ALGO_FALLBACK=0: a requested algorithm that cannot serve this call is an error instead
+    // of a silent switch to the size table (reference src/coll/selection/selector_impl.hpp:311-318)
+    auto fallback_allowed = [&](const char* why) {
+        CCL_THROW_IF_NOT(!forced || env_data::get().algo_fallback, coll_name(p.ctype), ": requested algorithm ", algo,
+                         " ", why, " and CCL_ALGO_FALLBACK=0");
+    };
     if (algo.empty()) {
         auto m = main_.find(p.ctype);
         CCL_THROW_IF_NOT(m != main_.end(), "no algorithm table for ", coll_name(p.ctype));
@@ -133,6 +140,7 @@ std::string algorithm_selector::select_cpu(const selector_param& p) const {
     }
     // names that have no CPU implementation of their own
     if (algo == "topo" || algo == "ring_rma" || algo == "offload") {
+        fallback_allowed("applies to device buffers only");
         LOG_DEBUG(coll_name(p.ctype), ": algorithm ", algo, " applies to device buffers only, using the size table");
         auto m = main_.find(p.ctype);
         const std::string* a = lookup(m->second, p.bytes);
@@ -154,8 +162,11 @@ std::string algorithm_selector::select_cpu(const selector_param& p) const {
             default: break;
         }
     }
-    if (p.vector_buf && (p.ctype == coll_allgatherv || p.ctype == coll_allgather))
+    if (p.vector_buf && (p.ctype == coll_allgatherv || p.ctype == coll_allgather) && algo != "naive" &&
+        algo != "flat") {
+        fallback_allowed("cannot address per-rank destination buffers");
         algo = "naive"; // per-rank destination buffers: only the naive pattern addresses them
+    }
     if (algo == "flat")
         algo = "naive";
     return algo;

@@ -11,6 +11,7 @@
 #include "core/log.hpp"
 #include "gpu/cuda_driver.hpp"
 #include "gpu/device_comm.hpp"
+#include "topo/topo.hpp"
 
 namespace cclx {
 
@@ -188,6 +189,30 @@ void host_comm::init_device() {
         CCL_THROW_IF_NOT(host_idx_[r] == host_idx_[rank()],
                          "the device communicator needs every rank on one node (NVLink domain); use the node "
                          "sub-communicator for multi-node jobs");
+    if (env_data::get().topo_fabric_check && size() > 1) {
+        // CCL_TOPO_FABRIC_VERTEX_CONNECTION_CHECK=1: name the pair of ranks without peer access before
+        // any memory is mapped (off by default: mapping the heap reports an unreachable peer as well).
+        // Devices are compared by PCI bus id, ordinals differ between processes.
+        const topo_info& t = topo_info::local();
+        int cur = 0;
+        cudaGetDevice(&cur);
+        char mine[32] = { 0 };
+        if (cur >= 0 && cur < t.gpu_count())
+            std::snprintf(mine, sizeof(mine), "%s", t.gpus[cur].pci_bus_id.c_str());
+        std::vector<char> all((size_t)size() * 32);
+        atl_->allgather(mine, all.data(), 32);
+        auto ordinal = [&](int r) {
+            for (int g = 0; g < t.gpu_count(); g++)
+                if (t.gpus[g].pci_bus_id == &all[(size_t)r * 32])
+                    return g;
+            return -1; // not visible to this process: nothing to compare
+        };
+        for (int r = 0; r < size(); r++) {
+            const int g = ordinal(r);
+            CCL_THROW_IF_NOT(r == rank() || g < 0 || g == cur || t.p2p(cur, g), "rank ", rank(), " (GPU ", mine,
+                             ") has no peer access to rank ", r, " (GPU ", &all[(size_t)r * 32], ")");
+        }
+    }
     dev_bs_.reset(new atl_bootstrap(*atl_, pm_));
     dev_.reset(new gpu::device_comm());
     dev_->init(*dev_bs_);

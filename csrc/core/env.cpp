@@ -9,6 +9,8 @@
 
 #include "core/log.hpp"
 
+extern char** environ; // POSIX: the process environment
+
 namespace cclx {
 
 static std::string lower(std::string s) {
@@ -135,6 +137,42 @@ const char* coll_env_suffix(int c) {
     return names[c];
 }
 
+// Names of the reference that a user may carry over and that change nothing here.  Each is
+// reported once, with the reason, so that a setting never disappears silently.
+void warn_about_names_without_effect() {
+    static const std::pair<const char*, const char*> table[] = {
+        { "CCL_FUSION_CYCLE_MS", "fused batches are cut at points of the program order, not on a timer" },
+        { "CCL_FUSION_CHECK_URGENT", "fused batches are cut at points of the program order, not on a timer" },
+        { "CCL_ATL_SYNC_COLL", "it configures the MPI transport" },
+        { "CCL_ENABLE_AUTO_CACHE", "it applies to the direct algorithms of the MPI transport" },
+        { "CCL_ATL_CACHE", "the mesh transport registers no memory" },
+        { "CCL_ATL_HMEM", "device buffers travel through NVLink kernels or pinned staging, not through the transport" },
+        { "CCL_USE_HMEM", "device buffers travel through NVLink kernels or pinned staging, not through the transport" },
+        { "CCL_ATL_SEND_PROXY", "device buffers are staged by the collective layer, not by the transport" },
+        { "CCL_ATL_RMA", "the mesh transport has no one-sided operations" },
+        { "CCL_ATL_EXTRA_EP", "every worker already owns an endpoint" },
+        { "CCL_STAGING_BUFFER", "staging memory is always pinned host memory" },
+        { "CCL_FRAMEWORK", "no framework-specific settings exist" },
+        { "CCL_DEBUG_TIMESTAMPS_LEVEL", "use CCL_SCHED_PROFILE or CCL_ITT_LEVEL for timing" },
+        { "CCL_MNIC", "one connection per peer and endpoint; interface choice is CCL_KVS_IFACE" },
+        { "CCL_MNIC_NAME", "one connection per peer and endpoint; interface choice is CCL_KVS_IFACE" },
+        { "CCL_MNIC_COUNT", "one connection per peer and endpoint; interface choice is CCL_KVS_IFACE" },
+    };
+    for (auto& kv : table)
+        if (std::getenv(kv.first))
+            LOG_WARN(kv.first, " is set but has no effect: ", kv.second);
+    // device knobs of the other backend: point at the CUDA ones
+    int reported = 0;
+    for (char** e = ::environ; e && *e && reported < 8; e++) {
+        const std::string kv(*e);
+        if (kv.rfind("CCL_ZE_", 0) == 0 || kv.rfind("CCL_SYCL_", 0) == 0 || kv.rfind("CCL_KERNEL_", 0) == 0) {
+            LOG_WARN(kv.substr(0, kv.find('=')), " is set but has no effect: Level Zero / SYCL knobs have no counterpart, the "
+                                                  "device path is configured by CCL_CUDA_*");
+            reported++;
+        }
+    }
+}
+
 } // namespace
 
 void env_data::parse() {
@@ -213,16 +251,21 @@ void env_data::parse() {
                                 { "mpi", atl_transport_t::mpi } });
     get_bool("CCL_ATL_SHM", atl_shm);
     get_size("CCL_ATL_SHM_RING_BYTES", atl_shm_ring_bytes);
-    get_bool("CCL_ATL_SYNC_COLL", atl_sync_coll);
     get_size("CCL_MAX_SHORT_SIZE", max_short_size);
     get_size("CCL_CHUNK_COUNT", chunk_count);
     get_size("CCL_MIN_CHUNK_SIZE", min_chunk_size);
     get_int("CCL_MAX_FLOW_CREDITS", max_flow_credits);
 
-    get_enum<kvs_mode_t>("CCL_KVS_MODE", kvs_mode,
-                         { { "internal", kvs_mode_t::internal }, { "user", kvs_mode_t::user } });
+    if (const char* km = std::getenv("CCL_KVS_MODE")) {
+        // the reference chooses between its PMI key-value store and MPI; only the first exists here
+        CCL_THROW_IF_NOT(lower(km) == "pmi" || lower(km) == "internal", "CCL_KVS_MODE=", km,
+                         ": this build has no MPI, the only mode is pmi");
+    }
     get_str("CCL_KVS_IP_PORT", kvs_ip_port);
     get_str("CCL_KVS_IP_EXCHANGE", kvs_ip_exchange);
+    kvs_ip_exchange = lower(kvs_ip_exchange);
+    CCL_THROW_IF_NOT(kvs_ip_exchange == "path" || kvs_ip_exchange == "env", "CCL_KVS_IP_EXCHANGE=", kvs_ip_exchange,
+                     " is not one of: path env");
     get_str("CCL_KVS_IFACE", kvs_iface);
     get_bool("CCL_KVS_PREFER_IPV6", kvs_prefer_ipv6);
     get_int("CCL_KVS_CONNECTION_TIMEOUT", kvs_connection_timeout_sec);
@@ -243,8 +286,6 @@ void env_data::parse() {
     get_bool("CCL_FUSION", fusion);
     get_size("CCL_FUSION_BYTES_THRESHOLD", fusion_bytes_threshold);
     get_size("CCL_FUSION_COUNT_THRESHOLD", fusion_count_threshold);
-    get_double("CCL_FUSION_CYCLE_MS", fusion_cycle_ms);
-    get_bool("CCL_FUSION_CHECK_URGENT", fusion_check_urgent);
     get_enum<priority_mode_t>("CCL_PRIORITY", priority_mode,
                               { { "none", priority_mode_t::none },
                                 { "direct", priority_mode_t::direct },
@@ -254,9 +295,17 @@ void env_data::parse() {
     get_bool("CCL_CACHE_FLUSH", cache_flush);
     get_bool("CCL_STRICT_ORDER", strict_order);
     get_bool("CCL_OP_SYNC", op_sync);
+    get_bool("CCL_BUFFER_CACHE", buffer_cache);
     get_size("CCL_BUFFER_CACHE_MAX_BYTES", buffer_cache_max_bytes);
+    get_bool("CCL_ALGO_FALLBACK", algo_fallback);
 
-    get_size("CCL_AR2D_CHUNK_COUNT", ar2d_chunk_count);
+    get_size("CCL_ALLREDUCE_2D_CHUNK_COUNT", ar2d_chunk_count);
+    CCL_THROW_IF_NOT(ar2d_chunk_count >= 1, "CCL_ALLREDUCE_2D_CHUNK_COUNT must be at least 1");
+    get_size("CCL_ALLREDUCE_2D_MIN_CHUNK_SIZE", ar2d_min_chunk_size);
+    CCL_THROW_IF_NOT(ar2d_min_chunk_size >= 1, "CCL_ALLREDUCE_2D_MIN_CHUNK_SIZE must be at least 1");
+    get_bool("CCL_ALLREDUCE_2D_SWITCH_DIMS", ar2d_switch_dims);
+    get_size("CCL_DTREE_PARTITION_COUNT", dtree_partition_count);
+    get_size("CCL_BCAST_PART_COUNT", bcast_part_count);
     get_size("CCL_ALLREDUCE_NREDUCE_SEGMENT_SIZE", nreduce_segment_size);
     get_bool("CCL_ALLREDUCE_NREDUCE_BUFFERING", nreduce_buffering);
     get_size("CCL_RS_CHUNK_COUNT", rs_chunk_count);
@@ -271,6 +320,7 @@ void env_data::parse() {
     get_bool("CCL_TOPO_ALGO", topo_algo);
     get_str("CCL_TOPO_P2P_ACCESS", topo_p2p_access);
     get_bool("CCL_TOPO_FABRIC_VERTEX_CONNECTION_CHECK", topo_fabric_check);
+    get_bool("CCL_TOPO_WA_FABRIC_VERTEX_CONNECTION_CHECK", topo_fabric_check); // the reference's spelling
 
     get_bool("CCL_ENABLE_CUDA_KERNELS", cuda_kernels);
     get_enum<ipc_exchange_t>("CCL_CUDA_IPC_EXCHANGE", ipc_exchange,
@@ -283,7 +333,6 @@ void env_data::parse() {
     get_int("CCL_CUDA_NVLS", nvls);
     get_int("CCL_CUDA_NVLS_MIN_RANKS", nvls_min_ranks);
     get_size("CCL_CUDA_ALLREDUCE_SMALL_THRESHOLD", ar_oneshot_threshold);
-    get_size("CCL_CUDA_ALLREDUCE_MEDIUM_THRESHOLD", ar_twoshot_threshold);
     get_size("CCL_CUDA_ALLREDUCE_PIPELINE_MIN", ar_pipelined_min);
     get_int("CCL_CUDA_ALLREDUCE_PIPELINE_BLOCKS", ar_pipelined_blocks);
     get_bool("CCL_CUDA_GEMM_2SM", gemm_2sm);
@@ -298,6 +347,7 @@ void env_data::parse() {
     get_size("CCL_CUDA_WAIT_TIMEOUT_MS", wait_timeout_ms);
     get_bool("CCL_CUDA_COPY_ENGINE", cuda_copy_engine);
     get_size("CCL_CUDA_IPC_CACHE_ENTRIES", ipc_cache_entries);
+    warn_about_names_without_effect();
 }
 
 void env_data::print(int rank) const {
@@ -313,7 +363,7 @@ void env_data::print(int rank) const {
        << " CCL_WORKER_WAIT=" << worker_wait << " CCL_SPIN_COUNT=" << spin_count;
     ss << "\n  CCL_ATL_TRANSPORT=" << (int)atl_transport << " CCL_ATL_SHM=" << atl_shm;
     ss << "\n  CCL_FUSION=" << fusion << " bytes<=" << fusion_bytes_threshold
-       << " count<=" << fusion_count_threshold << " cycle_ms=" << fusion_cycle_ms;
+       << " count<=" << fusion_count_threshold;
     ss << "\n  CCL_PRIORITY=" << (int)priority_mode << " CCL_CACHE_KEY=" << (int)cache_key
        << " CCL_CACHE_FLUSH=" << cache_flush << " CCL_STRICT_ORDER=" << strict_order
        << " CCL_OP_SYNC=" << op_sync << " CCL_UNORDERED_COLL=" << unordered_coll;
@@ -325,7 +375,7 @@ void env_data::print(int rank) const {
        << " CCL_CUDA_SYMM_HEAP_SIZE=" << symm_heap_bytes << " CCL_CUDA_TMP_BUF_SIZE=" << tmp_buf_bytes
        << " CCL_CUDA_NVLS=" << nvls;
     ss << "\n  CCL_CUDA_ALLREDUCE_SMALL_THRESHOLD=" << ar_oneshot_threshold
-       << " CCL_CUDA_ALLREDUCE_MEDIUM_THRESHOLD=" << ar_twoshot_threshold
+       << " CCL_CUDA_ALLREDUCE_PIPELINE_MIN=" << ar_pipelined_min
        << " CCL_CUDA_WAIT_TIMEOUT_MS=" << wait_timeout_ms;
     LOG_INFO(ss.str());
 }

@@ -24,7 +24,6 @@ enum class yield_t { none, pause, sleep, sched_yield };
 enum class launcher_t { hydra, torchrun, pmix, none };
 enum class backend_t { native, stub };
 enum class ipc_exchange_t { sockets, pidfd, fabric, cudaipc };
-enum class kvs_mode_t { internal, user };
 
 struct env_data {
     // logging / debug
@@ -56,16 +55,14 @@ struct env_data {
     atl_transport_t atl_transport = atl_transport_t::tcp;
     bool atl_shm = true; // same-host pairs use the shared-memory rings
     size_t atl_shm_ring_bytes = 4u << 20;
-    bool atl_sync_coll = false;
     size_t max_short_size = 0;
     size_t chunk_count = 1;
     size_t min_chunk_size = 65536;
     int max_flow_credits = 16;
 
     // kvs
-    kvs_mode_t kvs_mode = kvs_mode_t::internal;
     std::string kvs_ip_port; // <ip>_<port>
-    std::string kvs_ip_exchange = "path"; // env | path (address via user)
+    std::string kvs_ip_exchange = "path"; // env: the main KVS must find its address in CCL_KVS_IP_PORT
     std::string kvs_iface;
     bool kvs_prefer_ipv6 = false;
     int kvs_connection_timeout_sec = 120;
@@ -81,17 +78,21 @@ struct env_data {
     bool fusion = false;
     size_t fusion_bytes_threshold = 16384;
     size_t fusion_count_threshold = 256;
-    double fusion_cycle_ms = 0.2;
-    bool fusion_check_urgent = true;
     priority_mode_t priority_mode = priority_mode_t::none;
     cache_key_t cache_key = cache_key_t::match_id;
     bool cache_flush = false;
     bool strict_order = false;
     bool op_sync = false;
+    bool buffer_cache = true; // CCL_BUFFER_CACHE=0: scratch memory is allocated and freed per schedule
     size_t buffer_cache_max_bytes = 256u << 20;
+    bool algo_fallback = true; // CCL_ALGO_FALLBACK=0: an algorithm that cannot run is an error
 
     // allreduce tuning (CPU)
     size_t ar2d_chunk_count = 1;
+    size_t ar2d_min_chunk_size = 65536;
+    bool ar2d_switch_dims = false; // first dimension = across nodes
+    size_t dtree_partition_count = 1;
+    size_t bcast_part_count = 0; // 0 = as many parts as workers
     size_t nreduce_segment_size = 2u << 20;
     bool nreduce_buffering = false;
     size_t rs_chunk_count = 1;
@@ -107,7 +108,7 @@ struct env_data {
     std::string topo_color = "fixed"; // fixed | cuda | env
     bool topo_algo = true;
     std::string topo_p2p_access = "auto"; // auto | 0 | 1
-    bool topo_fabric_check = true;
+    bool topo_fabric_check = false; // check peer access between all ranks' GPUs before the heap is mapped
 
     // CUDA device path
     bool cuda_kernels = true; // CCL_ENABLE_CUDA_KERNELS (reference CCL_ENABLE_SYCL_KERNELS)
@@ -117,7 +118,6 @@ struct env_data {
     int nvls = -1; // -1 auto, 0 off, 1 force
     int nvls_min_ranks = 3; // communicators smaller than this use peer loads even when NVLS exists
     size_t ar_oneshot_threshold = 256u << 10; // <= : one-shot
-    size_t ar_twoshot_threshold = 16u << 20; // <= : two-shot single launch; above: chunked
     size_t ar_pipelined_min = 512u << 10; // >= : ordinary buffers take the chunk pipeline
     int ar_pipelined_blocks = 128; // blocks of the chunk pipeline (few SMs: compute keeps the rest)
     bool cuda_check_nan = false; // debug: scan reduction results for NaN / Inf
@@ -130,9 +130,9 @@ struct env_data {
     int cuda_max_blocks = 0; // 0 = auto (co-resident cap)
     int cuda_block_threads = 512;
     size_t wait_timeout_ms = 20000; // bound of every device-side wait
-    bool cuda_copy_engine = false; // large allgather through copy engines
+    bool cuda_copy_engine = false; // large equal-block allgather into symmetric / registered memory goes through the copy engines
     bool cuda_graph_safe = true;
-    size_t ipc_cache_entries = 1000;
+    size_t ipc_cache_entries = 1000; // registered allocations that may be open at once
 
     void parse();
     void print(int rank) const;

@@ -193,6 +193,12 @@ void device_comm::symm_free(void* p, int emu_rank) {
 // allocation's BASE plus the offset of the buffer inside it travel to the peers, which open the
 // handle once.  Here the exchange happens at registration, not per operation.
 int device_comm::register_user(void* const* ptrs, const size_t* bytes) {
+    // every rank registers and deregisters in the same order, so the count is the same everywhere
+    size_t live = 0;
+    for (auto& g : regs_)
+        live += g.live ? 1 : 0;
+    CCL_THROW_IF_NOT(live < env_data::get().ipc_cache_entries, live,
+                     " registered allocations are open (CCL_CUDA_IPC_CACHE_ENTRIES); deregister some first");
     user_reg r;
     r.live = true;
     r.base.assign(world_, nullptr);

@@ -206,6 +206,8 @@ void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_o
     if (algo == ga_auto) {
         if (W == 1)
             algo = ga_copy;
+        else if (symm && maxb > env_data::get().ag_small_threshold && env_data::get().cuda_copy_engine)
+            algo = ga_ce; // CCL_CUDA_COPY_ENGINE=1: large blocks move by the copy engines, the SMs stay free
         else if (symm && (maxb > env_data::get().ag_small_threshold || vout.registered))
             algo = (dc.nvls() && !vout.registered) ? ga_nvls : ga_symm;
         else if (maxb <= env_data::get().ag_small_threshold && rounded <= dc.staging_bytes())

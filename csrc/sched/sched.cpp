@@ -74,7 +74,7 @@ void* buffer_cache::take(size_t bytes) {
 void buffer_cache::give(void* p, size_t bytes) {
     const size_t b = bucket_of(bytes);
     std::lock_guard<std::mutex> lk(mu_);
-    if (cached_ + b > env_data::get().buffer_cache_max_bytes) {
+    if (!env_data::get().buffer_cache || cached_ + b > env_data::get().buffer_cache_max_bytes) {
         std::free(p);
         return;
     }

@@ -175,3 +175,65 @@ def _lowp_and_custom(comm):
 
 def test_low_precision_and_custom_reduction():
     assert all(run_ranks(_lowp_and_custom, 3))
+
+
+def _chunked(comm, fake_nodes):
+    """allreduce / reduce_scatter / alltoallv with sizes that do and do not divide into the chunk counts."""
+    import os
+
+    W, r = comm.size, comm.rank
+    if fake_nodes:
+        os.environ["CCL_TOPO_FAKE_HOST"] = f"node{r // (W // fake_nodes)}"
+    for count in (7, 4099, 70001):
+        base = (np.arange(count) % 11).astype(np.float64)
+        buf = base + r
+        comm.allreduce(buf).wait()
+        assert np.array_equal(buf, base * W + sum(range(W))), count
+        send = (base + 2 * r).astype(np.float32)
+        out = np.zeros(count, np.float32)
+        comm.allreduce(send, out, op="max").wait()
+        assert np.array_equal(out, (base + 2 * (W - 1)).astype(np.float32))
+        assert np.array_equal(send, (base + 2 * r).astype(np.float32))
+    rcnt = 3001
+    send = np.tile(np.arange(rcnt, dtype=np.float64), W) + r
+    out = np.zeros(rcnt, np.float64)
+    comm.reduce_scatter(send, out).wait()
+    assert np.array_equal(out, np.arange(rcnt) * W + sum(range(W)))
+    # alltoallv with unequal blocks, some of them shorter than one chunk
+    sc = [(q + 1) * 997 if (q + r) % 2 else 3 for q in range(W)]
+    rc = [(r + 1) * 997 if (p + r) % 2 else 3 for p in range(W)]
+    send = np.concatenate([np.full(sc[q], r * 100 + q, np.int32) for q in range(W)])
+    recv = np.zeros(sum(rc), np.int32)
+    comm.alltoallv(send, sc, recv, rc).wait()
+    assert np.array_equal(recv, np.concatenate([np.full(rc[p], p * 100 + r, np.int32) for p in range(W)]))
+    for root in range(W):
+        b = np.full(50001, float(r))
+        comm.broadcast(b, root=root).wait()
+        assert np.all(b == root)
+    return True
+
+
+@pytest.mark.parametrize("env,world,nodes", [
+    ({"CCL_ALLREDUCE": "ring", "CCL_REDUCE_SCATTER": "ring", "CCL_RS_CHUNK_COUNT": "4", "CCL_RS_MIN_CHUNK_SIZE": "64"}, 3, 0),
+    ({"CCL_ALLREDUCE": "ring", "CCL_RS_CHUNK_COUNT": "16", "CCL_RS_MIN_CHUNK_SIZE": "1", "CCL_ATL_SHM": "0"}, 4, 0),
+    ({"CCL_ALLREDUCE": "nreduce", "CCL_ALLREDUCE_NREDUCE_SEGMENT_SIZE": "4096"}, 3, 0),
+    ({"CCL_ALLREDUCE": "nreduce", "CCL_ALLREDUCE_NREDUCE_SEGMENT_SIZE": "16K", "CCL_ALLREDUCE_NREDUCE_BUFFERING": "1"}, 4, 0),
+    ({"CCL_ALLREDUCE": "double_tree", "CCL_DTREE_PARTITION_COUNT": "3"}, 5, 0),
+    ({"CCL_ALLREDUCE": "2d"}, 4, 2),
+    ({"CCL_ALLREDUCE": "2d", "CCL_ALLREDUCE_2D_CHUNK_COUNT": "3", "CCL_ALLREDUCE_2D_MIN_CHUNK_SIZE": "256"}, 4, 2),
+    ({"CCL_ALLREDUCE": "2d", "CCL_ALLREDUCE_2D_CHUNK_COUNT": "5", "CCL_ALLREDUCE_2D_MIN_CHUNK_SIZE": "1",
+      "CCL_ALLREDUCE_2D_SWITCH_DIMS": "1", "CCL_RS_CHUNK_COUNT": "2", "CCL_RS_MIN_CHUNK_SIZE": "128"}, 6, 3),
+    ({"CCL_ALLTOALLV": "naive", "CCL_CHUNK_COUNT": "4", "CCL_MIN_CHUNK_SIZE": "16"}, 3, 0),
+    ({"CCL_ALLTOALLV": "scatter", "CCL_CHUNK_COUNT": "3", "CCL_MIN_CHUNK_SIZE": "1024", "CCL_ALLTOALL_SCATTER_MAX_OPS": "1"}, 4, 0),
+    ({"CCL_WORKER_COUNT": "2", "CCL_BCAST_PART_COUNT": "3", "CCL_MIN_CHUNK_SIZE": "1024"}, 3, 0),
+    ({"CCL_WORKER_COUNT": "2", "CCL_MAX_SHORT_SIZE": "64K", "CCL_MIN_CHUNK_SIZE": "1024"}, 2, 0),
+    ({"CCL_BUFFER_CACHE": "0", "CCL_ALLREDUCE": "rabenseifner"}, 3, 0),
+], ids=["rs-chunks", "rs-chunks-16-sockets", "nreduce-segments", "nreduce-buffering", "dtree-parts", "2d-two-nodes",
+        "2d-chunks", "2d-chunks-switched", "alltoallv-naive-chunks", "alltoallv-scatter-chunks", "bcast-parts",
+        "max-short-size", "no-buffer-cache"])
+def test_chunking_and_partition_knobs(env, world, nodes):
+    """Every knob that cuts a message into chunks, segments or parts gives the same results as the uncut
+    algorithm: CCL_RS_CHUNK_COUNT, CCL_ALLREDUCE_NREDUCE_SEGMENT_SIZE / _BUFFERING, CCL_DTREE_PARTITION_COUNT,
+    CCL_ALLREDUCE_2D_CHUNK_COUNT / _SWITCH_DIMS over two and three simulated nodes, CCL_CHUNK_COUNT,
+    CCL_BCAST_PART_COUNT, CCL_MAX_SHORT_SIZE, CCL_BUFFER_CACHE."""
+    assert all(run_ranks(_chunked, world, nodes, env=env))

@@ -200,3 +200,45 @@ def test_init_from_env_under_torchrun_uses_the_agent_store(tmp_path):
                          capture_output=True, text=True, env=env, timeout=240)
     assert out.returncode == 0, out.stderr[-3000:]
     assert out.stdout.count("rank-ok") == 3
+
+
+def _run_py(code, **env):
+    full = dict(os.environ, PYTHONPATH=str(_lib.LIBDIR.parent.parent), **env)
+    return subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=full)
+
+
+def test_algo_fallback_switch():
+    """A requested algorithm that exists only for device buffers falls back to the size table, unless
+    CCL_ALGO_FALLBACK=0 makes that an error."""
+    code = "from oneccl_b200.comm import select_cpu_algo as s; print(s('allreduce', 1 << 20))"
+    out = _run_py(code, CCL_ALLREDUCE="topo")
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.split() == ["nreduce"]  # the size table's choice at 1 MiB
+    out = _run_py(code, CCL_ALLREDUCE="topo", CCL_ALGO_FALLBACK="0")
+    assert out.returncode != 0
+    assert "CCL_ALGO_FALLBACK" in out.stderr
+
+
+def test_names_without_effect_are_reported():
+    """Settings carried over from the reference that change nothing here are named in a warning, the
+    Level Zero / SYCL families included; names that do something stay silent."""
+    code = "from oneccl_b200.comm import select_cpu_algo as s; s('allreduce', 8)"
+    out = _run_py(code, CCL_FUSION_CYCLE_MS="1", CCL_ZE_ENABLE="1", CCL_SYCL_ALLREDUCE_TMP_BUF="1",
+                  CCL_ATL_SYNC_COLL="1", CCL_WORKER_COUNT="2")
+    assert out.returncode == 0, out.stderr
+    for name in ("CCL_FUSION_CYCLE_MS", "CCL_ZE_ENABLE", "CCL_SYCL_ALLREDUCE_TMP_BUF", "CCL_ATL_SYNC_COLL"):
+        assert name + " is set but has no effect" in out.stderr, out.stderr
+    assert "CCL_WORKER_COUNT is set" not in out.stderr
+
+
+def test_kvs_mode_and_ip_exchange_values():
+    code = "from oneccl_b200.comm import KVS; k = KVS.create_main(); print(k.address)"
+    assert _run_py(code, CCL_KVS_MODE="pmi").returncode == 0
+    out = _run_py(code, CCL_KVS_MODE="mpi")
+    assert out.returncode != 0 and "no MPI" in out.stderr
+    # env exchange: the address must be given outside the program
+    out = _run_py(code, CCL_KVS_IP_EXCHANGE="env")
+    assert out.returncode != 0 and "CCL_KVS_IP_PORT" in out.stderr
+    out = _run_py(code, CCL_KVS_IP_EXCHANGE="env", CCL_KVS_IP_PORT="127.0.0.1_29871")
+    assert out.returncode == 0, out.stderr
+    assert "29871" in out.stdout
