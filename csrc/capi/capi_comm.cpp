@@ -192,6 +192,20 @@ CCLX_API int cclx_comm_rank(void* c) {
 CCLX_API int cclx_comm_size(void* c) {
     return ((comm_handle*)c)->c->size();
 }
+// transport counters of the communicator's world: 0 messages sent, 1 bytes sent, 2 bytes received,
+// 3 unexpected messages, 4 one-sided writes done as cross-memory copies, 5 one-sided writes sent as messages
+CCLX_API long long cclx_comm_transport_stat(void* c, int which) {
+    atl_transport& t = ((comm_handle*)c)->c->atl().transport();
+    switch (which) {
+        case 0: return (long long)t.msgs_sent.load();
+        case 1: return (long long)t.bytes_sent.load();
+        case 2: return (long long)t.bytes_received.load();
+        case 3: return (long long)t.unexpected_msgs.load();
+        case 4: return (long long)t.rma_direct_writes.load();
+        case 5: return (long long)t.rma_message_writes.load();
+        default: return -1;
+    }
+}
 CCLX_API long long cclx_comm_id(void* c) {
     return (long long)((comm_handle*)c)->c->id();
 }

@@ -337,6 +337,65 @@ void allreduce_ring(sched& s, const buf_desc& b) {
     allgatherv_ring(s, nullptr, b.recv, cnt, off, b.dtype, 1000);
 }
 
+// Ring allreduce by one-sided writes (reference src/coll/algorithms/allreduce/allreduce_rma.cpp:121-330):
+// every rank registers its result buffer, a scratch area with one slot per reduce-scatter step and a flag
+// per step, tells them to its left neighbour (its only writer) and learns those of its right neighbour.
+// A step writes the block, then the flag; the receiver waits on the flag in its own memory, so no
+// receive is ever posted.  Regions and flags are set up again on every run of a cached schedule, and a
+// writer cannot start before it has the description of this run, which orders runs against one another.
+void allreduce_ring_rma(sched& s, const buf_desc& b) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(b.dtype);
+    copy_in(s, b.send, b.recv, b.count * esz);
+    if (N == 1)
+        return;
+    std::vector<size_t> cnt, off;
+    block_partition(b.count, N, cnt, off);
+    const size_t slot = (cnt[0] * esz + 63) & ~(size_t)63; // the first block is never smaller than another
+    const int steps = 2 * (N - 1);
+    struct regions {
+        atl_mr mine[3], next[3]; // result buffer, scratch slots, flags
+    };
+    auto reg = std::make_shared<regions>();
+    char* scratch = (char*)s.alloc_tmp(slot * (size_t)(N - 1) + 64);
+    uint64_t* flags = (uint64_t*)s.alloc_tmp(sizeof(uint64_t) * (size_t)steps);
+    const int next = (r + 1) % N, prev = (r - 1 + N) % N;
+    s.add<function_entry>([reg, flags, steps] {
+        for (int i = 0; i < steps; i++)
+            __atomic_store_n(&flags[i], 0, __ATOMIC_RELEASE);
+    });
+    s.add<register_entry>(b.recv, b.count * esz, &reg->mine[0]);
+    s.add<register_entry>(scratch, slot * (size_t)(N - 1), &reg->mine[1]);
+    s.add<register_entry>(flags, sizeof(uint64_t) * (size_t)steps, &reg->mine[2]);
+    s.add_barrier();
+    s.add<send_entry>(reg->mine, sizeof(reg->mine), prev, 0);
+    s.add<recv_entry>(reg->next, sizeof(reg->next), next, 0);
+    s.add_barrier();
+    for (int st = 0; st < steps; st++) {
+        const bool scatter = st < N - 1;
+        const int k = scatter ? st : st - (N - 1);
+        // reduce-scatter: block r-k-1 goes into the neighbour's slot k and is added to its block;
+        // allgather: the finished block r-k goes straight into the neighbour's result buffer
+        const int sb = scatter ? (r - k - 1 + 2 * N) % N : (r - k + 2 * N) % N;
+        const int rb = (r - k - 2 + 2 * N) % N; // reduce-scatter only
+        if (scatter)
+            s.add<write_entry>(at(b.recv, off[sb], esz), cnt[sb] * esz, &reg->next[1], (uint64_t)k * slot);
+        else
+            s.add<write_entry>(at(b.recv, off[sb], esz), cnt[sb] * esz, &reg->next[0], (uint64_t)(off[sb] * esz));
+        s.add_barrier();
+        s.add<write_entry>((uint64_t)1, &reg->next[2], (uint64_t)st * sizeof(uint64_t));
+        s.add<wait_value_entry>((const volatile uint64_t*)&flags[st], 1);
+        s.add_barrier();
+        if (scatter) {
+            s.add<reduce_local_entry>(scratch + (size_t)k * slot, at(b.recv, off[rb], esz), cnt[rb], b.dtype, b.op, b.fn);
+            s.add_barrier();
+        }
+    }
+    for (int i = 0; i < 3; i++)
+        s.add<deregister_entry>(&reg->mine[i]);
+}
+
 void allreduce_recursive_doubling(sched& s, const buf_desc& b) {
     host_comm* c = s.comm();
     const int N = c->size(), r = c->rank();

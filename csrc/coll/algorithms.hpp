@@ -34,6 +34,7 @@ void allreduce_recursive_doubling(sched& s, const buf_desc& b);
 void allreduce_rabenseifner(sched& s, const buf_desc& b);
 void allreduce_nreduce(sched& s, const buf_desc& b);
 void allreduce_2d(sched& s, const buf_desc& b);
+void allreduce_ring_rma(sched& s, const buf_desc& b);
 void allreduce_double_tree(sched& s, const buf_desc& b);
 
 // reduce_scatter: send has recv_count * size elements; recv gets block `rank`

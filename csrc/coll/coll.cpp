@@ -298,6 +298,8 @@ void build_cpu(sched& s, host_comm& comm, const coll_param& p, const coll_attr& 
                 algo::allreduce_2d(s, b);
             else if (a == "double_tree")
                 algo::allreduce_double_tree(s, b);
+            else if (a == "ring_rma")
+                algo::allreduce_ring_rma(s, b);
             else
                 CCL_THROW("allreduce: unknown algorithm ", a);
             break;

@@ -138,8 +138,17 @@ std::string algorithm_selector::select_cpu(const selector_param& p) const {
         const std::string* a = lookup(m->second, p.bytes);
         algo = a ? *a : m->second.back().algo;
     }
+    // one-sided ring: needs the transport's one-sided writes switched on, and a predefined reduction
+    // is not required (the reduction runs on the receiver)
+    if (algo == "ring_rma" && p.ctype == coll_allreduce && !env_data::get().atl_rma) {
+        fallback_allowed("needs CCL_ATL_RMA=1");
+        algo.clear();
+        auto m = main_.find(p.ctype);
+        const std::string* a = lookup(m->second, p.bytes);
+        algo = a ? *a : m->second.back().algo;
+    }
     // names that have no CPU implementation of their own
-    if (algo == "topo" || algo == "ring_rma" || algo == "offload") {
+    if (algo == "topo" || (algo == "ring_rma" && p.ctype != coll_allreduce) || algo == "offload") {
         fallback_allowed("applies to device buffers only");
         LOG_DEBUG(coll_name(p.ctype), ": algorithm ", algo, " applies to device buffers only, using the size table");
         auto m = main_.find(p.ctype);

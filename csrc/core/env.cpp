@@ -149,7 +149,6 @@ void warn_about_names_without_effect() {
         { "CCL_ATL_HMEM", "device buffers travel through NVLink kernels or pinned staging, not through the transport" },
         { "CCL_USE_HMEM", "device buffers travel through NVLink kernels or pinned staging, not through the transport" },
         { "CCL_ATL_SEND_PROXY", "device buffers are staged by the collective layer, not by the transport" },
-        { "CCL_ATL_RMA", "the mesh transport has no one-sided operations" },
         { "CCL_ATL_EXTRA_EP", "every worker already owns an endpoint" },
         { "CCL_STAGING_BUFFER", "staging memory is always pinned host memory" },
         { "CCL_FRAMEWORK", "no framework-specific settings exist" },
@@ -251,6 +250,8 @@ void env_data::parse() {
                                 { "mpi", atl_transport_t::mpi } });
     get_bool("CCL_ATL_SHM", atl_shm);
     get_size("CCL_ATL_SHM_RING_BYTES", atl_shm_ring_bytes);
+    get_bool("CCL_ATL_RMA", atl_rma);
+    get_bool("CCL_ATL_CMA", atl_cma);
     get_size("CCL_MAX_SHORT_SIZE", max_short_size);
     get_size("CCL_CHUNK_COUNT", chunk_count);
     get_size("CCL_MIN_CHUNK_SIZE", min_chunk_size);

@@ -4,7 +4,8 @@
 // recv_entry.hpp:55-85, recv_reduce_entry.hpp:80-135), reduce_local
 // (reduce_local_entry.cpp:98-125), copy (copy/copy_entry.cpp), sync
 // (sync_entry.hpp:25-75), function (function_entry.hpp:20-49), subsched
-// (subsched_entry.hpp:22-202), deps (deps_entry.cpp:24-43), wait_value, probe.
+// (subsched_entry.hpp:22-202), deps (deps_entry.cpp:24-43), wait_value, probe,
+// register / deregister / write (one-sided).
 #pragma once
 #include <cstring>
 #include <functional>
@@ -148,6 +149,53 @@ private:
     const volatile uint64_t* ptr_;
     uint64_t value_;
     bool ge_;
+};
+
+// One-sided operations (reference src/sched/entry/{register,deregister,write}_entry.hpp).  A region is
+// registered when the entry runs, so a cached schedule registers anew on every run and the description
+// it sends to its writers is always current.
+class register_entry : public sched_entry {
+public:
+    register_entry(sched* s, void* buf, size_t bytes, atl_mr* out) : sched_entry(s), buf_(buf), bytes_(bytes), out_(out) {}
+    const char* name() const override { return "REGISTER"; }
+    void start() override;
+
+private:
+    void* buf_;
+    size_t bytes_;
+    atl_mr* out_;
+};
+
+class deregister_entry : public sched_entry {
+public:
+    deregister_entry(sched* s, atl_mr* mr) : sched_entry(s), mr_(mr) {}
+    const char* name() const override { return "DEREGISTER"; }
+    void start() override;
+
+private:
+    atl_mr* mr_;
+};
+
+// writes `bytes` from `buf`, or one 64-bit value, at `offset` of the region *mr; the region
+// description is read when the entry starts (an earlier entry received it)
+class write_entry : public sched_entry {
+public:
+    write_entry(sched* s, const void* buf, size_t bytes, const atl_mr* mr, uint64_t offset)
+            : sched_entry(s), buf_(buf), bytes_(bytes), mr_(mr), offset_(offset) {}
+    write_entry(sched* s, uint64_t value, const atl_mr* mr, uint64_t offset)
+            : sched_entry(s), buf_(&value_), bytes_(sizeof(uint64_t)), mr_(mr), offset_(offset), value_(value) {}
+    const char* name() const override { return "WRITE"; }
+    bool uses_credit() const override { return true; }
+    void start() override;
+    void update() override;
+
+private:
+    const void* buf_;
+    size_t bytes_;
+    const atl_mr* mr_;
+    uint64_t offset_;
+    uint64_t value_ = 0;
+    atl_req req_;
 };
 
 // dependency on caller-provided predicates (events of earlier operations)

@@ -128,6 +128,22 @@ void send_entry::update() {
     status_ = req_.is_done() ? entry_status::complete : entry_status::started;
 }
 
+void register_entry::start() {
+    *out_ = owner_->comm()->atl().mr_reg(buf_, bytes_);
+    status_ = entry_status::complete;
+}
+void deregister_entry::start() {
+    owner_->comm()->atl().mr_dereg(*mr_);
+    status_ = entry_status::complete;
+}
+void write_entry::start() {
+    owner_->comm()->atl().rma_write(owner_->ep(), buf_, bytes_, *mr_, offset_, &req_);
+    update();
+}
+void write_entry::update() {
+    status_ = req_.is_done() ? entry_status::complete : entry_status::started;
+}
+
 void recv_entry::start() {
     owner_->comm()->atl().recv(owner_->ep(), buf_, bytes_, src_, owner_->tag(step_), &req_);
     update();

@@ -46,6 +46,18 @@ struct atl_tag {
     static constexpr uint64_t UNORDERED_SPAN = 1u << 20;
 };
 
+// A registered memory region, as its owner describes it to a peer (plain data: it travels in a message).
+// One-sided writes address it by offset.  Counterpart of the reference's atl_mr_t
+// (src/atl/atl_def.h:160-175); here the key is the owner's pid, because between processes of one host
+// the write is a cross-memory copy (process_vm_writev) that needs no pinning, and between hosts it is
+// a message that the owner's progress engine applies to the region.
+struct atl_mr {
+    uint64_t addr = 0;
+    uint64_t len = 0;
+    int32_t pid = 0;
+    int32_t owner = -1; // world rank
+};
+
 // process-wide mesh of connections among the ranks of one "world" (one KVS rendezvous)
 class atl_transport {
 public:
@@ -60,6 +72,12 @@ public:
     virtual void poll(int ep) = 0;
     virtual bool same_host(int peer) const = 0;
     virtual const char* name() const = 0;
+    // one-sided writes: register, tell the region to the writers by an ordinary message, write.
+    // Writes of one rank to one region arrive in the order they were issued on one endpoint.
+    virtual atl_mr mr_reg(void* buf, size_t len) = 0;
+    virtual void mr_dereg(const atl_mr& mr) = 0;
+    virtual void rma_write(int ep, const void* buf, size_t len, const atl_mr& mr, uint64_t offset, atl_req* req) = 0;
+    std::atomic<uint64_t> rma_direct_writes{ 0 }, rma_message_writes{ 0 };
     // statistics
     std::atomic<uint64_t> bytes_sent{ 0 }, bytes_received{ 0 }, msgs_sent{ 0 }, unexpected_msgs{ 0 };
 };
@@ -86,6 +104,11 @@ public:
     }
     void poll(int ep) { tr_->poll(ep); }
     void wait(int ep, atl_req* req);
+    atl_mr mr_reg(void* buf, size_t len) { return tr_->mr_reg(buf, len); }
+    void mr_dereg(const atl_mr& mr) { tr_->mr_dereg(mr); }
+    void rma_write(int ep, const void* buf, size_t len, const atl_mr& mr, uint64_t offset, atl_req* req) {
+        tr_->rma_write(ep, buf, len, mr, offset, req);
+    }
 
     // blocking helpers used during setup (run on endpoint 0 with internal tags)
     void allgather(const void* send, void* recv, size_t bytes_per_rank);

@@ -22,6 +22,7 @@
 #include <sys/mman.h>
 #include <sys/stat.h>
 #include <sys/socket.h>
+#include <sys/uio.h>
 #include <unistd.h>
 
 #include <algorithm>
@@ -51,7 +52,12 @@ struct out_msg {
     const char* payload;
     size_t sent = 0; // of header + payload
     atl_req* req;
+    std::vector<char> owned; // payload kept by the message itself (one-sided writes carried as messages)
 };
+
+// tag of a one-sided write that travels as a message: payload = target address, then the data.
+// No schedule produces it (communicator id, schedule id and operation id all at their maxima).
+constexpr uint64_t RMA_WRITE_TAG = ~0ull;
 
 struct posted_recv {
     uint64_t tag;
@@ -332,6 +338,78 @@ public:
         ps.posted.push_back(posted_recv{ tag, (char*)buf, len, req });
     }
 
+    atl_mr mr_reg(void* buf, size_t len) override {
+        std::lock_guard<std::mutex> lk(mr_mu_);
+        regions_.emplace_back((char*)buf, len);
+        atl_mr mr;
+        mr.addr = (uint64_t)(uintptr_t)buf;
+        mr.len = len;
+        mr.pid = (int32_t)getpid();
+        mr.owner = rank_;
+        return mr;
+    }
+
+    void mr_dereg(const atl_mr& mr) override {
+        std::lock_guard<std::mutex> lk(mr_mu_);
+        for (auto it = regions_.begin(); it != regions_.end(); ++it)
+            if ((uint64_t)(uintptr_t)it->first == mr.addr && it->second == mr.len) {
+                regions_.erase(it);
+                return;
+            }
+    }
+
+    void rma_write(int e, const void* buf, size_t len, const atl_mr& mr, uint64_t offset, atl_req* req) override {
+        CCL_THROW_IF_NOT(mr.owner >= 0 && mr.owner < size_, "one-sided write to an unknown region");
+        CCL_THROW_IF_NOT(offset + len <= mr.len, "one-sided write of ", len, " bytes at offset ", offset,
+                         " leaves the region of ", mr.len, " bytes");
+        req->reset();
+        if (mr.owner == rank_) {
+            std::memcpy((char*)(uintptr_t)mr.addr + offset, buf, len);
+            req->done.store(1, std::memory_order_release);
+            return;
+        }
+        if (same_host_[mr.owner] && env_data::get().atl_cma && cma_ok_.load(std::memory_order_relaxed)) {
+            // cross-memory copy into the owner's address space: complete when the call returns
+            size_t done = 0;
+            bool failed = false;
+            while (done < len) {
+                iovec l{ (char*)buf + done, len - done };
+                iovec r{ (char*)(uintptr_t)mr.addr + offset + done, len - done };
+                const ssize_t n = process_vm_writev(mr.pid, &l, 1, &r, 1, 0);
+                if (n <= 0) {
+                    failed = true;
+                    break;
+                }
+                done += (size_t)n;
+            }
+            if (!failed) {
+                rma_direct_writes++;
+                req->done.store(1, std::memory_order_release);
+                return;
+            }
+            CCL_THROW_IF_NOT(done == 0, "cross-memory write stopped after ", done, " of ", len, " bytes: ",
+                             std::strerror(errno));
+            // not permitted here (ptrace policy, container): every later write goes as a message
+            LOG_INFO("process_vm_writev: ", std::strerror(errno), "; one-sided writes travel as messages");
+            cma_ok_.store(false, std::memory_order_relaxed);
+        }
+        endpoint& ep = eps_[e];
+        std::lock_guard<std::mutex> lk(ep.mu);
+        peer_state& ps = ep.peers[mr.owner];
+        rma_message_writes++;
+        ps.outq.emplace_back();
+        out_msg& m = ps.outq.back();
+        m.owned.resize(sizeof(uint64_t) + len);
+        const uint64_t target = mr.addr + offset;
+        std::memcpy(m.owned.data(), &target, sizeof(target));
+        std::memcpy(m.owned.data() + sizeof(target), buf, len);
+        m.hdr.tag = RMA_WRITE_TAG;
+        m.hdr.len = m.owned.size();
+        m.payload = m.owned.data();
+        m.req = req;
+        flush(ps);
+    }
+
     bool probe(int e, int src, uint64_t tag, size_t* len) override {
         endpoint& ep = eps_[e];
         std::lock_guard<std::mutex> lk(ep.mu);
@@ -514,6 +592,10 @@ private:
             ps.in_req->done.store(1, std::memory_order_release);
             ps.in_req = nullptr;
         }
+        else if (ps.in_unexp && ps.in_unexp->tag == RMA_WRITE_TAG) {
+            apply_remote_write(ps.in_unexp->data);
+            ps.unexp.pop_back(); // the message under construction is always the last one
+        }
         else if (ps.in_unexp)
             ps.in_unexp->complete = true;
         ps.in_unexp = nullptr;
@@ -521,6 +603,29 @@ private:
         ps.in_body = false;
         ps.hdr_got = 0;
         ps.in_got = 0;
+    }
+
+    // a one-sided write that came as a message: only registered memory is ever written
+    void apply_remote_write(const std::vector<char>& msg) {
+        if (msg.size() < sizeof(uint64_t))
+            return;
+        uint64_t target;
+        std::memcpy(&target, msg.data(), sizeof(target));
+        const size_t len = msg.size() - sizeof(target);
+        char* dst = (char*)(uintptr_t)target;
+        bool inside = false;
+        {
+            std::lock_guard<std::mutex> lk(mr_mu_);
+            for (auto& r : regions_)
+                if (dst >= r.first && dst + len <= r.first + r.second)
+                    inside = true;
+        }
+        if (!inside) {
+            LOG_ERROR("dropped a one-sided write of ", len, " bytes outside every registered region");
+            return;
+        }
+        std::memcpy(dst, msg.data() + sizeof(target), len);
+        std::atomic_thread_fence(std::memory_order_release);
     }
 
     void drain(peer_state& ps) {
@@ -593,6 +698,9 @@ private:
     std::vector<char> same_host_;
     size_t ring_cap_ = 0;
     std::vector<std::pair<void*, size_t>> maps_;
+    std::mutex mr_mu_;
+    std::vector<std::pair<char*, size_t>> regions_;
+    std::atomic<bool> cma_ok_{ true };
 };
 
 } // namespace

@@ -200,6 +200,13 @@ class Communicator:
     def id(self) -> int:
         return int(self._lib.cclx_comm_id(self._h))
 
+    def transport_stats(self) -> dict:
+        """Counters of the host transport under this communicator: messages and bytes, messages that
+        arrived before their receive was posted, one-sided writes by cross-memory copy and by message."""
+        names = ("msgs_sent", "bytes_sent", "bytes_received", "unexpected_msgs", "rma_direct_writes",
+                 "rma_message_writes")
+        return {n: int(self._lib.cclx_comm_transport_stat(self._h, k)) for k, n in enumerate(names)}
+
     @property
     def local_rank(self) -> int:
         return self._lib.cclx_comm_local_rank(self._h)

@@ -237,3 +237,53 @@ def test_chunking_and_partition_knobs(env, world, nodes):
     CCL_ALLREDUCE_2D_CHUNK_COUNT / _SWITCH_DIMS over two and three simulated nodes, CCL_CHUNK_COUNT,
     CCL_BCAST_PART_COUNT, CCL_MAX_SHORT_SIZE, CCL_BUFFER_CACHE."""
     assert all(run_ranks(_chunked, world, nodes, env=env))
+
+
+def _ring_rma(comm):
+    W, r = comm.size, comm.rank
+    for count in (5, 4099, 300001):
+        base = (np.arange(count) % 13).astype(np.float64)
+        for _ in range(3):  # repeated runs reuse scratch memory and flags
+            buf = base + r
+            comm.allreduce(buf).wait()
+            assert np.array_equal(buf, base * W + sum(range(W))), count
+        send = (base + r).astype(np.int32)
+        out = np.zeros(count, np.int32)
+        comm.allreduce(send, out, op="max").wait()
+        assert np.array_equal(out, (base + W - 1).astype(np.int32))
+    # a cached schedule is started again with the same buffers
+    buf = np.zeros(1000, np.float32)
+    for it in range(4):
+        buf[:] = r + it
+        comm.allreduce(buf, match_id="rma_cached", to_cache=True).wait()
+        assert np.all(buf == sum(range(W)) + W * it)
+    return comm.transport_stats()
+
+
+@pytest.mark.parametrize("env,direct", [
+    ({}, True),
+    ({"CCL_ATL_CMA": "0"}, False),
+    ({"CCL_ATL_CMA": "0", "CCL_ATL_SHM": "0", "CCL_WORKER_COUNT": "2"}, False),
+], ids=["cross-memory", "messages-over-rings", "messages-over-sockets"])
+@pytest.mark.parametrize("world", [2, 5])
+def test_allreduce_ring_by_one_sided_writes(env, direct, world):
+    """CCL_ALLREDUCE=ring_rma with CCL_ATL_RMA=1: blocks and flags are written into the neighbour's registered
+    memory, by process_vm_writev between processes of one host or as messages that the owner applies."""
+    env = dict(env, CCL_ALLREDUCE="ring_rma", CCL_ATL_RMA="1")
+    for st in run_ranks(_ring_rma, world, env=env):
+        if direct:
+            assert st["rma_direct_writes"] > 0 and st["rma_message_writes"] == 0, st
+        else:
+            assert st["rma_message_writes"] > 0 and st["rma_direct_writes"] == 0, st
+
+
+def test_ring_rma_without_the_transport_switch_falls_back():
+    for st in run_ranks(_ring_rma_off, 2, env={"CCL_ALLREDUCE": "ring_rma"}):
+        assert st["rma_direct_writes"] == 0 and st["rma_message_writes"] == 0
+
+
+def _ring_rma_off(comm):
+    buf = np.full(100000, comm.rank + 1.0)
+    comm.allreduce(buf).wait()
+    assert np.all(buf == 3.0)
+    return comm.transport_stats()
