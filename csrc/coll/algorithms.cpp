@@ -634,18 +634,55 @@ void allreduce_double_tree(sched& s, const buf_desc& b) {
 }
 
 // ---------------------------------------------------------------------------- alltoallv
+namespace {
+// In place (send == recv; every pair exchanges equal amounts, so the block layout is the same on both
+// sides): blocks are received into scratch memory and copied over the send data once every send has left
+// (reference src/coll/algorithms/alltoallv.cpp:129-200).
+struct a2a_landing {
+    char* base; // where block p lands: base + roffs[p] * esz
+    bool staged;
+};
+a2a_landing a2a_prepare(sched& s, const void* send, void* recv, const std::vector<size_t>& scounts,
+                        const std::vector<size_t>& soffs, const std::vector<size_t>& rcounts,
+                        const std::vector<size_t>& roffs, size_t esz) {
+    const int r = s.comm()->rank();
+    if (send == recv) {
+        size_t total = 0;
+        for (size_t i = 0; i < rcounts.size(); i++)
+            total = std::max(total, roffs[i] + rcounts[i]);
+        return a2a_landing{ (char*)s.alloc_tmp(total * esz + 64), true };
+    }
+    s.add<copy_entry>(at(send, soffs[r], esz), at(recv, roffs[r], esz), std::min(scounts[r], rcounts[r]) * esz);
+    return a2a_landing{ (char*)recv, false };
+}
+void a2a_finish(sched& s, const a2a_landing& l, void* recv, const std::vector<size_t>& rcounts,
+                const std::vector<size_t>& roffs, size_t esz) {
+    if (!l.staged)
+        return;
+    const int N = s.comm()->size(), r = s.comm()->rank();
+    for (int p = 0; p < N; p++)
+        if (p != r && rcounts[p])
+            s.add<copy_entry>(l.base + roffs[p] * esz, at(recv, roffs[p], esz), rcounts[p] * esz);
+    s.add_barrier();
+}
+} // namespace
+
 void alltoallv_naive(sched& s, const void* send, const std::vector<size_t>& scounts, const std::vector<size_t>& soffs,
                      void* recv, const std::vector<size_t>& rcounts, const std::vector<size_t>& roffs, int dtype) {
     host_comm* c = s.comm();
     const int N = c->size(), r = c->rank();
     const size_t esz = dtype_size(dtype);
-    s.add<copy_entry>(at(send, soffs[r], esz), at(recv, roffs[r], esz), std::min(scounts[r], rcounts[r]) * esz);
+    const a2a_landing land = a2a_prepare(s, send, recv, scounts, soffs, rcounts, roffs, esz);
     for (int k = 1; k < N; k++) {
         const int src = (r - k + N) % N, dst = (r + k) % N;
-        chunked_recv(s, at(recv, roffs[src], esz), rcounts[src], esz, src, 0);
-        chunked_send(s, at(send, soffs[dst], esz), scounts[dst], esz, dst, 0);
+        // The step is the distance between the ranks, as in alltoallv_scatter: the size table sees this
+        // rank's own send total, so two ranks of one alltoallv may pick different patterns, and the
+        // messages of the two must still match.
+        chunked_recv(s, land.base + roffs[src] * esz, rcounts[src], esz, src, (uint64_t)k);
+        chunked_send(s, at(send, soffs[dst], esz), scounts[dst], esz, dst, (uint64_t)k);
     }
     s.add_barrier();
+    a2a_finish(s, land, recv, rcounts, roffs, esz);
 }
 
 void alltoallv_scatter(sched& s, const void* send, const std::vector<size_t>& scounts,
@@ -656,12 +693,12 @@ void alltoallv_scatter(sched& s, const void* send, const std::vector<size_t>& sc
     const size_t esz = dtype_size(dtype);
     if (max_ops == 0)
         max_ops = 1;
-    s.add<copy_entry>(at(send, soffs[r], esz), at(recv, roffs[r], esz), std::min(scounts[r], rcounts[r]) * esz);
+    const a2a_landing land = a2a_prepare(s, send, recv, scounts, soffs, rcounts, roffs, esz);
     // flow control: at most max_ops exchanges in flight, then a barrier point
     size_t in_batch = 0;
     for (int k = 1; k < N; k++) {
         const int src = (r - k + N) % N, dst = (r + k) % N;
-        chunked_recv(s, at(recv, roffs[src], esz), rcounts[src], esz, src, (uint64_t)k);
+        chunked_recv(s, land.base + roffs[src] * esz, rcounts[src], esz, src, (uint64_t)k);
         chunked_send(s, at(send, soffs[dst], esz), scounts[dst], esz, dst, (uint64_t)k);
         if (++in_batch == max_ops) {
             s.add_barrier();
@@ -669,6 +706,7 @@ void alltoallv_scatter(sched& s, const void* send, const std::vector<size_t>& sc
         }
     }
     s.add_barrier();
+    a2a_finish(s, land, recv, rcounts, roffs, esz);
 }
 
 // ---------------------------------------------------------------------------- barrier

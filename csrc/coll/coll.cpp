@@ -719,11 +719,16 @@ event_ptr start_sched(host_comm& comm, const coll_param& p, const coll_attr& att
         comm.cache().flush();
     master_sched* m = nullptr;
     std::unique_ptr<master_sched> owned;
+    uint64_t launch_id = executor::KEEP_ID;
     if (cacheable) {
         const std::string key = coll_cache_key(comm, p, attr);
         m = comm.cache().find(key);
-        if (m)
+        if (m) {
             stats().cache_hits++;
+            // every call draws an id, hit or miss, so the ranks stay in step whatever their caches hold
+            if (fixed_id == NO_SCHED_ID)
+                launch_id = comm.next_sched_id();
+        }
         else {
             auto fresh = build_master(comm, p, attr, fixed_id != NO_SCHED_ID ? fixed_id : comm.next_sched_id());
             m = fresh.get();
@@ -743,7 +748,7 @@ event_ptr start_sched(host_comm& comm, const coll_param& p, const coll_attr& att
         owned = build_master(comm, p, attr, sid);
         m = owned.get();
     }
-    const uint64_t ticket = executor::get().start(m);
+    const uint64_t ticket = executor::get().start(m, launch_id);
     return std::make_shared<host_event>(m, ticket, std::move(owned));
 }
 

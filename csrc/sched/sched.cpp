@@ -224,6 +224,7 @@ void subsched_entry::start() {
         sub_->op_base = owner_->op_base;
         builder_(*sub_);
     }
+    sub_->set_sched_id(owner_->sched_id()); // a cached owner runs under a new id every time
     update();
 }
 void subsched_entry::update() {
@@ -323,6 +324,12 @@ void sched::profile(std::string& out) const {
 // ---- master ---------------------------------------------------------------------------
 master_sched::master_sched(host_comm* comm, uint64_t sched_id) : comm_(comm), sched_id_(sched_id) {}
 master_sched::~master_sched() = default;
+
+void master_sched::renew_id(uint64_t id) {
+    sched_id_ = id;
+    for (auto& p : partials_)
+        p->set_sched_id(id); // nested schedules take the id of their owner when they start
+}
 
 sched* master_sched::add_partial(int ep) {
     partials_.emplace_back(new sched(comm_, sched_id_, ep));
@@ -603,25 +610,31 @@ void executor::launch_now(master_sched* m) {
         workers_[p->ep() % workers_.size()]->add(p.get());
 }
 
-uint64_t executor::start(master_sched* m) {
+uint64_t executor::start(master_sched* m, uint64_t new_id) {
     CCL_THROW_IF_NOT(!workers_.empty(), "executor is not running");
     if (!m->req().on_last) {
         m->req().on_last = [this, m] {
             if (m->user_complete)
                 m->user_complete();
             bool again = false;
+            uint64_t next_id = KEEP_ID;
             {
                 std::lock_guard<std::mutex> lk(m->launch_mu);
                 if (m->delayed_launches > 0) {
                     m->delayed_launches--;
                     again = true;
+                    next_id = m->pending_ids.front();
+                    m->pending_ids.pop_front();
                 }
                 else
                     m->in_flight = false;
             }
-            if (again)
+            if (again) {
                 for (auto& p : m->partials())
                     p->reset();
+                if (next_id != KEEP_ID)
+                    m->renew_id(next_id);
+            }
             m->done.fetch_add(1, std::memory_order_acq_rel);
             if (again)
                 launch_now(m);
@@ -631,8 +644,10 @@ uint64_t executor::start(master_sched* m) {
     bool now = false;
     {
         std::lock_guard<std::mutex> lk(m->launch_mu);
-        if (m->in_flight)
+        if (m->in_flight) {
             m->delayed_launches++;
+            m->pending_ids.push_back(new_id);
+        }
         else {
             m->in_flight = true;
             now = true;
@@ -642,6 +657,8 @@ uint64_t executor::start(master_sched* m) {
         if (ticket > 1)
             for (auto& p : m->partials())
                 p->reset();
+        if (new_id != KEEP_ID)
+            m->renew_id(new_id);
         launch_now(m);
     }
     return ticket;

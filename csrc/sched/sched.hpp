@@ -116,6 +116,7 @@ public:
     host_comm* comm() const { return comm_; }
     int ep() const { return ep_; }
     uint64_t sched_id() const { return sched_id_; }
+    void set_sched_id(uint64_t id) { sched_id_ = id; }
     uint64_t tag(uint64_t step) const;
 
     // building
@@ -160,6 +161,12 @@ public:
     std::vector<std::unique_ptr<sched>>& partials() { return partials_; }
     uint64_t sched_id() const { return sched_id_; }
     host_comm* comm() const { return comm_; }
+    // A cached schedule takes a new id on every launch (reference sched.cpp: the id is updated at each
+    // commit).  Ranks may disagree on which calls hit their caches (a key made of buffer addresses hits
+    // on one rank and misses on another), but they agree on the order of calls, so the id drawn per
+    // call is the same everywhere while an id kept from build time would not be.
+    void renew_id(uint64_t id);
+    std::deque<uint64_t> pending_ids; // ids of launches queued behind the running one (under launch_mu)
 
     // launch tickets: launch k is complete when done >= k
     std::atomic<uint64_t> issued{ 0 }, done{ 0 };
@@ -232,7 +239,9 @@ public:
     void shutdown();
     int worker_count() const { return (int)workers_.size(); }
     // returns the launch ticket
-    uint64_t start(master_sched* m);
+    static constexpr uint64_t KEEP_ID = ~0ull;
+    // `new_id`: schedule id of this launch (KEEP_ID: the one the schedule was built with)
+    uint64_t start(master_sched* m, uint64_t new_id = KEEP_ID);
     void wait(master_sched* m, uint64_t ticket);
     bool test(master_sched* m, uint64_t ticket);
     void launch_now(master_sched* m); // arm + enqueue (internal)
