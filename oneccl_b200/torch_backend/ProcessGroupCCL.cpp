@@ -138,6 +138,36 @@ private:
     cudaEvent_t done_ = nullptr;
 };
 
+// what endCoalescing hands back: complete when every operation issued inside the batch is
+class CoalescedWorkCCL : public Work {
+public:
+    explicit CoalescedWorkCCL(std::vector<c10::intrusive_ptr<Work>> parts)
+            : Work(-1, OpType::COALESCED), parts_(std::move(parts)) {}
+    bool isCompleted() override {
+        for (auto& p : parts_)
+            if (!p->isCompleted())
+                return false;
+        return true;
+    }
+    bool isSuccess() const override { return true; }
+    bool wait(std::chrono::milliseconds timeout = kNoTimeout) override {
+        for (auto& p : parts_)
+            p->wait(timeout);
+        return true;
+    }
+    void synchronize() override { wait(); }
+    c10::intrusive_ptr<c10::ivalue::Future> getFuture() override {
+        // the parts' futures carry the device events; the batch as a whole completes on the host side
+        auto f = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
+        wait();
+        f->markCompleted(c10::IValue(std::vector<at::Tensor>{}));
+        return f;
+    }
+
+private:
+    std::vector<c10::intrusive_ptr<Work>> parts_;
+};
+
 std::atomic<int> pg_counter{ 0 };
 
 } // namespace
@@ -217,6 +247,8 @@ public:
             c10::cuda::CUDAStreamGuard g(c10::cuda::getStreamFromExternal(c.comm_stream, c.dev));
             w->mark_launched();
         }
+        if (coalescing_)
+            batch_.push_back(w);
         return w;
     }
 
@@ -357,6 +389,19 @@ public:
             }
         }
         return finish(c, w);
+    }
+
+    c10::intrusive_ptr<Work> allgather_coalesced(std::vector<std::vector<at::Tensor>>& output_lists,
+                                                 std::vector<at::Tensor>& inputs,
+                                                 const AllgatherOptions& opts = AllgatherOptions()) override {
+        TORCH_CHECK(output_lists.size() == inputs.size(), "ccl backend: one output list per input tensor");
+        std::vector<c10::intrusive_ptr<Work>> parts;
+        for (size_t i = 0; i < inputs.size(); i++) {
+            std::vector<std::vector<at::Tensor>> outs{ output_lists[i] };
+            std::vector<at::Tensor> in{ inputs[i] };
+            parts.push_back(allgather(outs, in, opts));
+        }
+        return c10::make_intrusive<CoalescedWorkCCL>(std::move(parts));
     }
 
     c10::intrusive_ptr<Work> allgather_into_tensor_coalesced(std::vector<at::Tensor>& outputs,
@@ -553,8 +598,8 @@ public:
     c10::intrusive_ptr<Work> endCoalescing() override {
         ccl::group_end();
         coalescing_ = false;
-        auto w = c10::make_intrusive<WorkCCL>(OpType::COALESCED, std::vector<at::Tensor>{}, std::vector<at::Tensor>{});
-        w->make_future(false, 0);
+        auto w = c10::make_intrusive<CoalescedWorkCCL>(std::move(batch_));
+        batch_.clear();
         return w;
     }
     bool supportsCoalescing() const override { return true; }
@@ -578,6 +623,7 @@ private:
     std::mutex mu_;
     std::map<c10::DeviceIndex, cudaStream_t> streams_;
     bool coalescing_ = false;
+    std::vector<c10::intrusive_ptr<Work>> batch_; // operations issued since startCoalescing
 };
 
 } // namespace c10d

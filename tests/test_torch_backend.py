@@ -199,3 +199,99 @@ def test_ccl_backend_cpu_remaining_operations():
         p.join(timeout=30)
     for rank, status, msg in res:
         assert status == "ok", f"rank {rank}:\n{msg}"
+
+
+def _worker_p2p_and_dtypes(rank, world, port, q):
+    """Point-to-point batches, the coalescing manager, every tensor dtype the backend maps, reductions,
+    non-contiguous inputs, and the tensor forms that sharded data parallelism uses."""
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        import torch.distributed as dist
+
+        import oneccl_b200.torch_backend  # noqa: F401
+
+        dist.init_process_group("ccl", rank=rank, world_size=world)
+        W = world
+        nxt, prv = (rank + 1) % W, (rank - 1) % W
+        # isend / irecv
+        got = torch.zeros(6)
+        rr = dist.irecv(got, src=prv)
+        rs = dist.isend(torch.full((6,), float(rank)), dst=nxt)
+        rr.wait()
+        rs.wait()
+        assert torch.all(got == prv)
+        # a batch in both directions at once
+        a, b = torch.zeros(4), torch.zeros(4)
+        ops = [dist.P2POp(dist.isend, torch.full((4,), float(rank + 1)), nxt),
+               dist.P2POp(dist.isend, torch.full((4,), float(-rank - 1)), prv),
+               dist.P2POp(dist.irecv, a, prv), dist.P2POp(dist.irecv, b, nxt)]
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+        assert torch.all(a == prv + 1) and torch.all(b == -(nxt + 1))
+        # dtypes x reductions
+        for dt in (torch.float32, torch.float64, torch.float16, torch.bfloat16, torch.int8, torch.uint8, torch.int32,
+                   torch.int64):
+            t = (torch.arange(33) % 3 + rank + 1).to(dt)
+            dist.all_reduce(t)
+            ref = sum((torch.arange(33) % 3 + p + 1) for p in range(W)).to(dt)
+            assert torch.equal(t, ref), dt
+            for op, fn in ((dist.ReduceOp.MAX, max), (dist.ReduceOp.MIN, min)):
+                t = torch.full((5,), rank + 1).to(dt)
+                dist.all_reduce(t, op=op)
+                assert torch.all(t == fn(range(1, W + 1))), (dt, op)
+        t = torch.full((3,), 2.0)
+        dist.all_reduce(t, op=dist.ReduceOp.PRODUCT)
+        assert torch.all(t == 2.0 ** W)
+        t = torch.full((4,), float(rank))
+        dist.all_reduce(t, op=dist.ReduceOp.AVG)
+        assert torch.allclose(t, torch.full((4,), (W - 1) / 2))
+        # bool travels as uint8
+        flag = torch.tensor([rank == 0, True])
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        assert flag.tolist() == [True, True]
+        # non-contiguous input
+        m = (torch.arange(12, dtype=torch.float32).reshape(3, 4) + rank).t()
+        assert not m.is_contiguous()
+        dist.all_reduce(m)
+        assert torch.equal(m, (torch.arange(12, dtype=torch.float32).reshape(3, 4) * W + sum(range(W))).t())
+        # sharded-parameter pattern: gather the shards, reduce-scatter the gradients
+        shard = torch.full((8,), float(rank))
+        full = torch.zeros(8 * W)
+        dist.all_gather_into_tensor(full, shard)
+        assert torch.equal(full, torch.arange(W, dtype=torch.float32).repeat_interleave(8))
+        grad = torch.arange(8 * W, dtype=torch.float32) + rank
+        out = torch.zeros(8)
+        dist.reduce_scatter_tensor(out, grad, op=dist.ReduceOp.AVG)
+        assert torch.allclose(out, torch.arange(8 * rank, 8 * rank + 8, dtype=torch.float32) + (W - 1) / 2)
+        # coalescing manager
+        xs = [torch.full((k + 1,), float(rank + k)) for k in range(4)]
+        with dist._coalescing_manager():
+            for x in xs:
+                dist.all_reduce(x)
+        for k, x in enumerate(xs):
+            assert torch.all(x == sum(p + k for p in range(W))), k
+        lst = [[torch.zeros(2) for _ in range(W)] for _ in range(2)]
+        dist.all_gather_coalesced(lst, [torch.full((2,), float(rank)), torch.full((2,), float(rank * 2))])
+        for p in range(W):
+            assert torch.all(lst[0][p] == p) and torch.all(lst[1][p] == 2 * p)
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok", ""))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def test_ccl_backend_cpu_p2p_batches_dtypes_and_sharded_patterns():
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_p2p_and_dtypes, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, status, msg in res:
+        assert status == "ok", f"rank {rank}: {msg}"
