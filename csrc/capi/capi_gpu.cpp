@@ -283,6 +283,10 @@ CCLX_API int cclx_reduce_local(const void* in, void* inout, size_t count, int dt
     return capi::guard([&] { launch_reduce_local(in, inout, count, dt, op, (cudaStream_t)stream); });
 }
 
+CCLX_API int cclx_transpose_blocks(const void* in, void* out, int rows, int cols, size_t block_bytes, void* stream) {
+    return capi::guard([&] { launch_transpose_blocks(in, out, rows, cols, block_bytes, (cudaStream_t)stream); });
+}
+
 CCLX_API int cclx_pack(const void* const* ptrs_dev, const size_t* offs_dev, int n, void* fused, int unpack,
                        size_t max_tensor_bytes, void* stream) {
     return capi::guard(

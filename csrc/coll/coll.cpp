@@ -646,6 +646,110 @@ event_ptr hier_device_allreduce(host_comm& comm, coll_param& p, const coll_attr&
     return device_coll(*node, ag, none);
 }
 
+// reduce_scatter on device buffers across nodes.  Send buffers are ordered by global rank, which the
+// check below requires to be node-major (rank = node * L + local).  The blocks are regrouped by local
+// rank, the node-level reduce_scatter leaves on local rank l the node's partial sums of the blocks of
+// every rank with local index l, and those ranks finish with a reduce_scatter among themselves on the
+// host path (CCL_REDUCE_SCATTER_SCALEOUT chooses its algorithm).  Per rank N * count elements cross
+// NVLink once and M * count elements cross the network stage, instead of N * count through the host.
+bool hier_reduce_scatter_possible(host_comm& comm, const coll_param& p, const coll_attr& attr) {
+    if (p.ctype != coll_reduce_scatter || !env_data::get().cuda_kernels || !env_data::get().topo_algo ||
+        attr.reduction_fn || attr.out_dtype >= 0 || attr.do_scale || p.count == 0 || p.reduction == red_custom)
+        return false;
+    const int L = comm.local_size();
+    if (L <= 0 || comm.size() % L != 0)
+        return false;
+    const std::vector<int>& h = comm.host_index();
+    for (int r = 0; r < comm.size(); r++)
+        if (h[r] != r / L)
+            return false;
+    return true;
+}
+
+event_ptr hier_device_reduce_scatter(host_comm& comm, coll_param& p, const coll_attr& attr) {
+    (void)attr;
+    auto node = comm.node_comm();
+    auto r2r = comm.r2r_comm();
+    const int L = node->size(), M = r2r->size();
+    const size_t esz = dtype_size(p.dtype);
+    const size_t block = p.count * esz; // what one rank receives
+    cudaStream_t st = (cudaStream_t)p.stream;
+    stats().device_calls[coll_reduce_scatter]++;
+    struct scratch {
+        void *grouped = nullptr, *slice = nullptr, *host_in = nullptr, *host_out = nullptr;
+        size_t cap_grouped = 0, cap_slice = 0, cap_out = 0;
+        static void grow_dev(void*& ptr, size_t& cap, size_t want) {
+            if (cap >= want)
+                return;
+            if (ptr)
+                CUDA_CHECK(cudaFree(ptr));
+            ptr = nullptr;
+            cap = 0;
+            CUDA_CHECK(cudaMalloc(&ptr, want));
+            cap = want;
+        }
+        ~scratch() {
+            if (grouped)
+                cudaFree(grouped);
+            if (slice)
+                cudaFree(slice);
+            if (host_in)
+                cudaFreeHost(host_in);
+            if (host_out)
+                cudaFreeHost(host_out);
+        }
+    };
+    static thread_local scratch sc;
+    const size_t slice_bytes = (size_t)M * block;
+    if (sc.cap_slice < slice_bytes) {
+        if (sc.host_in)
+            CUDA_CHECK(cudaFreeHost(sc.host_in));
+        sc.host_in = nullptr;
+        CUDA_CHECK(cudaMallocHost(&sc.host_in, slice_bytes));
+    }
+    scratch::grow_dev(sc.slice, sc.cap_slice, slice_bytes);
+    if (sc.cap_out < block) {
+        if (sc.host_out)
+            CUDA_CHECK(cudaFreeHost(sc.host_out));
+        sc.host_out = nullptr;
+        sc.cap_out = 0;
+        CUDA_CHECK(cudaMallocHost(&sc.host_out, block));
+        sc.cap_out = block;
+    }
+    // 1. node-major -> local-rank-major (nothing to move when one of the two dimensions is 1)
+    const void* grouped = p.send_buf;
+    if (L > 1 && M > 1) {
+        scratch::grow_dev(sc.grouped, sc.cap_grouped, (size_t)L * M * block);
+        gpu::launch_transpose_blocks(p.send_buf, sc.grouped, M, L, block, st);
+        grouped = sc.grouped;
+    }
+    // 2. inside the node: the partial sums of the M blocks that belong to my local index
+    coll_param rs = p;
+    rs.send_buf = grouped;
+    rs.recv_buf = sc.slice;
+    rs.count = (size_t)M * p.count;
+    rs.deps.clear();
+    coll_attr plain;
+    device_coll(*node, rs, plain)->wait();
+    CUDA_CHECK(cudaMemcpyAsync(sc.host_in, sc.slice, slice_bytes, cudaMemcpyDeviceToHost, st));
+    CUDA_CHECK(cudaStreamSynchronize(st));
+    // 3. among the ranks with my local index, one per node: block m goes to node m
+    coll_param rx;
+    rx.ctype = coll_reduce_scatter;
+    rx.send_buf = sc.host_in;
+    rx.recv_buf = sc.host_out;
+    rx.count = p.count;
+    rx.dtype = p.dtype;
+    rx.reduction = p.reduction;
+    rx.device = false;
+    coll_attr host_attr;
+    host_attr.scaleout = true;
+    coll_create(*r2r, rx, host_attr)->wait();
+    CUDA_CHECK(cudaMemcpyAsync(p.recv_buf, sc.host_out, block, cudaMemcpyHostToDevice, st));
+    CUDA_CHECK(cudaStreamSynchronize(st)); // the pinned buffer is reused by the next call
+    return make_completed_event();
+}
+
 bool same_node(host_comm& comm) {
     const std::vector<int>& h = comm.host_index();
     for (int v : h)
@@ -943,6 +1047,8 @@ event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr) {
             ev = device_coll(comm, p, attr);
         else if (hier_allreduce_possible(comm, p, attr))
             ev = hier_device_allreduce(comm, p, attr);
+        else if (hier_reduce_scatter_possible(comm, p, attr))
+            ev = hier_device_reduce_scatter(comm, p, attr);
         else
             ev = staged_device_coll(comm, p, attr);
         if (sync)

@@ -159,6 +159,7 @@ void launch_wait_unset_flag(device_comm& dc, cudaStream_t st);
 
 // local helpers
 void launch_reduce_local(const void* in, void* inout, size_t count, int dt, int op, cudaStream_t st);
+void launch_transpose_blocks(const void* in, void* out, int rows, int cols, size_t block_bytes, cudaStream_t st);
 void launch_pack(const void* const* ptrs_dev, const size_t* offs_dev, int n, void* fused, bool unpack,
                  size_t max_tensor_bytes, cudaStream_t st);
 

@@ -482,6 +482,38 @@ void launch_reduce_local(const void* in, void* inout, size_t count, int dt, int 
     CUDA_CHECK(cudaGetLastError());
 }
 
+// Block transpose: `in` holds rows x cols blocks of block_bytes each, row-major; `out` gets the same
+// blocks column-major (block (r, c) moves to position c * rows + r).  A reduce_scatter across nodes
+// needs it: send buffers are ordered by global rank (node-major), the node-level stage wants the
+// blocks grouped by local rank (reference src/coll/algorithms/reduce_scatter/sycl/reduce_scatter_sycl.cpp:176-204).
+template <class V>
+__global__ void transpose_blocks_kernel(const V* __restrict__ in, V* __restrict__ out, int rows, int cols,
+                                        size_t per_block) {
+    const size_t total = (size_t)rows * (size_t)cols * per_block;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t blk = i / per_block, e = i - blk * per_block; // output block and offset inside it
+        const size_t c = blk / (size_t)rows, r = blk - c * (size_t)rows;
+        out[i] = in[(r * (size_t)cols + c) * per_block + e];
+    }
+}
+
+void launch_transpose_blocks(const void* in, void* out, int rows, int cols, size_t block_bytes, cudaStream_t st) {
+    if (rows <= 0 || cols <= 0 || block_bytes == 0)
+        return;
+    CCL_THROW_IF_NOT(in != out, "block transpose works out of place only");
+    const bool wide = block_bytes % 16 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0;
+    const size_t per_block = wide ? block_bytes / 16 : block_bytes;
+    const size_t total = (size_t)rows * (size_t)cols * per_block;
+    const int threads = 256;
+    const int blocks = (int)std::min<size_t>((total + threads - 1) / threads, 148 * 8);
+    if (wide)
+        transpose_blocks_kernel<uint4><<<blocks, threads, 0, st>>>((const uint4*)in, (uint4*)out, rows, cols, per_block);
+    else
+        transpose_blocks_kernel<unsigned char>
+            <<<blocks, threads, 0, st>>>((const unsigned char*)in, (unsigned char*)out, rows, cols, per_block);
+    CUDA_CHECK(cudaGetLastError());
+}
+
 void launch_pack(const void* const* ptrs_dev, const size_t* offs_dev, int n, void* fused, bool unpack,
                  size_t max_tensor_bytes, cudaStream_t st) {
     if (n <= 0)

@@ -313,3 +313,16 @@ def reduce_local(inp: torch.Tensor, inout: torch.Tensor, op="sum", stream=None):
     _lib.check(lib.cclx_reduce_local(inp.data_ptr(), inout.data_ptr(), inout.numel(), torch_to_ccl(inout.dtype),
                                      reduce_op_code(op), _stream_ptr(stream)))
     return inout
+
+
+def transpose_blocks(inp: torch.Tensor, rows: int, cols: int, out: Optional[torch.Tensor] = None, stream=None):
+    """``inp`` seen as ``rows x cols`` equal blocks (row-major) comes out with the blocks in column-major
+    order: the regrouping from rank order (node-major) to local-rank order that a reduce_scatter across
+    nodes starts with."""
+    assert inp.is_cuda and inp.is_contiguous() and inp.numel() % (rows * cols) == 0
+    if out is None:
+        out = torch.empty_like(inp)
+    block_bytes = inp.numel() // (rows * cols) * inp.element_size()
+    lib = _lib.load()
+    _lib.check(lib.cclx_transpose_blocks(inp.data_ptr(), out.data_ptr(), rows, cols, block_bytes, _stream_ptr(stream)))
+    return out
