@@ -53,8 +53,9 @@ void purge_recycle() {
 
 class host_event : public event_impl {
 public:
-    host_event(master_sched* m, uint64_t ticket, std::unique_ptr<master_sched> owned)
-            : m_(m), ticket_(ticket), owned_(std::move(owned)) {}
+    host_event(master_sched* m, uint64_t ticket, std::unique_ptr<master_sched> owned,
+               std::shared_ptr<master_sched> cached = nullptr)
+            : m_(m), ticket_(ticket), owned_(std::move(owned)), cached_(std::move(cached)) {}
     ~host_event() override {
         if (owned_ && !owned_->ticket_complete(ticket_)) {
             std::lock_guard<std::mutex> lk(recycle_mu);
@@ -73,6 +74,7 @@ private:
     master_sched* m_;
     uint64_t ticket_;
     std::unique_ptr<master_sched> owned_;
+    std::shared_ptr<master_sched> cached_; // a cached schedule may leave the cache while this event lives
 };
 
 class cuda_event_impl : public event_impl {
@@ -823,10 +825,12 @@ event_ptr start_sched(host_comm& comm, const coll_param& p, const coll_attr& att
         comm.cache().flush();
     master_sched* m = nullptr;
     std::unique_ptr<master_sched> owned;
+    std::shared_ptr<master_sched> cached;
     uint64_t launch_id = executor::KEEP_ID;
     if (cacheable) {
         const std::string key = coll_cache_key(comm, p, attr);
-        m = comm.cache().find(key);
+        cached = comm.cache().find(key);
+        m = cached.get();
         if (m) {
             stats().cache_hits++;
             // every call draws an id, hit or miss, so the ranks stay in step whatever their caches hold
@@ -835,8 +839,9 @@ event_ptr start_sched(host_comm& comm, const coll_param& p, const coll_attr& att
         }
         else {
             auto fresh = build_master(comm, p, attr, fixed_id != NO_SCHED_ID ? fixed_id : comm.next_sched_id());
-            m = fresh.get();
-            comm.cache().insert(key, std::move(fresh));
+            cached = std::move(fresh);
+            m = cached.get();
+            comm.cache().insert(key, cached);
         }
     }
     else {
@@ -853,7 +858,7 @@ event_ptr start_sched(host_comm& comm, const coll_param& p, const coll_attr& att
         m = owned.get();
     }
     const uint64_t ticket = executor::get().start(m, launch_id);
-    return std::make_shared<host_event>(m, ticket, std::move(owned));
+    return std::make_shared<host_event>(m, ticket, std::move(owned), std::move(cached));
 }
 
 // ---- unordered collectives -------------------------------------------------------------------

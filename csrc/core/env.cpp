@@ -294,6 +294,7 @@ void env_data::parse() {
     get_enum<cache_key_t>("CCL_CACHE_KEY", cache_key,
                           { { "full", cache_key_t::full }, { "match_id", cache_key_t::match_id } });
     get_bool("CCL_CACHE_FLUSH", cache_flush);
+    get_size("CCL_SCHED_CACHE_MAX_ENTRIES", sched_cache_max_entries);
     get_bool("CCL_STRICT_ORDER", strict_order);
     get_bool("CCL_OP_SYNC", op_sync);
     get_bool("CCL_BUFFER_CACHE", buffer_cache);

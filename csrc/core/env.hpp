@@ -83,6 +83,7 @@ struct env_data {
     priority_mode_t priority_mode = priority_mode_t::none;
     cache_key_t cache_key = cache_key_t::match_id;
     bool cache_flush = false;
+    size_t sched_cache_max_entries = 4096; // per communicator
     bool strict_order = false;
     bool op_sync = false;
     bool buffer_cache = true; // CCL_BUFFER_CACHE=0: scratch memory is allocated and freed per schedule

@@ -712,7 +712,7 @@ void executor::unlock_workers() {
 }
 
 // ---- cache ----------------------------------------------------------------------------
-master_sched* sched_cache::find(const std::string& key) {
+std::shared_ptr<master_sched> sched_cache::find(const std::string& key) {
     std::lock_guard<std::mutex> lk(mu_);
     auto it = map_.find(key);
     if (it == map_.end()) {
@@ -720,20 +720,34 @@ master_sched* sched_cache::find(const std::string& key) {
         return nullptr;
     }
     hits++;
-    return it->second.get();
+    it->second.last_use = ++clock_;
+    return it->second.m;
 }
 
-void sched_cache::insert(const std::string& key, std::unique_ptr<master_sched> m) {
+void sched_cache::insert(const std::string& key, std::shared_ptr<master_sched> m) {
     std::lock_guard<std::mutex> lk(mu_);
+    const size_t cap = std::max<size_t>(env_data::get().sched_cache_max_entries, 1);
+    while (map_.size() >= cap) {
+        auto victim = map_.end();
+        for (auto it = map_.begin(); it != map_.end(); ++it)
+            if (!it->second.m->in_flight && (victim == map_.end() || it->second.last_use < victim->second.last_use))
+                victim = it;
+        if (victim == map_.end())
+            break; // everything is running: exceed the bound rather than wait
+        map_.erase(victim);
+        evictions++;
+    }
     m->cached = true;
     m->cache_key = key;
-    map_[key] = std::move(m);
+    slot& s = map_[key];
+    s.m = std::move(m);
+    s.last_use = ++clock_;
 }
 
 void sched_cache::flush() {
     std::lock_guard<std::mutex> lk(mu_);
     for (auto it = map_.begin(); it != map_.end();) {
-        if (!it->second->in_flight)
+        if (!it->second.m->in_flight)
             it = map_.erase(it);
         else
             ++it;

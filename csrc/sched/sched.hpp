@@ -269,15 +269,24 @@ private:
 // ---- schedule cache -------------------------------------------------------------------
 class sched_cache {
 public:
-    master_sched* find(const std::string& key);
-    void insert(const std::string& key, std::unique_ptr<master_sched> m);
+    // The schedule stays alive while the caller holds the pointer, whatever the cache does meanwhile.
+    std::shared_ptr<master_sched> find(const std::string& key);
+    // At most CCL_SCHED_CACHE_MAX_ENTRIES schedules are kept: a program that reuses a match_id with new
+    // buffers every time (keys contain the buffer addresses) would otherwise grow the cache without
+    // bound.  The least recently used schedule that is not running makes room.
+    void insert(const std::string& key, std::shared_ptr<master_sched> m);
     void flush(); // drops schedules that are not in flight
     size_t size();
-    uint64_t hits = 0, misses = 0;
+    uint64_t hits = 0, misses = 0, evictions = 0;
 
 private:
+    struct slot {
+        std::shared_ptr<master_sched> m;
+        uint64_t last_use = 0;
+    };
     std::mutex mu_;
-    std::unordered_map<std::string, std::unique_ptr<master_sched>> map_;
+    uint64_t clock_ = 0;
+    std::unordered_map<std::string, slot> map_;
 };
 
 uint64_t now_ns();

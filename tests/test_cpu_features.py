@@ -33,6 +33,35 @@ def test_schedule_cache_and_relaunch():
     assert all(h == 5 for h in run_ranks(_cache, 2))
 
 
+def _cache_bound(comm):
+    W, r = comm.size, comm.rank
+    # one name, a new buffer every step: every call misses (keys hold the addresses) and the cache must not grow
+    keep = []
+    for step in range(40):
+        x = np.full(300, float(r + step), np.float32)
+        keep.append(x)  # keeps the addresses distinct
+        comm.allreduce(x, to_cache=True, match_id="grad").wait()
+        assert np.all(x == sum(p + step for p in range(W)))
+        assert comm.cache_size() <= 8
+    # un-waited events of evicted schedules stay valid
+    evs = []
+    for step in range(20):
+        x = np.full(100, 1.0, np.float32)
+        keep.append(x)
+        evs.append((comm.allreduce(x, to_cache=True, match_id="g2"), x))
+    for e, x in evs:
+        e.wait()
+        assert np.all(x == W)
+    # schedules that were running could not be evicted; the next insertion trims the cache again
+    last = np.ones(10, np.float32)
+    comm.allreduce(last, to_cache=True, match_id="g3").wait()
+    return comm.cache_size()
+
+
+def test_schedule_cache_is_bounded():
+    assert all(n <= 8 for n in run_ranks(_cache_bound, 3, env={"CCL_SCHED_CACHE_MAX_ENTRIES": "8"}))
+
+
 def _fusion(comm):
     from oneccl_b200.comm import stats
 
