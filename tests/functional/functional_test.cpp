@@ -9,6 +9,8 @@
 // the configuration keeps one in `keep-one-in` (default 97); every rank evaluates the same hash, and
 // every datatype x reduction pair is always kept once per operation.  Values are small integers, exact
 // in every datatype including float16 / bfloat16, and every element is checked against a closed form.
+// FUNCTIONAL_TEST_DYNAMIC_POINTER=1 re-allocates the buffers before the second iteration of a cached
+// configuration; FUNCTIONAL_TEST_VERBOSE=1 names every configuration before it runs.
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
@@ -26,6 +28,7 @@ namespace {
 
 int g_rank = 0, g_size = 1;
 long g_configs = 0, g_failures = 0;
+bool g_dynamic_pointers = false; // FUNCTIONAL_TEST_DYNAMIC_POINTER=1
 
 // ---- datatypes ------------------------------------------------------------------------------
 struct dtype_desc {
@@ -278,6 +281,16 @@ bool run_config(const config& c, const ccl::communicator& comm) {
     const int iterations = c.cached ? 2 : 1; // the second run takes the schedule from the cache
     bool ok = true;
     for (int it = 0; it < iterations && ok; it++) {
+        if (it > 0 && g_dynamic_pointers) {
+            // the reference's "dynamic pointer" mode (test_impl.hpp:326-372): new allocations under the
+            // same match_id; the old ones stay alive so that the addresses really differ
+            for (int b = 0; b < B; b++) {
+                bufs.send.emplace_back(bufs.send[b].size());
+                bufs.recv.emplace_back(bufs.recv[b].size());
+                std::swap(bufs.send[b], bufs.send.back());
+                std::swap(bufs.recv[b], bufs.recv.back());
+            }
+        }
         // ---- fill: the in-place forms keep their input where the operation defines it
         std::vector<void*> sptr(B), rptr(B);
         for (int b = 0; b < B; b++) {
@@ -462,6 +475,7 @@ int main(int argc, char** argv) {
     g_rank = std::atoi(argv[1]);
     g_size = std::atoi(argv[2]);
     const uint64_t keep = argc > 4 ? (uint64_t)std::atoll(argv[4]) : 97;
+    g_dynamic_pointers = std::getenv("FUNCTIONAL_TEST_DYNAMIC_POINTER") != nullptr;
     const bool verbose = std::getenv("FUNCTIONAL_TEST_VERBOSE") != nullptr; // names every configuration first
     ccl::init();
     auto kvs = bootstrap_kvs(g_rank, argv[3]);

@@ -22,6 +22,7 @@ CASES = [
     (4, "53", {}),  # alltoallv blocks on both sides of the algorithm threshold within one call
     (3, "97", {"CCL_WORKER_COUNT": "2", "CCL_FUSION": "1", "CCL_PRIORITY": "lifo"}),
     (3, "97", {"CCL_CACHE_KEY": "full"}),  # cache hits differ between ranks (keys hold buffer addresses)
+    (2, "97", {"FUNCTIONAL_TEST_DYNAMIC_POINTER": "1", "CCL_SCHED_CACHE_MAX_ENTRIES": "16"}),
     (3, "97", {"CCL_UNORDERED_COLL": "1", "CCL_ATL_SHM": "0", "CCL_MAX_FLOW_CREDITS": "2"}),
     (4, "97", {"CCL_ALLREDUCE": "ring_rma", "CCL_ATL_RMA": "1", "CCL_ALLTOALL": "scatter", "CCL_ALLTOALLV": "scatter",
                "CCL_REDUCE": "rabenseifner", "CCL_ALLGATHERV": "ring", "CCL_REDUCE_SCATTER": "ring",
@@ -34,7 +35,8 @@ CASES = [
 
 
 @pytest.mark.parametrize("world,keep,env", CASES,
-                         ids=["w2", "w4-dense", "w3-workers-fusion", "w3-full-cache-key", "w3-unordered-sockets",
+                         ids=["w2", "w4-dense", "w3-workers-fusion", "w3-full-cache-key", "w2-dynamic-pointers",
+                              "w3-unordered-sockets",
                               "w4-ring-algorithms", "w4-tree-algorithms"])
 def test_functional_matrix(exe, world, keep, env):
     outs = _run_ranks(exe, world, extra_args=(keep,), env=env, timeout=300)
