@@ -193,7 +193,8 @@ CCLX_API int cclx_comm_size(void* c) {
     return ((comm_handle*)c)->c->size();
 }
 // transport counters of the communicator's world: 0 messages sent, 1 bytes sent, 2 bytes received,
-// 3 unexpected messages, 4 one-sided writes done as cross-memory copies, 5 one-sided writes sent as messages
+// 3 unexpected messages, 4 one-sided writes done as cross-memory copies, 5 one-sided writes sent as messages,
+// 6 long messages sent by rendezvous (read out of this process by the receiver)
 CCLX_API long long cclx_comm_transport_stat(void* c, int which) {
     atl_transport& t = ((comm_handle*)c)->c->atl().transport();
     switch (which) {
@@ -203,6 +204,7 @@ CCLX_API long long cclx_comm_transport_stat(void* c, int which) {
         case 3: return (long long)t.unexpected_msgs.load();
         case 4: return (long long)t.rma_direct_writes.load();
         case 5: return (long long)t.rma_message_writes.load();
+        case 6: return (long long)t.rndv_sends.load();
         default: return -1;
     }
 }

@@ -171,14 +171,14 @@ void block_partition(size_t count, int parts, std::vector<size_t>& counts, std::
 
 // ---------------------------------------------------------------------------- reduce_scatter
 void reduce_scatter_ring_v(sched& s, void* inout, const std::vector<size_t>& counts, const std::vector<size_t>& offs,
-                           int dtype, int op, reduction_fn_t fn, uint64_t step_base) {
+                           int dtype, int op, reduction_fn_t fn, uint64_t step_base, const void* local) {
     host_comm* c = s.comm();
     const int N = c->size(), r = c->rank();
     if (N == 1)
         return;
     const size_t esz = dtype_size(dtype);
     size_t maxc = *std::max_element(counts.begin(), counts.end());
-    void* tmp = s.alloc_tmp(maxc * esz + 64);
+    void* tmp = local ? nullptr : s.alloc_tmp(maxc * esz + 64);
     const int next = (r + 1) % N, prev = (r - 1 + N) % N;
     const auto& e = env_data::get();
     for (int st = 0; st < N - 1; st++) {
@@ -192,13 +192,21 @@ void reduce_scatter_ring_v(sched& s, void* inout, const std::vector<size_t>& cou
         for (size_t k = 0; k < sc; k++) {
             size_t off, n;
             chunk_range(counts[sb], sc, k, off, n);
-            s.add<send_entry>(at(inout, offs[sb] + off, esz), n * esz, next, step_base + st + k * CHUNK_TAG_STRIDE);
+            // the first block that leaves holds only this rank's data; later ones are partial sums
+            const void* src = (local && st == 0) ? (const void*)at(local, offs[sb] + off, esz)
+                                                 : (const void*)at(inout, offs[sb] + off, esz);
+            s.add<send_entry>(src, n * esz, next, step_base + st + k * CHUNK_TAG_STRIDE);
         }
         for (size_t k = 0; k < rc; k++) {
             size_t off, n;
             chunk_range(counts[rb], rc, k, off, n);
-            s.add<recv_reduce_entry>(at(inout, offs[rb] + off, esz), n, dtype, op, prev,
-                                     step_base + st + k * CHUNK_TAG_STRIDE, fn, at(tmp, off, esz));
+            if (local)
+                s.add<recv_reduce_entry>(at(inout, offs[rb] + off, esz), n, dtype, op, prev,
+                                         step_base + st + k * CHUNK_TAG_STRIDE, fn, nullptr,
+                                         at(local, offs[rb] + off, esz));
+            else
+                s.add<recv_reduce_entry>(at(inout, offs[rb] + off, esz), n, dtype, op, prev,
+                                         step_base + st + k * CHUNK_TAG_STRIDE, fn, at(tmp, off, esz));
         }
         s.add_barrier();
     }
@@ -213,14 +221,13 @@ void reduce_scatter_ring(sched& s, const buf_desc& b) {
         copy_in(s, b.send, b.recv, rc * esz);
         return;
     }
-    // work on a scratch copy of the whole send buffer so that send stays intact
+    // partial sums live in scratch memory so that send stays intact; this rank's own contribution is
+    // read from send where it is needed
     void* work = s.alloc_tmp(rc * N * esz + 64);
-    s.add<copy_entry>(b.send, work, rc * N * esz);
-    s.add_barrier();
     std::vector<size_t> cnt(N, rc), off(N);
     for (int i = 0; i < N; i++)
         off[i] = (size_t)i * rc;
-    reduce_scatter_ring_v(s, work, cnt, off, b.dtype, b.op, b.fn, 0);
+    reduce_scatter_ring_v(s, work, cnt, off, b.dtype, b.op, b.fn, 0, b.send);
     s.add<copy_entry>(at(work, off[r], esz), b.recv, rc * esz);
 }
 
@@ -328,12 +335,16 @@ void allreduce_ring(sched& s, const buf_desc& b) {
     host_comm* c = s.comm();
     const int N = c->size();
     const size_t esz = dtype_size(b.dtype);
-    copy_in(s, b.send, b.recv, b.count * esz);
-    if (N == 1)
+    if (N == 1) {
+        copy_in(s, b.send, b.recv, b.count * esz);
         return;
+    }
     std::vector<size_t> cnt, off;
     block_partition(b.count, N, cnt, off);
-    reduce_scatter_ring_v(s, b.recv, cnt, off, b.dtype, b.op, b.fn, 0);
+    // out of place: no copy of send into recv first, every block of recv is written by the ring itself
+    // (N - 1 blocks as reduction targets, the remaining one by the allgather)
+    const void* local = (b.send && b.send != b.recv) ? b.send : nullptr;
+    reduce_scatter_ring_v(s, b.recv, cnt, off, b.dtype, b.op, b.fn, 0, local);
     allgatherv_ring(s, nullptr, b.recv, cnt, off, b.dtype, 1000);
 }
 

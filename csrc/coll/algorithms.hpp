@@ -41,8 +41,10 @@ void allreduce_double_tree(sched& s, const buf_desc& b);
 void reduce_scatter_ring(sched& s, const buf_desc& b); // b.count = recv_count
 void reduce_scatter_naive(sched& s, const buf_desc& b);
 // variable block sizes (used by allreduce ring / rabenseifner internals)
+// `local` (optional): this rank's contribution lives there and `inout` starts out undefined; blocks are
+// received straight into `inout` and combined with `local`, so an out-of-place caller copies nothing
 void reduce_scatter_ring_v(sched& s, void* inout, const std::vector<size_t>& counts, const std::vector<size_t>& offs,
-                           int dtype, int op, reduction_fn_t fn, uint64_t step_base);
+                           int dtype, int op, reduction_fn_t fn, uint64_t step_base, const void* local = nullptr);
 
 // allgatherv: counts/offsets in elements of dtype, recv holds all blocks
 void allgatherv_naive(sched& s, const void* send, void* recv, const std::vector<size_t>& counts,

@@ -252,6 +252,7 @@ void env_data::parse() {
     get_size("CCL_ATL_SHM_RING_BYTES", atl_shm_ring_bytes);
     get_bool("CCL_ATL_RMA", atl_rma);
     get_bool("CCL_ATL_CMA", atl_cma);
+    get_size("CCL_ATL_CMA_THRESHOLD", atl_cma_threshold);
     get_size("CCL_MAX_SHORT_SIZE", max_short_size);
     get_size("CCL_CHUNK_COUNT", chunk_count);
     get_size("CCL_MIN_CHUNK_SIZE", min_chunk_size);

@@ -56,7 +56,8 @@ struct env_data {
     bool atl_shm = true; // same-host pairs use the shared-memory rings
     size_t atl_shm_ring_bytes = 4u << 20;
     bool atl_rma = false; // CCL_ATL_RMA: one-sided writes (the ring_rma allreduce needs them)
-    bool atl_cma = true; // CCL_ATL_CMA: same-host one-sided writes are cross-memory copies, not messages
+    bool atl_cma = true; // CCL_ATL_CMA: cross-memory copies between processes of one host (one-sided writes, long messages)
+    size_t atl_cma_threshold = 64u << 10; // messages of at least this size are read out of the sender's memory
     size_t max_short_size = 0;
     size_t chunk_count = 1;
     size_t min_chunk_size = 65536;

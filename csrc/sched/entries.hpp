@@ -52,11 +52,13 @@ private:
     atl_req req_;
 };
 
-// receive `count` elements into a temporary, then inout = op(tmp, inout)
+// receive `count` elements into a temporary, then inout = op(tmp, inout).  With a `local` operand the
+// message lands in `inout` itself and inout = op(local, inout): an out-of-place reduction needs neither
+// the temporary nor a copy of the local contribution into the result buffer first.
 class recv_reduce_entry : public sched_entry {
 public:
     recv_reduce_entry(sched* s, void* inout, size_t count, int dtype, int op, int src, uint64_t step,
-                      reduction_fn_t fn = nullptr, void* tmp = nullptr);
+                      reduction_fn_t fn = nullptr, void* tmp = nullptr, const void* local = nullptr);
     const char* name() const override { return "RECV_REDUCE"; }
     void start() override;
     void update() override;
@@ -68,6 +70,7 @@ private:
     uint64_t step_;
     reduction_fn_t fn_;
     void* tmp_;
+    const void* local_;
     atl_req req_;
 };
 

@@ -153,14 +153,15 @@ void recv_entry::update() {
 }
 
 recv_reduce_entry::recv_reduce_entry(sched* s, void* inout, size_t count, int dtype, int op, int src, uint64_t step,
-                                     reduction_fn_t fn, void* tmp)
+                                     reduction_fn_t fn, void* tmp, const void* local)
         : sched_entry(s), inout_(inout), count_(count), dtype_(dtype), op_(op), src_(src), step_(step), fn_(fn),
-          tmp_(tmp) {
-    if (!tmp_)
+          tmp_(tmp), local_(local) {
+    if (!tmp_ && !local_)
         tmp_ = s->alloc_tmp(count * dtype_size(dtype));
 }
 void recv_reduce_entry::start() {
-    owner_->comm()->atl().recv(owner_->ep(), tmp_, count_ * dtype_size(dtype_), src_, owner_->tag(step_), &req_);
+    owner_->comm()->atl().recv(owner_->ep(), local_ ? inout_ : tmp_, count_ * dtype_size(dtype_), src_,
+                               owner_->tag(step_), &req_);
     update();
 }
 void recv_reduce_entry::update() {
@@ -168,7 +169,7 @@ void recv_reduce_entry::update() {
         status_ = entry_status::started;
         return;
     }
-    comp_reduce(tmp_, count_, inout_, dtype_, op_, fn_);
+    comp_reduce(local_ ? local_ : tmp_, count_, inout_, dtype_, op_, fn_);
     status_ = entry_status::complete;
 }
 

@@ -53,6 +53,20 @@ struct out_msg {
     size_t sent = 0; // of header + payload
     atl_req* req;
     std::vector<char> owned; // payload kept by the message itself (one-sided writes carried as messages)
+    size_t payload_len = 0; // bytes that follow the header on the wire (hdr.len may announce more: rendezvous)
+};
+
+// Rendezvous between processes of one host: a long message travels as a descriptor of the sender's
+// buffer; the receiver copies it straight into the posted buffer (process_vm_readv: one copy instead of
+// one into the ring and one out of it) and acknowledges, which completes the send.  The length field of
+// the header carries the flag, the descriptor follows as payload.
+constexpr uint64_t RNDV_FLAG = 1ull << 63;
+constexpr uint64_t RNDV_ACK_TAG = ~0ull - 1; // payload: the cookie of the descriptor
+struct rndv_desc {
+    uint64_t addr;
+    uint64_t cookie; // the sender's request, echoed in the acknowledgement
+    int32_t pid;
+    int32_t pad;
 };
 
 // tag of a one-sided write that travels as a message: payload = target address, then the data.
@@ -70,6 +84,10 @@ struct unexpected_msg {
     uint64_t tag;
     std::vector<char> data;
     bool complete = false;
+    bool rndv = false; // no data yet: `desc` says where the sender keeps them
+    uint64_t rndv_len = 0;
+    rndv_desc desc{};
+    size_t size() const { return rndv ? (size_t)rndv_len : data.size(); }
 };
 
 // single-producer / single-consumer byte ring in shared memory
@@ -125,6 +143,9 @@ struct peer_state {
     size_t in_got = 0;
     atl_req* in_req = nullptr; // when receiving straight into a posted buffer
     unexpected_msg* in_unexp = nullptr;
+    size_t body_len = 0; // payload bytes of the message being received
+    bool in_ctrl = false; // the payload is a descriptor or an acknowledgement, received into `ctrl`
+    char ctrl[sizeof(rndv_desc)];
     std::list<posted_recv> posted;
     std::list<unexpected_msg> unexp;
 };
@@ -201,7 +222,12 @@ public:
             char ip[64];
             int port;
             char host[64];
+            int pid;
+            uint64_t probe; // address of a word every rank of this host tries to read
         } mine{};
+        static const uint64_t probe_word = 0x636d615f70726f62ull;
+        mine.pid = (int)getpid();
+        mine.probe = (uint64_t)(uintptr_t)&probe_word;
         std::snprintf(mine.ip, sizeof(mine.ip), "%s", ip.c_str());
         mine.port = ntohs(a.sin_port);
         std::snprintf(mine.host, sizeof(mine.host), "%s", host);
@@ -210,6 +236,25 @@ public:
         same_host_.resize(size_);
         for (int r = 0; r < size_; r++)
             same_host_[r] = std::strncmp(table[r].host, mine.host, sizeof(mine.host)) == 0;
+        // can this process read a neighbour's memory?  (ptrace policy and containers may forbid it; the
+        // answer is assumed to be the same in both directions between processes of one job on one host)
+        rndv_min_ = env.atl_cma ? env.atl_cma_threshold : 0;
+        if (rndv_min_) {
+            bool tried = false, ok = true;
+            for (int r = 0; r < size_ && !tried; r++) {
+                if (r == rank_ || !same_host_[r])
+                    continue;
+                tried = true;
+                uint64_t got = 0;
+                iovec l{ &got, sizeof(got) };
+                iovec rm{ (void*)(uintptr_t)table[r].probe, sizeof(got) };
+                ok = process_vm_readv(table[r].pid, &l, 1, &rm, 1, 0) == (ssize_t)sizeof(got) && got == probe_word;
+            }
+            if (!ok) {
+                LOG_INFO("process_vm_readv is not permitted here: long messages go through the rings");
+                rndv_min_ = 0;
+            }
+        }
 
         for (auto& ep : eps_) {
             ep.peers.resize(size_);
@@ -299,10 +344,28 @@ public:
             req->done.store(1, std::memory_order_release);
             return;
         }
+        if (rndv_min_ && len >= rndv_min_ && same_host_[dst]) {
+            rndv_sends++;
+            ps.outq.emplace_back();
+            out_msg& m = ps.outq.back();
+            rndv_desc d{};
+            d.addr = (uint64_t)(uintptr_t)buf;
+            d.cookie = (uint64_t)(uintptr_t)req;
+            d.pid = (int32_t)getpid();
+            m.owned.assign((const char*)&d, (const char*)&d + sizeof(d));
+            m.hdr.tag = tag;
+            m.hdr.len = RNDV_FLAG | (uint64_t)len;
+            m.payload = m.owned.data();
+            m.payload_len = sizeof(d);
+            m.req = nullptr; // the acknowledgement completes the request, not the departure of the descriptor
+            flush(ps);
+            return;
+        }
         out_msg m;
         m.hdr.tag = tag;
         m.hdr.len = len;
         m.payload = (const char*)buf;
+        m.payload_len = len;
         m.req = req;
         ps.outq.push_back(m);
         flush(ps);
@@ -327,7 +390,14 @@ public:
                 ps.unexp.erase(it);
                 return;
             }
-            CCL_THROW_IF_NOT(it->data.size() <= len, "receive buffer too small: ", len, " < ", it->data.size());
+            CCL_THROW_IF_NOT(it->size() <= len, "receive buffer too small: ", len, " < ", it->size());
+            if (it->rndv) {
+                const rndv_desc d = it->desc;
+                const size_t n = it->size();
+                ps.unexp.erase(it);
+                pull_rendezvous(ps, d, n, (char*)buf, req);
+                return;
+            }
             std::memcpy(buf, it->data.data(), it->data.size());
             req->bytes = it->data.size();
             bytes_received += it->data.size();
@@ -406,6 +476,7 @@ public:
         m.hdr.tag = RMA_WRITE_TAG;
         m.hdr.len = m.owned.size();
         m.payload = m.owned.data();
+        m.payload_len = m.owned.size();
         m.req = req;
         flush(ps);
     }
@@ -417,7 +488,7 @@ public:
         for (auto& u : ep.peers[src].unexp)
             if (u.tag == tag && u.complete) {
                 if (len)
-                    *len = u.data.size();
+                    *len = u.size();
                 return true;
             }
         return false;
@@ -568,25 +639,91 @@ private:
     void flush(peer_state& ps) {
         while (!ps.outq.empty()) {
             out_msg& m = ps.outq.front();
-            const size_t total = sizeof(wire_header) + m.hdr.len;
+            const size_t total = sizeof(wire_header) + m.payload_len;
             while (m.sent < total) {
                 size_t w;
                 if (m.sent < sizeof(wire_header))
-                    w = link_write(ps, (char*)&m.hdr + m.sent, sizeof(wire_header) - m.sent, m.payload, m.hdr.len);
+                    w = link_write(ps, (char*)&m.hdr + m.sent, sizeof(wire_header) - m.sent, m.payload, m.payload_len);
                 else {
                     const size_t off = m.sent - sizeof(wire_header);
-                    w = link_write(ps, m.payload + off, m.hdr.len - off, nullptr, 0);
+                    w = link_write(ps, m.payload + off, m.payload_len - off, nullptr, 0);
                 }
                 if (w == 0)
                     return;
                 m.sent += w;
             }
-            m.req->done.store(1, std::memory_order_release);
+            if (m.req)
+                m.req->done.store(1, std::memory_order_release);
             ps.outq.pop_front();
         }
     }
 
+    // copies a rendezvous message out of the sender's memory and acknowledges it
+    void pull_rendezvous(peer_state& ps, const rndv_desc& d, size_t len, char* dst, atl_req* req) {
+        size_t done = 0;
+        while (done < len) {
+            iovec l{ dst + done, len - done };
+            iovec r{ (char*)(uintptr_t)d.addr + done, len - done };
+            const ssize_t n = process_vm_readv(d.pid, &l, 1, &r, 1, 0);
+            CCL_THROW_IF_NOT(n > 0, "cross-memory read of ", len, " bytes from process ", d.pid, " failed: ",
+                             std::strerror(errno), " (CCL_ATL_CMA=0 sends long messages through the rings)");
+            done += (size_t)n;
+        }
+        bytes_received += len;
+        req->bytes = len;
+        req->done.store(1, std::memory_order_release);
+        ps.outq.emplace_back();
+        out_msg& m = ps.outq.back();
+        m.owned.assign((const char*)&d.cookie, (const char*)&d.cookie + sizeof(d.cookie));
+        m.hdr.tag = RNDV_ACK_TAG;
+        m.hdr.len = sizeof(d.cookie);
+        m.payload = m.owned.data();
+        m.payload_len = sizeof(d.cookie);
+        m.req = nullptr;
+        flush(ps);
+    }
+
+    // a descriptor or an acknowledgement has arrived in ps.ctrl
+    void finish_control(peer_state& ps) {
+        if (ps.in_hdr.tag == RNDV_ACK_TAG && !(ps.in_hdr.len & RNDV_FLAG)) {
+            uint64_t cookie;
+            std::memcpy(&cookie, ps.ctrl, sizeof(cookie));
+            ((atl_req*)(uintptr_t)cookie)->done.store(1, std::memory_order_release);
+            return;
+        }
+        rndv_desc d;
+        std::memcpy(&d, ps.ctrl, sizeof(d));
+        const size_t len = (size_t)(ps.in_hdr.len & ~RNDV_FLAG);
+        for (auto it = ps.posted.begin(); it != ps.posted.end(); ++it) {
+            if (it->tag != ps.in_hdr.tag)
+                continue;
+            CCL_THROW_IF_NOT(len <= it->cap, "receive buffer too small: ", it->cap, " < ", len);
+            char* dst = it->buf;
+            atl_req* req = it->req;
+            ps.posted.erase(it);
+            pull_rendezvous(ps, d, len, dst, req);
+            return;
+        }
+        ps.unexp.emplace_back();
+        unexpected_msg& u = ps.unexp.back();
+        u.tag = ps.in_hdr.tag;
+        u.rndv = true;
+        u.rndv_len = len;
+        u.desc = d;
+        u.complete = true;
+        unexpected_msgs++;
+    }
+
     void finish_incoming(peer_state& ps) {
+        if (ps.in_ctrl) {
+            ps.in_ctrl = false;
+            ps.in_dst = nullptr;
+            ps.in_body = false;
+            ps.hdr_got = 0;
+            ps.in_got = 0;
+            finish_control(ps);
+            return;
+        }
         bytes_received += ps.in_hdr.len;
         if (ps.in_req) {
             ps.in_req->done.store(1, std::memory_order_release);
@@ -642,6 +779,14 @@ private:
                 ps.in_got = 0;
                 ps.in_req = nullptr;
                 ps.in_unexp = nullptr;
+                const bool rndv = (ps.in_hdr.len & RNDV_FLAG) != 0;
+                if (rndv || ps.in_hdr.tag == RNDV_ACK_TAG) {
+                    ps.in_ctrl = true;
+                    ps.body_len = rndv ? sizeof(rndv_desc) : sizeof(uint64_t);
+                    ps.in_dst = ps.ctrl;
+                    continue;
+                }
+                ps.body_len = (size_t)ps.in_hdr.len;
                 bool matched = false;
                 for (auto it = ps.posted.begin(); it != ps.posted.end(); ++it) {
                     if (it->tag == ps.in_hdr.tag) {
@@ -669,11 +814,11 @@ private:
                     continue;
                 }
             }
-            const size_t r = link_read(ps, ps.in_dst + ps.in_got, ps.in_hdr.len - ps.in_got);
+            const size_t r = link_read(ps, ps.in_dst + ps.in_got, ps.body_len - ps.in_got);
             if (r == 0)
                 return;
             ps.in_got += r;
-            if (ps.in_got == ps.in_hdr.len)
+            if (ps.in_got == ps.body_len)
                 finish_incoming(ps);
         }
     }
@@ -701,6 +846,7 @@ private:
     std::mutex mr_mu_;
     std::vector<std::pair<char*, size_t>> regions_;
     std::atomic<bool> cma_ok_{ true };
+    size_t rndv_min_ = 0; // messages of at least this size between processes of one host go by rendezvous (0: never)
 };
 
 } // namespace

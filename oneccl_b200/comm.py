@@ -204,7 +204,7 @@ class Communicator:
         """Counters of the host transport under this communicator: messages and bytes, messages that
         arrived before their receive was posted, one-sided writes by cross-memory copy and by message."""
         names = ("msgs_sent", "bytes_sent", "bytes_received", "unexpected_msgs", "rma_direct_writes",
-                 "rma_message_writes")
+                 "rma_message_writes", "rndv_sends")
         return {n: int(self._lib.cclx_comm_transport_stat(self._h, k)) for k, n in enumerate(names)}
 
     @property

@@ -287,3 +287,45 @@ def _ring_rma_off(comm):
     comm.allreduce(buf).wait()
     assert np.all(buf == 3.0)
     return comm.transport_stats()
+
+
+def _rendezvous(comm):
+    import time
+
+    W, r = comm.size, comm.rank
+    n = 300000
+    nxt, prv = (r + 1) % W, (r - 1) % W
+    # the send is issued first everywhere: descriptors arrive before any receive is posted
+    out = np.arange(n, dtype=np.float64) + r
+    es = comm.send(out, nxt)
+    time.sleep(0.2)
+    got = np.zeros(n)
+    comm.recv(got, prv).wait()
+    es.wait()
+    assert np.array_equal(got, np.arange(n, dtype=np.float64) + prv)
+    # receive posted first
+    got[:] = 0
+    er = comm.recv(got, nxt)
+    time.sleep(0.05)
+    comm.send(out, prv).wait()
+    er.wait()
+    assert np.array_equal(got, np.arange(n, dtype=np.float64) + nxt)
+    # collectives with long and short messages mixed
+    buf = np.full(1 << 20, float(r + 1), np.float32)
+    comm.allreduce(buf).wait()
+    assert np.all(buf == W * (W + 1) / 2)
+    small = np.full(10, float(r), np.float32)
+    comm.allreduce(small).wait()
+    assert np.all(small == sum(range(W)))
+    return comm.transport_stats()
+
+
+@pytest.mark.parametrize("env,expect", [({}, True), ({"CCL_ATL_SHM": "0"}, True), ({"CCL_ATL_CMA": "0"}, False),
+                                        ({"CCL_ATL_CMA_THRESHOLD": "16M"}, False)],
+                         ids=["rings", "sockets", "cma-off", "threshold-above"])
+def test_long_messages_between_processes_of_one_host_go_by_rendezvous(env, expect):
+    """A long message travels as a descriptor; the receiver reads the sender's buffer with one
+    cross-memory copy and acknowledges.  Descriptors that arrive before their receive wait in the
+    unexpected queue without any data."""
+    for st in run_ranks(_rendezvous, 3, env=env):
+        assert (st["rndv_sends"] > 0) == expect, st
