@@ -84,8 +84,11 @@ void algorithm_selector::reload() {
     main_.clear();
     forced_.clear();
     forced_gpu_.clear();
-    // default tables (message bytes -> algorithm); tuned for a socket transport
-    main_[coll_allreduce] = { { 0, 8192, "recursive_doubling" }, { 8193, 1u << 20, "nreduce" }, { (1u << 20) + 1, SZ_MAX, "ring" } };
+    // default tables (message bytes -> algorithm).  The allreduce switch points are the reference's
+    // (8 KiB, 1 MiB; src/coll/selection/selector.hpp:25-31) except that the ring takes over from 512 KiB:
+    // measured on this transport with 2 and 4 ranks it ties with nreduce at 256-512 KiB and is 13-20 %
+    // faster at 1 MiB, because its out-of-place form copies nothing and long messages go by rendezvous.
+    main_[coll_allreduce] = { { 0, 8192, "recursive_doubling" }, { 8193, 512u << 10, "nreduce" }, { (512u << 10) + 1, SZ_MAX, "ring" } };
     main_[coll_allgather] = { { 0, 32768, "naive" }, { 32769, SZ_MAX, "ring" } };
     main_[coll_allgatherv] = { { 0, 32768, "naive" }, { 32769, SZ_MAX, "ring" } };
     main_[coll_alltoall] = { { 0, 1u << 20, "naive" }, { (1u << 20) + 1, SZ_MAX, "scatter" } };
@@ -158,7 +161,7 @@ std::string algorithm_selector::select_cpu(const selector_param& p) const {
     if (algo == "direct") {
         // no MPI underneath: "direct" is the table's choice, except where a direct pattern exists
         switch (p.ctype) {
-            case coll_allreduce: algo = p.bytes <= 8192 ? "recursive_doubling" : (p.bytes <= (1u << 20) ? "nreduce" : "ring"); break;
+            case coll_allreduce: algo = p.bytes <= 8192 ? "recursive_doubling" : (p.bytes <= (512u << 10) ? "nreduce" : "ring"); break;
             case coll_allgather:
             case coll_allgatherv: algo = "naive"; break;
             case coll_alltoall:

@@ -110,7 +110,7 @@ void fusion_manager::launch(std::vector<pending>& batch) {
     const size_t bytes = total * esz;
     if (bytes <= 8192)
         algo::allreduce_recursive_doubling(*s, d);
-    else if (bytes <= (1u << 20))
+    else if (bytes <= (512u << 10))
         algo::allreduce_nreduce(*s, d);
     else
         algo::allreduce_ring(*s, d);

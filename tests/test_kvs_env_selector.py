@@ -213,7 +213,7 @@ def test_algo_fallback_switch():
     code = "from oneccl_b200.comm import select_cpu_algo as s; print(s('allreduce', 1 << 20))"
     out = _run_py(code, CCL_ALLREDUCE="topo")
     assert out.returncode == 0, out.stderr
-    assert out.stdout.split() == ["nreduce"]  # the size table's choice at 1 MiB
+    assert out.stdout.split() == ["ring"]  # the size table's choice at 1 MiB
     out = _run_py(code, CCL_ALLREDUCE="topo", CCL_ALGO_FALLBACK="0")
     assert out.returncode != 0
     assert "CCL_ALGO_FALLBACK" in out.stderr
