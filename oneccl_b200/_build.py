@@ -190,4 +190,9 @@ def build_all(verbose: bool = False):
 
 
 if __name__ == "__main__":
-    build_all(verbose="-v" in sys.argv)
+    # python -m oneccl_b200._build [-v] [--sanitize address|thread]
+    if "--sanitize" in sys.argv:
+        kind = sys.argv[sys.argv.index("--sanitize") + 1]
+        print(build_native(verbose="-v" in sys.argv, sanitize=kind))  # path for CCL_B200_LIBRARY
+    else:
+        build_all(verbose="-v" in sys.argv)

@@ -38,3 +38,23 @@ def test_all_operations_under_sanitizer(sanitizer):
         for o in outs:
             assert marker not in o and "LeakSanitizer" not in o, (mode, o[-4000:])
         assert outs[0].count("PASSED") == 71, (mode, outs[0][-2000:])
+    # the functional matrix, thinly sampled, over the paths the example does not reach: one-sided writes
+    # (as messages: the sanitizers cannot see a cross-memory copy), rendezvous for every message, bounded cache
+    ft = exe.parent / f"functional_{sanitizer}"
+    cmd[cmd.index(str(ROOT / "examples" / "cpu" / "cpu_all_ops_test.cpp"))] = str(ROOT / "tests" / "functional" /
+                                                                              "functional_test.cpp")
+    cmd[cmd.index(str(exe))] = str(ft)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    for mode in ({"CCL_ALLREDUCE": "ring_rma", "CCL_ATL_RMA": "1", "CCL_ATL_CMA": "0"},
+                 {"CCL_ATL_CMA_THRESHOLD": "1", "CCL_SCHED_CACHE_MAX_ENTRIES": "4", "CCL_WORKER_COUNT": "2"},
+                 {"CCL_RS_CHUNK_COUNT": "3", "CCL_RS_MIN_CHUNK_SIZE": "64", "CCL_CHUNK_COUNT": "2", "CCL_MIN_CHUNK_SIZE": "64",
+                  "CCL_ALLREDUCE": "ring", "CCL_REDUCE_SCATTER": "ring", "CCL_ALLTOALLV": "scatter"}):
+        addr = os.path.join(tempfile.mkdtemp(prefix="cclx_san_addr_"), "addr")
+        env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1", TSAN_OPTIONS="halt_on_error=0 report_signal_unsafe=0", **mode)
+        procs = [subprocess.Popen([str(ft), str(rk), "3", addr, "797"], stdout=subprocess.PIPE,
+                                  stderr=subprocess.STDOUT, text=True, env=env) for rk in range(3)]
+        outs = [p.communicate(timeout=900)[0] for p in procs]
+        for o in outs:
+            assert marker not in o and "LeakSanitizer" not in o, (mode, o[-4000:])
+        assert "PASSED" in outs[0].splitlines()[-1], (mode, outs[0][-2000:])
