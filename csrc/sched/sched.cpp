@@ -120,12 +120,23 @@ void sched_entry::do_progress() {
 }
 
 // ---- concrete entries -----------------------------------------------------------------
+namespace {
+// a transport request that ended because the peer is gone turns into the schedule's error
+inline entry_status request_status(const atl_req& req, const char* what, int peer) {
+    if (!req.is_done())
+        return entry_status::started;
+    if (req.error)
+        CCL_THROW(what, ": rank ", peer, " of the communicator has left the job (process gone or connection closed)");
+    return entry_status::complete;
+}
+} // namespace
+
 void send_entry::start() {
     owner_->comm()->atl().send(owner_->ep(), buf_, bytes_, dst_, owner_->tag(step_), &req_);
     update();
 }
 void send_entry::update() {
-    status_ = req_.is_done() ? entry_status::complete : entry_status::started;
+    status_ = request_status(req_, "send", dst_);
 }
 
 void register_entry::start() {
@@ -141,7 +152,7 @@ void write_entry::start() {
     update();
 }
 void write_entry::update() {
-    status_ = req_.is_done() ? entry_status::complete : entry_status::started;
+    status_ = request_status(req_, "one-sided write", mr_->owner);
 }
 
 void recv_entry::start() {
@@ -149,7 +160,7 @@ void recv_entry::start() {
     update();
 }
 void recv_entry::update() {
-    status_ = req_.is_done() ? entry_status::complete : entry_status::started;
+    status_ = request_status(req_, "recv", src_);
 }
 
 recv_reduce_entry::recv_reduce_entry(sched* s, void* inout, size_t count, int dtype, int op, int src, uint64_t step,
@@ -165,7 +176,7 @@ void recv_reduce_entry::start() {
     update();
 }
 void recv_reduce_entry::update() {
-    if (!req_.is_done()) {
+    if (request_status(req_, "recv", src_) != entry_status::complete) {
         status_ = entry_status::started;
         return;
     }

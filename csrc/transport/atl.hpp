@@ -21,9 +21,11 @@ class pmi;
 struct atl_req {
     std::atomic<int> done{ 0 };
     size_t bytes = 0; // received size
+    int error = 0; // set before `done` when the operation cannot complete: the peer's process is gone
     void reset() {
         done.store(0, std::memory_order_relaxed);
         bytes = 0;
+        error = 0;
     }
     bool is_done() const { return done.load(std::memory_order_acquire) != 0; }
 };
@@ -77,7 +79,7 @@ public:
     virtual atl_mr mr_reg(void* buf, size_t len) = 0;
     virtual void mr_dereg(const atl_mr& mr) = 0;
     virtual void rma_write(int ep, const void* buf, size_t len, const atl_mr& mr, uint64_t offset, atl_req* req) = 0;
-    std::atomic<uint64_t> rma_direct_writes{ 0 }, rma_message_writes{ 0 }, rndv_sends{ 0 };
+    std::atomic<uint64_t> rma_direct_writes{ 0 }, rma_message_writes{ 0 }, rndv_sends{ 0 }, peers_lost{ 0 };
     // statistics
     std::atomic<uint64_t> bytes_sent{ 0 }, bytes_received{ 0 }, msgs_sent{ 0 }, unexpected_msgs{ 0 };
 };

@@ -18,6 +18,7 @@
 #include <fcntl.h>
 #include <netinet/in.h>
 #include <netinet/tcp.h>
+#include <signal.h>
 #include <sys/epoll.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -28,6 +29,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cstring>
+#include <ctime>
 #include <deque>
 #include <list>
 #include <mutex>
@@ -143,6 +145,9 @@ struct peer_state {
     size_t in_got = 0;
     atl_req* in_req = nullptr; // when receiving straight into a posted buffer
     unexpected_msg* in_unexp = nullptr;
+    bool closed = false; // the socket reported end of stream or a reset
+    bool dead = false; // the peer is gone: nothing more will arrive, nothing can be delivered
+    std::vector<atl_req*> awaiting_ack; // rendezvous sends the peer has not read yet
     size_t body_len = 0; // payload bytes of the message being received
     bool in_ctrl = false; // the payload is a descriptor or an acknowledgement, received into `ctrl`
     char ctrl[sizeof(rndv_desc)];
@@ -155,6 +160,8 @@ struct endpoint {
     std::vector<int> shm_peers;
     std::mutex mu;
     int epfd = -1;
+    uint64_t last_liveness_ns = 0;
+    uint64_t liveness_tick = 0;
 };
 
 void set_nonblock(int fd) {
@@ -238,6 +245,9 @@ public:
             same_host_[r] = std::strncmp(table[r].host, mine.host, sizeof(mine.host)) == 0;
         // can this process read a neighbour's memory?  (ptrace policy and containers may forbid it; the
         // answer is assumed to be the same in both directions between processes of one job on one host)
+        pids_.resize(size_);
+        for (int r = 0; r < size_; r++) // a pid means something only inside this host's pid namespace
+            pids_[r] = (same_host_[r] && ::kill(table[r].pid, 0) == 0) ? table[r].pid : 0;
         rndv_min_ = env.atl_cma ? env.atl_cma_threshold : 0;
         if (rndv_min_) {
             bool tried = false, ok = true;
@@ -344,8 +354,13 @@ public:
             req->done.store(1, std::memory_order_release);
             return;
         }
+        if (ps.dead) {
+            fail(req);
+            return;
+        }
         if (rndv_min_ && len >= rndv_min_ && same_host_[dst]) {
             rndv_sends++;
+            ps.awaiting_ack.push_back(req);
             ps.outq.emplace_back();
             out_msg& m = ps.outq.back();
             rndv_desc d{};
@@ -403,6 +418,10 @@ public:
             bytes_received += it->data.size();
             ps.unexp.erase(it);
             req->done.store(1, std::memory_order_release);
+            return;
+        }
+        if (ps.dead) {
+            fail(req);
             return;
         }
         ps.posted.push_back(posted_recv{ tag, (char*)buf, len, req });
@@ -597,6 +616,10 @@ private:
                 return 0;
             if (errno == EINTR)
                 continue;
+            if (errno == EPIPE || errno == ECONNRESET) {
+                ps.closed = true;
+                return 0;
+            }
             CCL_THROW("tcp transport: send failed: ", std::strerror(errno));
         }
     }
@@ -607,12 +630,18 @@ private:
             ssize_t r = ::recv(ps.fd, dst, n, 0);
             if (r > 0)
                 return (size_t)r;
-            if (r == 0)
-                return 0; // peer closed; pending operations time out at a higher level
+            if (r == 0) {
+                ps.closed = true; // end of stream: the peer exited or closed its transport
+                return 0;
+            }
             if (errno == EAGAIN || errno == EWOULDBLOCK)
                 return 0;
             if (errno == EINTR)
                 continue;
+            if (errno == ECONNRESET) {
+                ps.closed = true;
+                return 0;
+            }
             CCL_THROW("tcp transport: recv failed: ", std::strerror(errno));
         }
     }
@@ -665,6 +694,10 @@ private:
             iovec l{ dst + done, len - done };
             iovec r{ (char*)(uintptr_t)d.addr + done, len - done };
             const ssize_t n = process_vm_readv(d.pid, &l, 1, &r, 1, 0);
+            if (n <= 0 && errno == ESRCH) { // the sender died after its descriptor left
+                fail(req);
+                return;
+            }
             CCL_THROW_IF_NOT(n > 0, "cross-memory read of ", len, " bytes from process ", d.pid, " failed: ",
                              std::strerror(errno), " (CCL_ATL_CMA=0 sends long messages through the rings)");
             done += (size_t)n;
@@ -688,7 +721,12 @@ private:
         if (ps.in_hdr.tag == RNDV_ACK_TAG && !(ps.in_hdr.len & RNDV_FLAG)) {
             uint64_t cookie;
             std::memcpy(&cookie, ps.ctrl, sizeof(cookie));
-            ((atl_req*)(uintptr_t)cookie)->done.store(1, std::memory_order_release);
+            atl_req* req = (atl_req*)(uintptr_t)cookie;
+            auto it = std::find(ps.awaiting_ack.begin(), ps.awaiting_ack.end(), req);
+            if (it != ps.awaiting_ack.end()) { // a request that was failed meanwhile is no longer listed
+                ps.awaiting_ack.erase(it);
+                req->done.store(1, std::memory_order_release);
+            }
             return;
         }
         rndv_desc d;
@@ -823,6 +861,53 @@ private:
         }
     }
 
+    static void fail(atl_req* req) {
+        req->error = 1;
+        req->done.store(1, std::memory_order_release);
+    }
+
+    // Nothing more will come from this peer and nothing can reach it: every operation that waits on it
+    // ends with an error, which the schedule turns into an exception on the caller's side.
+    void fail_peer(peer_state& ps, int p, const char* why) {
+        if (ps.dead)
+            return;
+        ps.dead = true;
+        peers_lost++;
+        const size_t pending = ps.posted.size() + ps.outq.size() + ps.awaiting_ack.size();
+        if (pending)
+            LOG_WARN("rank ", p, " is gone (", why, "): failing ", pending, " pending operation(s)");
+        else
+            LOG_DEBUG("rank ", p, " is gone (", why, ")");
+        for (auto& r : ps.posted)
+            fail(r.req);
+        ps.posted.clear();
+        for (auto& m : ps.outq)
+            if (m.req)
+                fail(m.req);
+        ps.outq.clear();
+        for (atl_req* r : ps.awaiting_ack)
+            fail(r);
+        ps.awaiting_ack.clear();
+    }
+
+    static bool process_gone(int pid) {
+        if (::kill(pid, 0) != 0)
+            return errno == ESRCH;
+        // a process that exited but was not reaped yet still has a pid: look at its state
+        char path[64], buf[256];
+        std::snprintf(path, sizeof(path), "/proc/%d/stat", pid);
+        int fd = ::open(path, O_RDONLY | O_CLOEXEC);
+        if (fd < 0)
+            return false;
+        const ssize_t n = ::read(fd, buf, sizeof(buf) - 1);
+        ::close(fd);
+        if (n <= 0)
+            return false;
+        buf[n] = 0;
+        const char* paren = std::strrchr(buf, ')');
+        return paren && (paren[2] == 'Z' || paren[2] == 'X');
+    }
+
     void progress(endpoint& ep) {
         for (auto& ps : ep.peers)
             if (!ps.outq.empty())
@@ -830,12 +915,41 @@ private:
         for (int p : ep.shm_peers)
             if (ep.peers[p].rx->readable())
                 drain(ep.peers[p]);
+        // Liveness of the peers behind shared-memory rings (a ring never reports that its other end died):
+        // every 100 ms, and only for peers this endpoint is waiting on.  What the peer wrote before it died
+        // is still in the ring and is delivered first.
+        if (!ep.shm_peers.empty() && (++ep.liveness_tick & 1023) == 0) {
+            timespec ts;
+            clock_gettime(CLOCK_MONOTONIC, &ts);
+            const uint64_t now = (uint64_t)ts.tv_sec * 1000000000ull + (uint64_t)ts.tv_nsec;
+            if (now - ep.last_liveness_ns > 100000000ull) {
+                ep.last_liveness_ns = now;
+                for (int p : ep.shm_peers) {
+                    peer_state& ps = ep.peers[p];
+                    if (ps.dead || pids_[p] == 0 || (ps.posted.empty() && ps.outq.empty() && ps.awaiting_ack.empty()))
+                        continue;
+                    if (process_gone(pids_[p])) {
+                        drain(ps);
+                        fail_peer(ps, p, "its process has exited");
+                    }
+                }
+            }
+        }
         if (ep.shm_peers.size() + 1 == ep.peers.size())
             return; // no socket on this endpoint
         epoll_event evs[64];
         int n = epoll_wait(ep.epfd, evs, 64, 0);
-        for (int i = 0; i < n; i++)
-            drain(ep.peers[evs[i].data.u32]);
+        for (int i = 0; i < n; i++) {
+            peer_state& ps = ep.peers[evs[i].data.u32];
+            drain(ps);
+            if (ps.closed && !ps.dead) {
+                epoll_ctl(ep.epfd, EPOLL_CTL_DEL, ps.fd, nullptr);
+                fail_peer(ps, (int)evs[i].data.u32, "it closed the connection");
+            }
+        }
+        for (auto& ps : ep.peers) // a reset seen while writing
+            if (ps.closed && !ps.dead)
+                fail_peer(ps, (int)(&ps - &ep.peers[0]), "the connection was reset");
     }
 
     int rank_, size_;
@@ -846,6 +960,7 @@ private:
     std::mutex mr_mu_;
     std::vector<std::pair<char*, size_t>> regions_;
     std::atomic<bool> cma_ok_{ true };
+    std::vector<int> pids_; // of the ranks on this host whose pid is visible here, else 0
     size_t rndv_min_ = 0; // messages of at least this size between processes of one host go by rendezvous (0: never)
 };
 
@@ -874,6 +989,7 @@ atl_comm::atl_comm(std::shared_ptr<atl_transport> tr, std::vector<int> world_ran
 void atl_comm::wait(int ep, atl_req* req) {
     while (!req->is_done())
         tr_->poll(ep);
+    CCL_THROW_IF_NOT(!req->error, "a peer of this communicator has left the job (process gone or connection closed)");
 }
 
 void atl_comm::allgather(const void* send_buf, void* recv_buf, size_t n) {
