@@ -752,6 +752,120 @@ event_ptr hier_device_reduce_scatter(host_comm& comm, coll_param& p, const coll_
     return make_completed_event();
 }
 
+// allgather of equal blocks on device buffers across nodes, on request (CCL_ALLGATHER=topo or
+// CCL_ALLGATHERV=topo; the default stages the whole result through the host).  The mirror image of the
+// reduce_scatter above: the ranks with my local index exchange their blocks on the host path (M blocks per
+// rank instead of N), the node gathers the M-block slices on the device, and a block transpose turns
+// the local-rank-major result into rank order.
+bool hier_allgather_possible(host_comm& comm, const coll_param& p, const coll_attr& attr) {
+    if ((p.ctype != coll_allgather && p.ctype != coll_allgatherv) || !env_data::get().cuda_kernels ||
+        !env_data::get().topo_algo || attr.out_dtype >= 0 || !p.recv_bufs.empty() || p.count == 0)
+        return false;
+    if (p.ctype == coll_allgatherv)
+        for (size_t c : p.recv_counts)
+            if (c != p.count)
+                return false;
+    const size_t bytes = p.count * dtype_size(p.dtype) * (size_t)comm.size();
+    if (!algorithm_selector::get().requested(p.ctype, bytes, "topo"))
+        return false;
+    const int L = comm.local_size();
+    if (L <= 0 || comm.size() % L != 0)
+        return false;
+    const std::vector<int>& h = comm.host_index();
+    for (int r = 0; r < comm.size(); r++)
+        if (h[r] != r / L)
+            return false;
+    return true;
+}
+
+event_ptr hier_device_allgather(host_comm& comm, coll_param& p, const coll_attr& attr) {
+    (void)attr;
+    auto node = comm.node_comm();
+    auto r2r = comm.r2r_comm();
+    const int L = node->size(), M = r2r->size();
+    const size_t esz = dtype_size(p.dtype);
+    const size_t block = p.count * esz;
+    const size_t slice_bytes = (size_t)M * block;
+    cudaStream_t st = (cudaStream_t)p.stream;
+    stats().device_calls[p.ctype]++;
+    struct scratch {
+        void *host_in = nullptr, *host_out = nullptr, *slice = nullptr, *grouped = nullptr;
+        size_t cap_in = 0, cap_out = 0, cap_slice = 0, cap_grouped = 0;
+        static void grow_host(void*& ptr, size_t& cap, size_t want) {
+            if (cap >= want)
+                return;
+            if (ptr)
+                CUDA_CHECK(cudaFreeHost(ptr));
+            ptr = nullptr;
+            cap = 0;
+            CUDA_CHECK(cudaMallocHost(&ptr, want));
+            cap = want;
+        }
+        static void grow_dev(void*& ptr, size_t& cap, size_t want) {
+            if (cap >= want)
+                return;
+            if (ptr)
+                CUDA_CHECK(cudaFree(ptr));
+            ptr = nullptr;
+            cap = 0;
+            CUDA_CHECK(cudaMalloc(&ptr, want));
+            cap = want;
+        }
+        ~scratch() {
+            if (host_in)
+                cudaFreeHost(host_in);
+            if (host_out)
+                cudaFreeHost(host_out);
+            if (slice)
+                cudaFree(slice);
+            if (grouped)
+                cudaFree(grouped);
+        }
+    };
+    static thread_local scratch sc;
+    scratch::grow_host(sc.host_in, sc.cap_in, block);
+    scratch::grow_host(sc.host_out, sc.cap_out, slice_bytes);
+    scratch::grow_dev(sc.slice, sc.cap_slice, slice_bytes);
+    // 1. my block to the ranks with my local index, theirs to me (in place: my block sits inside recv)
+    const void* mine = p.send_buf ? p.send_buf : (const char*)p.recv_buf + (size_t)comm.rank() * block;
+    CUDA_CHECK(cudaMemcpyAsync(sc.host_in, mine, block, cudaMemcpyDeviceToHost, st));
+    CUDA_CHECK(cudaStreamSynchronize(st));
+    coll_param ag;
+    ag.ctype = coll_allgather;
+    ag.send_buf = sc.host_in;
+    ag.recv_buf = sc.host_out;
+    ag.count = p.count;
+    ag.dtype = p.dtype;
+    ag.device = false;
+    coll_attr host_attr;
+    host_attr.scaleout = true;
+    coll_create(*r2r, ag, host_attr)->wait();
+    CUDA_CHECK(cudaMemcpyAsync(sc.slice, sc.host_out, slice_bytes, cudaMemcpyHostToDevice, st));
+    // 2. inside the node: everybody's slice, local-rank-major; 3. into rank order
+    const bool regroup = L > 1 && M > 1;
+    void* gathered = p.recv_buf;
+    if (regroup) {
+        scratch::grow_dev(sc.grouped, sc.cap_grouped, (size_t)L * slice_bytes);
+        gathered = sc.grouped;
+    }
+    coll_param ng;
+    ng.ctype = coll_allgather;
+    ng.send_buf = sc.slice;
+    ng.recv_buf = gathered;
+    ng.count = (size_t)M * p.count;
+    ng.dtype = p.dtype;
+    ng.device = true;
+    ng.stream = p.stream;
+    coll_attr plain;
+    event_ptr ev = device_coll(*node, ng, plain);
+    if (regroup) {
+        ev->wait();
+        gpu::launch_transpose_blocks(sc.grouped, p.recv_buf, L, M, block, st);
+    }
+    CUDA_CHECK(cudaStreamSynchronize(st)); // scratch memory is reused by the next call
+    return make_completed_event();
+}
+
 bool same_node(host_comm& comm) {
     const std::vector<int>& h = comm.host_index();
     for (int v : h)
@@ -1054,6 +1168,8 @@ event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr) {
             ev = hier_device_allreduce(comm, p, attr);
         else if (hier_reduce_scatter_possible(comm, p, attr))
             ev = hier_device_reduce_scatter(comm, p, attr);
+        else if (hier_allgather_possible(comm, p, attr))
+            ev = hier_device_allgather(comm, p, attr);
         else
             ev = staged_device_coll(comm, p, attr);
         if (sync)

@@ -184,6 +184,14 @@ std::string algorithm_selector::select_cpu(const selector_param& p) const {
     return algo;
 }
 
+bool algorithm_selector::requested(coll_type c, size_t bytes, const char* algo) const {
+    auto f = forced_.find(c);
+    if (f == forced_.end())
+        return false;
+    const std::string* a = lookup(f->second, bytes);
+    return a && *a == algo;
+}
+
 std::string algorithm_selector::forced_gpu(coll_type c, size_t bytes) const {
     auto f = forced_gpu_.find(c);
     if (f == forced_gpu_.end())

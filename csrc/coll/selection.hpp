@@ -37,6 +37,8 @@ public:
     std::string select_cpu(const selector_param& p) const;
     // "" when the environment does not force a GPU algorithm for this size
     std::string forced_gpu(coll_type c, size_t bytes) const;
+    // does CCL_<COLL> name `algo` for this size?  (names such as "topo" that only device buffers honour)
+    bool requested(coll_type c, size_t bytes, const char* algo) const;
     static const std::vector<std::string>& known_cpu_algos(coll_type c);
     // parses a specification; throws on syntax errors or unknown names
     static std::vector<algo_range> parse(const std::string& spec, const std::vector<std::string>& allowed);

@@ -34,12 +34,14 @@ def test_block_transpose_matches_a_permute(rows, cols, block, dtype):
         assert torch.equal(out2, ref)
 
 
-def _rs_fake_nodes(rank, world, addr_file, q):
+def _rs_fake_nodes(rank, world, addr_file, q, mode="reduce_scatter"):
     try:
         os.environ["CCL_TOPO_FAKE_HOST"] = f"node{rank}"
         os.environ["CCL_CUDA_NVLS"] = "0"
         os.environ["CCL_CUDA_SYMM_HEAP_SIZE"] = "64M"
         os.environ["CCL_CUDA_TMP_BUF_SIZE"] = "8M"
+        if mode == "allgather":
+            os.environ["CCL_ALLGATHER"] = "topo"
         from oneccl_b200.comm import KVS, Communicator, stats
 
         if rank == 0:
@@ -57,6 +59,8 @@ def _rs_fake_nodes(rank, world, addr_file, q):
         torch.cuda.set_device(0)
         ok = comm.local_size == 1
         for count, dtype in ((1000, torch.float32), (4099, torch.bfloat16), (70000, torch.float32)):
+            if mode != "reduce_scatter":
+                break
             base = (torch.arange(count * world, device="cuda") % 7).to(dtype)
             send = base + rank
             recv = torch.zeros(count, device="cuda", dtype=dtype)
@@ -65,20 +69,29 @@ def _rs_fake_nodes(rank, world, addr_file, q):
             ref = base[rank * count:(rank + 1) * count].float() * world + sum(range(world))
             ok = ok and bool(torch.equal(recv.float(), ref))
             ok = ok and bool(torch.equal(send, base + rank))  # the send buffer is left alone
-        before = stats("device_calls", "reduce_scatter")
+        # allgather on request (CCL_ALLGATHER=topo): my block crosses the nodes on the host path, the node gathers
+        for count, dtype in ((1000, torch.float32), (4099, torch.bfloat16)):
+            if mode != "allgather":
+                break
+            mine = torch.full((count,), float(rank + 1), device="cuda", dtype=dtype)
+            out = torch.zeros(count * world, device="cuda", dtype=dtype)
+            comm.allgather(mine, out).wait()
+            torch.cuda.synchronize()
+            ref = torch.arange(1, world + 1, device="cuda").repeat_interleave(count).to(dtype)
+            ok = ok and bool(torch.equal(out, ref))
+        calls = stats("device_calls", mode)
         comm.barrier().wait()
         comm.close()
-        q.put((rank, "ok", ok and before >= 3))
+        q.put((rank, "ok", ok and calls >= 2))
     except Exception:
         q.put((rank, "error", traceback.format_exc()))
 
 
-@pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a GPU")
-def test_reduce_scatter_across_fake_nodes_takes_the_hierarchical_path():
+def _run_fake_nodes(mode):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     addr = os.path.join(tempfile.mkdtemp(prefix="cclx_hrs_"), "addr")
-    procs = [ctx.Process(target=_rs_fake_nodes, args=(r, 2, addr, q)) for r in range(2)]
+    procs = [ctx.Process(target=_rs_fake_nodes, args=(r, 2, addr, q, mode)) for r in range(2)]
     for p in procs:
         p.start()
     res = {}
@@ -89,3 +102,14 @@ def test_reduce_scatter_across_fake_nodes_takes_the_hierarchical_path():
     for p in procs:
         p.join(timeout=30)
     assert res == {0: True, 1: True}
+
+
+@pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a GPU")
+def test_reduce_scatter_across_fake_nodes_takes_the_hierarchical_path():
+    _run_fake_nodes("reduce_scatter")
+
+
+@pytest.mark.skipif(not torch.cuda.is_available(), reason="needs a GPU")
+def test_allgather_across_fake_nodes_on_request():
+    """CCL_ALLGATHER=topo: own block across the nodes on the host path, node-level gather on the device."""
+    _run_fake_nodes("allgather")
