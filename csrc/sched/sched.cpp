@@ -742,7 +742,7 @@ void sched_cache::insert(const std::string& key, std::shared_ptr<master_sched> m
     while (map_.size() >= cap) {
         auto victim = map_.end();
         for (auto it = map_.begin(); it != map_.end(); ++it)
-            if (!it->second.m->in_flight && (victim == map_.end() || it->second.last_use < victim->second.last_use))
+            if (it->second.m->idle() && (victim == map_.end() || it->second.last_use < victim->second.last_use))
                 victim = it;
         if (victim == map_.end())
             break; // everything is running: exceed the bound rather than wait
@@ -759,7 +759,7 @@ void sched_cache::insert(const std::string& key, std::shared_ptr<master_sched> m
 void sched_cache::flush() {
     std::lock_guard<std::mutex> lk(mu_);
     for (auto it = map_.begin(); it != map_.end();) {
-        if (!it->second.m->in_flight)
+        if (it->second.m->idle())
             it = map_.erase(it);
         else
             ++it;

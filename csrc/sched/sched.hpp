@@ -175,7 +175,12 @@ public:
     // a launch requested while the schedule runs is queued and started by the
     // worker that completes the current one
     std::mutex launch_mu;
-    bool in_flight = false;
+    std::atomic<bool> in_flight{ false }; // written under launch_mu; the schedule cache reads it without
+    // true when no launch is running or queued and the worker that finished the last one is done with this object
+    bool idle() const {
+        return !in_flight.load(std::memory_order_acquire) &&
+               done.load(std::memory_order_acquire) == issued.load(std::memory_order_acquire);
+    }
     int delayed_launches = 0;
     bool cached = false;
     int priority = 0;
