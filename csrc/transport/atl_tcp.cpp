@@ -245,25 +245,27 @@ public:
             same_host_[r] = std::strncmp(table[r].host, mine.host, sizeof(mine.host)) == 0;
         // can this process read a neighbour's memory?  (ptrace policy and containers may forbid it; the
         // answer is assumed to be the same in both directions between processes of one job on one host)
-        pids_.resize(size_);
-        for (int r = 0; r < size_; r++) // a pid means something only inside this host's pid namespace
-            pids_[r] = (same_host_[r] && ::kill(table[r].pid, 0) == 0) ? table[r].pid : 0;
-        rndv_min_ = env.atl_cma ? env.atl_cma_threshold : 0;
-        if (rndv_min_) {
-            bool tried = false, ok = true;
-            for (int r = 0; r < size_ && !tried; r++) {
-                if (r == rank_ || !same_host_[r])
-                    continue;
-                tried = true;
-                uint64_t got = 0;
-                iovec l{ &got, sizeof(got) };
-                iovec rm{ (void*)(uintptr_t)table[r].probe, sizeof(got) };
-                ok = process_vm_readv(table[r].pid, &l, 1, &rm, 1, 0) == (ssize_t)sizeof(got) && got == probe_word;
-            }
-            if (!ok) {
-                LOG_INFO("process_vm_readv is not permitted here: long messages go through the rings");
-                rndv_min_ = 0;
-            }
+        // Which same-host peers live in this pid namespace?  Reading a known word out of the peer answers it
+        // (a pid alone could belong to an unrelated process of another container).  A verified pid serves the
+        // liveness check; cross-memory transfers need every same-host peer verified, and the answer is
+        // assumed to be the same in both directions between processes of one job.
+        pids_.assign(size_, 0);
+        bool all_readable = true;
+        for (int r = 0; r < size_; r++) {
+            if (r == rank_ || !same_host_[r])
+                continue;
+            uint64_t got = 0;
+            iovec l{ &got, sizeof(got) };
+            iovec rm{ (void*)(uintptr_t)table[r].probe, sizeof(got) };
+            if (process_vm_readv(table[r].pid, &l, 1, &rm, 1, 0) == (ssize_t)sizeof(got) && got == probe_word)
+                pids_[r] = table[r].pid;
+            else
+                all_readable = false;
+        }
+        rndv_min_ = (env.atl_cma && all_readable) ? env.atl_cma_threshold : 0;
+        if (env.atl_cma && !all_readable) {
+            LOG_INFO("process_vm_readv is not permitted between the ranks of this host: long messages go through the rings");
+            cma_ok_.store(false, std::memory_order_relaxed);
         }
 
         for (auto& ep : eps_) {
