@@ -917,7 +917,7 @@ void reduce_rabenseifner(sched& s, const buf_desc& b, int root) {
 
 // ---------------------------------------------------------------------------- point to point
 void send_direct(sched& s, const void* buf, size_t bytes, int peer, uint64_t seq) {
-    s.add<send_entry>(buf, bytes, peer, seq & 0xffff);
+    s.add<send_entry>(buf, bytes, peer, seq & 0xffff, /*one_way=*/true);
 }
 void recv_direct(sched& s, void* buf, size_t bytes, int peer, uint64_t seq) {
     s.add<recv_entry>(buf, bytes, peer, seq & 0xffff);

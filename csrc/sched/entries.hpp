@@ -19,8 +19,8 @@ namespace cclx {
 
 class send_entry : public sched_entry {
 public:
-    send_entry(sched* s, const void* buf, size_t bytes, int dst, uint64_t step)
-            : sched_entry(s), buf_(buf), bytes_(bytes), dst_(dst), step_(step) {}
+    send_entry(sched* s, const void* buf, size_t bytes, int dst, uint64_t step, bool one_way = false)
+            : sched_entry(s), buf_(buf), bytes_(bytes), dst_(dst), step_(step), one_way_(one_way) {}
     const char* name() const override { return "SEND"; }
     bool uses_credit() const override { return true; }
     void start() override;
@@ -33,6 +33,7 @@ private:
     size_t bytes_;
     int dst_;
     uint64_t step_;
+    bool one_way_; // a user's point-to-point send: nothing comes back from dst_ meanwhile
     atl_req req_;
 };
 

@@ -132,7 +132,7 @@ inline entry_status request_status(const atl_req& req, const char* what, int pee
 } // namespace
 
 void send_entry::start() {
-    owner_->comm()->atl().send(owner_->ep(), buf_, bytes_, dst_, owner_->tag(step_), &req_);
+    owner_->comm()->atl().send(owner_->ep(), buf_, bytes_, dst_, owner_->tag(step_), &req_, one_way_);
     update();
 }
 void send_entry::update() {

@@ -344,7 +344,7 @@ public:
     bool same_host(int peer) const override { return same_host_[peer]; }
     const char* name() const override { return eps_[0].shm_peers.empty() ? "tcp" : "shm+tcp"; }
 
-    void send(int e, const void* buf, size_t len, int dst, uint64_t tag, atl_req* req) override {
+    void send(int e, const void* buf, size_t len, int dst, uint64_t tag, atl_req* req, bool one_way) override {
         endpoint& ep = eps_[e];
         std::lock_guard<std::mutex> lk(ep.mu);
         req->reset();
@@ -360,7 +360,8 @@ public:
             fail(req);
             return;
         }
-        if (rndv_min_ && len >= rndv_min_ && same_host_[dst]) {
+        // one-way streams catch up with the rings only above the ring capacity
+        if (rndv_min_ && len >= rndv_min_ && same_host_[dst] && (!one_way || len >= ring_cap_)) {
             rndv_sends++;
             ps.awaiting_ack.push_back(req);
             ps.outq.emplace_back();

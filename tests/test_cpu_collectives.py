@@ -293,7 +293,7 @@ def _rendezvous(comm):
     import time
 
     W, r = comm.size, comm.rank
-    n = 300000
+    n = 600000  # 4.8 MB: above the ring capacity, where one-way point-to-point sends take the rendezvous too
     nxt, prv = (r + 1) % W, (r - 1) % W
     # the send is issued first everywhere: descriptors arrive before any receive is posted
     out = np.arange(n, dtype=np.float64) + r
