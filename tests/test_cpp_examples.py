@@ -121,3 +121,19 @@ def test_all_operations_through_the_typed_api(bindir, world):
     assert "FAILED" not in text
     # 5 datatypes x 2 iterations x 7 operation groups + the final line
     assert text.count("PASSED") == 5 * 2 * 7 + 1
+
+
+CUDA_FLAGS = ("-I/usr/local/cuda/include", "-L/usr/local/cuda/lib64", "-lcudart")
+
+
+@pytest.mark.parametrize("name", ["cuda_allreduce", "cuda_all_ops"])
+def test_cuda_examples_build_against_the_public_header(bindir, name):
+    """The device-buffer examples compile and link with g++ and the CUDA runtime alone; without a GPU they say so
+    and exit cleanly (their run on GPUs is tests/test_zzz_cuda_examples.py)."""
+    import torch
+
+    exe = bindir / name
+    _build(ROOT / "examples" / "cuda" / f"{name}.cpp", exe, extra=CUDA_FLAGS)
+    if not torch.cuda.is_available():
+        outs = _run_ranks(exe, 1)
+        assert outs[0][0] == 0 and "no CUDA device" in outs[0][1]
