@@ -70,9 +70,9 @@ public:
     // `dst` / `src` are world ranks of this transport
     // `one_way`: the sender is not receiving from `dst` at the same time (a user's point-to-point stream).
     // Between processes of one host such messages keep to the rings, where the sender's copy-in and the
-    // receiver's copy-out overlap on two cores (measured 7-8 GB/s at 128 KiB - 1 MiB against 3-5 GB/s for one
-    // cross-memory copy); exchanges inside collectives, where every rank copies in both directions anyway,
-    // halve their copy work with the rendezvous.
+    // receiver's copy-out overlap on two cores (measured level with one cross-memory copy up to 512 KiB and
+    // 1.4-1.6x faster at 1-2 MiB); exchanges inside collectives, where every rank copies in both directions
+    // anyway, halve their copy work with the rendezvous (allreduce of 1-4 MiB: 10-25 % faster).
     virtual void send(int ep, const void* buf, size_t len, int dst, uint64_t tag, atl_req* req, bool one_way = false) = 0;
     virtual void recv(int ep, void* buf, size_t len, int src, uint64_t tag, atl_req* req) = 0;
     virtual bool probe(int ep, int src, uint64_t tag, size_t* len) = 0;

@@ -137,3 +137,32 @@ def test_cuda_examples_build_against_the_public_header(bindir, name):
     if not torch.cuda.is_available():
         outs = _run_ranks(exe, 1)
         assert outs[0][0] == 0 and "no CUDA device" in outs[0][1]
+    # the benchmark tool with device buffers compiled in
+    _build(ROOT / "examples" / "benchmark" / "benchmark.cpp", bindir / "benchmark_cuda", extra=("-DCCL_BENCH_CUDA",) + CUDA_FLAGS)
+
+
+def test_benchmark_tool_options_and_result_check(bindir, tmp_path):
+    """The option set of the reference's benchmark: lists of collectives / datatypes / reductions, explicit
+    element counts, several operations in flight, in-place buffers, persistent operations, result check on
+    every iteration, CSV file."""
+    exe = bindir / "benchmark"
+    if not exe.exists():
+        _build(ROOT / "examples" / "benchmark" / "benchmark.cpp", exe)
+    csv = tmp_path / "out.csv"
+    outs = _run_ranks(exe, 3, extra_args=("-l", "all", "-d", "int8,bfloat16,float32", "-r", "sum,max", "-y", "1,17,1027",
+                                          "-c", "all", "-i", "3", "-w", "1", "-n", "2", "-x", "on", "-o", str(csv)))
+    for rc, o, err in outs:
+        assert rc == 0 and "CHECK FAILED" not in o, o[-2000:] + err[-2000:]
+    rows = [l for l in outs[0][1].splitlines() if l and not l.startswith("#") and "," in l]
+    # 3 reducing collectives x 2 reductions + 5 others, x 3 datatypes x 3 counts
+    assert len(rows) == (3 * 2 + 5) * 3 * 3
+    assert all(len(r.split(",")) == 11 for r in rows)  # with wait_t_avg
+    assert outs[0][1].strip().endswith("PASSED")
+    assert len(csv.read_text().splitlines()) == len(rows) + 1
+    # in place, not persistent, automatic iteration count
+    outs = _run_ranks(exe, 2, extra_args=("-l", "allreduce,allgatherv,reduce-scatter,alltoall", "-q", "1", "-p", "0",
+                                          "-f", "1024", "-t", "262144", "-i", "8", "-c", "last"))
+    for rc, o, err in outs:
+        assert rc == 0 and "CHECK FAILED" not in o, o[-2000:] + err[-2000:]
+    reps = [int(l.split(",")[5]) for l in outs[0][1].splitlines() if l.startswith("allreduce,")]
+    assert reps[0] == 8 and reps[-1] < 8  # 1 MiB of float32 runs fewer repetitions
