@@ -10,6 +10,7 @@
 #include "bootstrap/kvs.hpp"
 #include "coll/coll.hpp"
 #include "coll/selection.hpp"
+#include "bootstrap/launcher.hpp"
 #include "comm/host_comm.hpp"
 #include "core/datatype.hpp"
 #include "core/env.hpp"
@@ -353,6 +354,31 @@ vector_class<communicator> create_communicators(int size, const vector_class<int
     v.push_back(create_communicator(size, local_ranks[0], k, attr));
     return v;
 }
+
+} // namespace v1
+
+namespace preview {
+
+communicator create_communicator(const comm_attr&) {
+    return v1::guarded([&] {
+        v1::init();
+        cclx::launcher_world w = cclx::bootstrap_from_launcher();
+        if (cclx::env_data::get().backend == cclx::backend_t::stub)
+            return communicator(w.size, w.rank);
+        return communicator(cclx::host_comm::create(w.size, w.rank, w.store));
+    });
+}
+
+vector_class<communicator> split_communicators(const vector_class<pair_class<communicator, comm_split_attr>>& attrs) {
+    vector_class<communicator> out;
+    for (auto& p : attrs)
+        out.push_back(v1::split_communicator(p.first, p.second));
+    return out;
+}
+
+} // namespace preview
+
+namespace v1 {
 
 void group_start() {
     guarded([] {

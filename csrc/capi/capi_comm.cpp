@@ -6,6 +6,7 @@
 #include "capi/capi_common.hpp"
 #include "coll/coll.hpp"
 #include "coll/selection.hpp"
+#include "bootstrap/launcher.hpp"
 #include "comm/host_comm.hpp"
 #include "core/comp.hpp"
 #include "core/datatype.hpp"
@@ -165,6 +166,17 @@ CCLX_API void* cclx_elastic_comm_create(void* h) {
 CCLX_API void* cclx_comm_create(int size, int rank, void* kvs_h) {
     comm_handle* h = nullptr;
     capi::guard([&] { h = new comm_handle{ host_comm::create(size, rank, ((kvs_handle*)kvs_h)->k) }; });
+    return h;
+}
+
+// rank, size and store from the process launcher (PMI-1 or torchrun-style variables)
+CCLX_API void* cclx_comm_create_from_launcher() {
+    comm_handle* h = nullptr;
+    capi::guard([&] {
+        env_data::get();
+        launcher_world w = bootstrap_from_launcher();
+        h = new comm_handle{ host_comm::create(w.size, w.rank, w.store) };
+    });
     return h;
 }
 

@@ -23,6 +23,7 @@
 #include <stdexcept>
 #include <string>
 #include <type_traits>
+#include <utility>
 #include <vector>
 
 #define CCL_MAJOR_VERSION 2021
@@ -46,6 +47,8 @@ namespace ccl {
 
 template <class T>
 using vector_class = std::vector<T>;
+template <class A, class B>
+using pair_class = std::pair<A, B>;
 template <class T>
 using shared_ptr_class = std::shared_ptr<T>;
 template <class T>
@@ -749,5 +752,24 @@ CCL_TYPED event recv(T* buf, size_t count, int peer, const communicator& comm,
 } // namespace v1
 
 using namespace v1;
+
+// Functions the reference keeps in ccl::preview (include/oneapi/ccl/api_functions.hpp:242-254,328-379).
+namespace preview {
+
+// A communicator whose size, rank and key-value store come from the process launcher: a PMI-1 process
+// manager (Hydra's mpiexec: PMI_FD / PMI_PORT), or torchrun-style variables (RANK, WORLD_SIZE, MASTER_ADDR,
+// MASTER_PORT); a process that no launcher started gets a communicator of size 1.
+CCL_API communicator create_communicator(const comm_attr& attr = default_comm_attr);
+
+template <class... Avs>
+comm_split_attr create_comm_split_attr(Avs&&... avs) {
+    return v1::create_comm_split_attr(std::forward<Avs>(avs)...);
+}
+
+// one split per (communicator, attribute) pair
+CCL_API vector_class<communicator> split_communicators(
+    const vector_class<pair_class<communicator, comm_split_attr>>& attrs);
+
+} // namespace preview
 
 } // namespace ccl

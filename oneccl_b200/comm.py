@@ -196,6 +196,17 @@ class Communicator:
             raise _lib.CclError(self._lib.cclx_last_error().decode())
         return Communicator(_handle=h, _parent=self)
 
+    @classmethod
+    def from_launcher(cls) -> "Communicator":
+        """World communicator whose rank, size and key-value store come from the process launcher: a PMI-1
+        process manager (Hydra's ``mpiexec``: ``PMI_FD`` / ``PMI_PORT``) or torchrun-style variables; the
+        C++ form is ``ccl::preview::create_communicator()``."""
+        lib = _lib.load()
+        h = lib.cclx_comm_create_from_launcher()
+        if not h:
+            raise _lib.CclError(lib.cclx_last_error().decode())
+        return cls(_handle=h)
+
     @property
     def id(self) -> int:
         return int(self._lib.cclx_comm_id(self._h))

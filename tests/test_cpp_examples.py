@@ -166,3 +166,25 @@ def test_benchmark_tool_options_and_result_check(bindir, tmp_path):
         assert rc == 0 and "CHECK FAILED" not in o, o[-2000:] + err[-2000:]
     reps = [int(l.split(",")[5]) for l in outs[0][1].splitlines() if l.startswith("allreduce,")]
     assert reps[0] == 8 and reps[-1] < 8  # 1 MiB of float32 runs fewer repetitions
+
+
+def _free_port_pair():
+    """A port p such that p + 1 is free as well (the store of a torchrun-style job listens next to the
+    rendezvous port)."""
+    import socket
+
+    for _ in range(50):
+        a = socket.socket()
+        a.bind(("127.0.0.1", 0))
+        p = a.getsockname()[1]
+        b = socket.socket()
+        try:
+            b.bind(("127.0.0.1", p + 1))
+        except OSError:
+            a.close()
+            b.close()
+            continue
+        a.close()
+        b.close()
+        return p
+    raise RuntimeError("no free port pair")
