@@ -89,6 +89,10 @@ CCLX_API int cclx_dc_clear_status(void* h) {
 CCLX_API int cclx_dc_abort(void* h) {
     return capi::guard([&] { ((device_comm*)h)->abort(); });
 }
+// test hook: the next collectives of emulated rank `rank` (-1: none) carry a falsified argument signature
+CCLX_API int cclx_dc_test_sig_skew(void* h, int rank) {
+    return capi::guard([&] { ((device_comm*)h)->test_sig_skew = rank + 1; });
+}
 CCLX_API int cclx_dc_set_timeout_ms(void* h, size_t ms) {
     return capi::guard([&] { ((device_comm*)h)->set_timeout_ms(ms); });
 }

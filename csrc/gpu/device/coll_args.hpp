@@ -41,6 +41,7 @@ struct coll_args {
     int emu;
     int flags;
     int peer; // point-to-point partner
+    int sig_skew; // test hook: rank + 1 whose argument signature is falsified (0 = none)
     const char* reg_in[ARG_MAX_RANKS]; // CF_REG_IN: rank p's send buffer as mapped here
     char* reg_out[ARG_MAX_RANKS]; // CF_REG_OUT: rank p's recv buffer as mapped here
 };

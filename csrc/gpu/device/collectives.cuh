@@ -89,6 +89,18 @@ __device__ __forceinline__ char* peer_out(const comm_dev& c, const coll_args& a,
     return (a.flags & CF_REG_OUT) ? a.reg_out[p] : c.heap[p] + a.out_off;
 }
 
+// What every rank must pass alike to one collective kernel: the kernel itself (`kind`), the element
+// count, and for the zero-copy forms the buffer kind and the offsets that are applied to the peers'
+// memory.  `sig_skew` is a test hook that makes one emulated rank disagree.
+__device__ __forceinline__ uint32_t kernel_signature(uint32_t kind, const coll_args& a, const comm_dev& c) {
+    const uint32_t f = (uint32_t)a.flags & (CF_SYMM_IN | CF_SYMM_OUT | CF_NVLS | CF_REG_IN | CF_REG_OUT);
+    const bool zc = f & (CF_SYMM_IN | CF_SYMM_OUT | CF_REG_IN | CF_REG_OUT);
+    uint32_t sg = arg_signature(kind, zc ? a.in_off : 0, zc ? a.out_off : 0, a.count, f);
+    if (a.sig_skew == c.rank + 1)
+        sg ^= 0x5a5a5a5au;
+    return sg ? sg : 1u;
+}
+
 // ---------------------------------------------------------------------------
 // one-shot allreduce: push my data into slot[rank] of everybody's staging,
 // one barrier, reduce the `world` slots locally.
@@ -97,6 +109,7 @@ __device__ __forceinline__ char* peer_out(const comm_dev& c, const coll_args& a,
 template <class T, class Tout, class Op>
 __global__ void __launch_bounds__(1024) allreduce_oneshot_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(1, a, c);
     typedef typename acc_of<T>::type A;
     constexpr int N = pack_traits<T>::N;
     const T* send = reinterpret_cast<const T*>(ra.send);
@@ -122,7 +135,7 @@ __global__ void __launch_bounds__(1024) allreduce_oneshot_kernel(const comm_dev*
                 st16(c.staging[p] + goff + (i << 4), v);
         }
     }
-    if (peer_barrier(c, s)) {
+    if (peer_barrier(c, s, sig)) {
         const char* mine = c.staging[c.rank] + (size_t)s.gen * c.staging_bytes;
         for (size_t i = lo + tid; i < hi; i += nt) {
             A acc[N];
@@ -144,6 +157,7 @@ __global__ void __launch_bounds__(1024) allreduce_oneshot_kernel(const comm_dev*
 template <class T, class Tout, class Op>
 __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(2, a, c);
     typedef typename acc_of<T>::type A;
     constexpr int N = pack_traits<T>::N;
     constexpr size_t RAWP = (size_t)N * sizeof(Tout); // bytes of one reduced pack
@@ -171,7 +185,7 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const comm_dev*
         for (size_t i = lo + tid; i < hi; i += nt)
             st16(dst + (i << 4), load_pack<T>(send, qlo + i, count, vin));
     }
-    bool ok = peer_barrier(c, s);
+    bool ok = peer_barrier(c, s, sig);
     // phase 2: reduce my slice and broadcast the result
     size_t mlo, mhi, lo, hi;
     split_range(npacks, W, c.rank, mlo, mhi);
@@ -207,7 +221,7 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const comm_dev*
             }
         }
     }
-    ok = peer_barrier(c, s);
+    ok = peer_barrier(c, s, sig);
     // phase 3: collect the other slices
     if (ok) {
         const char* outr = c.staging[c.rank] + gbase + in_bytes;
@@ -266,6 +280,7 @@ __global__ void __launch_bounds__(1024) allreduce_twoshot_kernel(const comm_dev*
 template <class T, class Tout, class Op, bool NVLS>
 __global__ void __launch_bounds__(1024) allreduce_pipelined_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(3, a, c);
     typedef typename acc_of<T>::type A;
     constexpr int N = pack_traits<T>::N;
     constexpr size_t RAWP = (size_t)N * sizeof(Tout); // bytes of one reduced pack
@@ -419,7 +434,7 @@ __global__ void __launch_bounds__(1024) allreduce_pipelined_kernel(const comm_de
             }
         }
         if (j <= nchunks)
-            ok = peer_barrier(c, s);
+            ok = peer_barrier(c, s, sig);
     }
     sync_end(c, gridDim.x, (uint32_t)(nchunks + 1), true);
 }
@@ -432,9 +447,12 @@ __global__ void __launch_bounds__(1024) allreduce_pipelined_kernel(const comm_de
 // The tail that does not fill a 16-byte pack is read before and written after
 // the second barrier so that in-place calls do not race.
 // ---------------------------------------------------------------------------
-template <class T, class Op, bool NVLS>
+// U = 16-byte packs in flight per thread of the NVLS form: 4 for a grid as wide as the GPU, 8 for the
+// narrow grids that leave most SMs to a concurrent compute kernel (gradient buckets during backward).
+template <class T, class Op, bool NVLS, int UNROLL = 4>
 __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(4, a, c);
     typedef typename acc_of<T>::type A;
     constexpr int N = pack_traits<T>::N;
     const int W = c.world;
@@ -446,7 +464,7 @@ __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* ta
     split_range(mhi - mlo, gridDim.x, blockIdx.x, lo, hi);
     const bool scale = a.do_scale != 0;
 
-    bool ok = peer_barrier(c, s);
+    bool ok = peer_barrier(c, s, sig);
     A tail_acc = A();
     if (ok) {
         if (NVLS) {
@@ -454,8 +472,8 @@ __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* ta
             char* out = c.mc_heap + a.out_off;
             size_t i = mlo + lo + tid;
             const size_t end = mlo + hi;
-            // four packs in flight per thread keep enough bytes on the wire for the switch round trip
-            constexpr int U = 4;
+            // several packs in flight per thread keep enough bytes on the wire for the switch round trip
+            constexpr int U = UNROLL;
             auto rescale = [&](uint4& v) {
                 A t0[N];
                 unpack16<T, A>(v, t0);
@@ -528,7 +546,7 @@ __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* ta
                                      to_acc<A, T>(__ldcv(reinterpret_cast<const T*>(peer_in(c, a, p)) + e)));
         }
     }
-    ok = peer_barrier(c, s);
+    ok = peer_barrier(c, s, sig);
     if (ok && blockIdx.x == 0 && tid < tail) {
         const size_t e = full * N + tid;
         reinterpret_cast<T*>(peer_out(c, a, c.rank))[e] =
@@ -546,6 +564,7 @@ __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* ta
 template <class T, class Tout, class Op>
 __global__ void __launch_bounds__(1024) reduce_scatter_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(5, a, c);
     typedef typename acc_of<T>::type A;
     constexpr int N = pack_traits<T>::N;
     const T* send = reinterpret_cast<const T*>(ra.send);
@@ -569,7 +588,7 @@ __global__ void __launch_bounds__(1024) reduce_scatter_kernel(const comm_dev* ta
         for (int k = 1; k < W; k++)
             st16(c.staging[(c.rank + k) % W] + gbase + (size_t)c.rank * slot + (i << 4), v[k]);
     }
-    if (peer_barrier(c, s)) {
+    if (peer_barrier(c, s, sig)) {
         const char* mine = c.staging[c.rank] + gbase;
         const T* own = send + (size_t)c.rank * a.stride;
         const bool vown = (((uintptr_t)own) & 15) == 0;
@@ -605,6 +624,7 @@ __global__ void __launch_bounds__(1024) reduce_scatter_kernel(const comm_dev* ta
 template <class T, class Tout, class Op, bool NVLS>
 __global__ void __launch_bounds__(1024) reduce_scatter_pipelined_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(6, a, c);
     typedef typename acc_of<T>::type A;
     constexpr int N = pack_traits<T>::N;
     const T* send = reinterpret_cast<const T*>(ra.send);
@@ -687,7 +707,7 @@ __global__ void __launch_bounds__(1024) reduce_scatter_pipelined_kernel(const co
             }
         }
         if (j < nchunks)
-            ok = peer_barrier(c, s);
+            ok = peer_barrier(c, s, sig);
     }
     sync_end(c, gridDim.x, (uint32_t)nchunks, true);
 }
@@ -697,6 +717,7 @@ __global__ void __launch_bounds__(1024) reduce_scatter_pipelined_kernel(const co
 template <class T, class Op, bool NVLS>
 __global__ void __launch_bounds__(1024) reduce_scatter_symm_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(7, a, c);
     typedef typename acc_of<T>::type A;
     constexpr int N = pack_traits<T>::N;
     T* recv = reinterpret_cast<T*>(ra.recv);
@@ -708,7 +729,7 @@ __global__ void __launch_bounds__(1024) reduce_scatter_symm_kernel(const comm_de
     const bool vout = (((uintptr_t)recv) & 15) == 0;
     size_t lo, hi;
     split_range(full, gridDim.x, blockIdx.x, lo, hi);
-    bool ok = peer_barrier(c, s);
+    bool ok = peer_barrier(c, s, sig);
     if (ok) {
         for (size_t i = lo + tid; i < hi; i += nt) {
             A acc[N];
@@ -730,7 +751,7 @@ __global__ void __launch_bounds__(1024) reduce_scatter_symm_kernel(const comm_de
             recv[e] = from_acc<T, A>(a.do_scale ? apply_scale<A>(acc, a.scale) : acc);
         }
     }
-    peer_barrier(c, s); // peers may still read my send buffer until here
+    peer_barrier(c, s, sig); // peers may still read my send buffer until here
     sync_end(c, gridDim.x, 2, false);
 }
 
@@ -745,6 +766,7 @@ __global__ void __launch_bounds__(1024) reduce_scatter_symm_kernel(const comm_de
 template <bool PUSH>
 __global__ void __launch_bounds__(1024) allgatherv_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(8, a, c);
     const int W = c.world;
     const size_t gbase = (size_t)s.gen * c.staging_bytes;
     char* recv = reinterpret_cast<char*>(ra.recv);
@@ -775,7 +797,7 @@ __global__ void __launch_bounds__(1024) allgatherv_kernel(const comm_dev* tab, c
             if (send != recv + ra.sdispl[c.rank])
                 block_copy<false>(recv + ra.sdispl[c.rank] + blo, send + blo, bhi - blo);
         }
-        if (peer_barrier(c, s)) {
+        if (peer_barrier(c, s, sig)) {
             if (uniform) {
                 // equal aligned blocks: one pass with the loads of all peers in flight together
                 const char* st = c.staging[c.rank] + gbase;
@@ -811,7 +833,7 @@ __global__ void __launch_bounds__(1024) allgatherv_kernel(const comm_dev* tab, c
             if (send != recv + ra.sdispl[c.rank])
                 block_copy<false>(recv + ra.sdispl[c.rank] + blo, send + blo, bhi - blo);
         }
-        if (peer_barrier(c, s)) {
+        if (peer_barrier(c, s, sig)) {
             for (int k = 1; k < W; k++) {
                 const int p = (c.rank + k) % W;
                 const size_t pb = ra.scount[p];
@@ -830,6 +852,7 @@ __global__ void __launch_bounds__(1024) allgatherv_kernel(const comm_dev* tab, c
 template <bool NVLS>
 __global__ void __launch_bounds__(1024) allgather_symm_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(9, a, c);
     const int W = c.world;
     const size_t bytes = a.count; // bytes per rank, multiple of 16, 16-byte aligned offsets
     const char* send = ra.send ? reinterpret_cast<const char*>(ra.send)
@@ -838,7 +861,7 @@ __global__ void __launch_bounds__(1024) allgather_symm_kernel(const comm_dev* ta
     size_t lo, hi;
     split_range(bytes >> 4, gridDim.x, blockIdx.x, lo, hi);
     // peers must have finished reading the previous contents of recv
-    bool ok = peer_barrier(c, s);
+    bool ok = peer_barrier(c, s, sig);
     if (ok) {
         const bool vin = (((uintptr_t)send) & 15) == 0;
         for (size_t i = lo + tid; i < hi; i += nt) {
@@ -854,7 +877,7 @@ __global__ void __launch_bounds__(1024) allgather_symm_kernel(const comm_dev* ta
             }
         }
     }
-    peer_barrier(c, s);
+    peer_barrier(c, s, sig);
     sync_end(c, gridDim.x, 2, false);
 }
 
@@ -869,6 +892,7 @@ __global__ void __launch_bounds__(1024) allgather_symm_kernel(const comm_dev* ta
 // ---------------------------------------------------------------------------
 static __global__ void __launch_bounds__(1024) alltoallv_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(10, a, c);
     const int W = c.world;
     const size_t slot = (c.staging_bytes / W) & ~(size_t)15;
     const char* send = reinterpret_cast<const char*>(ra.send);
@@ -923,7 +947,7 @@ static __global__ void __launch_bounds__(1024) alltoallv_kernel(const comm_dev* 
         const size_t hdr = ((size_t)g * MAX_BLOCKS + blockIdx.x) * MAX_RANKS;
         if (tid < (size_t)W)
             c.aux[tid][hdr + c.rank] = more ? 1u : 0u;
-        if (!peer_barrier(c, s)) {
+        if (!peer_barrier(c, s, sig)) {
             rounds++;
             break;
         }
@@ -974,13 +998,14 @@ static __global__ void __launch_bounds__(1024) alltoallv_kernel(const comm_dev* 
 // a.count = bytes per peer (multiple of 16); send is 16-byte aligned and distinct from recv.
 static __global__ void __launch_bounds__(1024) alltoall_symm_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(11, a, c);
     const int W = c.world;
     const size_t b = a.count;
     const char* send = reinterpret_cast<const char*>(ra.send);
     size_t lo, hi;
     split_range(b >> 4, gridDim.x, blockIdx.x, lo, hi);
     // peers must have finished reading the previous contents of recv
-    bool ok = peer_barrier(c, s);
+    bool ok = peer_barrier(c, s, sig);
     if (ok) {
         const size_t doff = (size_t)c.rank * b;
         for (size_t i = lo + tid; i < hi; i += nt) {
@@ -991,7 +1016,7 @@ static __global__ void __launch_bounds__(1024) alltoall_symm_kernel(const comm_d
                 st16(peer_out(c, a, (c.rank + k) % W) + doff + (i << 4), v[k]);
         }
     }
-    peer_barrier(c, s);
+    peer_barrier(c, s, sig);
     sync_end(c, gridDim.x, 2, false);
 }
 
@@ -1001,6 +1026,7 @@ static __global__ void __launch_bounds__(1024) alltoall_symm_kernel(const comm_d
 // ---------------------------------------------------------------------------
 static __global__ void __launch_bounds__(1024) broadcast_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(12, a, c);
     const int W = c.world;
     const size_t bytes = a.count;
     const size_t gbase = (size_t)s.gen * c.staging_bytes;
@@ -1024,7 +1050,7 @@ static __global__ void __launch_bounds__(1024) broadcast_kernel(const comm_dev* 
         if (recv != send)
             block_copy<false>(recv + l, send + l, h - l);
     }
-    if (peer_barrier(c, s)) {
+    if (peer_barrier(c, s, sig)) {
         if (c.rank != a.root && h > l)
             block_copy<true>(recv + l, c.staging[c.rank] + gbase + l, h - l);
     }
@@ -1038,6 +1064,7 @@ static __global__ void __launch_bounds__(1024) broadcast_kernel(const comm_dev* 
 template <class T, class Tout, class Op>
 __global__ void __launch_bounds__(1024) reduce_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
+    const uint32_t sig = kernel_signature(13, a, c);
     typedef typename acc_of<T>::type A;
     constexpr int N = pack_traits<T>::N;
     const T* send = reinterpret_cast<const T*>(ra.send);
@@ -1055,7 +1082,7 @@ __global__ void __launch_bounds__(1024) reduce_kernel(const comm_dev* tab, coll_
         for (size_t i = lo + tid; i < hi; i += nt)
             st16(dst + (i << 4), load_pack<T>(send, i, count, vin));
     }
-    if (peer_barrier(c, s) && c.rank == a.root) {
+    if (peer_barrier(c, s, sig) && c.rank == a.root) {
         const bool vout = out_vec_ok<Tout, N>(recv);
         const char* mine = c.staging[c.rank] + gbase;
         for (size_t i = lo + tid; i < hi; i += nt) {
@@ -1080,7 +1107,8 @@ __global__ void __launch_bounds__(1024) reduce_kernel(const comm_dev* tab, coll_
 // barrier only
 static __global__ void __launch_bounds__(64) barrier_kernel(const comm_dev* tab, coll_args a) {
     CCLX_KERNEL_PROLOGUE();
-    peer_barrier(c, s);
+    const uint32_t sig = kernel_signature(14, a, c);
+    peer_barrier(c, s, sig);
     sync_end(c, gridDim.x, 1, false);
 }
 

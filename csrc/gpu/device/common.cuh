@@ -173,7 +173,14 @@ __device__ __forceinline__ bool wait_flag_sys(const comm_dev& c, const uint32_t*
 // All threads of the block must call it.  Writes made by any thread of the
 // block before the call are visible to the peers' threads after their call
 // returns (bar.sync + release.sys / acquire.sys + bar.sync).
-__device__ __forceinline__ bool peer_barrier(const comm_dev& c, block_sync& s) {
+//
+// `sig` (non-zero, first barrier of a kernel, block 0 only) is a hash of the arguments that must be
+// equal on every rank because the kernel applies them to the peers' memory (buffer kind, heap offsets,
+// count).  Every rank leaves its value in the peers' signature words before it raises its flag and
+// compares the peers' values with its own once their flags have arrived; a difference ends the kernel
+// with ST_ARG_MISMATCH before any data is touched.  The slot is chosen by the barrier's epoch, so a
+// peer that is already in its next kernel writes another slot.
+__device__ __forceinline__ bool peer_barrier(const comm_dev& c, block_sync& s, uint32_t sig = 0) {
     __shared__ int bar_fail;
     if (threadIdx.x == 0)
         bar_fail = 0;
@@ -182,16 +189,39 @@ __device__ __forceinline__ bool peer_barrier(const comm_dev& c, block_sync& s) {
     const uint32_t target = s.epoch + s.used;
     if (s.ok && threadIdx.x < (unsigned)c.world) {
         const int p = threadIdx.x;
+        const bool check = sig != 0 && blockIdx.x == 0;
+        const int slot = SIG_BASE_WORD + (int)(target % SIG_SLOTS) * MAX_RANKS;
+        if (check)
+            c.p2p_flags[p][slot + c.rank] = sig;
         // the release store is the only system-scope fence of the barrier: it orders the
         // block's earlier writes (made visible to this thread by bar.sync) before the flag
         st_release_sys(c.flags[p] + blockIdx.x * MAX_RANKS + c.rank, target);
         if (!wait_flag_sys(c, c.flags[c.rank] + blockIdx.x * MAX_RANKS + p, target, p, ST_BARRIER_TIMEOUT))
             bar_fail = 1;
+        else if (check) {
+            const uint32_t theirs = ld_volatile_u32(c.p2p_flags[c.rank] + slot + p);
+            if (theirs != sig) {
+                report(c, ST_ARG_MISMATCH, p, theirs);
+                bar_fail = 1;
+            }
+        }
     }
     __syncthreads();
     if (bar_fail)
         s.ok = false;
     return s.ok;
+}
+
+// Hash of the arguments of a zero-copy collective that every rank must pass alike (never zero).
+__device__ __forceinline__ uint32_t arg_signature(uint32_t kind, size_t in_off, size_t out_off, size_t count,
+                                                  uint32_t flags) {
+    unsigned long long h = 0x9E3779B97F4A7C15ull * (kind + 1);
+    h = (h ^ (unsigned long long)in_off) * 0xBF58476D1CE4E5B9ull;
+    h = (h ^ (unsigned long long)out_off) * 0x94D049BB133111EBull;
+    h = (h ^ (unsigned long long)count) * 0xBF58476D1CE4E5B9ull;
+    h = (h ^ flags) * 0x94D049BB133111EBull;
+    const uint32_t r = (uint32_t)(h >> 32) ^ (uint32_t)h;
+    return r ? r : 1u;
 }
 
 // ---- typed packs --------------------------------------------------------------

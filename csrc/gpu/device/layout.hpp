@@ -18,7 +18,8 @@ enum : uint32_t {
     ST_FLAG_TIMEOUT = 3,
     ST_MBAR_TIMEOUT = 4,
     ST_BAD_ARGS = 5,
-    ST_NOT_FINITE = 6 // debug scan found NaN / Inf in a reduction result (CCL_CUDA_CHECK_NAN)
+    ST_NOT_FINITE = 6, // debug scan found NaN / Inf in a reduction result (CCL_CUDA_CHECK_NAN)
+    ST_ARG_MISMATCH = 7 // a zero-copy collective was called with a different buffer kind, offset or count on a peer
 };
 
 // words of comm_dev::state
@@ -51,6 +52,12 @@ constexpr int P2P_ACK_BASE = MAX_RANKS * P2P_BLOCKS;
 constexpr int P2P_SPARE_WORD = 2 * MAX_RANKS * P2P_BLOCKS; // never written: timeout test
 constexpr int P2P_FLAG_WORDS = 2 * MAX_RANKS * P2P_BLOCKS + 16;
 constexpr int P2P_SEQ_WORDS = 2 * MAX_RANKS * P2P_BLOCKS;
+// Argument signatures of the zero-copy collectives live behind the point-to-point flags in the same
+// peer-mapped page: SIG_SLOTS generations x MAX_RANKS writers x one word (see peer_barrier).
+constexpr int SIG_SLOTS = 4;
+constexpr int SIG_BASE_WORD = 640;
+static_assert(P2P_FLAG_WORDS <= SIG_BASE_WORD && SIG_BASE_WORD + SIG_SLOTS * MAX_RANKS <= 1024,
+              "signature words must fit the 4 KiB page of the point-to-point flags");
 
 // auxiliary flag region (words): [0, A2A_HDR_WORDS) alltoallv consensus, the rest is
 // handed out to the fused kernels by the host

@@ -155,8 +155,10 @@ void device_comm::check_status() const {
         if (s[0] != dev::ST_OK) {
             static const char* what[] = { "ok",           "barrier timeout", "aborted",
                                           "flag timeout", "mbarrier timeout", "bad arguments",
-                                          "NaN or Inf in a reduction result (detail = element index)" };
-            const char* w = s[0] < 7 ? what[s[0]] : "unknown";
+                                          "NaN or Inf in a reduction result (detail = element index)",
+                                          "a peer called this collective with another buffer kind, offset or count "
+                                          "(zero-copy collectives need the same symmetric offset on every rank)" };
+            const char* w = s[0] < 8 ? what[s[0]] : "unknown";
             CCL_THROW("device communicator error on rank ", table_host_[e].rank, ": ", w, " (block ", s[1],
                       ", peer ", s[2], ", detail ", s[3], ")");
         }

@@ -92,6 +92,10 @@ public:
     // pointer of rank q's buffer of registration `id`, as mapped in this process
     char* user_base(int id, int q) const { return regs_[id].base[q]; }
 
+    // test hook: rank + 1 whose argument signature is falsified in the next collectives (0 = none), so that
+    // the cross-rank argument check can be exercised with all ranks emulated on one GPU
+    int test_sig_skew = 0;
+
     // per-algorithm launch counters (observability)
     std::vector<unsigned long long> algo_hits = std::vector<unsigned long long>(ga_last * (int)coll_last, 0);
 

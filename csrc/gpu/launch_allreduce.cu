@@ -152,16 +152,25 @@ void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, i
         prepare_args(dc, a, ra, st);
         // per-rank slice, 16 KiB of it per block
         const int blocks = pick_blocks(dc, bytes / 16 / W + 1, 1024, o.blocks);
+        // a grid that the caller kept narrow (it runs beside a compute kernel) makes up for the missing
+        // blocks with full-size blocks and twice the loads in flight per thread
+        const bool narrow = o.blocks > 0 && blocks * 4 <= dc.sm_count();
+        const int th = narrow ? 1024 : threads;
         CCLX_DISPATCH_DTYPE(dt_in, T, {
             if (algo == ga_nvls) {
                 if constexpr (std::is_same<T, float>::value || std::is_same<T, __nv_bfloat16>::value ||
-                              std::is_same<T, __half>::value)
-                    launch_kernel(dc, dev::allreduce_symm_kernel<T, dev::op_sum, true>, blocks, threads, st,
-                                  dc.table(), a);
+                              std::is_same<T, __half>::value) {
+                    if (narrow)
+                        launch_kernel(dc, dev::allreduce_symm_kernel<T, dev::op_sum, true, 8>, blocks, th, st,
+                                      dc.table(), a);
+                    else
+                        launch_kernel(dc, dev::allreduce_symm_kernel<T, dev::op_sum, true, 4>, blocks, th, st,
+                                      dc.table(), a);
+                }
             }
             else {
                 CCLX_DISPATCH_OP(op, OP,
-                                 launch_kernel(dc, dev::allreduce_symm_kernel<T, OP, false>, blocks, threads, st,
+                                 launch_kernel(dc, dev::allreduce_symm_kernel<T, OP, false>, blocks, th, st,
                                                dc.table(), a));
             }
         });

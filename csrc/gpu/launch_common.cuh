@@ -2,6 +2,9 @@
 // and the real-vs-emulated launch helper.
 #pragma once
 #include <algorithm>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "core/env.hpp"
 #include "core/log.hpp"
@@ -133,6 +136,7 @@ inline void fill_registered(const device_comm& dc, dev::coll_args& a, const zc_v
 // table is uploaded to the device (the stream is drained first because an
 // earlier launch may still read the previous table).
 inline void prepare_args(device_comm& dc, dev::coll_args& a, const dev::rank_args* ra, cudaStream_t st) {
+    a.sig_skew = dc.test_sig_skew;
     if (dc.emulated()) {
         CUDA_CHECK(cudaStreamSynchronize(st));
         CUDA_CHECK(cudaMemcpy(dc.emu_args_dev(), ra, dc.world() * sizeof(dev::rank_args), cudaMemcpyHostToDevice));
@@ -147,6 +151,28 @@ inline void prepare_args(device_comm& dc, dev::coll_args& a, const dev::rank_arg
     }
 }
 
+// Blocks of one kernel that can be resident at the same time on an otherwise idle GPU (occupancy of the
+// kernel at this block size x SMs), looked up once per (kernel, block size).  Blocks of a collective kernel
+// wait for the block of the same index on every peer, so a grid above this number could leave a block
+// waiting for a peer's block that is queued behind it: launch_kernel refuses such a grid.  (The
+// reference states the same rule for its SYCL kernels: threads <= hardware threads, else deadlock,
+// src/coll/algorithms/allreduce/sycl/allreduce_small_sycl_impl.hpp:170-182.)
+template <class K>
+int resident_blocks(const device_comm& dc, K kernel, int threads) {
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, int> cache;
+    std::lock_guard<std::mutex> g(mu);
+    const auto key = std::make_pair((const void*)kernel, threads * 64 + dc.device_id());
+    auto it = cache.find(key);
+    if (it != cache.end())
+        return it->second;
+    int per_sm = 0;
+    CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
+    const int n = per_sm * dc.sm_count();
+    cache[key] = n;
+    return n;
+}
+
 template <class K, class... Args>
 void launch_kernel(device_comm& dc, K kernel, int blocks, int threads, cudaStream_t st, Args... args) {
     dc.check_status();
@@ -156,6 +182,9 @@ void launch_kernel(device_comm& dc, K kernel, int blocks, int threads, cudaStrea
         CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)kernel, grid, dim3(threads), argv, 0, st));
     }
     else {
+        const int cap = resident_blocks(dc, kernel, threads);
+        CCL_THROW_IF_NOT(blocks <= cap, "a collective kernel was asked for ", blocks, " blocks of ", threads,
+                         " threads but only ", cap, " can be resident at once");
         kernel<<<blocks, threads, 0, st>>>(args...);
         CUDA_CHECK(cudaGetLastError());
     }

@@ -107,6 +107,10 @@ __global__ void __launch_bounds__(SQN_MAX_BLOCKS) sq_norm_final_kernel(const flo
         out[0] += sh[0];
 }
 
+__global__ void bump_step_kernel(int* step) {
+    *step += 1;
+}
+
 struct adamw_args {
     float lr, beta1, beta2, eps, weight_decay;
     float bias1, bias2; // 1 - beta^t
@@ -120,7 +124,12 @@ template <class T>
 __global__ void __launch_bounds__(512)
     adamw_flat_kernel(float* __restrict__ master, const T* __restrict__ grad, float* __restrict__ m,
                       float* __restrict__ v, __nv_bfloat16* __restrict__ model, size_t n, adamw_args a,
-                      const float* __restrict__ sq_norm) {
+                      const float* __restrict__ sq_norm, const int* __restrict__ step_dev) {
+    if (step_dev) { // step number kept on the device: the launch can be replayed from a CUDA graph
+        const float t = (float)*step_dev;
+        a.bias1 = 1.f - powf(a.beta1, t);
+        a.bias2 = 1.f - powf(a.beta2, t);
+    }
     float clip = 1.f;
     if (a.max_norm > 0.f && sq_norm) {
         const float norm = sqrtf(*sq_norm) * a.grad_scale;
@@ -412,13 +421,20 @@ CCLX_API int cclx_sq_norm(const void* g, size_t n, int dt, float* out, float* pa
     });
 }
 
+// `step_dev` (optional): device word holding the step number.  When given, the launch first adds one to
+// it and the update takes its bias corrections from it instead of `step`, so that the same launch
+// sequence can be replayed from a CUDA graph.
 CCLX_API int cclx_adamw_flat(float* master, const void* grad, int grad_dt, float* m, float* v, void* model_bf16,
                              size_t n, size_t n_decay, float lr, float beta1, float beta2, float eps,
                              float weight_decay, int step, float grad_scale, float max_norm, const float* sq_norm,
-                             void* stream) {
+                             int* step_dev, void* stream) {
     return cclx::capi::guard([&] {
         if (n == 0)
             return;
+        if (step_dev) {
+            bump_step_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(step_dev);
+            CUDA_CHECK(cudaGetLastError());
+        }
         adamw_args a;
         a.lr = lr;
         a.beta1 = beta1;
@@ -433,10 +449,10 @@ CCLX_API int cclx_adamw_flat(float* master, const void* grad, int grad_dt, float
         const int blocks = grid_for(n, 512);
         if (grad_dt == 11)
             adamw_flat_kernel<__nv_bfloat16><<<blocks, 512, 0, (cudaStream_t)stream>>>(
-                master, (const __nv_bfloat16*)grad, m, v, (__nv_bfloat16*)model_bf16, n, a, sq_norm);
+                master, (const __nv_bfloat16*)grad, m, v, (__nv_bfloat16*)model_bf16, n, a, sq_norm, step_dev);
         else if (grad_dt == 9)
             adamw_flat_kernel<float><<<blocks, 512, 0, (cudaStream_t)stream>>>(master, (const float*)grad, m, v,
-                                                                               (__nv_bfloat16*)model_bf16, n, a, sq_norm);
+                                                                               (__nv_bfloat16*)model_bf16, n, a, sq_norm, step_dev);
         else
             CCL_THROW("adamw_flat supports float32 and bfloat16 gradients");
         CUDA_CHECK(cudaGetLastError());

@@ -41,6 +41,7 @@ def _proto(lib):
         "cclx_dc_clear_status": (i, [vp]),
         "cclx_dc_abort": (i, [vp]),
         "cclx_dc_set_timeout_ms": (i, [vp, sz]),
+        "cclx_dc_test_sig_skew": (i, [vp, i]),
         "cclx_dc_algo_hits": (C.c_ulonglong, [vp, i, i]),
         "cclx_gpu_algo_from_name": (i, [C.c_char_p]),
         "cclx_dc_symm_alloc": (sz, [vp, sz]),

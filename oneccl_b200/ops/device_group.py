@@ -115,6 +115,11 @@ class DeviceGroup:
     def set_timeout_ms(self, ms: int):
         _lib.check(self._lib.cclx_dc_set_timeout_ms(self._h, ms))
 
+    def test_sig_skew(self, rank: int):
+        """Test hook: falsify the argument signature that emulated rank `rank` presents in the next
+        collectives (-1 switches it off), to exercise the cross-rank argument check on one GPU."""
+        _lib.check(self._lib.cclx_dc_test_sig_skew(self._h, rank))
+
     def algo_hits(self, coll: str, algo: str) -> int:
         return int(self._lib.cclx_dc_algo_hits(self._h, COLL[coll], GPU_ALGO[algo]))
 

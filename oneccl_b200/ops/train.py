@@ -80,10 +80,12 @@ class FlatAdamW:
     gradient is read in its own dtype (bf16 buckets are never widened in
     memory).  ``max_norm`` > 0 enables clipping by the global norm, which is
     computed on the device and consumed on the device (no host sync).
+    ``device_step=True`` keeps the step number (bias corrections) in a device word that the
+    kernel sequence increments itself, which is what a step replayed from a CUDA graph needs.
     """
 
     def __init__(self, model_flat: torch.Tensor, n_decay: int, lr=3e-4, betas=(0.9, 0.95), eps=1e-8,
-                 weight_decay=0.1, max_norm: float = 1.0):
+                 weight_decay=0.1, max_norm: float = 1.0, device_step: bool = False):
         self.model_flat = model_flat if model_flat.dtype == torch.bfloat16 else None
         self.master = model_flat.detach().to(torch.float32).clone()
         self._fp32_model = model_flat if model_flat.dtype == torch.float32 else None
@@ -93,6 +95,7 @@ class FlatAdamW:
         self.lr, self.betas, self.eps, self.weight_decay, self.max_norm = lr, betas, eps, weight_decay, max_norm
         self.step_count = 0
         self._norm = torch.zeros(1, dtype=torch.float32, device=model_flat.device)
+        self._step_dev = torch.zeros(1, dtype=torch.int32, device=model_flat.device) if device_step else None
 
     def step(self, flat_grad: torch.Tensor, grad_scale: float = 1.0):
         self.step_count += 1
@@ -106,8 +109,9 @@ class FlatAdamW:
             self.master.data_ptr(), flat_grad.data_ptr(), torch_to_ccl(flat_grad.dtype), self.m.data_ptr(),
             self.v.data_ptr(), 0 if self.model_flat is None else self.model_flat.data_ptr(), self.master.numel(),
             self.n_decay, self.lr, self.betas[0], self.betas[1], self.eps, self.weight_decay, self.step_count,
-            grad_scale, self.max_norm, norm_ptr, _stream_ptr()))
-        _bump()
+            grad_scale, self.max_norm, norm_ptr, 0 if self._step_dev is None else self._step_dev.data_ptr(),
+            _stream_ptr()))
+        _bump(1 if self._step_dev is None else 2)
         if self._fp32_model is not None:
             self._fp32_model.copy_(self.master)
 

@@ -4,13 +4,27 @@
 and its gradients into one flat buffer taken from the symmetric heap, cut into
 buckets (default 25 MB, the reference's fusion idea applied to gradients:
 src/fusion/fusion.cpp:145-376 packs small allreduces into one buffer).  Because
-``p.grad`` are views of the bucket, no pack / unpack copy exists: autograd
-accumulates straight into peer-visible memory.  When the last gradient of a
-bucket has been accumulated, the bucket's allreduce is launched on a side
-stream (zero-copy two-shot / NVLS kernel, in place, optionally fused with the
-1/world scale), so communication overlaps the rest of backward.  The optimizer
-(:class:`oneccl_b200.ops.train.FlatAdamW`) then reads the reduced bf16 bucket
-directly and keeps fp32 master weights.
+``p.grad`` are views of the flat buffer, no pack / unpack copy exists: autograd
+accumulates straight into peer-visible memory.
+
+Overlap with backward (the role of the reference's priority queue,
+src/sched/queue/queue.cpp:100-152, played by CUDA stream priorities):
+
+* the flat layout follows the order in which gradients become ready, and a bucket is a
+  plain range of it, so a parameter larger than the bucket size (a tied embedding) is cut
+  into several buckets instead of forming one oversized one;
+* a bucket is reduced as soon as the last parameter overlapping it has its gradient, on a
+  high-priority side stream, in place, with the 1/world scale fused (zero-copy NVLS or peer
+  load kernel);
+* while backward still runs, the allreduce uses a *narrow* grid (``comm_blocks`` thread
+  blocks), which leaves the other SMs to the backward GEMMs instead of time-slicing the
+  whole GPU with them; buckets that are launched when nothing is left to overlap with
+  (the last one, or whatever ``finish`` still finds) use the full-width grid.
+
+``GraphedTrainStep`` captures the whole step (forward, backward with the bucket
+allreduces on their side stream, clipping, AdamW) into one CUDA graph, so that a step costs
+one launch on the host; the collective kernels keep their epoch and staging state in device
+memory, which is what makes the replay valid.
 """
 from __future__ import annotations
 
@@ -22,31 +36,42 @@ import torch.nn as nn
 from ..ops.device_group import DeviceGroup
 from ..ops.train import FlatAdamW
 
+# Thread blocks of a bucket allreduce that overlaps backward.  On 8 x B200 the in-switch reduction
+# reaches most of its bandwidth from 16 blocks of 1024 threads on (8 loads of 16 bytes in flight per
+# thread); more blocks take SMs from backward without finishing the bucket sooner.
+OVERLAP_BLOCKS = 16
+
 
 class _Bucket:
-    __slots__ = ("start", "end", "params", "pending", "event")
+    __slots__ = ("start", "end", "n_params", "pending", "t_ready", "t_start", "t_end")
 
-    def __init__(self, start):
+    def __init__(self, start, end):
         self.start = start
-        self.end = start
-        self.params = []
+        self.end = end
+        self.n_params = 0
         self.pending = 0
-        self.event = None
+        self.t_ready = self.t_start = self.t_end = None
 
 
 class DataParallel:
     def __init__(self, module: nn.Module, group: DeviceGroup, bucket_mb: float = 25.0, scale_in_allreduce: bool = True,
-                 broadcast_from: Optional[int] = 0, algo: str = "auto", comm_blocks: int = 0):
+                 broadcast_from: Optional[int] = 0, algo: str = "auto", comm_blocks: int = -1,
+                 high_priority: bool = True, record_timeline: bool = False, reducer: Optional[str] = None):
         assert not group.emulated_mode or group.world == 1, "DataParallel drives one rank per process"
         self.module = module
         self.group = group
         self.world = group.world
         self.algo = algo
-        self.comm_blocks = comm_blocks
+        # -1: the measured default for overlapped buckets; 0: the kernel's own (full-width) choice
+        self.comm_blocks = OVERLAP_BLOCKS if comm_blocks < 0 else comm_blocks
         self.scale_in_allreduce = scale_in_allreduce and self.world > 1
+        self.record_timeline = record_timeline
+        # None: this library's allreduce kernels.  "nccl": torch.distributed's default (NCCL) group reduces the
+        # buckets instead, everything else unchanged (a comparison arm for the benchmark).
+        self.reducer = reducer
         self.launches = 0
 
-        # ---- flat layout: decay params in reverse registration order, then the rest
+        # ---- flat layout in gradient-ready order: matrices in reverse registration order, then the rest
         decay = [p for p in module.parameters() if p.requires_grad and p.dim() >= 2]
         other = [p for p in module.parameters() if p.requires_grad and p.dim() < 2]
         seen, order = set(), []
@@ -81,67 +106,142 @@ class DataParallel:
             # instead of handing autograd a gradient to add; the callback does the bucket accounting
             p._grad_sink = (p.grad, self._on_grad)
 
-        # ---- buckets over the flat gradient
-        cap = max(1, int(bucket_mb * (1 << 20) / self.flat_grad.element_size()))
+        # ---- buckets: ranges of the flat gradient, cut every `cap` elements inside the matrices and
+        # inside the rest (a parameter may span several buckets; starts stay 16-byte aligned)
+        cap = max(8, int(bucket_mb * (1 << 20) / self.flat_grad.element_size()) // 8 * 8)
+        n_decay_al = (n_decay + 7) // 8 * 8
         self.buckets: List[_Bucket] = []
-        b = _Bucket(0)
+        for lo, hi in ((0, n_decay_al), (n_decay_al, total)):
+            s = lo
+            while s < hi:
+                e = min(s + cap, hi)
+                if hi - e < cap // 4:  # no sliver at the end of a region
+                    e = hi
+                self.buckets.append(_Bucket(s, e))
+                s = e
+        self._buckets_of = {}
         for p, o in zip(order, offs):
-            if b.params and (o + p.numel() - b.start) > cap:
-                b.end = o
-                self.buckets.append(b)
-                b = _Bucket(o)
-            b.params.append(p)
-        b.end = total
-        self.buckets.append(b)
-        self._bucket_of = {}
-        for bi, b in enumerate(self.buckets):
-            for p in b.params:
-                self._bucket_of[id(p)] = bi
-        self.comm_stream = torch.cuda.Stream()
+            mine = [bi for bi, b in enumerate(self.buckets) if b.start < o + p.numel() and o < b.end]
+            self._buckets_of[id(p)] = mine
+            for bi in mine:
+                self.buckets[bi].n_params += 1
+        lo_pri, hi_pri = torch.cuda.Stream.priority_range()
+        self.comm_stream = torch.cuda.Stream(priority=hi_pri if high_priority else lo_pri)
         self._hooks = [p.register_post_accumulate_grad_hook(self._on_grad) for p in order]
         self._armed = False
         self._seen = set()
+        self._unlaunched = 0
+        self.t_step = self.t_backward_end = None
         if broadcast_from is not None and self.world > 1:
             group.broadcast(self.flat_param, root=broadcast_from)
             torch.cuda.synchronize()
 
     # ---- per step -------------------------------------------------------------------
     def zero_grad(self):
+        if self.record_timeline:
+            self.t_step = torch.cuda.Event(enable_timing=True)
+            self.t_step.record()
         self.flat_grad.zero_()
         for b in self.buckets:
-            b.pending = len(b.params)
+            b.pending = b.n_params
+        self._unlaunched = len(self.buckets)
         self._seen = set()
         self._armed = True
 
-    def _launch_bucket(self, b: _Bucket):
-        ev = torch.cuda.Event()
+    def _launch(self, bs: List[_Bucket], overlapped: bool):
+        """One allreduce over the adjacent buckets `bs` (buckets that become ready together travel together)."""
+        timing = self.record_timeline
+        ev = torch.cuda.Event(enable_timing=timing)
         ev.record()
         self.comm_stream.wait_event(ev)
-        seg = self.flat_grad[b.start:b.end]
+        seg = self.flat_grad[bs[0].start:bs[-1].end]
         with torch.cuda.stream(self.comm_stream):
-            self.group.allreduce(seg, seg, algo=self.algo, blocks=self.comm_blocks,
-                                 scale=(1.0 / self.world) if self.scale_in_allreduce else None,
-                                 stream=self.comm_stream)
-        if self.world > 1:
+            t0 = t1 = None
+            if timing:
+                t0 = torch.cuda.Event(enable_timing=True)
+                t0.record()
+            if self.reducer == "nccl":
+                if self.world > 1:
+                    import torch.distributed as dist
+
+                    dist.all_reduce(seg, op=dist.ReduceOp.AVG if self.scale_in_allreduce else dist.ReduceOp.SUM)
+            else:
+                self.group.allreduce(seg, seg, algo=self.algo, blocks=self.comm_blocks if overlapped else 0,
+                                     scale=(1.0 / self.world) if self.scale_in_allreduce else None,
+                                     stream=self.comm_stream)
+            if timing:
+                t1 = torch.cuda.Event(enable_timing=True)
+                t1.record()
+            for b in bs:
+                b.t_ready, b.t_start, b.t_end = ev, t0, t1
+        self._unlaunched -= len(bs)
+        if self.world > 1 and self.reducer is None:
             self.launches += 1
+
+    def _launch_ready(self, ready: List[_Bucket]):
+        if not ready:
+            return
+        # nothing else waits for gradients: backward is over, there is no compute left to share the GPU with
+        overlapped = self._unlaunched > len(ready)
+        run = [ready[0]]
+        for b in ready[1:]:
+            if b.start == run[-1].end:
+                run.append(b)
+            else:
+                self._launch(run, overlapped)
+                run = [b]
+        self._launch(run, overlapped)
 
     def _on_grad(self, p):
         if not self._armed or id(p) in self._seen:
             return  # a parameter counts once per step, whether its layer or autograd reports it
         self._seen.add(id(p))
-        b = self.buckets[self._bucket_of[id(p)]]
-        b.pending -= 1
-        if b.pending == 0:
-            self._launch_bucket(b)
+        ready = []
+        for bi in self._buckets_of[id(p)]:
+            b = self.buckets[bi]
+            b.pending -= 1
+            if b.pending == 0:
+                ready.append(b)
+        self._launch_ready(ready)
 
     def finish(self):
         """Make the compute stream wait for the outstanding bucket allreduces."""
-        for b in self.buckets:
-            if b.pending > 0:  # parameters that received no gradient this step
-                b.pending = 0
-                self._launch_bucket(b)
+        if self.record_timeline:
+            self.t_backward_end = torch.cuda.Event(enable_timing=True)
+            self.t_backward_end.record()
+        late = [b for b in self.buckets if b.pending > 0]  # parameters that received no gradient this step
+        for b in late:
+            b.pending = 0
+        self._launch_ready(late)
         torch.cuda.current_stream().wait_stream(self.comm_stream)
         self._armed = False
+
+    def timeline(self):
+        """Per-bucket times of the last step in ms after its start (``record_timeline=True``): when the
+        bucket's last gradient was ready, when its allreduce started and ended on the side stream, plus
+        the end of backward.  Call after a device synchronisation."""
+        assert self.record_timeline and self.t_step is not None
+        rows = []
+        for i, b in enumerate(self.buckets):
+            rows.append({"bucket": i, "mbytes": (b.end - b.start) * self.flat_grad.element_size() / 2**20,
+                         "ready": self.t_step.elapsed_time(b.t_ready), "start": self.t_step.elapsed_time(b.t_start),
+                         "end": self.t_step.elapsed_time(b.t_end)})
+        return {"backward_end": self.t_step.elapsed_time(self.t_backward_end), "buckets": rows}
+
+    def close(self):
+        """Detach from the module: remove the gradient hooks and give the flat gradient back to the
+        symmetric heap (collective in multi-process mode, like the allocation)."""
+        for hk in self._hooks:
+            hk.remove()
+        self._hooks = []
+        for p in self.module.parameters():
+            if hasattr(p, "_grad_sink"):
+                del p._grad_sink
+            p.grad = None
+        if self.flat_grad is not None:
+            torch.cuda.synchronize()
+            self.group.symm_free(self.flat_grad)
+            self.flat_grad = None
 
     @property
     def grad_scale(self) -> float:
@@ -163,3 +263,55 @@ def train_step(ddp: DataParallel, opt: FlatAdamW, idx: torch.Tensor, targets: to
     ddp.finish()
     opt.step(ddp.flat_grad, grad_scale=ddp.grad_scale)
     return loss
+
+
+class GraphedTrainStep:
+    """``train_step`` captured once into a CUDA graph and replayed.
+
+    The optimizer must keep its step number on the device (``make_optimizer(device_step=True)``).
+    Capture needs the lazily created state of the libraries involved (cuBLAS workspaces, autograd
+    buffers, the column-sum counters) to exist already, so two eager steps run first on a side
+    stream; parameters and optimizer state are put back afterwards, so constructing this object does
+    not train.  ``__call__`` copies the batch into the graph's static input tensors (the copies are
+    ordinary stream work, pinned host tensors are fine), replays the graph and returns the static
+    loss tensor, which the next call overwrites.
+    """
+
+    def __init__(self, ddp: DataParallel, opt: FlatAdamW, idx: torch.Tensor, targets: torch.Tensor, warmup: int = 2):
+        assert opt._step_dev is not None, "GraphedTrainStep needs an optimizer with device_step=True"
+        assert not ddp.record_timeline, "event timing cannot be captured; record the timeline on an eager step"
+        self.ddp, self.opt = ddp, opt
+        dev = ddp.flat_param.device
+        self.idx = torch.empty(idx.shape, dtype=idx.dtype, device=dev)
+        self.targets = torch.empty(targets.shape, dtype=targets.dtype, device=dev)
+        self.idx.copy_(idx)
+        self.targets.copy_(targets)
+        keep = [t.clone() for t in (ddp.flat_param, opt.master, opt.m, opt.v, opt._step_dev)]
+        step_count = opt.step_count
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                train_step(ddp, opt, self.idx, self.targets)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        launches0 = ddp.launches
+        from ..ops import train as train_ops
+
+        count0 = train_ops.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = train_step(ddp, opt, self.idx, self.targets)
+        # kernels of this library that one replay launches (collective kernels, layer and training kernels)
+        self.launches_per_step = (ddp.launches - launches0) + (train_ops.launch_count - count0)
+        for t, k in zip((ddp.flat_param, opt.master, opt.m, opt.v, opt._step_dev), keep):
+            t.copy_(k)
+        opt.step_count = step_count
+        torch.cuda.synchronize()
+
+    def __call__(self, idx: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        self.idx.copy_(idx, non_blocking=True)
+        self.targets.copy_(targets, non_blocking=True)
+        self.graph.replay()
+        self.opt.step_count += 1
+        return self.loss

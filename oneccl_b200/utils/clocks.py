@@ -13,10 +13,11 @@ _QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,
 
 
 class ClockSampler:
-    """Context manager: starts ``nvidia-smi -lms`` for one GPU index, parses the rows on exit."""
+    """Context manager: starts one ``nvidia-smi -lms`` for a GPU index or a list of indices (an empty
+    list samples nothing: in a multi-process job one rank watches every GPU), parses the rows on exit."""
 
-    def __init__(self, gpu_index: int = 0, period_ms: int = 100):
-        self.gpu_index = gpu_index
+    def __init__(self, gpu_index=0, period_ms: int = 200):
+        self.gpu_index = [gpu_index] if isinstance(gpu_index, int) else list(gpu_index)
         self.period_ms = period_ms
         self.rows = []  # (arrival time, csv line)
         self._windows = []  # [begin, end] pairs of time.monotonic(); empty = everything counts
@@ -25,11 +26,11 @@ class ClockSampler:
 
     def __enter__(self):
         exe = shutil.which("nvidia-smi")
-        if exe is None:
+        if exe is None or not self.gpu_index:
             return self
         try:
             self._proc = subprocess.Popen(
-                [exe, f"--query-gpu={_QUERY}", "--format=csv,noheader,nounits", "-i", str(self.gpu_index),
+                [exe, f"--query-gpu={_QUERY}", "--format=csv,noheader,nounits", "-i", ",".join(str(i) for i in self.gpu_index),
                  "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self._proc = None
@@ -44,7 +45,7 @@ class ClockSampler:
         return self
 
     def __exit__(self, *exc):
-        if self._proc is not None:
+        if self._proc is not None and self._proc.poll() is None:
             self._proc.terminate()  # the exact child started above
             try:
                 self._proc.wait(timeout=5)

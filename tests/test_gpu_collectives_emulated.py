@@ -415,6 +415,57 @@ def test_wait_timeout_reports_status():
     g.close()
 
 
+@pytest.mark.parametrize("algo", ["symm", "twoshot"])
+def test_argument_mismatch_between_ranks_is_reported(algo):
+    """Zero-copy kernels apply this rank's offsets and count to the peers' memory, so every rank must pass
+    the same ones.  The first barrier of a kernel compares a signature of those arguments across ranks; a
+    rank that disagrees (here: one emulated rank's signature is falsified) ends the kernel with
+    ST_ARG_MISMATCH before any data is touched, and the communicator works again after the status is cleared."""
+    from oneccl_b200 import CclError
+    from oneccl_b200.ops.device_group import DeviceGroup
+
+    W = 4
+    g = DeviceGroup.emulated(W, heap_bytes=48 << 20, staging_bytes=1 << 20)
+    bufs = g.symm_empty((4096,), dtype=torch.float32)
+    for r, b in enumerate(bufs):
+        b.fill_(float(r + 1))
+    g.test_sig_skew(2)
+    g.allreduce(bufs, bufs, algo=algo)
+    torch.cuda.synchronize()
+    assert all(g.status(r) == 7 for r in range(W)), [g.status(r) for r in range(W)]  # ST_ARG_MISMATCH
+    for r, b in enumerate(bufs):  # nothing was reduced
+        assert torch.equal(b, torch.full_like(b, float(r + 1)))
+    with pytest.raises(CclError, match="buffer kind, offset or count"):
+        g.check()
+    g.clear_status()
+    g.test_sig_skew(-1)
+    g.allreduce(bufs, bufs, algo=algo)
+    torch.cuda.synchronize()
+    g.check()
+    assert torch.equal(bufs[0], torch.full_like(bufs[0], 10.0))
+    g.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("blocks", [1, 2, 5])
+def test_allreduce_symmetric_narrow_grid(group, dtype, blocks):
+    """The few-block form used beside a compute kernel (1024-thread blocks, eight loads in flight per
+    thread in the in-switch variant) against the fp32 sum, on a size that leaves a ragged tail."""
+    W = group.world
+    n = 300_003
+    bufs = group.symm_empty((n,), dtype=dtype)
+    src = _inputs(W, n, dtype, seed=5)
+    for b, s in zip(bufs, src):
+        b.copy_(s)
+    ref = torch.stack([s.double() for s in src]).sum(0) / W
+    group.allreduce(bufs, bufs, blocks=blocks, scale=1.0 / W)
+    torch.cuda.synchronize()
+    group.check()
+    for b in bufs:
+        torch.testing.assert_close(b.double(), ref, **_tol(dtype, W))
+    group.symm_free(bufs)
+
+
 @pytest.mark.parametrize("topk", [1, 2])
 def test_moe_fused_dispatch_and_combine(group, topk):
     """Rows go straight into the owning expert's symmetric buffer and come back by peer loads with

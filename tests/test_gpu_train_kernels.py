@@ -86,3 +86,43 @@ def test_moe_gather_and_combine_kernels():
     ref = (xs[pos].view(T, k, H).float() * w.unsqueeze(-1)).sum(1)
     torch.cuda.synchronize()
     torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_graphed_train_step_matches_eager_steps():
+    """The whole step (forward, backward with bucket launches on the side stream, clipping, AdamW with the
+    step number kept on the device) replayed from one CUDA graph gives the losses and weights of the same
+    steps launched eagerly, and building the graph does not train."""
+    from oneccl_b200.models.gpt2 import GPT2, GPT2Config
+    from oneccl_b200.ops.device_group import DeviceGroup
+    from oneccl_b200.parallel.ddp import DataParallel, GraphedTrainStep, train_step
+
+    cfg = GPT2Config(2, 4, 256, 64, 1000)
+    gen = torch.Generator().manual_seed(3)
+    batches = [(torch.randint(0, cfg.vocab, (4, 64), generator=gen).cuda(),
+                torch.randint(0, cfg.vocab, (4, 64), generator=gen).cuda()) for _ in range(4)]
+    results = []
+    for graphed in (False, True):
+        torch.manual_seed(0)
+        model = GPT2(cfg, fused_ops=True).cuda().to(torch.bfloat16)
+        group = DeviceGroup.emulated(1, heap_bytes=64 << 20, staging_bytes=1 << 20)
+        ddp = DataParallel(model, group, bucket_mb=0.25)
+        assert len(ddp.buckets) > 3
+        opt = ddp.make_optimizer(lr=1e-3, device_step=graphed)
+        if graphed:
+            before = ddp.flat_param.clone()
+            step = GraphedTrainStep(ddp, opt, *batches[0])
+            assert torch.equal(before, ddp.flat_param) and opt.step_count == 0
+            assert step.launches_per_step > 10
+        else:
+            def step(i, t):
+                return train_step(ddp, opt, i, t)
+        losses = [float(step(i, t).detach()) for i, t in batches]
+        torch.cuda.synchronize()
+        results.append((losses, ddp.flat_param.float().clone()))
+        del step
+        ddp.close()
+        group.close()
+    (l0, w0), (l1, w1) = results
+    for a, b in zip(l0, l1):
+        assert abs(a - b) < 1e-3, (l0, l1)
+    torch.testing.assert_close(w0, w1, rtol=0, atol=2e-3)
