@@ -44,7 +44,7 @@ std::list<std::pair<std::unique_ptr<master_sched>, uint64_t>> recycle;
 void purge_recycle() {
     std::lock_guard<std::mutex> lk(recycle_mu);
     for (auto it = recycle.begin(); it != recycle.end();) {
-        if (it->first->ticket_complete(it->second))
+        if (it->first->ticket_retired(it->second))
             it = recycle.erase(it);
         else
             ++it;
@@ -57,7 +57,7 @@ public:
                std::shared_ptr<master_sched> cached = nullptr)
             : m_(m), ticket_(ticket), owned_(std::move(owned)), cached_(std::move(cached)) {}
     ~host_event() override {
-        if (owned_ && !owned_->ticket_complete(ticket_)) {
+        if (owned_ && !owned_->ticket_retired(ticket_)) {
             std::lock_guard<std::mutex> lk(recycle_mu);
             recycle.emplace_back(std::move(owned_), ticket_);
         }
@@ -1085,7 +1085,7 @@ void unordered_on_message(host_comm& comm, unordered_state& st, unordered_state:
 // st.mu is held.  name != nullptr: rank 0 announces it; otherwise post the receive of the next message
 void unordered_post_round(host_comm& comm, unordered_state& st, const std::string* name) {
     // schedules of finished rounds are released a few rounds later, never from their own callback
-    while (st.live.size() > 4 && st.live.front()->m->ticket_complete(1) && !st.live.front()->m->in_flight)
+    while (st.live.size() > 4 && st.live.front()->m->ticket_retired(1) && !st.live.front()->m->in_flight)
         st.live.pop_front();
     const uint64_t k = st.rounds++;
     std::unique_ptr<unordered_state::round> r(new unordered_state::round());

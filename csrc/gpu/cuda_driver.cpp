@@ -42,6 +42,7 @@ const driver_api& driver() {
         LOAD(DeviceGetAttribute);
         LOAD(CtxGetCurrent);
         LOAD(MemGetAddressRange);
+        LOAD(PointerGetAttributes);
         LOAD(MemCreate);
         LOAD(MemRelease);
         LOAD(MemAddressReserve);

@@ -23,6 +23,7 @@ struct driver_api {
     decltype(&cuDeviceGetAttribute) DeviceGetAttribute = nullptr;
     decltype(&cuCtxGetCurrent) CtxGetCurrent = nullptr;
     decltype(&cuMemGetAddressRange) MemGetAddressRange = nullptr;
+    decltype(&cuPointerGetAttributes) PointerGetAttributes = nullptr;
     decltype(&cuMemCreate) MemCreate = nullptr;
     decltype(&cuMemRelease) MemRelease = nullptr;
     decltype(&cuMemAddressReserve) MemAddressReserve = nullptr;

@@ -174,7 +174,7 @@ __device__ __forceinline__ bool wait_flag_sys(const comm_dev& c, const uint32_t*
 // block before the call are visible to the peers' threads after their call
 // returns (bar.sync + release.sys / acquire.sys + bar.sync).
 //
-// `sig` (non-zero, first barrier of a kernel, block 0 only) is a hash of the arguments that must be
+// `sig` (non-zero; used by the first barrier of a kernel) is a hash of the arguments that must be
 // equal on every rank because the kernel applies them to the peers' memory (buffer kind, heap offsets,
 // count).  Every rank leaves its value in the peers' signature words before it raises its flag and
 // compares the peers' values with its own once their flags have arrived; a difference ends the kernel
@@ -189,7 +189,7 @@ __device__ __forceinline__ bool peer_barrier(const comm_dev& c, block_sync& s, u
     const uint32_t target = s.epoch + s.used;
     if (s.ok && threadIdx.x < (unsigned)c.world) {
         const int p = threadIdx.x;
-        const bool check = sig != 0 && blockIdx.x == 0;
+        const bool check = sig != 0 && s.used == 1; // every block checks: all of them write the same word
         const int slot = SIG_BASE_WORD + (int)(target % SIG_SLOTS) * MAX_RANKS;
         if (check)
             c.p2p_flags[p][slot + c.rank] = sig;

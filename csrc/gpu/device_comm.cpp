@@ -4,6 +4,7 @@
 
 #include "core/env.hpp"
 #include "core/log.hpp"
+#include "gpu/buffer_exchange.hpp"
 #include "gpu/cuda_driver.hpp"
 
 namespace cclx {
@@ -41,6 +42,8 @@ void device_comm::init(bootstrap_if& bs) {
     threads_ = env.cuda_block_threads;
     heap_.create(bs, env.symm_heap_bytes, env.tmp_buf_bytes, env.ipc_exchange, env.nvls);
     build_tables();
+    if (env.auto_register && world_ > 1)
+        exch_.reset(new buffer_exchange(*this, bs));
     bs.barrier();
 }
 
@@ -119,6 +122,7 @@ void device_comm::destroy() {
     if (!table_dev_)
         return;
     cudaDeviceSynchronize();
+    exch_.reset();
     for (auto& r : regs_)
         for (void* m : r.opened)
             cudaIpcCloseMemHandle(m);

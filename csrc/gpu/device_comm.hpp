@@ -40,6 +40,8 @@ enum gpu_algo : int {
 const char* gpu_algo_name(int a);
 int gpu_algo_from_name(const std::string& s); // -1 when unknown
 
+class buffer_exchange;
+
 class device_comm {
 public:
     device_comm() = default;
@@ -92,6 +94,9 @@ public:
     // pointer of rank q's buffer of registration `id`, as mapped in this process
     char* user_base(int id, int q) const { return regs_[id].base[q]; }
 
+    // automatic sharing of ordinary buffers (multi-process mode with CCL_CUDA_AUTO_REGISTER=1), else null
+    buffer_exchange* exchange() const { return exch_.get(); }
+
     // test hook: rank + 1 whose argument signature is falsified in the next collectives (0 = none), so that
     // the cross-rank argument check can be exercised with all ranks emulated on one GPU
     int test_sig_skew = 0;
@@ -108,6 +113,7 @@ private:
         std::vector<void*> opened; // IPC mappings this registration holds (closed on deregistration)
     };
     std::vector<user_reg> regs_;
+    std::shared_ptr<buffer_exchange> exch_; // shared_ptr: the type is incomplete in this header
     bootstrap_if* bs_ = nullptr;
     int rank_ = 0, world_ = 0;
     bool emulated_ = false;

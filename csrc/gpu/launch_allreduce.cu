@@ -92,10 +92,8 @@ void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, i
     // zero-copy needs both buffers of every rank in the symmetric heap or in a registered allocation,
     // at equal offsets; the in-switch reduction needs both in the heap (the multicast window covers only it)
     zc_view vin, vout;
-    if (dt_in == dt_out) {
-        vin = zero_copy_view(dc, ra, false, bytes);
-        vout = zero_copy_view(dc, ra, true, bytes);
-    }
+    if (dt_in == dt_out && W > 1)
+        zero_copy_views(dc, ra, true, bytes, true, bytes, vin, vout);
     const bool symmetric = vin.ok && vout.ok;
     const bool in_heap = symmetric && !vin.registered && !vout.registered;
     const size_t in_off = vin.off, out_off = vout.off;

@@ -10,6 +10,7 @@
 #include "core/log.hpp"
 #include "gpu/cuda_driver.hpp"
 #include "gpu/device/collectives.cuh"
+#include "gpu/buffer_exchange.hpp"
 #include "gpu/device_comm.hpp"
 
 namespace cclx {
@@ -77,9 +78,11 @@ inline int pick_blocks(const device_comm& dc, size_t units, size_t units_per_blo
 // the symmetric heap on every rank, or the same offset of one registered allocation on every rank.
 struct zc_view {
     bool ok = false;
-    bool registered = false;
+    bool registered = false; // peers are reached through per-rank pointers (not heap base + one offset)
     size_t off = 0; // heap offset, or offset inside the registration
     int id = -1;
+    bool shared = false; // the per-rank pointers came from the automatic buffer exchange: ptr[]
+    char* ptr[dev::MAX_RANKS] = {};
 };
 
 inline zc_view zero_copy_view(const device_comm& dc, const dev::rank_args* ra, bool recv_side, size_t bytes) {
@@ -121,13 +124,55 @@ inline zc_view zero_copy_view(const device_comm& dc, const dev::rank_args* ra, b
     return v;
 }
 
+// rank q's buffer of a registered / automatically shared view, as mapped in this process
+inline char* view_ptr(const device_comm& dc, const zc_view& v, int q) {
+    return v.shared ? v.ptr[q] : dc.user_base(v.id, q) + v.off;
+}
+
+// Both sides of a collective at once.  Small messages decide locally (symmetric heap or explicit
+// registration, as zero_copy_view).  From CCL_CUDA_AUTO_REGISTER_MIN_BYTES on, in multi-process mode, the
+// ranks tell one another where their buffers live (buffer_exchange): ordinary cudaMalloc memory, e.g. a
+// torch tensor, then takes the zero-copy kernels as well, offsets may differ between ranks, and all ranks
+// reach the same verdict (zero-copy only if every rank's buffer can be shared).  The sizes are the same on
+// every rank, so either all ranks enter the exchange or none does.
+inline void zero_copy_views(device_comm& dc, const dev::rank_args* ra, bool want_in, size_t in_bytes, bool want_out,
+                            size_t out_bytes, zc_view& vin, zc_view& vout) {
+    if (want_in)
+        vin = zero_copy_view(dc, ra, false, in_bytes);
+    if (want_out)
+        vout = zero_copy_view(dc, ra, true, out_bytes);
+    buffer_exchange* bx = dc.exchange();
+    const size_t big = std::max(want_in ? in_bytes : 0, want_out ? out_bytes : 0);
+    if (dc.emulated() || !bx || big < env_data::get().auto_register_min)
+        return;
+    shared_view in, out;
+    bx->exchange(want_in ? ra[0].send : nullptr, in_bytes, want_out ? ra[0].recv : nullptr, out_bytes, in, out);
+    auto apply = [&](const shared_view& sv, zc_view& v) {
+        v = zc_view();
+        if (!sv.ok)
+            return;
+        v.ok = true;
+        if (sv.heap_equal) {
+            v.off = sv.heap_off;
+            return;
+        }
+        v.registered = v.shared = true;
+        for (int q = 0; q < dc.world(); q++)
+            v.ptr[q] = sv.ptr[q];
+    };
+    if (want_in)
+        apply(in, vin);
+    if (want_out)
+        apply(out, vout);
+}
+
 // peers' addresses of a registered buffer into the argument block
 inline void fill_registered(const device_comm& dc, dev::coll_args& a, const zc_view& v, bool recv_side) {
     for (int q = 0; q < dc.world(); q++) {
         if (recv_side)
-            a.reg_out[q] = dc.user_base(v.id, q) + v.off;
+            a.reg_out[q] = view_ptr(dc, v, q);
         else
-            a.reg_in[q] = dc.user_base(v.id, q) + v.off;
+            a.reg_in[q] = view_ptr(dc, v, q);
     }
     a.flags |= recv_side ? dev::CF_REG_OUT : dev::CF_REG_IN;
 }

@@ -31,9 +31,9 @@ void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t rc,
     a.do_scale = o.do_scale ? 1 : 0;
 
     // send buffers in the symmetric heap or in a registered allocation: pull (or NVLS) without staging
-    zc_view vin;
+    zc_view vin, vnone;
     if (dt_in == dt_out)
-        vin = zero_copy_view(dc, ra, false, rc * esz * W);
+        zero_copy_views(dc, ra, true, rc * esz * W, false, 0, vin, vnone);
     const bool symmetric = vin.ok;
     const size_t in_off = vin.off;
     (void)entries;
@@ -193,9 +193,9 @@ void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_o
     dev::coll_args a{};
 
     // equal 16-byte-multiple blocks into a symmetric or registered recv buffer: direct stores
-    zc_view vout;
+    zc_view vout, vnone;
     if (W > 1)
-        vout = zero_copy_view(dc, ra, true, total);
+        zero_copy_views(dc, ra, false, 0, true, total, vnone, vout);
     bool symm = vout.ok;
     const size_t out_off = vout.off;
     for (int p = 0; p < W && symm; p++)
@@ -234,7 +234,7 @@ void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_o
             const int r = dc.emulated() ? e : dc.rank();
             for (int k = 1; k < W; k++) {
                 const int p = (r + k) % W;
-                const char* peer = vout.registered ? dc.user_base(vout.id, p) + vout.off : dc.heap().base(p) + out_off;
+                const char* peer = vout.registered ? view_ptr(dc, vout, p) : dc.heap().base(p) + out_off;
                 CUDA_CHECK(cudaMemcpyAsync((char*)ra[e].recv + (size_t)p * maxb, peer + (size_t)p * maxb, maxb,
                                            cudaMemcpyDeviceToDevice, st));
             }
@@ -332,9 +332,9 @@ void launch_alltoallv(device_comm& dc, const dev::rank_args* ra, const launch_op
     }
     // the direct path must be chosen by every rank or by none: it depends only on the block size and
     // on recv being a symmetric or registered allocation, which is a collective property
-    zc_view vout;
+    zc_view vout, vnone;
     if (symm && uniform)
-        vout = zero_copy_view(dc, ra, true, b * W);
+        zero_copy_views(dc, ra, false, 0, true, b * W, vnone, vout);
     symm = symm && vout.ok;
     const size_t out_off = vout.off;
     symm = symm && uniform;

@@ -383,8 +383,13 @@ void sched_queue::dump(std::string& out) {
 static void finish_sched(sched* s, const std::string* err) {
     request* r = s->req;
     if (err) {
-        if (r)
+        // The failed partial has left its queue like a finished one: it is counted, so that the launch is
+        // retired (and its master may be destroyed or relaunched) only when every sibling partial, possibly
+        // still queued on another worker, has left too.  Waiters are released at once by the error flag.
+        if (r) {
             r->set_error(*err);
+            r->part_done();
+        }
         return;
     }
     if (env_data::get().sched_profile) {
@@ -626,7 +631,7 @@ uint64_t executor::start(master_sched* m, uint64_t new_id) {
     CCL_THROW_IF_NOT(!workers_.empty(), "executor is not running");
     if (!m->req().on_last) {
         m->req().on_last = [this, m] {
-            if (m->user_complete)
+            if (m->user_complete && !m->req().has_error())
                 m->user_complete();
             bool again = false;
             uint64_t next_id = KEEP_ID;

@@ -171,6 +171,9 @@ public:
     // launch tickets: launch k is complete when done >= k
     std::atomic<uint64_t> issued{ 0 }, done{ 0 };
     bool ticket_complete(uint64_t t) const { return done.load(std::memory_order_acquire) >= t || req_.has_error(); }
+    // every partial of launch t has left the workers' queues: only then may the object go away (a failed
+    // launch is complete for its waiter before that)
+    bool ticket_retired(uint64_t t) const { return done.load(std::memory_order_acquire) >= t; }
     // cached-schedule relaunch protocol (reference sched_restart_manager.cpp:19-146):
     // a launch requested while the schedule runs is queued and started by the
     // worker that completes the current one

@@ -19,7 +19,7 @@ src/sched/queue/queue.cpp:100-152, played by CUDA stream priorities):
 * while backward still runs, the allreduce uses a *narrow* grid (``comm_blocks`` thread
   blocks), which leaves the other SMs to the backward GEMMs instead of time-slicing the
   whole GPU with them; buckets that are launched when nothing is left to overlap with
-  (the last one, or whatever ``finish`` still finds) use the full-width grid.
+  (the last ones, or whatever ``finish`` still finds) use ``tail_blocks``.
 
 ``GraphedTrainStep`` captures the whole step (forward, backward with the bucket
 allreduces on their side stream, clipping, AdamW) into one CUDA graph, so that a step costs
@@ -36,10 +36,14 @@ import torch.nn as nn
 from ..ops.device_group import DeviceGroup
 from ..ops.train import FlatAdamW
 
-# Thread blocks of a bucket allreduce that overlaps backward.  On 8 x B200 the in-switch reduction
-# reaches most of its bandwidth from 16 blocks of 1024 threads on (8 loads of 16 bytes in flight per
-# thread); more blocks take SMs from backward without finishing the bucket sooner.
-OVERLAP_BLOCKS = 16
+# Thread blocks of a bucket allreduce.  Measured with oneccl_b200.benchmarks.ddp_overlap_bench on B200s:
+# the in-switch (NVLS) reduction of a 25 MB bucket among 8 GPUs is as fast from 4 to 8 blocks of 1024 threads
+# (8 loads of 16 bytes in flight per thread) as from any wider grid, 80 us, and 100 MB are faster narrow
+# (0.24 ms) than GPU-wide (0.29 ms), so every bucket uses the narrow grid and the SMs stay with backward.
+# The peer-load form that two GPUs use needs its loads spread over more SMs: 32 blocks while backward
+# runs, the full width for the last buckets of a step.
+NVLS_BLOCKS = 8
+PEER_OVERLAP_BLOCKS = 32
 
 
 class _Bucket:
@@ -62,8 +66,10 @@ class DataParallel:
         self.group = group
         self.world = group.world
         self.algo = algo
-        # -1: the measured default for overlapped buckets; 0: the kernel's own (full-width) choice
-        self.comm_blocks = OVERLAP_BLOCKS if comm_blocks < 0 else comm_blocks
+        # -1: the measured default; 0: the kernel's own (full-width) choice
+        nvls = group.nvls and group.world >= 3
+        self.comm_blocks = (NVLS_BLOCKS if nvls else PEER_OVERLAP_BLOCKS) if comm_blocks < 0 else comm_blocks
+        self.tail_blocks = self.comm_blocks if nvls else 0
         self.scale_in_allreduce = scale_in_allreduce and self.world > 1
         self.record_timeline = record_timeline
         # None: this library's allreduce kernels.  "nccl": torch.distributed's default (NCCL) group reduces the
@@ -166,7 +172,7 @@ class DataParallel:
 
                     dist.all_reduce(seg, op=dist.ReduceOp.AVG if self.scale_in_allreduce else dist.ReduceOp.SUM)
             else:
-                self.group.allreduce(seg, seg, algo=self.algo, blocks=self.comm_blocks if overlapped else 0,
+                self.group.allreduce(seg, seg, algo=self.algo, blocks=self.comm_blocks if overlapped else self.tail_blocks,
                                      scale=(1.0 / self.world) if self.scale_in_allreduce else None,
                                      stream=self.comm_stream)
             if timing:

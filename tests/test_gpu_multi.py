@@ -177,6 +177,91 @@ def _fused(comm):
     return True
 
 
+def _auto_shared(comm):
+    """Ordinary torch tensors, at a different offset of their allocation on every rank and re-allocated between
+    iterations (the reference's dynamic-pointer mode, tests/functional/test_impl.hpp:326-372): from 256 KiB on
+    the ranks exchange allocation handles by themselves and the zero-copy kernels run."""
+    r, W = comm.rank, comm.size
+    torch.cuda.set_device(r)
+    dev = torch.device("cuda", r)
+    g = comm.device_group
+    n = 1 << 19  # 2 MiB of float32
+    keep = []
+    for it in range(4):
+        pad = 16 * (r + it)
+        raw = torch.empty(n + 4096, device=dev)
+        x = raw[pad:pad + n]
+        x.fill_(float(r + 1))
+        before = g.algo_hits("allreduce", "symm")
+        comm.allreduce(x).wait()
+        torch.cuda.synchronize()
+        assert g.algo_hits("allreduce", "symm") == before + 1, "ordinary buffers did not take the zero-copy kernel"
+        assert torch.all(x == W * (W + 1) / 2)
+        # reduce_scatter: zero-copy on the send side; allgather / alltoall: on the recv side
+        per = 1 << 17
+        send = torch.arange(per * W, device=dev, dtype=torch.float32) + r
+        out = torch.empty(per + 64, device=dev)[32 + 4 * r:32 + 4 * r + per]
+        comm.reduce_scatter(send, out).wait()
+        ref = torch.arange(per * W, dtype=torch.float32)[r * per:(r + 1) * per] * W + sum(range(W))
+        assert torch.equal(out.cpu(), ref)
+        gathered = torch.empty(per * W + 256, device=dev)[4 * r:4 * r + per * W]
+        comm.allgather(out, gathered).wait()
+        assert torch.equal(gathered.cpu(), torch.arange(per * W, dtype=torch.float32) * W + sum(range(W)))
+        a = (torch.arange(per * W, dtype=torch.float32) + 1e6 * r).to(dev)
+        b = torch.empty(per * W + 128, device=dev)[8 * r:8 * r + per * W]
+        comm.alltoall(a, b).wait()
+        refb = torch.cat([torch.arange(per, dtype=torch.float32) + per * r + 1e6 * p for p in range(W)])
+        assert torch.equal(b.cpu(), refb)
+        if it % 2 == 0:
+            keep.append(raw)  # some allocations stay, some are freed and their addresses reused
+        del raw, x, send, out, gathered, a, b
+    torch.cuda.synchronize()
+    g.check()
+    return True
+
+
+@needs2
+def test_ordinary_buffers_are_shared_automatically():
+    assert all(run_ranks(_auto_shared, _world(), env=ENV, timeout=300))
+
+
+def _mismatch(comm):
+    """Two ranks pass different offsets of a symmetric buffer to a small (locally decided) zero-copy allreduce:
+    the kernels notice at their first barrier and report ST_ARG_MISMATCH instead of reducing the wrong bytes."""
+    from oneccl_b200 import CclError
+
+    r = comm.rank
+    torch.cuda.set_device(r)
+    g = comm.device_group
+    s = g.symm_empty((4096,), dtype=torch.float32)
+    s.fill_(float(r + 1))
+    torch.cuda.synchronize()
+    g.barrier()
+    view = s[16 * r:16 * r + 1000]
+    g.allreduce(view, view, algo="symm")
+    torch.cuda.synchronize()
+    code = g.status()
+    raised = False
+    try:
+        g.check()
+    except CclError:
+        raised = True
+    untouched = bool(torch.all(s == float(r + 1)))
+    g.clear_status()
+    g.barrier()
+    g.allreduce(s, s, algo="symm")
+    torch.cuda.synchronize()
+    g.check()
+    return code, raised, untouched, float(s[0])
+
+
+@needs2
+def test_unequal_symmetric_offsets_are_reported():
+    res = run_ranks(_mismatch, 2, env=ENV, timeout=120)
+    for code, raised, untouched, total in res:
+        assert code == 7 and raised and untouched and total == 3.0, res
+
+
 @needs2
 def test_fused_gemm_real():
     assert all(run_ranks(_fused, _world(), env=ENV, timeout=300))
