@@ -376,6 +376,31 @@ vector_class<communicator> split_communicators(const vector_class<pair_class<com
     return out;
 }
 
+namespace {
+event coalesced(const vector_class<void*>& bufs, const vector_class<size_t>& counts, datatype dtype, reduction rtype,
+                const communicator& comm, const stream* s, const allreduce_attr& attr) {
+    if (comm.is_stub())
+        return event(cclx::make_completed_event());
+    return v1::guarded([&] {
+        CCL_THROW_IF_NOT(comm.impl() != nullptr, "communicator is not initialised");
+        cclx::coll_attr a = v1::to_attr(attr);
+        std::vector<const void*> send(bufs.begin(), bufs.end());
+        const bool device = s && s->is_device();
+        return event(cclx::coll_allreduce_coalesced(*comm.impl(), send, bufs, counts, (int)dtype, (int)rtype, a,
+                                                    device ? (void*)s->get_native() : nullptr, device));
+    });
+}
+} // namespace
+
+event allreduce_coalesced(const vector_class<void*>& bufs, const vector_class<size_t>& counts, datatype dtype,
+                          reduction rtype, const communicator& comm, const stream& s, const allreduce_attr& attr) {
+    return coalesced(bufs, counts, dtype, rtype, comm, &s, attr);
+}
+event allreduce_coalesced(const vector_class<void*>& bufs, const vector_class<size_t>& counts, datatype dtype,
+                          reduction rtype, const communicator& comm, const allreduce_attr& attr) {
+    return coalesced(bufs, counts, dtype, rtype, comm, nullptr, attr);
+}
+
 } // namespace preview
 
 namespace v1 {

@@ -291,10 +291,17 @@ CCLX_API int cclx_transpose_blocks(const void* in, void* out, int rows, int cols
     return capi::guard([&] { launch_transpose_blocks(in, out, rows, cols, block_bytes, (cudaStream_t)stream); });
 }
 
-CCLX_API int cclx_pack(const void* const* ptrs_dev, const size_t* offs_dev, int n, void* fused, int unpack,
-                       size_t max_tensor_bytes, void* stream) {
-    return capi::guard(
-        [&] { launch_pack(ptrs_dev, offs_dev, n, fused, unpack != 0, max_tensor_bytes, (cudaStream_t)stream); });
+// fused small-message allreduce: n tensors per entry (tensor-major pointer arrays), one pack kernel, one
+// zero-copy allreduce on the fused symmetric buffer, one unpack kernel
+CCLX_API int cclx_dc_allreduce_fused(void* h, const void* const* send, void* const* recv, const size_t* counts, int n,
+                                     int dt, int op, float scale, int do_scale, void* stream) {
+    return capi::guard([&] {
+        launch_allreduce_fused(*(device_comm*)h, send, recv, counts, n, dt, op, make_opts(ga_auto, 0, scale, do_scale),
+                               (cudaStream_t)stream);
+    });
+}
+CCLX_API unsigned long long cclx_dc_fused_batches(void* h) {
+    return ((device_comm*)h)->fuse().batches;
 }
 
 // ---- tcgen05 GEMM, plain and fused with a collective ------------------------------

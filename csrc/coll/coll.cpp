@@ -77,6 +77,8 @@ private:
     std::shared_ptr<master_sched> cached_; // a cached schedule may leave the cache while this event lives
 };
 
+thread_local bool tl_no_fusion = false; // set while coll_allreduce_coalesced issues its buffers one by one
+
 class cuda_event_impl : public event_impl {
 public:
     cuda_event_impl(gpu::device_comm* dc, cudaStream_t st) : dc_(dc) {
@@ -1162,6 +1164,17 @@ event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr) {
             if (d)
                 d->wait();
         event_ptr ev;
+        if (env.fusion && !tl_no_fusion && env.cuda_kernels && same_node(comm) && comm.size() > 1) {
+            // small allreduces of one stream are packed into one launch sequence; any other device operation of
+            // this communicator first sends the waiting batch on its way (operation order)
+            if (p.ctype == coll_allreduce && !sync && p.deps.empty()) {
+                event_ptr fe = fusion_manager::get().try_add(comm, p, attr);
+                if (fe)
+                    return fe;
+            }
+            else
+                fusion_manager::get().flush(&comm);
+        }
         if (env.cuda_kernels && same_node(comm))
             ev = device_coll(comm, p, attr);
         else if (hier_allreduce_possible(comm, p, attr))
@@ -1196,7 +1209,7 @@ event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr) {
     }
 
     // ---- fusion of small allreduces; anything else first cuts the pending batch (operation order)
-    if (env.fusion) {
+    if (env.fusion && !tl_no_fusion) {
         if (p.ctype == coll_allreduce && !sync) {
             event_ptr fe = fusion_manager::get().try_add(comm, p, attr);
             if (fe)
@@ -1218,6 +1231,76 @@ event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr) {
     if (sync)
         ev->wait();
     return ev;
+}
+
+// ---- several buffers, one operation ----------------------------------------------------------------
+namespace {
+class multi_event : public event_impl {
+public:
+    explicit multi_event(std::vector<event_ptr> parts) : parts_(std::move(parts)) {}
+    void wait() override {
+        for (auto& e : parts_)
+            e->wait();
+    }
+    bool test() override {
+        for (auto& e : parts_)
+            if (!e->test())
+                return false;
+        return true;
+    }
+
+private:
+    std::vector<event_ptr> parts_;
+};
+} // namespace
+
+event_ptr coll_allreduce_coalesced(host_comm& comm, const std::vector<const void*>& send, const std::vector<void*>& recv,
+                                   const std::vector<size_t>& counts, int dtype, int reduction, const coll_attr& attr,
+                                   void* stream, bool device) {
+    const env_data& env = env_data::get();
+    CCL_THROW_IF_NOT(send.size() == recv.size() && send.size() == counts.size(), "buffer and count lists differ in length");
+    if (send.empty())
+        return make_completed_event();
+    const bool fused = device && env.cuda_kernels && same_node(comm) && comm.size() > 1 && attr.out_dtype < 0 &&
+                       !attr.reduction_fn && reduction != red_custom && dtype <= dt_last_predefined && attr.gpu_algo.empty();
+    if (fused) {
+        if (!comm.has_device()) {
+            cudaPointerAttributes pa;
+            if (cudaPointerGetAttributes(&pa, recv[0]) == cudaSuccess && pa.type == cudaMemoryTypeDevice)
+                CUDA_CHECK(cudaSetDevice(pa.device));
+            else
+                (void)cudaGetLastError();
+        }
+        gpu::device_comm* dc = comm.device();
+        CUDA_CHECK(cudaSetDevice(dc->device_id()));
+        stats().calls[coll_allreduce] += send.size();
+        stats().device_calls[coll_allreduce] += send.size();
+        gpu::launch_opts o;
+        o.scale = attr.scale;
+        o.do_scale = attr.do_scale;
+        gpu::launch_allreduce_fused(*dc, send.data(), recv.data(), counts.data(), (int)send.size(), dtype, reduction, o,
+                                    (cudaStream_t)stream);
+        return std::make_shared<cuda_event_impl>(dc, (cudaStream_t)stream);
+    }
+    std::vector<event_ptr> parts;
+    struct no_fusion_scope { // the buffers of one coalesced call are not queued again behind one another
+        bool prev = tl_no_fusion;
+        no_fusion_scope() { tl_no_fusion = true; }
+        ~no_fusion_scope() { tl_no_fusion = prev; }
+    } scope;
+    for (size_t k = 0; k < send.size(); k++) {
+        coll_param p;
+        p.ctype = coll_allreduce;
+        p.send_buf = send[k];
+        p.recv_buf = recv[k];
+        p.count = counts[k];
+        p.dtype = dtype;
+        p.reduction = reduction;
+        p.stream = stream;
+        p.device = device;
+        parts.push_back(coll_create(comm, p, attr));
+    }
+    return std::make_shared<multi_event>(std::move(parts));
 }
 
 // ---- group ------------------------------------------------------------------------------------

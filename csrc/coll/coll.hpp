@@ -62,6 +62,15 @@ struct coll_param {
 // entry point used by the API layer
 event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr);
 
+// Allreduce of several buffers as one operation (send[k] -> recv[k], counts[k] elements of `dtype`).  Device
+// buffers of a single node travel as one fused sequence: pack kernel, one allreduce on a buffer of the
+// symmetric heap, unpack kernel (gpu::launch_allreduce_fused).  Anything else is issued buffer by buffer;
+// the returned event covers all of them.  Used by the fusion manager for device operations and by the
+// torch backend's allreduce_coalesced.
+event_ptr coll_allreduce_coalesced(host_comm& comm, const std::vector<const void*>& send, const std::vector<void*>& recv,
+                                   const std::vector<size_t>& counts, int dtype, int reduction, const coll_attr& attr,
+                                   void* stream, bool device);
+
 // group API (reference src/coll/group/group.cpp:19-73): only send/recv may be
 // issued between start and end; they are posted together at group_end
 void group_start();

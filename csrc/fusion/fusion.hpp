@@ -37,6 +37,8 @@ private:
         host_comm* comm;
         coll_param p;
         std::shared_ptr<fused_event> ev;
+        float scale = 1.0f; // device operations: fused output scale of the operation
+        bool do_scale = false;
     };
     void launch(std::vector<pending>& batch);
     std::mutex mu_;

@@ -1223,7 +1223,8 @@ __global__ void __launch_bounds__(1024) reduce_local_kernel(const T* in, T* inou
 
 struct pack_table {
     const void* const* ptrs; // device array of n tensor pointers
-    const size_t* offs; // device array of n+1 byte offsets into the fused buffer (16-byte aligned)
+    const size_t* offs; // device array of n byte offsets into the fused buffer (16-byte aligned)
+    const size_t* lens; // device array of n tensor sizes in bytes
     int n;
 };
 
@@ -1231,7 +1232,7 @@ template <bool UNPACK>
 __global__ void __launch_bounds__(512) pack_kernel(pack_table t, char* fused) {
     // blockIdx.y walks tensors, blockIdx.x strides inside one tensor
     for (int k = blockIdx.y; k < t.n; k += gridDim.y) {
-        const size_t bytes = t.offs[k + 1] - t.offs[k];
+        const size_t bytes = t.lens[k];
         size_t lo, hi;
         split_range((bytes + 15) >> 4, gridDim.x, blockIdx.x, lo, hi);
         const size_t l = lo << 4, h = (hi << 4) < bytes ? (hi << 4) : bytes;

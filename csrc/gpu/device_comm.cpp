@@ -123,6 +123,12 @@ void device_comm::destroy() {
         return;
     cudaDeviceSynchronize();
     exch_.reset();
+    if (fuse_.tab_host) {
+        cudaFreeHost(fuse_.tab_host);
+        for (auto& e : fuse_.used)
+            cudaEventDestroy(e);
+        fuse_ = fuse_state();
+    }
     for (auto& r : regs_)
         for (void* m : r.opened)
             cudaIpcCloseMemHandle(m);

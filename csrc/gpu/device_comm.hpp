@@ -94,6 +94,21 @@ public:
     // pointer of rank q's buffer of registration `id`, as mapped in this process
     char* user_base(int id, int q) const { return regs_[id].base[q]; }
 
+    // state of the fused small-message allreduce (launch_allreduce_fused): one buffer in the symmetric heap
+    // that the tensors of a batch are packed into, and a ring of pinned pointer / offset tables that the
+    // pack kernels read while the host already fills the next one
+    struct fuse_state {
+        size_t buf_off = (size_t)-1; // heap offset of the fused buffer
+        size_t buf_bytes = 0;
+        static constexpr int SLOTS = 8, MAX_TENSORS = 1024;
+        char* tab_host = nullptr; // SLOTS x entries x MAX_TENSORS x (pointer, offset, byte length)
+        char* tab_dev = nullptr;
+        cudaEvent_t used[SLOTS] = {};
+        int next = 0;
+        unsigned long long batches = 0, tensors = 0;
+    };
+    fuse_state& fuse() { return fuse_; }
+
     // automatic sharing of ordinary buffers (multi-process mode with CCL_CUDA_AUTO_REGISTER=1), else null
     buffer_exchange* exchange() const { return exch_.get(); }
 
@@ -113,6 +128,7 @@ private:
         std::vector<void*> opened; // IPC mappings this registration holds (closed on deregistration)
     };
     std::vector<user_reg> regs_;
+    fuse_state fuse_;
     std::shared_ptr<buffer_exchange> exch_; // shared_ptr: the type is incomplete in this header
     bootstrap_if* bs_ = nullptr;
     int rank_ = 0, world_ = 0;
@@ -170,8 +186,16 @@ void launch_wait_unset_flag(device_comm& dc, cudaStream_t st);
 // local helpers
 void launch_reduce_local(const void* in, void* inout, size_t count, int dt, int op, cudaStream_t st);
 void launch_transpose_blocks(const void* in, void* out, int rows, int cols, size_t block_bytes, cudaStream_t st);
-void launch_pack(const void* const* ptrs_dev, const size_t* offs_dev, int n, void* fused, bool unpack,
-                 size_t max_tensor_bytes, cudaStream_t st);
+void launch_pack(const void* const* ptrs_dev, const size_t* offs_dev, const size_t* lens_dev, int n, void* fused,
+                 bool unpack, size_t max_tensor_bytes, cudaStream_t st);
+
+// Small-message fusion on the device (the reference's fusion manager builds copy-in -> allreduce -> copy-out
+// schedules on the host, src/fusion/fusion.cpp:145-376): `n` tensors per rank are packed into one buffer of
+// the symmetric heap by one kernel, reduced by ONE zero-copy allreduce and unpacked by one kernel.  `send` and
+// `recv` hold n pointers per entry, tensor-major ([k * entries + e]; entries = world() in emulation mode, else
+// 1); `counts` n element counts.  Tensors that do not fit the fused buffer are reduced one by one.
+void launch_allreduce_fused(device_comm& dc, const void* const* send, void* const* recv, const size_t* counts, int n,
+                            int dt, int op, const launch_opts& o, cudaStream_t st);
 
 int selected_allreduce_algo(const device_comm& dc, size_t bytes, bool symmetric, int dt, int op);
 

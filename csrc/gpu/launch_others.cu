@@ -514,11 +514,11 @@ void launch_transpose_blocks(const void* in, void* out, int rows, int cols, size
     CUDA_CHECK(cudaGetLastError());
 }
 
-void launch_pack(const void* const* ptrs_dev, const size_t* offs_dev, int n, void* fused, bool unpack,
-                 size_t max_tensor_bytes, cudaStream_t st) {
+void launch_pack(const void* const* ptrs_dev, const size_t* offs_dev, const size_t* lens_dev, int n, void* fused,
+                 bool unpack, size_t max_tensor_bytes, cudaStream_t st) {
     if (n <= 0)
         return;
-    dev::pack_table t{ ptrs_dev, offs_dev, n };
+    dev::pack_table t{ ptrs_dev, offs_dev, lens_dev, n };
     const int bx = (int)std::max<size_t>(1, std::min<size_t>(max_tensor_bytes / (64 << 10) + 1, 32));
     dim3 grid(bx, std::min(n, 1024));
     if (unpack)
@@ -526,6 +526,104 @@ void launch_pack(const void* const* ptrs_dev, const size_t* offs_dev, int n, voi
     else
         dev::pack_kernel<false><<<grid, 512, 0, st>>>(t, (char*)fused);
     CUDA_CHECK(cudaGetLastError());
+}
+
+void launch_allreduce_fused(device_comm& dc, const void* const* send, void* const* recv, const size_t* counts, int n,
+                            int dt, int op, const launch_opts& o, cudaStream_t st) {
+    if (n <= 0)
+        return;
+    const int W = dc.world();
+    const int entries = dc.emulated() ? W : 1;
+    const size_t esz = predefined_dtype_size(dt);
+    typedef device_comm::fuse_state FS;
+    FS& f = dc.fuse();
+    const env_data& env = env_data::get();
+    if (f.buf_off == (size_t)-1) {
+        // first use (the same call on every rank: symmetric allocations are collective by program order)
+        f.buf_bytes = std::max<size_t>(env.fusion_bytes_threshold * env.fusion_count_threshold, (size_t)4 << 20);
+        char* p = (char*)dc.symm_alloc(f.buf_bytes, 0);
+        f.buf_off = dc.symm_offset(p, dc.emulated() ? 0 : -1);
+        const size_t per_entry = (size_t)FS::MAX_TENSORS * (sizeof(void*) + 2 * sizeof(size_t));
+        CUDA_CHECK(cudaHostAlloc((void**)&f.tab_host, (size_t)FS::SLOTS * entries * per_entry, cudaHostAllocMapped));
+        CUDA_CHECK(cudaHostGetDevicePointer((void**)&f.tab_dev, f.tab_host, 0));
+        for (auto& e : f.used)
+            CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    // per entry: MAX_TENSORS pointers (send then recv of a group), MAX_TENSORS offsets, MAX_TENSORS byte lengths
+    const size_t per_entry = (size_t)FS::MAX_TENSORS * (sizeof(void*) + 2 * sizeof(size_t));
+
+    auto single = [&](int k) {
+        std::vector<dev::rank_args> ra(entries);
+        for (int e = 0; e < entries; e++) {
+            ra[e] = dev::rank_args{};
+            ra[e].send = send[(size_t)k * entries + e];
+            ra[e].recv = recv[(size_t)k * entries + e];
+        }
+        launch_allreduce(dc, ra.data(), counts[k], dt, dt, op, o, st);
+    };
+
+    int k = 0;
+    while (k < n) {
+        // next group: consecutive tensors whose 16-byte-rounded sizes fit the fused buffer
+        if (r16(counts[k] * esz) > f.buf_bytes / 2) {
+            single(k++);
+            continue;
+        }
+        int first = k;
+        size_t used = 0, biggest = 0;
+        std::vector<size_t> offs;
+        while (k < n && k - first < FS::MAX_TENSORS / 2 && r16(counts[k] * esz) <= f.buf_bytes / 2 &&
+               used + r16(counts[k] * esz) <= f.buf_bytes) {
+            offs.push_back(used);
+            used += r16(counts[k] * esz);
+            biggest = std::max(biggest, counts[k] * esz);
+            k++;
+        }
+        const int m = k - first;
+        if (m == 1) {
+            single(first);
+            continue;
+        }
+        // a table slot may be rewritten only when the kernels that read it have run
+        const int slot = f.next;
+        f.next = (f.next + 1) % FS::SLOTS;
+        CUDA_CHECK(cudaEventSynchronize(f.used[slot]));
+        std::vector<dev::rank_args> ra(entries);
+        // Rounded slots leave up to 15 bytes of padding behind a tensor; the allreduce runs over `used` bytes, so the
+        // padding is reduced too (whatever it holds) and never unpacked.
+        for (int pass = 0; pass < 2; pass++) { // 0: send pointers for the pack, 1: recv pointers for the unpack
+            if (pass == 1) {
+                for (int e = 0; e < entries; e++) {
+                    ra[e] = dev::rank_args{};
+                    ra[e].send = ra[e].recv = dc.heap().base(dc.emulated() ? e : dc.rank()) + f.buf_off;
+                }
+                launch_allreduce(dc, ra.data(), used / esz, dt, dt, op, o, st);
+            }
+            for (int e = 0; e < entries; e++) {
+                char* th = f.tab_host + ((size_t)(slot * entries + e)) * per_entry;
+                char* td = f.tab_dev + ((size_t)(slot * entries + e)) * per_entry;
+                // pack and unpack read different halves of the pointer table: [0, m) send, [m, 2m) recv
+                const void** ptrs = (const void**)th;
+                size_t* of = (size_t*)(th + (size_t)FS::MAX_TENSORS * sizeof(void*));
+                size_t* ln = of + FS::MAX_TENSORS;
+                if (pass == 0) {
+                    for (int j = 0; j < m; j++) {
+                        ptrs[j] = send[(size_t)(first + j) * entries + e];
+                        ptrs[m + j] = recv[(size_t)(first + j) * entries + e];
+                        of[j] = offs[j];
+                        ln[j] = counts[first + j] * esz;
+                    }
+                }
+                char* fused = dc.heap().base(dc.emulated() ? e : dc.rank()) + f.buf_off;
+                const void* const* pd = (const void* const*)td + (pass == 0 ? 0 : m);
+                const size_t* od = (const size_t*)(td + (size_t)FS::MAX_TENSORS * sizeof(void*));
+                launch_pack(pd, od, od + FS::MAX_TENSORS, m, fused, pass == 1, biggest, st);
+            }
+        }
+        CUDA_CHECK(cudaEventRecord(f.used[slot], st));
+        f.batches++;
+        f.tensors += m;
+    }
 }
 
 } // namespace gpu

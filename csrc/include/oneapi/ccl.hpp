@@ -770,6 +770,18 @@ comm_split_attr create_comm_split_attr(Avs&&... avs) {
 CCL_API vector_class<communicator> split_communicators(
     const vector_class<pair_class<communicator, comm_split_attr>>& attrs);
 
+// Extension (no counterpart in the oneCCL specification): in-place allreduce of several buffers of one
+// datatype as ONE operation.  Device buffers of a single node are packed into a buffer of the symmetric heap by
+// one kernel, reduced by one zero-copy allreduce and unpacked by one kernel, on the given stream; host buffers
+// are issued one by one.  The event covers every buffer.  What CCL_FUSION=1 does behind the ordinary allreduce,
+// without the queueing.
+CCL_API event allreduce_coalesced(const vector_class<void*>& bufs, const vector_class<size_t>& counts, datatype dtype,
+                                  reduction rtype, const communicator& comm, const stream& s,
+                                  const allreduce_attr& attr = default_allreduce_attr);
+CCL_API event allreduce_coalesced(const vector_class<void*>& bufs, const vector_class<size_t>& counts, datatype dtype,
+                                  reduction rtype, const communicator& comm,
+                                  const allreduce_attr& attr = default_allreduce_attr);
+
 } // namespace preview
 
 } // namespace ccl

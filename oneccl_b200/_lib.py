@@ -61,7 +61,8 @@ def _proto(lib):
         "cclx_dc_sendrecv": (i, [vp, pp, pp, psz, pi, pi, i, vp]),
         "cclx_dc_wait_unset_flag": (i, [vp, vp]),
         "cclx_reduce_local": (i, [vp, vp, sz, i, i, vp]),
-        "cclx_pack": (i, [vp, vp, i, vp, i, sz, vp]),
+        "cclx_dc_allreduce_fused": (i, [vp, pp, pp, psz, i, i, i, f, i, vp]),
+        "cclx_dc_fused_batches": (C.c_ulonglong, [vp]),
         "cclx_transpose_blocks": (i, [vp, vp, i, i, sz, vp]),
         "cclx_gemm_bf16": (i, [vp, vp, vp, i, i, i, i, i, vp, vp]),
         "cclx_gemm_bf16_2sm": (i, [vp, vp, vp, i, i, i, i, i, vp, vp]),

@@ -207,6 +207,32 @@ class DeviceGroup:
         self._finish(rc)
         return recv
 
+    def allreduce_fused(self, tensors, op="sum", scale: Optional[float] = None, stream=None):
+        """In-place allreduce of a list of (small) tensors as ONE collective: one kernel packs them into a
+        buffer of the symmetric heap, one zero-copy allreduce reduces it, one kernel unpacks.  Real mode:
+        ``tensors`` is this rank's list.  Emulated mode: a list (per tensor) of lists (per rank)."""
+        n = len(tensors)
+        if self.emulated_mode:
+            flat = [t for per_rank in tensors for t in per_rank]  # tensor-major
+            first = tensors[0][0]
+            counts = [per_rank[0].numel() for per_rank in tensors]
+        else:
+            flat = list(tensors)
+            first = tensors[0]
+            counts = [t.numel() for t in tensors]
+        for t in flat:
+            assert t.is_contiguous() and t.dtype == first.dtype
+        ptrs = self._ptrs(flat)
+        rc = self._lib.cclx_dc_allreduce_fused(self._h, ptrs, ptrs, _lib.size_array(counts), n, torch_to_ccl(first.dtype),
+                                               reduce_op_code(op), 1.0 if scale is None else float(scale),
+                                               0 if scale is None else 1, _stream_ptr(stream))
+        self._finish(rc)
+        return tensors
+
+    @property
+    def fused_batches(self) -> int:
+        return int(self._lib.cclx_dc_fused_batches(self._h))
+
     def reduce_scatter(self, send, recv, op="sum", algo="auto", blocks=0, scale: Optional[float] = None, stream=None):
         s, r = self._lists(send, recv)
         for a, b in zip(s, r):

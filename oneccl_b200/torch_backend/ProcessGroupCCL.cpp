@@ -20,6 +20,7 @@
 #include <pybind11/chrono.h>
 
 #include <map>
+#include <thread>
 #include <mutex>
 
 #include "oneapi/ccl.hpp"
@@ -94,21 +95,51 @@ public:
             cudaEventDestroy(done_);
     }
     bool isCompleted() override {
-        if (cuda_)
-            return cudaEventQuery(done_) == cudaSuccess;
+        if (cuda_) {
+            if (cudaEventQuery(done_) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return false;
+            }
+            check_device();
+            return true;
+        }
         for (auto& e : events_)
             if (!e.test())
                 return false;
         return true;
     }
-    bool isSuccess() const override { return true; }
-    bool wait(std::chrono::milliseconds /*timeout*/ = kNoTimeout) override {
+    // a device-side failure (bounded wait ran out, abort, argument mismatch) is recorded in the communicator's
+    // status word; once the event has fired it is turned into this Work's exception
+    void check_device() {
+        try {
+            for (auto& e : events_)
+                (void)e.test();
+        }
+        catch (...) {
+            std::lock_guard<std::mutex> lk(mutex_);
+            if (!exception_)
+                exception_ = std::current_exception();
+        }
+    }
+    bool isSuccess() const override { return !exception_; }
+    bool wait(std::chrono::milliseconds timeout = kNoTimeout) override {
         if (cuda_) {
+            if (timeout != kNoTimeout) {
+                // a caller that gives a time limit wants to know on the host: poll the event until then
+                const auto deadline = std::chrono::steady_clock::now() + timeout;
+                while (cudaEventQuery(done_) != cudaSuccess) {
+                    (void)cudaGetLastError();
+                    TORCH_CHECK(std::chrono::steady_clock::now() < deadline, "ccl backend: operation timed out after ",
+                                timeout.count(), " ms");
+                    std::this_thread::yield();
+                }
+                check_device();
+                if (exception_)
+                    std::rethrow_exception(exception_);
+            }
             // stream semantics: later work on the caller's stream is ordered after the collective
             auto cur = c10::cuda::getCurrentCUDAStream(device_);
             C10_CUDA_CHECK(cudaStreamWaitEvent(cur.stream(), done_, 0));
-            for (auto& e : events_)
-                (void)e; // device status is checked by the next launch of the communicator
             return true;
         }
         for (auto& e : events_)
@@ -220,8 +251,12 @@ public:
             auto it = streams_.find(c.dev);
             if (it == streams_.end()) {
                 c10::cuda::CUDAGuard g(c.dev);
+                // highest priority: a bucket allreduce launched during backward runs beside the GEMM that is on
+                // the GPU instead of waiting behind all of its waves
                 cudaStream_t s;
-                C10_CUDA_CHECK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+                int lo = 0, hi = 0;
+                C10_CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+                C10_CUDA_CHECK(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, hi));
                 it = streams_.emplace(c.dev, s).first;
             }
             c.comm_stream = it->second;
@@ -262,6 +297,7 @@ public:
         auto w = c10::make_intrusive<WorkCCL>(OpType::ALLREDUCE, tensors, std::vector<at::Tensor>{ t });
         ccl::allreduce_attr attr;
         const bool avg = opts.reduceOp.op_ == ReduceOp::AVG;
+        TORCH_CHECK(!avg || at::isFloatingType(t.scalar_type()), "ccl backend: ReduceOp.AVG needs a floating-point tensor");
         if (avg && c.cuda)
             attr.set<ccl::device_attr_ext_id::scale>(1.0f / (float)getSize());
         if (c.cuda)
@@ -282,15 +318,38 @@ public:
 
     c10::intrusive_ptr<Work> allreduce_coalesced(std::vector<at::Tensor>& tensors,
                                                  const AllreduceCoalescedOptions& opts) override {
-        // small tensors: the library's fusion (CCL_FUSION=1) packs them; otherwise one op per tensor
-        c10::intrusive_ptr<Work> last;
+        TORCH_CHECK(!tensors.empty(), "ccl backend: empty tensor list");
+        bool one_kind = tensors[0].is_cuda();
+        for (auto& t : tensors)
+            one_kind = one_kind && t.is_cuda() && t.device() == tensors[0].device() &&
+                       t.scalar_type() == tensors[0].scalar_type() && t.is_contiguous();
+        if (one_kind) {
+            // CUDA tensors of one dtype: ONE fused operation (pack kernel, one allreduce on a buffer of the
+            // symmetric heap, unpack kernel) and one Work that covers every tensor
+            auto c = begin(tensors[0]);
+            auto w = c10::make_intrusive<WorkCCL>(OpType::ALLREDUCE_COALESCED, tensors, tensors);
+            ccl::allreduce_attr attr;
+            if (opts.reduceOp.op_ == ReduceOp::AVG)
+                attr.set<ccl::device_attr_ext_id::scale>(1.0f / (float)getSize());
+            std::vector<void*> bufs;
+            std::vector<size_t> counts;
+            for (auto& t : tensors) {
+                bufs.push_back(t.data_ptr());
+                counts.push_back((size_t)t.numel());
+            }
+            w->add(ccl::preview::allreduce_coalesced(bufs, counts, to_ccl_dtype(tensors[0].scalar_type()),
+                                                     to_ccl_op(opts.reduceOp), comm_, c.stream, attr));
+            return finish(c, w);
+        }
+        // mixed lists: one operation per tensor; the returned Work completes when all of them have
+        std::vector<c10::intrusive_ptr<Work>> parts;
         AllreduceOptions o;
         o.reduceOp = opts.reduceOp;
         for (auto& t : tensors) {
             std::vector<at::Tensor> one{ t };
-            last = allreduce(one, o);
+            parts.push_back(allreduce(one, o));
         }
-        return last;
+        return c10::make_intrusive<CoalescedWorkCCL>(std::move(parts));
     }
 
     c10::intrusive_ptr<Work> broadcast(std::vector<at::Tensor>& tensors, const BroadcastOptions& opts) override {
@@ -422,6 +481,7 @@ public:
                                               std::vector<at::Tensor>{ in });
         ccl::reduce_scatter_attr attr;
         const bool avg = opts.reduceOp.op_ == ReduceOp::AVG;
+        TORCH_CHECK(!avg || at::isFloatingType(in.scalar_type()), "ccl backend: ReduceOp.AVG needs a floating-point tensor");
         if (avg && c.cuda)
             attr.set<ccl::device_attr_ext_id::scale>(1.0f / (float)getSize());
         if (c.cuda)

@@ -466,6 +466,38 @@ def test_allreduce_symmetric_narrow_grid(group, dtype, blocks):
     group.symm_free(bufs)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_small_allreduces_pack_reduce_unpack(group, dtype):
+    """Many small tensors as ONE collective: pack kernel -> one zero-copy allreduce on a buffer of the symmetric
+    heap -> unpack kernel, against the fp32 sum; odd sizes, unaligned starts and canaries around every tensor,
+    one tensor too large for the fused buffer (reduced on its own), twice in a row (table slots are reused)."""
+    W = group.world
+    sizes = [1, 17, 255, 4096, 3, 1000, 32771, 8, 2_500_000, 77]
+    for rep in range(2):
+        bufs, views, refs = [], [], []
+        for k, n in enumerate(sizes):
+            src = _inputs(W, n, dtype, seed=100 * rep + k)
+            per_rank_buf, per_rank_view = [], []
+            for r in range(W):
+                b, v = _padded(n + 1, dtype)
+                v = v[1:]  # starts that are not 16-byte aligned
+                v.copy_(src[r])
+                per_rank_buf.append(b)
+                per_rank_view.append(v)
+            bufs.append(per_rank_buf)
+            views.append(per_rank_view)
+            refs.append(torch.stack([x.double() for x in src]).sum(0) / W)
+        before = group.fused_batches
+        group.allreduce_fused(views, scale=1.0 / W)
+        torch.cuda.synchronize()
+        group.check()
+        assert group.fused_batches > before
+        for k, n in enumerate(sizes):
+            for r in range(W):
+                torch.testing.assert_close(views[k][r].double(), refs[k], **_tol(dtype, W))
+                assert _canary_ok(bufs[k][r], n + 1) and float(bufs[k][r][CANARY]) == 77.0
+
+
 @pytest.mark.parametrize("topk", [1, 2])
 def test_moe_fused_dispatch_and_combine(group, topk):
     """Rows go straight into the owning expert's symmetric buffer and come back by peer loads with
