@@ -731,7 +731,44 @@ __global__ void __launch_bounds__(1024) reduce_scatter_symm_kernel(const comm_de
     split_range(full, gridDim.x, blockIdx.x, lo, hi);
     bool ok = peer_barrier(c, s, sig);
     if (ok) {
-        for (size_t i = lo + tid; i < hi; i += nt) {
+        size_t i = lo + tid;
+        if (NVLS) {
+            // four in-switch reductions in flight per thread: the round trip through the switch is long
+            constexpr int U = 4;
+            const char* src = c.mc_heap + a.in_off + blk;
+            for (; i + (U - 1) * nt < hi; i += U * nt) {
+                uint4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    v[u] = multimem_ld_reduce_add16<T>(src + ((i + u * nt) << 4));
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    A acc[N];
+                    unpack16<T, A>(v[u], acc);
+                    store_pack<T, A, N>(recv, i + u * nt, rc, vout, acc, a.scale, a.do_scale != 0);
+                }
+            }
+        }
+        else {
+            // two packs x world peer loads in flight per thread
+            for (; i + nt < hi; i += 2 * nt) {
+                uint4 v0[MAX_RANKS], v1[MAX_RANKS];
+                for (int p = 0; p < W; p++) {
+                    v0[p] = ld_cv16(peer_in(c, a, p) + blk + (i << 4));
+                    v1[p] = ld_cv16(peer_in(c, a, p) + blk + ((i + nt) << 4));
+                }
+                A acc0[N], acc1[N];
+                unpack16<T, A>(v0[0], acc0);
+                unpack16<T, A>(v1[0], acc1);
+                for (int p = 1; p < W; p++) {
+                    accum16<T, A, Op>(v0[p], acc0);
+                    accum16<T, A, Op>(v1[p], acc1);
+                }
+                store_pack<T, A, N>(recv, i, rc, vout, acc0, a.scale, a.do_scale != 0);
+                store_pack<T, A, N>(recv, i + nt, rc, vout, acc1, a.scale, a.do_scale != 0);
+            }
+        }
+        for (; i < hi; i += nt) {
             A acc[N];
             if (NVLS) {
                 unpack16<T, A>(multimem_ld_reduce_add16<T>(c.mc_heap + a.in_off + blk + (i << 4)), acc);
@@ -864,7 +901,28 @@ __global__ void __launch_bounds__(1024) allgather_symm_kernel(const comm_dev* ta
     bool ok = peer_barrier(c, s, sig);
     if (ok) {
         const bool vin = (((uintptr_t)send) & 15) == 0;
-        for (size_t i = lo + tid; i < hi; i += nt) {
+        size_t i = lo + tid;
+        if (vin) {
+            // four local loads in flight per thread before their stores go out
+            constexpr int U = 4;
+            for (; i + (U - 1) * nt < hi; i += U * nt) {
+                uint4 v[U];
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    v[u] = *reinterpret_cast<const uint4*>(send + ((i + u * nt) << 4));
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    if (NVLS) {
+                        multimem_st16(c.mc_heap + a.out_off + doff + ((i + u * nt) << 4), v[u]);
+                    }
+                    else {
+                        for (int k = 0; k < W; k++)
+                            st16(peer_out(c, a, (c.rank + k) % W) + doff + ((i + u * nt) << 4), v[u]);
+                    }
+                }
+            }
+        }
+        for (; i < hi; i += nt) {
             uint4 v = load_pack<unsigned char>(reinterpret_cast<const unsigned char*>(send), i, bytes, vin);
             if (NVLS) {
                 multimem_st16(c.mc_heap + a.out_off + doff + (i << 4), v);

@@ -148,11 +148,24 @@ void launch_allreduce(device_comm& dc, const dev::rank_args* ra, size_t count, i
         if (vout.registered)
             fill_registered(dc, a, vout, true);
         prepare_args(dc, a, ra, st);
-        // per-rank slice, 16 KiB of it per block
-        const int blocks = pick_blocks(dc, bytes / 16 / W + 1, 1024, o.blocks);
-        // a grid that the caller kept narrow (it runs beside a compute kernel) makes up for the missing
-        // blocks with full-size blocks and twice the loads in flight per thread
-        const bool narrow = o.blocks > 0 && blocks * 4 <= dc.sm_count();
+        // Grid width.  In-switch reduction: the traffic of a GPU's links is carried by a handful of blocks (measured
+        // on 4 and 8 B200s: 4 to 8 blocks of 1024 threads with eight loads in flight per thread are as fast as or
+        // faster than any wider grid from 1 MB to 1 GiB), so the automatic choice stays narrow and leaves the SMs
+        // to whatever else runs.  Peer loads need their requests spread over many SMs: 8 KiB of the per-rank
+        // slice per block, up to the whole GPU.
+        int blocks;
+        bool narrow;
+        if (algo == ga_nvls && o.blocks == 0) {
+            blocks = pick_blocks(dc, bytes / 16 / W + 1, 128, 8);
+            blocks = std::min(blocks, (int)((bytes / 16 / W) / 128 + 1));
+            narrow = true;
+        }
+        else {
+            blocks = pick_blocks(dc, bytes / 16 / W + 1, 512, o.blocks);
+            // a grid that the caller kept narrow (it runs beside a compute kernel) makes up for the missing
+            // blocks with full-size blocks and twice the loads in flight per thread
+            narrow = o.blocks > 0 && blocks * 4 <= dc.sm_count();
+        }
         const int th = narrow ? 1024 : threads;
         CCLX_DISPATCH_DTYPE(dt_in, T, {
             if (algo == ga_nvls) {

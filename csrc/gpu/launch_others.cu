@@ -40,7 +40,9 @@ void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t rc,
     int algo = o.algo;
     if (algo == ga_auto)
         algo = (symmetric && W > 1 && rc * esz > env_data::get().rs_small_threshold)
-                   ? ((dc.nvls() && nvls_type_ok(dt_in, op) && !vin.registered) ? ga_nvls : ga_symm)
+                   ? ((dc.nvls() && nvls_type_ok(dt_in, op) && !vin.registered && W >= env_data::get().nvls_min_ranks)
+                          ? ga_nvls
+                          : ga_symm)
                    : ga_push;
     if ((algo == ga_symm || algo == ga_nvls) && !symmetric)
         CCL_THROW("reduce_scatter algorithm ", gpu_algo_name(algo),
@@ -209,7 +211,12 @@ void launch_allgatherv(device_comm& dc, const dev::rank_args* ra, const launch_o
         else if (symm && maxb > env_data::get().ag_small_threshold && env_data::get().cuda_copy_engine)
             algo = ga_ce; // CCL_CUDA_COPY_ENGINE=1: large blocks move by the copy engines, the SMs stay free
         else if (symm && (maxb > env_data::get().ag_small_threshold || vout.registered))
-            algo = (dc.nvls() && !vout.registered) ? ga_nvls : ga_symm;
+            // one multimem.st reaches every peer, which wins while latency counts; large blocks move faster as
+            // plain peer stores (measured on 4 B200s: 1 GiB gathered in 1.27 ms by peer stores, 1.55 ms by multimem.st)
+            algo = (dc.nvls() && !vout.registered && W >= env_data::get().nvls_min_ranks &&
+                    maxb <= env_data::get().ag_nvls_max_block)
+                       ? ga_nvls
+                       : ga_symm;
         else if (maxb <= env_data::get().ag_small_threshold && rounded <= dc.staging_bytes())
             algo = ga_push;
         else

@@ -11,10 +11,11 @@ timed launches between two CUDA events on the launching stream, time = max
 over ranks / iters.  Bus bandwidth uses the NCCL-tests convention: allreduce
 2(n-1)/n * S/t, reduce_scatter / allgather / alltoall (n-1)/n * S/t with S the
 full message size.  Every size is reported for three arms: "ours" (ordinary
-device tensors, staged through the symmetric heap), "ours_symm" (tensors
-allocated from the symmetric heap: zero-copy, NVLS when available) and "nccl".
-Iteration counts shrink for very large messages to bound the run time; the
-counts used are recorded in every row.
+device tensors: staged through the symmetric heap below 256 KiB, shared with the
+peers automatically and reduced zero-copy from there on), "ours_symm" (tensors
+allocated from the symmetric heap: zero-copy, NVLS when available) and "nccl",
+with the ratios NCCL time / our time per arm ("ordinary_vs_nccl",
+"symmetric_vs_nccl"; above 1 = faster than NCCL).
 """
 from __future__ import annotations
 
@@ -86,6 +87,8 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--arms", default="ours,ours_symm,nccl")
     ap.add_argument("--heap", default="6G")
+    ap.add_argument("--shrink-large", action="store_true",
+                    help="a fifth of the iterations above 64 MiB (the counts used are recorded in every row)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -138,8 +141,9 @@ def main():
                 if n_in == 0 or n_out == 0:
                     continue
                 Sb = max(n_in, n_out) * esz
-                iters = args.iters if Sb <= (64 << 20) else max(10, args.iters // 5)
-                warm = args.warmup if Sb <= (64 << 20) else max(3, args.warmup // 5)
+                shrink = args.shrink_large and Sb > (64 << 20)
+                iters = max(10, args.iters // 5) if shrink else args.iters
+                warm = max(3, args.warmup // 5) if shrink else args.warmup
                 gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
                 factor = {"allreduce": 2.0 * (world - 1) / world}.get(coll, (world - 1) / world)
                 row = {"coll": coll, "dtype": dname, "bytes": Sb, "n_gpus": world, "iters": iters, "warmup": warm,
@@ -181,8 +185,11 @@ def main():
                         if b is not a:
                             grp.symm_free(b)
                     del a, b
-                if "nccl" in arms and "ours_symm" in arms:
-                    row["best_vs_nccl"] = row["nccl_us"] / min(row.get("ours_us", 1e30), row["ours_symm_us"])
+                if "nccl" in arms:
+                    if "ours" in arms:
+                        row["ordinary_vs_nccl"] = row["nccl_us"] / row["ours_us"]
+                    if "ours_symm" in arms:
+                        row["symmetric_vs_nccl"] = row["nccl_us"] / row["ours_symm_us"]
                 rows.append(row)
                 if rank == 0:
                     line = json.dumps(row)
