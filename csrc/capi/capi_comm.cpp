@@ -4,6 +4,7 @@
 
 #include "bootstrap/kvs.hpp"
 #include "capi/capi_common.hpp"
+#include "coll/algorithms.hpp"
 #include "coll/coll.hpp"
 #include "coll/selection.hpp"
 #include "bootstrap/launcher.hpp"
@@ -196,6 +197,17 @@ CCLX_API void* cclx_comm_r2r(void* c) {
     comm_handle* h = nullptr;
     capi::guard([&] { h = new comm_handle{ ((comm_handle*)c)->c->r2r_comm() }; });
     return h;
+}
+
+// neighbours of `rank` in double-tree number `which` (0 / 1): out = { parent, left, right, root }
+CCLX_API int cclx_bin_tree(int size, int rank, int which, int root, int* out) {
+    return capi::guard([&] {
+        cclx::algo::bin_tree t(size, rank, which, root);
+        out[0] = t.parent;
+        out[1] = t.left;
+        out[2] = t.right;
+        out[3] = t.root_rank;
+    });
 }
 
 CCLX_API int cclx_comm_rank(void* c) {

@@ -274,6 +274,33 @@ void allgatherv_naive(sched& s, const void* send, void* recv, const std::vector<
     s.add_barrier();
 }
 
+// flat: every peer gets a sub-schedule of its own (reference allgatherv.cpp:327-395 spreads the peers over
+// the partial schedules of the workers), so the exchanges with different peers progress independently, and
+// the blocks are sent straight from the user's send buffer, without waiting for the local copy.
+void allgatherv_flat(sched& s, const void* send, void* recv, const std::vector<size_t>& counts,
+                     const std::vector<size_t>& offs, int dtype) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(dtype);
+    char* mine = at(recv, offs[r], esz);
+    const void* src = send ? send : mine;
+    const size_t my_bytes = counts[r] * esz;
+    if (send && send != mine)
+        s.add<copy_entry>(send, mine, my_bytes); // no barrier: nobody below depends on it
+    for (int k = 1; k < N; k++) {
+        const int p = (r + k) % N;
+        void* dst = at(recv, offs[p], esz);
+        const size_t pb = counts[p] * esz;
+        s.add<subsched_entry>(
+            [=](sched& sub) {
+                sub.add<recv_entry>(dst, pb, p, 0);
+                sub.add<send_entry>(src, my_bytes, p, 0);
+            },
+            "AG_FLAT_PEER");
+    }
+    s.add_barrier();
+}
+
 void allgatherv_ring(sched& s, const void* send, void* recv, const std::vector<size_t>& counts,
                      const std::vector<size_t>& offs, int dtype, uint64_t step_base) {
     host_comm* c = s.comm();
@@ -595,52 +622,209 @@ void allreduce_2d(sched& s, const buf_desc& b) {
     }
 }
 
-void allreduce_double_tree(sched& s, const buf_desc& b) {
+// ---------------------------------------------------------------------------- double binary tree
+// Two complementary binary trees over the ranks (the topology of the reference's double-tree operations,
+// src/common/utils/tree.hpp:22-216 and src/coll/algorithms/double_tree_ops.cpp:118-331, built here from the
+// in-order numbering instead of being taken over).  Positions 1..N in in-order: a position's height is the
+// number of trailing zero bits, odd positions are leaves, a node of height h has the children i - 2^(h-1) and
+// i + 2^(h-1) (a right child beyond N is replaced by the highest node of its subtree that exists), the root
+// is the largest power of two <= N.  Tree A puts rank i-1 on position i; tree B puts rank i mod N there, a
+// shift by one, so that the inner nodes of A (odd ranks) are leaves of B and the other way round: every
+// rank forwards data in one tree only, which is what lets the two halves of a message travel at full rate.
+// A root other than the tree's own swaps places with it.
+bin_tree::bin_tree(int size, int rank, int which, int root) {
+    const int N = size;
+    auto height = [](int i) {
+        int h = 0;
+        while (!(i & 1)) {
+            i >>= 1;
+            h++;
+        }
+        return h;
+    };
+    int top = 1;
+    while (top * 2 <= N)
+        top *= 2;
+    std::vector<int> par(N + 1, 0), lc(N + 1, 0), rc(N + 1, 0);
+    for (int i = 1; i <= N; i++) {
+        const int h = height(i);
+        if (h == 0)
+            continue;
+        lc[i] = i - (1 << (h - 1));
+        int r = 0;
+        for (int k = h; k >= 1 && !r; k--) // highest existing node of the right subtree
+            if (i + (1 << (k - 1)) <= N)
+                r = i + (1 << (k - 1));
+        rc[i] = r;
+        par[lc[i]] = i;
+        if (r)
+            par[r] = i;
+    }
+    // position -> rank
+    std::vector<int> at(N + 1, 0);
+    for (int i = 1; i <= N; i++)
+        at[i] = which == 0 ? i - 1 : i % N;
+    if (root >= 0 && at[top] != root) {
+        for (int i = 1; i <= N; i++)
+            if (at[i] == root) {
+                std::swap(at[i], at[top]);
+                break;
+            }
+    }
+    int me = 0;
+    for (int i = 1; i <= N; i++)
+        if (at[i] == rank)
+            me = i;
+    parent = par[me] ? at[par[me]] : -1;
+    left = lc[me] ? at[lc[me]] : -1;
+    right = rc[me] ? at[rc[me]] : -1;
+    root_rank = at[top];
+}
+
+// reduce towards the root of `t`: accumulate the children's contributions into acc, hand the result up
+static void reduce_bin_tree(sched& s, void* acc, size_t count, int dtype, int op, reduction_fn_t fn, const bin_tree& t,
+                            uint64_t tag) {
+    const size_t bytes = count * dtype_size(dtype);
+    void* tmp = (t.left >= 0 || t.right >= 0) ? s.alloc_tmp(bytes + 64) : nullptr;
+    for (int child : { t.left, t.right })
+        if (child >= 0) {
+            s.add<recv_reduce_entry>(acc, count, dtype, op, child, tag, fn, tmp);
+            s.add_barrier();
+        }
+    if (t.parent >= 0) {
+        s.add<send_entry>(acc, bytes, t.parent, tag);
+        s.add_barrier();
+    }
+}
+
+static void bcast_bin_tree(sched& s, void* buf, size_t bytes, const bin_tree& t, uint64_t tag) {
+    if (t.parent >= 0) {
+        s.add<recv_entry>(buf, bytes, t.parent, tag);
+        s.add_barrier();
+    }
+    for (int child : { t.left, t.right })
+        if (child >= 0)
+            s.add<send_entry>(buf, bytes, child, tag);
+    s.add_barrier();
+}
+
+// number of pipeline parts a half is cut into (CCL_DTREE_PARTITION_COUNT; reference
+// src/coll/algorithms/double_tree_ops.cpp:146-151)
+static size_t dtree_parts(size_t count) {
+    const size_t want = std::min(std::max<size_t>(env_data::get().dtree_partition_count, 1), MAX_CHUNKS);
+    return std::min(want, std::max<size_t>(count, 1));
+}
+
+void bcast_double_tree(sched& s, void* buf, size_t count, int dtype, int root) {
     host_comm* c = s.comm();
-    const int N = c->size();
-    const size_t esz = dtype_size(b.dtype);
-    copy_in(s, b.send, b.recv, b.count * esz);
-    if (N == 1)
+    const int N = c->size(), r = c->rank();
+    if (N == 1 || count == 0)
         return;
-    // two halves travel through two binomial trees with different roots, so a rank
-    // that is an inner node of one tree is a leaf (or near-leaf) of the other
+    const size_t esz = dtype_size(dtype);
+    const size_t h0 = count / 2, h1 = count - h0;
+    for (int which = 0; which < 2; which++) {
+        const size_t n = which == 0 ? h0 : h1;
+        if (n == 0)
+            continue;
+        void* base = which == 0 ? buf : at(buf, h0, esz);
+        const bin_tree t(N, r, which, root);
+        const size_t parts = dtree_parts(n);
+        // the halves (and the parts of a half) are independent streams: sub-schedules progress side by side
+        for (size_t k = 0; k < parts; k++) {
+            size_t o, m;
+            chunk_range(n, parts, k, o, m);
+            void* p = at(base, o, esz);
+            const uint64_t tag = 2000 * (uint64_t)which + k;
+            s.add<subsched_entry>([=](sched& sub) { bcast_bin_tree(sub, p, m * esz, t, tag); },
+                                  which == 0 ? "DTREE_BCAST_A" : "DTREE_BCAST_B");
+        }
+    }
+    s.add_barrier();
+}
+
+void reduce_double_tree(sched& s, const buf_desc& b, int root) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(b.dtype);
+    const size_t bytes = b.count * esz;
+    // every rank accumulates in a work buffer; the root's is its recv buffer
+    void* acc = b.recv;
+    if (b.send) {
+        if (r != root || !b.recv)
+            acc = s.alloc_tmp(bytes + 64);
+        if (acc != b.send) {
+            s.add<copy_entry>(b.send, acc, bytes);
+            s.add_barrier();
+        }
+    }
+    if (N == 1 || b.count == 0)
+        return;
     const size_t h0 = b.count / 2, h1 = b.count - h0;
-    const int root0 = 0, root1 = N / 2;
     const int dtype = b.dtype, op = b.op;
     reduction_fn_t fn = b.fn;
-    // CCL_DTREE_PARTITION_COUNT > 1: each half is cut into parts that follow one another down
-    // the tree, the broadcast of part k running beside the reduction of part k+1 (reference
-    // src/coll/algorithms/double_tree_ops.cpp:146-151)
-    const size_t want = std::min(std::max<size_t>(env_data::get().dtree_partition_count, 1), MAX_CHUNKS);
-    auto tree = [=](sched& sub, void* base, size_t count, int root, uint64_t tag0) {
-        const size_t parts = std::min(want, std::max<size_t>(count, 1));
-        if (parts == 1) {
-            reduce_tree(sub, buf_desc{ nullptr, base, count, dtype, op, fn }, root, tag0);
-            bcast_tree(sub, base, count * dtype_size(dtype), root, tag0 + 500);
-            return;
+    for (int which = 0; which < 2; which++) {
+        const size_t n = which == 0 ? h0 : h1;
+        if (n == 0)
+            continue;
+        void* base = which == 0 ? acc : at(acc, h0, esz);
+        const bin_tree t(N, r, which, root);
+        const size_t parts = dtree_parts(n);
+        for (size_t k = 0; k < parts; k++) {
+            size_t o, m;
+            chunk_range(n, parts, k, o, m);
+            void* p = at(base, o, esz);
+            const uint64_t tag = 2000 * (uint64_t)which + k;
+            s.add<subsched_entry>([=](sched& sub) { reduce_bin_tree(sub, p, m, dtype, op, fn, t, tag); },
+                                  which == 0 ? "DTREE_REDUCE_A" : "DTREE_REDUCE_B");
         }
-        for (size_t t = 0; t <= parts; t++) {
-            if (t < parts) {
-                size_t o, n;
-                chunk_range(count, parts, t, o, n);
-                void* p = at(base, o, dtype_size(dtype));
-                sub.add<subsched_entry>(
-                    [=](sched& ss) { reduce_tree(ss, buf_desc{ nullptr, p, n, dtype, op, fn }, root, tag0); }, "DTREE_R");
-            }
-            if (t >= 1) {
-                size_t o, n;
-                chunk_range(count, parts, t - 1, o, n);
-                void* p = at(base, o, dtype_size(dtype));
-                sub.add<subsched_entry>(
-                    [=](sched& ss) { bcast_tree(ss, p, n * dtype_size(dtype), root, tag0 + 500); }, "DTREE_B");
-            }
-            sub.add_barrier();
-        }
-    };
+    }
+    s.add_barrier();
+}
+
+void allreduce_double_tree(sched& s, const buf_desc& b) {
+    host_comm* c = s.comm();
+    const int N = c->size(), r = c->rank();
+    const size_t esz = dtype_size(b.dtype);
+    copy_in(s, b.send, b.recv, b.count * esz);
+    if (N == 1 || b.count == 0)
+        return;
+    // Half 0 is reduced up tree A and broadcast down it, half 1 uses tree B; each tree keeps its own root, so
+    // nothing is swapped and the trees stay exactly complementary.  Parts of a half follow one another: the
+    // broadcast of part k runs beside the reduction of part k+1.
+    const size_t h0 = b.count / 2, h1 = b.count - h0;
+    const int dtype = b.dtype, op = b.op;
+    reduction_fn_t fn = b.fn;
     void* recv = b.recv;
-    if (h0)
-        s.add<subsched_entry>([=](sched& sub) { tree(sub, recv, h0, root0, 0); }, "DTREE_A");
-    s.add<subsched_entry>([=](sched& sub) { tree(sub, at(recv, h0, dtype_size(dtype)), h1, root1, 1000); }, "DTREE_B");
+    for (int which = 0; which < 2; which++) {
+        const size_t n = which == 0 ? h0 : h1;
+        if (n == 0)
+            continue;
+        void* base = which == 0 ? recv : at(recv, h0, esz);
+        const bin_tree t(N, r, which, -1);
+        const size_t parts = dtree_parts(n);
+        const uint64_t tag0 = 4000 * (uint64_t)which;
+        s.add<subsched_entry>(
+            [=](sched& half) {
+                for (size_t k = 0; k <= parts; k++) {
+                    if (k < parts) {
+                        size_t o, m;
+                        chunk_range(n, parts, k, o, m);
+                        void* p = at(base, o, esz);
+                        half.add<subsched_entry>(
+                            [=](sched& ss) { reduce_bin_tree(ss, p, m, dtype, op, fn, t, tag0 + k); }, "DTREE_R");
+                    }
+                    if (k >= 1) {
+                        size_t o, m;
+                        chunk_range(n, parts, k - 1, o, m);
+                        void* p = at(base, o, esz);
+                        half.add<subsched_entry>(
+                            [=](sched& ss) { bcast_bin_tree(ss, p, m * esz, t, tag0 + 2000 + (k - 1)); }, "DTREE_B");
+                    }
+                    half.add_barrier();
+                }
+            },
+            which == 0 ? "DTREE_A" : "DTREE_B");
+    }
     s.add_barrier();
 }
 

@@ -37,6 +37,17 @@ void allreduce_2d(sched& s, const buf_desc& b);
 void allreduce_ring_rma(sched& s, const buf_desc& b);
 void allreduce_double_tree(sched& s, const buf_desc& b);
 
+// one rank's neighbours in one of the two complementary binary trees (which = 0 / 1) over `size` ranks;
+// root >= 0 puts that rank at the top (it swaps places with the tree's own root), -1 keeps the tree's root
+struct bin_tree {
+    bin_tree(int size, int rank, int which, int root);
+    int parent = -1, left = -1, right = -1;
+    int root_rank = -1;
+};
+// halves of the message travel through the two trees at the same time
+void bcast_double_tree(sched& s, void* buf, size_t count, int dtype, int root);
+void reduce_double_tree(sched& s, const buf_desc& b, int root);
+
 // reduce_scatter: send has recv_count * size elements; recv gets block `rank`
 void reduce_scatter_ring(sched& s, const buf_desc& b); // b.count = recv_count
 void reduce_scatter_naive(sched& s, const buf_desc& b);
@@ -51,6 +62,8 @@ void allgatherv_naive(sched& s, const void* send, void* recv, const std::vector<
                       const std::vector<size_t>& offs, int dtype, uint64_t step_base = 0);
 void allgatherv_ring(sched& s, const void* send, void* recv, const std::vector<size_t>& counts,
                      const std::vector<size_t>& offs, int dtype, uint64_t step_base = 0);
+void allgatherv_flat(sched& s, const void* send, void* recv, const std::vector<size_t>& counts,
+                     const std::vector<size_t>& offs, int dtype);
 void allgatherv_multi_bcast(sched& s, const void* send, void* recv, const std::vector<size_t>& counts,
                             const std::vector<size_t>& offs, int dtype);
 // vector-of-buffers form: one destination buffer per rank

@@ -272,8 +272,9 @@ std::string coll_cache_key(const host_comm& comm, const coll_param& p, const col
 // ---- CPU schedule construction --------------------------------------------------------------
 namespace {
 
+// `part` of `parts` (block-sliced collectives only): the schedule handles the part-th slice of every block
 void build_cpu(sched& s, host_comm& comm, const coll_param& p, const coll_attr& attr, size_t off_elems,
-               size_t count_elems) {
+               size_t count_elems, int part = 0, int parts = 1) {
     const int N = comm.size();
     const size_t esz = dtype_size(p.dtype);
     selector_param sp;
@@ -318,10 +319,25 @@ void build_cpu(sched& s, host_comm& comm, const coll_param& p, const coll_attr& 
                 break;
             }
             std::vector<size_t> offs = prefix(counts);
+            if (parts > 1) {
+                // slice k of every rank's block, gathered into the matching places of recv
+                std::vector<size_t> pc(N), po(N);
+                for (int q = 0; q < N; q++) {
+                    std::vector<size_t> c1, o1;
+                    algo::block_partition(counts[q], parts, c1, o1);
+                    pc[q] = c1[part];
+                    po[q] = offs[q] + o1[part];
+                }
+                const char* src = p.send_buf ? (const char*)p.send_buf + (po[comm.rank()] - offs[comm.rank()]) * esz : nullptr;
+                algo::allgatherv_ring(s, src, p.recv_buf, pc, po, p.dtype);
+                break;
+            }
             if (a == "ring")
                 algo::allgatherv_ring(s, p.send_buf, p.recv_buf, counts, offs, p.dtype);
             else if (a == "multi_bcast")
                 algo::allgatherv_multi_bcast(s, p.send_buf, p.recv_buf, counts, offs, p.dtype);
+            else if (a == "flat")
+                algo::allgatherv_flat(s, p.send_buf, p.recv_buf, counts, offs, p.dtype);
             else
                 algo::allgatherv_naive(s, p.send_buf, p.recv_buf, counts, offs, p.dtype);
             break;
@@ -332,11 +348,23 @@ void build_cpu(sched& s, host_comm& comm, const coll_param& p, const coll_attr& 
             std::vector<size_t> rc = p.ctype == coll_alltoall ? std::vector<size_t>(N, p.count) : p.recv_counts;
             sp.bytes = total(sc) * esz;
             const std::string a = algorithm_selector::get().select_cpu(sp);
+            std::vector<size_t> so = prefix(sc), ro = prefix(rc);
+            if (parts > 1) {
+                for (int q = 0; q < N; q++) { // slice `part` of every block, on the send and on the recv side
+                    std::vector<size_t> c1, o1;
+                    algo::block_partition(sc[q], parts, c1, o1);
+                    so[q] += o1[part];
+                    sc[q] = c1[part];
+                    algo::block_partition(rc[q], parts, c1, o1);
+                    ro[q] += o1[part];
+                    rc[q] = c1[part];
+                }
+            }
             if (a == "scatter")
-                algo::alltoallv_scatter(s, p.send_buf, sc, prefix(sc), p.recv_buf, rc, prefix(rc), p.dtype,
+                algo::alltoallv_scatter(s, p.send_buf, sc, so, p.recv_buf, rc, ro, p.dtype,
                                         env_data::get().alltoall_scatter_max_ops);
             else
-                algo::alltoallv_naive(s, p.send_buf, sc, prefix(sc), p.recv_buf, rc, prefix(rc), p.dtype);
+                algo::alltoallv_naive(s, p.send_buf, sc, so, p.recv_buf, rc, ro, p.dtype);
             break;
         }
         case coll_barrier: {
@@ -361,6 +389,8 @@ void build_cpu(sched& s, host_comm& comm, const coll_param& p, const coll_attr& 
                 algo::bcast_naive(s, rbuf, count_elems * esz, p.root);
             else if (a == "ring")
                 algo::bcast_ring(s, rbuf, count_elems, p.dtype, p.root);
+            else if (a == "double_tree")
+                algo::bcast_double_tree(s, rbuf, count_elems, p.dtype, p.root);
             else
                 algo::bcast_tree(s, rbuf, count_elems * esz, p.root);
             break;
@@ -374,6 +404,8 @@ void build_cpu(sched& s, host_comm& comm, const coll_param& p, const coll_attr& 
                 algo::reduce_rabenseifner(s, b, p.root);
             else if (a == "ring")
                 algo::reduce_ring(s, b, p.root);
+            else if (a == "double_tree")
+                algo::reduce_double_tree(s, b, p.root);
             else
                 algo::reduce_tree(s, b, p.root);
             break;
@@ -388,29 +420,84 @@ void build_cpu(sched& s, host_comm& comm, const coll_param& p, const coll_attr& 
                 algo::reduce_scatter_naive(s, b);
             break;
         }
-        case coll_send: algo::send_direct(s, p.send_buf, p.count * esz, p.peer, 0); break;
-        case coll_recv: algo::recv_direct(s, p.recv_buf, p.count * esz, p.peer, 0); break;
+        case coll_send:
+        case coll_recv: {
+            // pieces of at most the large-message size, one tag each (reference parallelizer.cpp:326-333)
+            const size_t big = std::max<size_t>(env_data::get().large_msg_size, 1);
+            const size_t bytes = p.count * esz;
+            size_t done = 0;
+            uint64_t step = 0;
+            do {
+                const size_t n = std::min(big, bytes - done);
+                if (p.ctype == coll_send)
+                    algo::send_direct(s, (const char*)p.send_buf + done, n, p.peer, step);
+                else
+                    algo::recv_direct(s, (char*)p.recv_buf + done, n, p.peer, step);
+                done += n;
+                step++;
+            } while (done < bytes);
+            break;
+        }
         default: CCL_THROW("unsupported collective ", (int)p.ctype);
     }
 }
 
-// how many partial schedules (reference parallelizer.cpp:77-154)
-int part_count(const host_comm& comm, const coll_param& p, size_t bytes) {
+// How many partial schedules an operation is cut into (reference parallelizer.cpp:77-154, 224-330):
+//  * allreduce / reduce / broadcast: one per worker once the message is long enough, and never fewer than
+//    bytes / CCL_ATL_LARGE_MSG_SIZE (1 GiB), so that no single transport message exceeds that size;
+//  * allgather(v): the ring form is cut per worker (part k gathers the k-th slice of every rank's block),
+//    multi_bcast and flat already spread their peers over sub-schedules, direct / naive stay whole;
+//  * alltoall(v): naive and scatter are cut into min(ranks, workers) parts (part k moves the k-th slice of
+//    every block), in-place calls stay whole;
+//  * reduce_scatter stays whole; send / recv are cut into pieces of at most the large-message size inside
+//    their one schedule (build_cpu).
+int part_count(const host_comm& comm, const coll_param& p, size_t bytes, const std::string& algo_name) {
     const int workers = executor::get().worker_count();
-    if (workers <= 1)
-        return 1;
     const env_data& env = env_data::get();
     const bool is_bcast = p.ctype == coll_bcast || p.ctype == coll_broadcast;
-    const bool splittable = p.ctype == coll_allreduce || p.ctype == coll_reduce || is_bcast;
-    if (!splittable || p.count < (size_t)workers * 64)
+    const bool reduce_like = p.ctype == coll_allreduce || p.ctype == coll_reduce || is_bcast;
+    if (reduce_like) {
+        const size_t esz = dtype_size(p.dtype);
+        const size_t big = std::max<size_t>(env.large_msg_size, 1);
+        size_t parts = 1;
+        if (is_bcast && env.bcast_part_count > 0)
+            // CCL_BCAST_PART_COUNT fixes the split of a broadcast
+            parts = std::min<size_t>(std::min<size_t>(env.bcast_part_count, 64), std::max<size_t>(p.count, 1));
+        else if (workers > 1 && p.count >= (size_t)workers * 64 && bytes > env.max_short_size &&
+                 bytes >= (size_t)workers * env.min_chunk_size)
+            // CCL_MAX_SHORT_SIZE keeps messages up to that size whole (reference parallelizer.cpp:224-235)
+            parts = workers;
+        const size_t need = (p.count * esz + big - 1) / big;
+        parts = std::max(parts, std::min<size_t>(need, 1024));
+        return (int)std::max<size_t>(1, std::min(parts, std::max<size_t>(p.count, 1)));
+    }
+    if (workers <= 1)
         return 1;
-    // CCL_BCAST_PART_COUNT fixes the split of a broadcast; CCL_MAX_SHORT_SIZE keeps messages up to
-    // that size whole (reference parallelizer.cpp:224-235)
-    if (is_bcast && env.bcast_part_count > 0)
-        return (int)std::min<size_t>(std::min<size_t>(env.bcast_part_count, 64), p.count);
-    if (bytes <= env.max_short_size || bytes < (size_t)workers * env.min_chunk_size)
-        return 1;
-    return workers;
+    if (p.ctype == coll_allgather || p.ctype == coll_allgatherv) {
+        if (algo_name != "ring" || !p.recv_bufs.empty())
+            return 1;
+        size_t least = (size_t)-1;
+        if (p.ctype == coll_allgather)
+            least = p.count;
+        else
+            for (size_t c : p.recv_counts)
+                least = std::min(least, c);
+        if (bytes <= env.max_short_size || least < (size_t)workers * 64)
+            return 1;
+        return workers;
+    }
+    if (p.ctype == coll_alltoall || p.ctype == coll_alltoallv) {
+        if (algo_name == "direct" || p.send_buf == p.recv_buf || !p.send_buf)
+            return 1;
+        // both sides of every block must cut it alike: the cut depends on the block sizes only when all of them
+        // are long enough, which a rank can check for its own blocks; equal blocks (alltoall) always qualify
+        if (p.ctype == coll_alltoallv)
+            return 1;
+        if (bytes <= env.max_short_size || p.count < (size_t)workers * 64)
+            return 1;
+        return std::min(comm.size(), workers);
+    }
+    return 1;
 }
 
 std::unique_ptr<master_sched> build_master(host_comm& comm, const coll_param& p, const coll_attr& attr,
@@ -424,7 +511,19 @@ std::unique_ptr<master_sched> build_master(host_comm& comm, const coll_param& p,
     if (p.ctype == coll_barrier)
         m->priority = 1 << 30; // barriers drain first
     const size_t bytes = selection_bytes(comm, p);
-    const int parts = part_count(comm, p, bytes);
+    std::string algo_name;
+    if (p.ctype != coll_barrier && p.ctype != coll_send && p.ctype != coll_recv) {
+        selector_param sp;
+        sp.ctype = p.ctype;
+        sp.comm_size = comm.size();
+        sp.vector_buf = !p.recv_bufs.empty();
+        sp.custom_fn = attr.reduction_fn != nullptr;
+        sp.scaleout = attr.scaleout;
+        sp.count = p.count;
+        sp.bytes = bytes;
+        algo_name = algorithm_selector::get().select_cpu(sp);
+    }
+    const int parts = part_count(comm, p, bytes, algo_name);
     std::vector<size_t> cnt, off;
     algo::block_partition(p.count, parts, cnt, off);
     std::vector<std::function<bool()>> deps;
@@ -439,6 +538,8 @@ std::unique_ptr<master_sched> build_master(host_comm& comm, const coll_param& p,
         }
         if (parts == 1)
             build_cpu(*s, comm, p, attr, 0, p.count);
+        else if (p.ctype == coll_allgather || p.ctype == coll_allgatherv || p.ctype == coll_alltoall)
+            build_cpu(*s, comm, p, attr, 0, p.count, i, parts); // part i: the i-th slice of every block
         else
             build_cpu(*s, comm, p, attr, off[i], cnt[i]);
     }

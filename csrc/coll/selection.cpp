@@ -179,8 +179,6 @@ std::string algorithm_selector::select_cpu(const selector_param& p) const {
         fallback_allowed("cannot address per-rank destination buffers");
         algo = "naive"; // per-rank destination buffers: only the naive pattern addresses them
     }
-    if (algo == "flat")
-        algo = "naive";
     return algo;
 }
 

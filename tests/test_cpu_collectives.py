@@ -141,6 +141,142 @@ def test_other_collectives_algorithm_overrides(env):
     assert all(run_ranks(_others, 3, env=env))
 
 
+def _split_ops(comm):
+    """Sizes long enough for every partition rule: ring allgather(v) cut per worker, alltoall cut per worker,
+    allreduce / broadcast / reduce and send / recv cut by the large-message size."""
+    W, r = comm.size, comm.rank
+    n = 5003
+    send = (np.arange(n) + 7 * r).astype(np.float32)
+    recv = np.zeros(n * W, np.float32)
+    comm.allgather(send, recv).wait()
+    assert np.array_equal(recv, np.concatenate([(np.arange(n) + 7 * p).astype(np.float32) for p in range(W)]))
+    counts = [3001 + 500 * p for p in range(W)]
+    recv = np.zeros(sum(counts), np.float64)
+    comm.allgatherv(np.arange(counts[r], dtype=np.float64) + r, recv, counts).wait()
+    assert np.array_equal(recv, np.concatenate([np.arange(c, dtype=np.float64) + p for p, c in enumerate(counts)]))
+    inplace = np.zeros(n * W, np.float32)
+    inplace[r * n:(r + 1) * n] = send
+    comm.allgather(inplace[r * n:(r + 1) * n], inplace).wait()
+    assert np.array_equal(inplace, np.concatenate([(np.arange(n) + 7 * p).astype(np.float32) for p in range(W)]))
+    a = (np.arange(W * n) + 100000 * r).astype(np.int64)
+    b = np.zeros(W * n, np.int64)
+    comm.alltoall(a, b).wait()
+    assert np.array_equal(b, np.concatenate([(np.arange(n) + n * r + 100000 * p) for p in range(W)]).astype(np.int64))
+    x = (np.arange(32771) % 13 + r).astype(np.float32)
+    comm.allreduce(x).wait()
+    assert np.array_equal(x, ((np.arange(32771) % 13) * W + sum(range(W))).astype(np.float32))
+    buf = np.full(20001, float(r), np.float64)
+    comm.broadcast(buf, root=W - 1).wait()
+    assert np.all(buf == W - 1)
+    out = np.zeros(9999, np.float32)
+    comm.reduce(np.full(9999, float(r + 1), np.float32), out, root=0).wait()
+    if r == 0:
+        assert np.all(out == W * (W + 1) / 2)
+    nxt, prv = (r + 1) % W, (r - 1) % W
+    got = np.zeros(30000, np.int32)
+    e1 = comm.recv(got, prv)
+    e2 = comm.send(np.arange(30000, dtype=np.int32) + r, nxt)
+    e1.wait()
+    e2.wait()
+    assert np.array_equal(got, np.arange(30000, dtype=np.int32) + prv)
+    return True
+
+
+@pytest.mark.parametrize("env", [
+    {"CCL_WORKER_COUNT": "2", "CCL_ALLGATHER": "ring", "CCL_ALLGATHERV": "ring", "CCL_ALLTOALL": "naive"},
+    {"CCL_WORKER_COUNT": "3", "CCL_ALLGATHER": "ring", "CCL_ALLGATHERV": "ring", "CCL_ALLTOALL": "scatter",
+     "CCL_ATL_LARGE_MSG_SIZE": "4096"},
+    {"CCL_ATL_LARGE_MSG_SIZE": "10000"},
+], ids=["two-workers", "three-workers-small-large-msg", "one-worker-small-large-msg"])
+def test_partition_rules_of_every_collective(env):
+    assert all(run_ranks(_split_ops, 3, env=env))
+
+
+def test_double_tree_is_a_pair_of_complementary_binary_trees():
+    """Both trees span all ranks with at most two children per node, the parent / child relations agree, and
+    a rank that forwards data in one tree (has children) is a leaf in the other, except where an odd size
+    leaves no choice; an explicit root swaps places with the tree's own root."""
+    import ctypes as C
+
+    from oneccl_b200 import _lib
+
+    lib = _lib.load()
+
+    def tree(n, which, root=-1):
+        nodes = []
+        for r in range(n):
+            out = (C.c_int * 4)()
+            assert lib.cclx_bin_tree(n, r, which, root, out) == 0
+            nodes.append(tuple(out))
+        return nodes
+
+    for n in list(range(2, 34)) + [64, 100]:
+        inner = []
+        for which in (0, 1):
+            t = tree(n, which)
+            roots = [r for r in range(n) if t[r][0] < 0]
+            assert roots == [t[0][3]], (n, which, roots)
+            seen = {roots[0]}
+            stack = [roots[0]]
+            depth = {roots[0]: 0}
+            while stack:  # every rank reachable exactly once, children point back at their parent
+                u = stack.pop()
+                for ch in t[u][1:3]:
+                    if ch >= 0:
+                        assert ch not in seen and t[ch][0] == u, (n, which, u, ch)
+                        seen.add(ch)
+                        depth[ch] = depth[u] + 1
+                        stack.append(ch)
+            assert len(seen) == n
+            assert max(depth.values()) <= n.bit_length()  # logarithmic height
+            inner.append({r for r in range(n) if t[r][1] >= 0 or t[r][2] >= 0})
+        both = inner[0] & inner[1]
+        assert len(both) <= 1, (n, both)  # complementary: forwarding in one tree means leaf in the other
+    t = tree(10, 0, root=7)
+    assert t[7][0] == -1 and t[7][3] == 7
+
+
+def _double_tree_ops(comm):
+    W, r = comm.size, comm.rank
+    for count in (1, 2, 17, 4099):
+        base = np.arange(count, dtype=np.float64) % 11
+        for root in sorted({0, W - 1, W // 2}):
+            buf = (base + 100 * root).astype(np.float32) if r == root else np.zeros(count, np.float32)
+            comm.broadcast(buf, root=root).wait()
+            assert np.array_equal(buf, (base + 100 * root).astype(np.float32)), ("bcast", count, root)
+            out = np.zeros(count, np.float32)
+            comm.reduce((base + r).astype(np.float32), out, root=root).wait()
+            if r == root:
+                assert np.array_equal(out, (base * W + sum(range(W))).astype(np.float32)), ("reduce", count, root)
+        x = (base + r).astype(np.float32)
+        comm.allreduce(x).wait()
+        assert np.array_equal(x, (base * W + sum(range(W))).astype(np.float32)), ("allreduce", count)
+    return True
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 7])
+@pytest.mark.parametrize("parts", ["1", "3"])
+def test_double_tree_broadcast_reduce_allreduce(world, parts):
+    env = {"CCL_BCAST": "double_tree", "CCL_BROADCAST": "double_tree", "CCL_REDUCE": "double_tree",
+           "CCL_ALLREDUCE": "double_tree", "CCL_DTREE_PARTITION_COUNT": parts}
+    assert all(run_ranks(_double_tree_ops, world, env=env))
+
+
+def _bcast_1000(comm):
+    b = np.arange(1000, dtype=np.float32)
+    comm.broadcast(b, root=0).wait()
+    return True
+
+
+def test_double_tree_schedule_uses_both_trees(capfd):
+    """The schedule dump of a double-tree broadcast names the two tree sub-schedules: the name is not an
+    alias of the single binomial tree."""
+    run_ranks(_bcast_1000, 4, env={"CCL_BCAST": "double_tree", "CCL_BROADCAST": "double_tree", "CCL_SCHED_DUMP": "1",
+                                   "CCL_LOG_LEVEL": "info"})
+    text = "".join(capfd.readouterr())
+    assert "DTREE_BCAST_A" in text and "DTREE_BCAST_B" in text, text[-2000:]
+
+
 def _lowp_and_custom(comm):
     import ctypes as C
 
