@@ -216,6 +216,10 @@ CCLX_API int cclx_comm_rank(void* c) {
 CCLX_API int cclx_comm_size(void* c) {
     return ((comm_handle*)c)->c->size();
 }
+// name of the transport that carries the communicator's host traffic ("tcp", "ofi:<provider>")
+CCLX_API const char* cclx_comm_transport_name(void* c) {
+    return ((comm_handle*)c)->c->atl().transport().name();
+}
 // transport counters of the communicator's world: 0 messages sent, 1 bytes sent, 2 bytes received,
 // 3 unexpected messages, 4 one-sided writes done as cross-memory copies, 5 one-sided writes sent as messages,
 // 6 long messages sent by rendezvous (read out of this process by the receiver)

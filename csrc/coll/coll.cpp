@@ -303,8 +303,13 @@ void build_cpu(sched& s, host_comm& comm, const coll_param& p, const coll_attr& 
                 algo::allreduce_2d(s, b);
             else if (a == "double_tree")
                 algo::allreduce_double_tree(s, b);
-            else if (a == "ring_rma")
-                algo::allreduce_ring_rma(s, b);
+            else if (a == "ring_rma") {
+                // a transport without one-sided writes (ofi) runs the two-sided ring
+                if (comm.atl().transport().has_rma())
+                    algo::allreduce_ring_rma(s, b);
+                else
+                    algo::allreduce_ring(s, b);
+            }
             else
                 CCL_THROW("allreduce: unknown algorithm ", a);
             break;

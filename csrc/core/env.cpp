@@ -352,6 +352,7 @@ void env_data::parse() {
     get_bool("CCL_CUDA_COPY_ENGINE", cuda_copy_engine);
     get_size("CCL_CUDA_IPC_CACHE_ENTRIES", ipc_cache_entries);
     get_size("CCL_ATL_LARGE_MSG_SIZE", large_msg_size);
+    get_str("CCL_OFI_LIBRARY_PATH", ofi_lib_path);
     get_bool("CCL_CUDA_AUTO_REGISTER", auto_register);
     get_size("CCL_CUDA_AUTO_REGISTER_MIN_BYTES", auto_register_min);
     warn_about_names_without_effect();

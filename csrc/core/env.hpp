@@ -137,6 +137,7 @@ struct env_data {
     bool cuda_copy_engine = false; // large equal-block allgather into symmetric / registered memory goes through the copy engines
     bool cuda_graph_safe = true;
     size_t ipc_cache_entries = 1000; // registered allocations that may be open at once
+    std::string ofi_lib_path; // CCL_OFI_LIBRARY_PATH: libfabric.so to open for CCL_ATL_TRANSPORT=ofi
     size_t large_msg_size = (size_t)1 << 30; // no single transport message of a split operation exceeds this
     size_t ag_nvls_max_block = 1u << 20; // allgather: blocks up to this size go out as multimem.st, larger ones as peer stores
     bool auto_register = true; // ordinary device buffers are shared with the peers automatically (buffer_exchange)

@@ -3,15 +3,17 @@
 //
 // Same contract as the reference's atl_base_comm (src/atl/atl_base_comm.hpp:32-281)
 // and its 64-bit tag layout (src/comm/atl_tag.hpp:28-190): a message is matched
-// by (source rank, tag) where tag = comm_id | sched_id | op_id.  The transports
-// behind it are this library's own: `tcp` (a socket mesh, any host) and `shm`
-// (single-producer rings in POSIX shared memory between ranks of one host,
-// layered under tcp); MPI / libfabric are not linked.
+// by (source rank, tag) where tag = comm_id | sched_id | op_id.  Two transports sit
+// behind it: this library's own `tcp` (a socket mesh on any host, with single-producer
+// rings in POSIX shared memory and cross-memory rendezvous between ranks of one host),
+// and `ofi` (libfabric's tagged messages, the library opened with dlopen).  MPI is not
+// available in the image; CCL_ATL_TRANSPORT=mpi falls back to `tcp` with a notice.
 #pragma once
 #include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <memory>
+#include <string>
 #include <vector>
 
 namespace cclx {
@@ -81,6 +83,7 @@ public:
     virtual const char* name() const = 0;
     // one-sided writes: register, tell the region to the writers by an ordinary message, write.
     // Writes of one rank to one region arrive in the order they were issued on one endpoint.
+    virtual bool has_rma() const { return true; }
     virtual atl_mr mr_reg(void* buf, size_t len) = 0;
     virtual void mr_dereg(const atl_mr& mr) = 0;
     virtual void rma_write(int ep, const void* buf, size_t len, const atl_mr& mr, uint64_t offset, atl_req* req) = 0;
@@ -90,6 +93,9 @@ public:
 };
 
 std::shared_ptr<atl_transport> create_tcp_transport(pmi& pm, int ep_count);
+// libfabric (opened at run time) behind the same interface; null with the reason in `why` when some rank
+// cannot load the library
+std::shared_ptr<atl_transport> create_ofi_transport(pmi& pm, int ep_count, std::string& why);
 
 // A communicator's view of the transport: rank translation + comm id.
 class atl_comm {

@@ -211,6 +211,11 @@ class Communicator:
     def id(self) -> int:
         return int(self._lib.cclx_comm_id(self._h))
 
+    @property
+    def transport_name(self) -> str:
+        """"tcp" (the library's socket / shared-memory mesh) or "ofi:<provider>" (libfabric)."""
+        return self._lib.cclx_comm_transport_name(self._h).decode()
+
     def transport_stats(self) -> dict:
         """Counters of the host transport under this communicator: messages and bytes, messages that
         arrived before their receive was posted, one-sided writes by cross-memory copy and by message."""
