@@ -551,7 +551,10 @@ private:
             int fd = ::shm_open(mine.name, O_CREAT | O_EXCL | O_RDWR | O_CLOEXEC, 0600);
             if (fd >= 0) {
                 if (::ftruncate(fd, (off_t)seg_bytes) == 0) {
-                    my_seg = ::mmap(nullptr, seg_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+                    // populated up front: a ring whose pages are touched for the first time costs a page fault per
+                    // 4 KiB on both sides, which made 16 KiB messages take 22 us instead of 14 until the whole ring
+                    // had been walked once (hundreds of operations)
+                    my_seg = ::mmap(nullptr, seg_bytes, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, fd, 0);
                     if (my_seg == MAP_FAILED)
                         my_seg = nullptr;
                 }
@@ -579,7 +582,7 @@ private:
                 int fd = ::shm_open(all[p].name, O_RDWR | O_CLOEXEC, 0600);
                 CCL_THROW_IF_NOT(fd >= 0, "can not open the shared-memory segment of rank ", p, ": ",
                                  std::strerror(errno));
-                void* seg = ::mmap(nullptr, seg_bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+                void* seg = ::mmap(nullptr, seg_bytes, PROT_READ | PROT_WRITE, MAP_SHARED | MAP_POPULATE, fd, 0);
                 ::close(fd);
                 CCL_THROW_IF_NOT(seg != MAP_FAILED, "can not map the shared-memory segment of rank ", p);
                 maps_.push_back({ seg, seg_bytes });
