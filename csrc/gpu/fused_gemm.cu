@@ -121,8 +121,14 @@ void gemm_bf16_plain(const void* A, const void* B, void* C, int M, int N, int K,
     launch(nullptr, P, bn, g, 1, false, st);
 }
 
+// CTA-pair form of the fused kernels (fused_gemm_2sm.cu)
+bool fused_gemm2_usable(int world, int M, int N, int K);
+int fused_gemm2_max_ctas();
+void launch_fused_gemm2(const dev::comm_dev* tab, const fused_params& P, int ctas, int ranks, bool coop, cudaStream_t st);
+
 struct fused_plan {
     device_comm* dc = nullptr;
+    bool two_sm = false; // CTA pairs (cta_group::2): rows per rank a multiple of 256, N a multiple of 256
     int mode = 0, M = 0, N = 0, K = 0, epilogue = 0, n_comm = 0, ctas = 0, bn = 256;
     int entries = 1;
     size_t x_off = 0, part_off = 0;
@@ -181,10 +187,19 @@ fused_plan* fused_plan_create(device_comm& dc, int mode, int M, int N, int K, in
     if (ctas > 0)
         per_rank = std::min(per_rank, ctas);
     // n_comm < 0 (or CCL_CUDA_AG_GEMM_CE=1 with n_comm == 0): the copy engines gather, no copy CTAs
+    p->two_sm = W > 1 && fused_gemm2_usable(W, M, N, K);
+    if (p->two_sm) {
+        const int cap = fused_gemm2_max_ctas() / (dc.emulated() ? W : 1);
+        per_rank = std::min(per_rank, cap) & ~1; // whole pairs, all of them resident at once
+        if (per_rank < 4)
+            p->two_sm = false;
+    }
     p->ce_gather = mode == GM_AG && W > 1 && (n_comm < 0 || (n_comm == 0 && env_data::get().ag_gemm_ce));
     p->n_comm = mode == GM_AG ? (n_comm > 0 ? n_comm : std::max(1, per_rank / 8)) : 0;
     if (W == 1)
         p->n_comm = mode == GM_AG ? 1 : 0;
+    if (p->two_sm && p->n_comm > 0)
+        p->n_comm = std::max(2, (p->n_comm + 1) & ~1); // copy CTAs come in pairs too (clusters of two)
     if (p->ce_gather) {
         p->n_comm = 0;
         CUDA_CHECK(cudaStreamCreateWithFlags(&p->side, cudaStreamNonBlocking));
@@ -274,13 +289,19 @@ void fused_plan_run(fused_plan* p, const void* const* A, const void* const* B, v
             p->lastA[e] = a;
         }
         if (B[e] != p->lastB[e]) {
-            p->P.r[e].tmB = make_map(B[e], p->N, p->K, p->bn);
+            p->P.r[e].tmB = make_map(B[e], p->N, p->K, p->two_sm ? 128 : p->bn); // a pair's CTA stages half of the B tile
             p->lastB[e] = B[e];
         }
         p->P.r[e].C = (__nv_bfloat16*)C[e];
     }
+    auto go = [&] {
+        if (p->two_sm)
+            launch_fused_gemm2(dc.table(), p->P, p->ctas, p->entries, dc.emulated(), st);
+        else
+            launch(dc.table(), p->P, p->bn, p->ctas, p->entries, dc.emulated(), st);
+    };
     if (!p->ce_gather) {
-        launch(dc.table(), p->P, p->bn, p->ctas, p->entries, dc.emulated(), st);
+        go();
         return;
     }
     // every rank has written its shard once it passed this barrier
@@ -304,7 +325,7 @@ void fused_plan_run(fused_plan* p, const void* const* A, const void* const* B, v
     }
     CUDA_CHECK(cudaEventRecord(p->ev_join, p->side));
     // the GEMM starts on the local shard at once and waits per 128-row block for the others
-    launch(dc.table(), p->P, p->bn, p->ctas, p->entries, dc.emulated(), st);
+    go();
     CUDA_CHECK(cudaStreamWaitEvent(st, p->ev_join, 0));
     // peers may overwrite their shard (next call) only after everybody has copied it
     launch_barrier(dc, st);

@@ -49,6 +49,62 @@ def test_gemm_silu_and_persistence(kernel):
     _check(out, _ref(a, w, silu=True), K)
 
 
+def _set_pairs(monkeypatch, on):
+    """CTA pairs (cta_group::2) on or off for the fused kernels; the knob is read when a plan is created."""
+    from oneccl_b200 import _lib
+
+    monkeypatch.setenv("CCL_CUDA_GEMM_2SM", "1" if on else "0")
+    _lib.load().cclx_env_reload()
+
+
+@pytest.mark.parametrize("pairs", [False, True], ids=["one-cta", "cta-pairs"])
+@pytest.mark.parametrize("world,shape", [(2, (1024, 1024, 512)), (4, (2048, 512, 448)), (2, (512, 256, 64))])
+@pytest.mark.parametrize("mode", ["ag_gemm", "gemm_rs_ring", "gemm_rs_owner"])
+def test_fused_gemm_larger_shapes_both_main_loops(monkeypatch, pairs, world, shape, mode):
+    """Several 256 x 256 tiles per shard, more K steps than pipeline stages, with the single-CTA main loop and
+    with CTA pairs, against the fp32 product."""
+    from oneccl_b200.ops.device_group import DeviceGroup
+    from oneccl_b200.ops.gemm import FusedPlan
+
+    _set_pairs(monkeypatch, pairs)
+    M, N, K = shape
+    grp = DeviceGroup.emulated(world, heap_bytes=128 << 20, staging_bytes=1 << 20)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    ws = [(torch.randn(N, K, generator=g, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(world)]
+    per = M // world
+    if mode == "ag_gemm":
+        plan = FusedPlan(grp, "ag_gemm", M, N, K, n_comm=2)
+        x = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+        for it in range(2):
+            for r in range(world):
+                plan.x_shard(r).copy_(x[r * per:(r + 1) * per] * (it + 1))
+            outs = plan.run(None, ws)
+            torch.cuda.synchronize()
+            grp.check()
+            for r in range(world):
+                assert plan.error(r) == 0
+                _check(outs[r], _ref(x * (it + 1), ws[r]), K)
+    else:
+        plan = FusedPlan(grp, "gemm_rs", M, N, K, n_comm=-2 if mode == "gemm_rs_ring" else -1)
+        hs = [torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+        full = sum(_ref(h, w) for h, w in zip(hs, ws))
+        for it in range(2):
+            outs = plan.run(hs, ws)
+            torch.cuda.synchronize()
+            grp.check()
+            for r in range(world):
+                assert plan.error(r) == 0
+                ref = full[r * per:(r + 1) * per]
+                err = (outs[r].float() - ref).abs().max().item()
+                assert err <= 2.0e-2 * ref.abs().max().item() + 1e-3, (mode, err)
+    plan.close()
+    grp.close()
+    monkeypatch.delenv("CCL_CUDA_GEMM_2SM")
+    from oneccl_b200 import _lib
+
+    _lib.load().cclx_env_reload()
+
+
 @pytest.mark.parametrize("world", [2, 4])
 @pytest.mark.parametrize("n_comm", [2, -1], ids=["copy-ctas", "copy-engines"])
 def test_ag_gemm_emulated(world, n_comm):
