@@ -39,25 +39,61 @@ def ulysses_heads_to_seq(comm: Communicator, x: torch.Tensor) -> torch.Tensor:
     return recv.permute(1, 0, 2, 3).reshape(S // W, W * h, D)  # block p = heads of rank p
 
 
-def ring_pass(comm: Communicator, t: torch.Tensor) -> torch.Tensor:
-    """Sends ``t`` to rank + 1 and returns what rank - 1 sent (one step of a ring rotation)."""
+class _RingTransfer:
+    """A rotation step in flight: ``wait()`` returns what rank - 1 sent."""
+
+    def __init__(self, out, events, stream, keep):
+        self.out, self.events, self.stream, self.keep = out, events, stream, keep
+
+    def wait(self) -> torch.Tensor:
+        for e in self.events:
+            e.wait()
+        if self.stream is not None:  # device transfer on a side stream: order the caller's stream after it
+            torch.cuda.current_stream().wait_stream(self.stream)
+        return self.out
+
+
+_side_streams = {}
+
+
+def ring_pass_start(comm: Communicator, t: torch.Tensor) -> _RingTransfer:
+    """Starts sending ``t`` to rank + 1 and receiving from rank - 1 and returns at once, so that the caller
+    can compute on ``t`` while the next block travels.  Host tensors progress on the worker threads; CUDA
+    tensors move on a side stream (the group makes send and recv one launch)."""
     W, r = comm.size, comm.rank
     if W == 1:
-        return t.clone()
+        return _RingTransfer(t.clone(), [], None, None)
     out = torch.empty_like(t)
     src = t.contiguous()
+    stream = None
+    kw = {}
+    if t.is_cuda:
+        key = (t.device.index, id(comm))
+        if key not in _side_streams:
+            _side_streams[key] = torch.cuda.Stream(priority=torch.cuda.Stream.priority_range()[1])
+        stream = _side_streams[key]
+        stream.wait_stream(torch.cuda.current_stream())  # `t` is complete before it is sent
+        kw = {"stream": stream}
     group_start()
-    es = comm.send(src, (r + 1) % W)
-    er = comm.recv(out, (r - 1) % W)
+    es = comm.send(src, (r + 1) % W, **kw)
+    er = comm.recv(out, (r - 1) % W, **kw)
     group_end()
-    es.wait()
-    er.wait()
-    return out
+    if t.is_cuda:
+        src.record_stream(stream)
+        out.record_stream(stream)
+        return _RingTransfer(out, [], stream, src)  # stream order is enough; no host wait
+    return _RingTransfer(out, [es, er], None, src)
+
+
+def ring_pass(comm: Communicator, t: torch.Tensor) -> torch.Tensor:
+    """Sends ``t`` to rank + 1 and returns what rank - 1 sent (one step of a ring rotation)."""
+    return ring_pass_start(comm, t).wait()
 
 
 def ring_attention(comm: Communicator, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """Non-causal attention over a sequence sharded across the ranks: K / V blocks travel around the
-    ring while every rank keeps a running (max, sum, output) for its queries.  q, k, v: [s, H, D]."""
+    ring while every rank keeps a running (max, sum, output) for its queries.  The next block is on its way
+    while the current one is being multiplied.  q, k, v: [s, H, D]."""
     W = comm.size
     scale = q.shape[-1] ** -0.5
     qh = q.float().permute(1, 0, 2)  # [H, s, D]
@@ -66,6 +102,7 @@ def ring_attention(comm: Communicator, q: torch.Tensor, k: torch.Tensor, v: torc
     o = torch.zeros_like(qh)
     kv = torch.stack([k, v]).contiguous()
     for step in range(W):
+        nxt = ring_pass_start(comm, kv) if step + 1 < W else None
         kh = kv[0].float().permute(1, 0, 2)
         vh = kv[1].float().permute(1, 0, 2)
         sc = torch.matmul(qh, kh.transpose(1, 2)) * scale  # [H, s, s_blk]
@@ -75,6 +112,6 @@ def ring_attention(comm: Communicator, q: torch.Tensor, k: torch.Tensor, v: torc
         l = l * alpha + p.sum(-1)
         o = o * alpha.unsqueeze(-1) + torch.matmul(p, vh)
         m = m_new
-        if step + 1 < W:
-            kv = ring_pass(comm, kv)
+        if nxt is not None:
+            kv = nxt.wait()
     return (o / l.unsqueeze(-1)).permute(1, 0, 2).to(q.dtype)
