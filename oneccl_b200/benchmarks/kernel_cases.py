@@ -85,7 +85,7 @@ def main():
         t = _time(lambda: g.broadcast(xs, xs, root=0), args.launches)
         out.update(bytes_per_rank=n * 2, algorithmic_hbm_bytes=W * n * 2 * 2, seconds=t)
     elif case == "pack_fused":
-        g = emu(64)
+        g = emu(160)
         tensors = [[torch.randn(2048, device="cuda").to(dt) for _ in range(W)] for _ in range(256)]
         t = _time(lambda: g.allreduce_fused(tensors), args.launches)
         out.update(tensors=256, bytes_each=4096, seconds=t)
@@ -94,7 +94,7 @@ def main():
 
         T, H, topk = 1024, 4096, 2
         cap = T * topk * W
-        g = emu((cap * H * 2 >> 20) + 64)
+        g = emu((cap * H * 2 >> 20) + 192)  # the heap also holds the flag, staging and point-to-point regions
         xrecv = g.symm_empty((cap, H), dtype=dt)  # also stands in for the experts' output
         cnt = g.symm_empty((256 * W * W,), dtype=torch.int32)
         metas = [torch.zeros(2 * W + 2, dtype=torch.int32, device="cuda") for _ in range(W)]
