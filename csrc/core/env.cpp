@@ -346,6 +346,7 @@ void env_data::parse() {
     get_size("CCL_CUDA_REDUCE_SCATTER_PIPELINE_MIN", rs_pipelined_min);
     get_size("CCL_CUDA_ALLGATHERV_SMALL_THRESHOLD", ag_small_threshold);
     get_size("CCL_CUDA_ALLGATHER_NVLS_MAX_BLOCK", ag_nvls_max_block);
+    get_size("CCL_CUDA_REDUCE_SCATTER_NVLS_MAX_BLOCK", rs_nvls_max_block);
     get_int("CCL_CUDA_MAX_BLOCKS", cuda_max_blocks);
     get_int("CCL_CUDA_BLOCK_THREADS", cuda_block_threads);
     get_size("CCL_CUDA_WAIT_TIMEOUT_MS", wait_timeout_ms);
