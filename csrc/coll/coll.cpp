@@ -697,6 +697,7 @@ event_ptr hier_device_allreduce(host_comm& comm, coll_param& p, const coll_attr&
 
     // scratch: this rank's slice on the device, its mirror in pinned host memory (kept per thread, grown on demand)
     struct scratch {
+        cudaEvent_t last = nullptr; // recorded behind the last asynchronous use
         void* dev = nullptr;
         void* host = nullptr;
         size_t cap = 0;
@@ -705,9 +706,20 @@ event_ptr hier_device_allreduce(host_comm& comm, coll_param& p, const coll_attr&
                 cudaFree(dev);
             if (host)
                 cudaFreeHost(host);
+            if (last)
+                cudaEventDestroy(last);
         }
     };
-    static thread_local scratch sc;
+    // the scratch belongs to the communicator (released with its device state); `last` orders a later call on
+    // another stream behind the asynchronous tail of this one
+    std::shared_ptr<void>& slot = comm.device_scratch(0);
+    if (!slot)
+        slot = std::make_shared<scratch>();
+    scratch& sc = *std::static_pointer_cast<scratch>(slot);
+    if (!sc.last)
+        CUDA_CHECK(cudaEventCreateWithFlags(&sc.last, cudaEventDisableTiming));
+    else
+        CUDA_CHECK(cudaStreamWaitEvent(st, sc.last, 0));
     if (sc.cap < slice_bytes) {
         if (sc.dev)
             CUDA_CHECK(cudaFree(sc.dev));
@@ -753,7 +765,9 @@ event_ptr hier_device_allreduce(host_comm& comm, coll_param& p, const coll_attr&
     ag.count = rc;
     ag.deps.clear();
     coll_attr none;
-    return device_coll(*node, ag, none);
+    event_ptr done = device_coll(*node, ag, none);
+    CUDA_CHECK(cudaEventRecord(sc.last, st)); // the allgather still reads sc.dev: the next user of the scratch waits for it
+    return done;
 }
 
 // reduce_scatter on device buffers across nodes.  Send buffers are ordered by global rank, which the
@@ -786,6 +800,7 @@ event_ptr hier_device_reduce_scatter(host_comm& comm, coll_param& p, const coll_
     cudaStream_t st = (cudaStream_t)p.stream;
     stats().device_calls[coll_reduce_scatter]++;
     struct scratch {
+        cudaEvent_t last = nullptr; // recorded behind the last asynchronous use
         void *grouped = nullptr, *slice = nullptr, *host_in = nullptr, *host_out = nullptr;
         size_t cap_grouped = 0, cap_slice = 0, cap_out = 0;
         static void grow_dev(void*& ptr, size_t& cap, size_t want) {
@@ -809,7 +824,16 @@ event_ptr hier_device_reduce_scatter(host_comm& comm, coll_param& p, const coll_
                 cudaFreeHost(host_out);
         }
     };
-    static thread_local scratch sc;
+    // the scratch belongs to the communicator (released with its device state); `last` orders a later call on
+    // another stream behind the asynchronous tail of this one
+    std::shared_ptr<void>& slot = comm.device_scratch(1);
+    if (!slot)
+        slot = std::make_shared<scratch>();
+    scratch& sc = *std::static_pointer_cast<scratch>(slot);
+    if (!sc.last)
+        CUDA_CHECK(cudaEventCreateWithFlags(&sc.last, cudaEventDisableTiming));
+    else
+        CUDA_CHECK(cudaStreamWaitEvent(st, sc.last, 0));
     const size_t slice_bytes = (size_t)M * block;
     if (sc.cap_slice < slice_bytes) {
         if (sc.host_in)
@@ -897,6 +921,7 @@ event_ptr hier_device_allgather(host_comm& comm, coll_param& p, const coll_attr&
     cudaStream_t st = (cudaStream_t)p.stream;
     stats().device_calls[p.ctype]++;
     struct scratch {
+        cudaEvent_t last = nullptr; // recorded behind the last asynchronous use
         void *host_in = nullptr, *host_out = nullptr, *slice = nullptr, *grouped = nullptr;
         size_t cap_in = 0, cap_out = 0, cap_slice = 0, cap_grouped = 0;
         static void grow_host(void*& ptr, size_t& cap, size_t want) {
@@ -930,7 +955,16 @@ event_ptr hier_device_allgather(host_comm& comm, coll_param& p, const coll_attr&
                 cudaFree(grouped);
         }
     };
-    static thread_local scratch sc;
+    // the scratch belongs to the communicator (released with its device state); `last` orders a later call on
+    // another stream behind the asynchronous tail of this one
+    std::shared_ptr<void>& slot = comm.device_scratch(2);
+    if (!slot)
+        slot = std::make_shared<scratch>();
+    scratch& sc = *std::static_pointer_cast<scratch>(slot);
+    if (!sc.last)
+        CUDA_CHECK(cudaEventCreateWithFlags(&sc.last, cudaEventDisableTiming));
+    else
+        CUDA_CHECK(cudaStreamWaitEvent(st, sc.last, 0));
     scratch::grow_host(sc.host_in, sc.cap_in, block);
     scratch::grow_host(sc.host_out, sc.cap_out, slice_bytes);
     scratch::grow_dev(sc.slice, sc.cap_slice, slice_bytes);

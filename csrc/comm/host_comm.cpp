@@ -240,6 +240,8 @@ void host_comm::release_device() {
         }
         catch (...) {
         }
+        for (auto& sc : dev_scratch_)
+            sc.reset();
         dev_.reset();
     }
 }

@@ -56,6 +56,9 @@ public:
 
     // device side: created on demand (needs a CUDA device selected by the caller)
     gpu::device_comm* device();
+    // scratch memory of the hierarchical (node / cross-node) device collectives, one slot per collective:
+    // owned by the communicator, freed when its device state is released
+    std::shared_ptr<void>& device_scratch(int which) { return dev_scratch_[which]; }
     bool has_device() const { return dev_ != nullptr; }
     void init_device();
     void release_device();
@@ -77,6 +80,7 @@ private:
     std::shared_ptr<host_comm> node_, r2r_;
     std::vector<int> host_idx_;
     sched_cache cache_;
+    std::shared_ptr<void> dev_scratch_[3]; // scratch of the hierarchical device collectives (released with the device state)
     std::unique_ptr<gpu::bootstrap_if> dev_bs_; // outlives dev_: later handle exchanges (buffer registration) use it
     std::unique_ptr<gpu::device_comm> dev_;
     std::unique_ptr<pmi> dev_pm_;
