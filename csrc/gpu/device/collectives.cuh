@@ -1171,22 +1171,35 @@ static __global__ void __launch_bounds__(64) barrier_kernel(const comm_dev* tab,
 }
 
 // ---------------------------------------------------------------------------
-// point-to-point (eager).  Every ordered pair owns one data slot at the
-// receiver, split among P2P_BLOCKS blocks; block b of the sender talks to
-// block b of the receiver through its own pair of sequence words, so no
-// grid-wide synchronisation is needed.
+// point-to-point.  Every ordered pair owns one data slot (at the receiver,
+// written by the sender's stores; or, in pull mode, at the sender, read by the
+// receiver's loads), cut into lanes: independent chains of chunks, each with a ring of P2P_STAGES
+// buffers of P2P_CHUNK_BYTES and its own pair of counters, so no grid-wide
+// synchronisation is needed and a message of any size is one launch.
 // p2p flag area of rank x (peer-mapped), in words:
-//   ready[(p*P2P_BLOCKS)+b] : written by sender p  when part b of its message is in x's slot[p]
-//   ack  [(q*P2P_BLOCKS)+b] : written by receiver q when it drained part b of x's message to q
-// send: wait ack >= seq-1 on my side, push, fence, set ready at the peer.
-// recv: wait ready >= seq on my side, copy out, set ack at the peer.
-// Messages larger than the slot are split by the host into rounds.  One launch
-// serves a list of operations (blockIdx.z), which is how send/recv issued inside
-// a group run side by side without ordering deadlocks; both sides derive the
-// number of active blocks from the byte count.
+//   ready[(p*P2P_LANES)+l] : chunks that sender p has put into lane l of x's slot[p] so far
+//   ack  [(q*P2P_LANES)+l] : chunks of x's messages to q that q has drained from lane l so far
+// Chunk number n of a lane (counted over the life of the communicator) uses stage n % P2P_STAGES.
+// send: wait ack >= n + 1 - P2P_STAGES on my side, push, fence, set ready = n + 1 at the peer.
+// recv: wait ready >= n + 1 on my side, copy out, set ack = n + 1 at the peer.
+// Chunk k of a message goes through lane k % nl, where nl = min(chunks, lanes in use) depends on the byte
+// count alone, so the two sides agree on it without talking.  How many blocks serve the lanes is each
+// side's own choice (block b takes lanes b, b + nb, ... one after the other, in rising order): a launch
+// keeps all its blocks resident at once, whatever the number of operations in it, and because both
+// sides walk the lanes in the same order the lowest unfinished lane of a message is always being
+// served on both sides.  One launch serves a list of operations (blockIdx.z), which is how send/recv
+// issued inside a group run side by side without ordering deadlocks.
+//
+// Inside a block, warp 0 does the waiting and the signalling and the other warps copy, so that the
+// system-scope fence in front of a flag (a round trip over NVLink for the sender) overlaps the copy of
+// the next chunk:
+//   control: wait(j + 1); arrive GO[j + 1]; sync DONE[j]; release flag(j)
+//   copiers: sync GO[j]; copy item j; arrive DONE[j]
+// GO and DONE alternate between two named barriers each; the control warp reaches GO[j + 2] only after
+// DONE[j] completed, so a barrier is never entered for a later phase while an earlier one is open.
 // ---------------------------------------------------------------------------
 static __global__ void __launch_bounds__(1024)
-    sendrecv_kernel(const comm_dev* tab, p2p_layout L, p2p_ops r0, const p2p_ops* emu_tab, int emu, size_t round_off) {
+    sendrecv_kernel(const comm_dev* tab, p2p_layout L, p2p_ops r0, const p2p_ops* emu_tab, int emu) {
     const int er = emu ? (int)blockIdx.y : 0;
     const comm_dev& c = tab[er];
     const p2p_ops& ops = emu ? emu_tab[er] : r0;
@@ -1197,60 +1210,86 @@ static __global__ void __launch_bounds__(1024)
     const int peer = op.peer;
     if (peer < 0)
         return;
-    // this round moves bytes [round_off, round_off + slot) of the message; a zero-byte
-    // message still synchronises the pair once
-    if (round_off >= op.bytes && !(op.bytes == 0 && round_off == 0))
-        return;
-    size_t bytes = op.bytes - round_off;
-    if (bytes > L.slot_bytes)
-        bytes = L.slot_bytes;
-    // both sides derive the same number of active blocks from the byte count
-    int nb = (int)(bytes >> 16);
-    nb = nb < 1 ? 1 : (nb > (int)gridDim.x ? (int)gridDim.x : nb);
+    // a zero-byte message still synchronises the pair once
+    const size_t nchunks = op.bytes ? (op.bytes + P2P_CHUNK_BYTES - 1) / P2P_CHUNK_BYTES : 1;
+    const int nl = nchunks < (size_t)L.lanes ? (int)nchunks : L.lanes;
+    const int nb = nl < (int)gridDim.x ? nl : (int)gridDim.x;
     const int b = blockIdx.x;
     if (b >= nb)
         return;
-    size_t lo, hi;
-    split_range((bytes + 15) >> 4, nb, b, lo, hi);
-    const size_t l = lo << 4, h = (hi << 4) < bytes ? (hi << 4) : bytes;
-    __shared__ uint32_t seq_s;
-    __shared__ int fail;
-    uint32_t* seqw = c.p2p_seq + ((op.is_send ? 0 : MAX_RANKS) + peer) * P2P_BLOCKS + b;
-    if (threadIdx.x == 0) {
+    __shared__ volatile int fail;
+    __shared__ volatile uint32_t stage_of[2];
+    if (threadIdx.x == 0)
         fail = 0;
-        seq_s = *seqw + 1;
-        if (op.is_send) {
-            // the receiver must have drained the previous message part of this pair
-            if (!wait_flag_sys(c, c.p2p_flags[c.rank] + P2P_ACK_BASE + peer * P2P_BLOCKS + b, seq_s - 1, peer,
-                               ST_FLAG_TIMEOUT))
-                fail = 1;
-        }
-        else {
-            if (!wait_flag_sys(c, c.p2p_flags[c.rank] + peer * P2P_BLOCKS + b, seq_s, peer, ST_FLAG_TIMEOUT))
-                fail = 1;
-        }
-    }
     __syncthreads();
-    if (fail)
-        return;
-    if (op.is_send) {
-        if (h > l)
-            block_copy<false>(L.data[peer] + (size_t)c.rank * L.slot_bytes + l,
-                              reinterpret_cast<const char*>(op.send) + round_off + l, h - l);
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            st_release_sys(c.p2p_flags[peer] + c.rank * P2P_BLOCKS + b, seq_s);
-            *seqw = seq_s;
+    const int nthr = blockDim.x;
+    enum { BAR_GO = 1, BAR_DONE = 3 };
+    if (threadIdx.x < 32) {
+        uint32_t* prev_signal = nullptr;
+        uint32_t prev_value = 0;
+        uint32_t j = 0;
+        for (int ln = b; ln < nl; ln += nb) {
+            const uint32_t mine = (uint32_t)((nchunks - ln + nl - 1) / nl); // chunks of this lane
+            uint32_t* seqw = c.p2p_seq + ((op.is_send ? 0 : MAX_RANKS) + peer) * P2P_LANES + ln;
+            const uint32_t* ack = c.p2p_flags[c.rank] + P2P_ACK_BASE + peer * P2P_LANES + ln;
+            const uint32_t* ready = c.p2p_flags[c.rank] + peer * P2P_LANES + ln;
+            uint32_t* signal = op.is_send ? c.p2p_flags[peer] + c.rank * P2P_LANES + ln
+                                          : c.p2p_flags[peer] + P2P_ACK_BASE + c.rank * P2P_LANES + ln;
+            const uint32_t n0 = *seqw;
+            for (uint32_t i = 0; i < mine; i++, j++) {
+                const uint32_t n = n0 + i;
+                if (threadIdx.x == 0) { // item j may start: its stage is free (send) or filled (recv)
+                    const bool ok = op.is_send ? wait_flag_sys(c, ack, n + 1 - P2P_STAGES, peer, ST_FLAG_TIMEOUT)
+                                               : wait_flag_sys(c, ready, n + 1, peer, ST_FLAG_TIMEOUT);
+                    if (!ok)
+                        fail = 1;
+                    stage_of[j & 1] = n % P2P_STAGES;
+                }
+                __syncwarp();
+                named_bar_arrive(BAR_GO + (j & 1), nthr);
+                if (fail)
+                    return; // the copiers leave at the barrier just released
+                if (prev_signal) { // the item before has been copied: tell the peer
+                    named_bar_sync(BAR_DONE + ((j - 1) & 1), nthr);
+                    if (threadIdx.x == 0)
+                        st_release_sys(prev_signal, prev_value);
+                }
+                prev_signal = signal;
+                prev_value = n + 1;
+            }
+            if (threadIdx.x == 0)
+                *seqw = n0 + mine;
         }
+        if (prev_signal) {
+            named_bar_sync(BAR_DONE + ((j - 1) & 1), nthr);
+            if (threadIdx.x == 0)
+                st_release_sys(prev_signal, prev_value);
+        }
+        return;
     }
-    else {
-        if (h > l)
-            block_copy<true>(reinterpret_cast<char*>(op.recv) + round_off + l,
-                             L.data[c.rank] + (size_t)peer * L.slot_bytes + l, h - l);
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            st_release_sys(c.p2p_flags[peer] + P2P_ACK_BASE + c.rank * P2P_BLOCKS + b, seq_s);
-            *seqw = seq_s;
+    // the ring of the pair: in the receiver's area (the sender stores across NVLink) or, in pull mode, in the
+    // sender's (the receiver loads across NVLink)
+    const int owner = (op.is_send != 0) == (L.pull != 0) ? c.rank : peer;
+    char* slot = L.data[owner] + (size_t)(owner == c.rank ? peer : c.rank) * L.slot_bytes;
+    const size_t wt = threadIdx.x - 32, wn = nthr - 32;
+    uint32_t j = 0;
+    for (int ln = b; ln < nl; ln += nb) {
+        const uint32_t mine = (uint32_t)((nchunks - ln + nl - 1) / nl);
+        char* ring = slot + (size_t)ln * P2P_STAGES * P2P_CHUNK_BYTES;
+        for (uint32_t i = 0; i < mine; i++, j++) {
+            const size_t l = ((size_t)ln + (size_t)i * nl) * P2P_CHUNK_BYTES;
+            const size_t len = op.bytes - l < P2P_CHUNK_BYTES ? op.bytes - l : P2P_CHUNK_BYTES;
+            named_bar_sync(BAR_GO + (j & 1), nthr);
+            if (fail)
+                return;
+            char* stage = ring + (size_t)stage_of[j & 1] * P2P_CHUNK_BYTES;
+            if (len) {
+                if (op.is_send)
+                    threads_copy<false>(stage, reinterpret_cast<const char*>(op.send) + l, len, wt, wn);
+                else
+                    threads_copy<true>(reinterpret_cast<char*>(op.recv) + l, stage, len, wt, wn);
+            }
+            named_bar_arrive(BAR_DONE + (j & 1), nthr);
         }
     }
 }

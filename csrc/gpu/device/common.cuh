@@ -364,14 +364,33 @@ __device__ __forceinline__ void store_out(Tout* dst, const A (&a)[N], float scal
 // 16-byte aligned, 4-byte when 4-byte aligned, bytes otherwise.  `volatile_src`
 // selects loads that bypass L1 (data written by another GPU).
 template <bool VOLATILE_SRC>
+__device__ __forceinline__ void threads_copy(void* dst, const void* src, size_t bytes, size_t tid, size_t nt);
+
+template <bool VOLATILE_SRC>
 __device__ __forceinline__ void block_copy(void* dst, const void* src, size_t bytes) {
-    const size_t tid = threadIdx.x, nt = blockDim.x;
+    threads_copy<VOLATILE_SRC>(dst, src, bytes, threadIdx.x, blockDim.x);
+}
+
+// The same copy by a subset of the block: `nt` threads numbered `tid` = 0 .. nt - 1.
+template <bool VOLATILE_SRC>
+__device__ __forceinline__ void threads_copy(void* dst, const void* src, size_t bytes, size_t tid, size_t nt) {
     const uintptr_t d = (uintptr_t)dst, s = (uintptr_t)src;
     if (((d | s) & 15) == 0) {
         const size_t nv = bytes >> 4;
         const uint4* sv = reinterpret_cast<const uint4*>(src);
         uint4* dv = reinterpret_cast<uint4*>(dst);
         size_t i = tid;
+        if (VOLATILE_SRC) { // a source behind NVLink: more loads in flight per thread
+            for (; i + 7 * nt < nv; i += 8 * nt) {
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    v[u] = __ldcv(sv + i + u * nt);
+#pragma unroll
+                for (int u = 0; u < 8; u++)
+                    dv[i + u * nt] = v[u];
+            }
+        }
         for (; i + 3 * nt < nv; i += 4 * nt) {
             uint4 a, b, c2, e;
             if (VOLATILE_SRC) {
@@ -417,6 +436,16 @@ __device__ __forceinline__ void block_copy(void* dst, const void* src, size_t by
         for (size_t k = tid; k < bytes; k += nt)
             db[k] = VOLATILE_SRC ? __ldcv(sb + k) : sb[k];
     }
+}
+
+// Named barriers (ids 1 .. 15; 0 is __syncthreads): `count` threads in total, those that call arrive do not
+// wait.  When a barrier completes, the memory accesses that its participants made before are performed
+// with respect to all of them.
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int count) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
 // Split [0, n) units into `parts` nearly equal contiguous ranges.

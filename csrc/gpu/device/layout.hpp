@@ -39,25 +39,30 @@ struct comm_dev {
     size_t heap_bytes;
     size_t staging_bytes; // one generation
     uint32_t* state; // local device words: epoch, generation, finished-block counter
-    uint32_t* p2p_seq; // local device words: per (direction, peer, block) message sequence numbers
+    uint32_t* p2p_seq; // local device words: per (direction, peer, lane) count of chunks moved so far
     volatile uint32_t* status; // host-mapped: [0] code, [1] block, [2] peer, [3] detail
     volatile uint32_t* abort_flag; // host-mapped, set by communicator abort
     unsigned long long timeout_ns;
 };
 
 
-// point-to-point flag area (see sendrecv_kernel)
-constexpr int P2P_BLOCKS = 16;
-constexpr int P2P_ACK_BASE = MAX_RANKS * P2P_BLOCKS;
-constexpr int P2P_SPARE_WORD = 2 * MAX_RANKS * P2P_BLOCKS; // never written: timeout test
-constexpr int P2P_FLAG_WORDS = 2 * MAX_RANKS * P2P_BLOCKS + 16;
-constexpr int P2P_SEQ_WORDS = 2 * MAX_RANKS * P2P_BLOCKS;
+// point-to-point (see sendrecv_kernel): every ordered pair has P2P_LANES independent chains of chunks,
+// each with a ring of P2P_STAGES chunk buffers at the receiver and a pair of counters
+constexpr int P2P_LANES = 64;
+constexpr int P2P_STAGES = 4; // chunks of one lane that may be in flight between a sender and its receiver
+constexpr size_t P2P_CHUNK_BYTES = 128u << 10;
+constexpr size_t P2P_SLOT_BYTES = (size_t)P2P_LANES * P2P_STAGES * P2P_CHUNK_BYTES; // per ordered pair, at the receiver
+constexpr int P2P_ACK_BASE = MAX_RANKS * P2P_LANES;
+constexpr int P2P_SPARE_WORD = 2 * MAX_RANKS * P2P_LANES; // never written: timeout test
+constexpr int P2P_FLAG_WORDS = 2 * MAX_RANKS * P2P_LANES + 16;
+constexpr int P2P_SEQ_WORDS = 2 * MAX_RANKS * P2P_LANES;
 // Argument signatures of the zero-copy collectives live behind the point-to-point flags in the same
 // peer-mapped page: SIG_SLOTS generations x MAX_RANKS writers x one word (see peer_barrier).
 constexpr int SIG_SLOTS = 4;
-constexpr int SIG_BASE_WORD = 640;
-static_assert(P2P_FLAG_WORDS <= SIG_BASE_WORD && SIG_BASE_WORD + SIG_SLOTS * MAX_RANKS <= 1024,
-              "signature words must fit the 4 KiB page of the point-to-point flags");
+constexpr int SIG_BASE_WORD = 4160;
+constexpr int P2P_PAGE_WORDS = 5120; // the peer-mapped area that holds both
+static_assert(P2P_FLAG_WORDS <= SIG_BASE_WORD && SIG_BASE_WORD + SIG_SLOTS * MAX_RANKS <= P2P_PAGE_WORDS,
+              "signature words must fit the area of the point-to-point flags");
 
 // auxiliary flag region (words): [0, A2A_HDR_WORDS) alltoallv consensus, the rest is
 // handed out to the fused kernels by the host
@@ -78,8 +83,10 @@ struct p2p_ops {
 };
 
 struct p2p_layout {
-    char* data[MAX_RANKS]; // p2p data areas, peer-mapped; slot s of rank x holds data from sender s
+    char* data[MAX_RANKS]; // p2p data areas, peer-mapped; slot s of rank x holds data from sender s (push) or for receiver s (pull)
     size_t slot_bytes;
+    int lanes; // lanes in use, at most P2P_LANES; the same on every rank
+    int pull; // 1: the ring of a pair lives at the sender and the receiver loads from it; 0: at the receiver, the sender stores into it
 };
 
 } // namespace dev

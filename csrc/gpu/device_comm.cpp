@@ -106,6 +106,8 @@ void device_comm::build_tables() {
     for (int p = 0; p < world_; p++)
         p2p_.data[p] = heap_.base(p) + R.p2p_data_off;
     p2p_.slot_bytes = R.p2p_slot_bytes;
+    p2p_.pull = env_data::get().p2p_pull ? 1 : 0;
+    p2p_.lanes = std::max(1, std::min(env_data::get().p2p_lanes, (int)dev::P2P_LANES));
     CUDA_CHECK(cudaDeviceSynchronize());
 }
 

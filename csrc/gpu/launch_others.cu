@@ -417,7 +417,6 @@ void launch_barrier(device_comm& dc, cudaStream_t st) {
 
 void launch_sendrecv(device_comm& dc, const dev::p2p_ops* ops, cudaStream_t st) {
     const int entries = dc.emulated() ? dc.world() : 1;
-    const size_t slot = dc.p2p().slot_bytes;
     size_t maxb = 0;
     int max_n = 0;
     for (int e = 0; e < entries; e++) {
@@ -445,22 +444,27 @@ void launch_sendrecv(device_comm& dc, const dev::p2p_ops* ops, cudaStream_t st) 
         tab = dc.emu_ops_dev();
     }
     const int emu = dc.emulated() ? 1 : 0;
-    const int blocks = (int)std::min<size_t>(dev::P2P_BLOCKS, std::max<size_t>(1, std::min(maxb, slot) >> 16));
-    for (size_t done = 0; done < std::max<size_t>(maxb, 1); done += slot) {
-        dim3 grid(blocks, entries, max_n);
-        const dev::comm_dev* t = dc.table();
-        dev::p2p_layout L = dc.p2p();
-        dev::p2p_ops r0 = ops[0];
-        size_t off = done;
-        if (dc.emulated()) {
-            void* argv[] = { (void*)&t, (void*)&L, (void*)&r0, (void*)&tab, (void*)&emu, (void*)&off };
-            CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)dev::sendrecv_kernel, grid, dim3(dc.threads()), argv, 0,
-                                                   st));
-        }
-        else {
-            dev::sendrecv_kernel<<<grid, dc.threads(), 0, st>>>(t, L, r0, tab, emu, off);
-            CUDA_CHECK(cudaGetLastError());
-        }
+    // Blocks wait for the peer's blocks, so all blocks of a launch must be resident at once: the lanes of an
+    // operation are shared out among as many blocks as fit (each side decides for itself; the lane a chunk
+    // travels through depends on the byte count alone).
+    const int threads = 1024; // one control warp and 31 warps that copy
+    const int fit = resident_blocks(dc, dev::sendrecv_kernel, threads) / (entries * max_n);
+    CCL_THROW_IF_NOT(fit >= 1, "point-to-point launch of ", entries * max_n, " operations does not fit the GPU");
+    const dev::p2p_layout L = dc.p2p();
+    const size_t chunks = std::max<size_t>(1, (maxb + dev::P2P_CHUNK_BYTES - 1) / dev::P2P_CHUNK_BYTES);
+    int blocks = (int)std::min<size_t>(std::min(fit, L.lanes), chunks);
+    if (env_data::get().p2p_max_blocks > 0)
+        blocks = std::min(blocks, env_data::get().p2p_max_blocks);
+    dim3 grid(blocks, entries, max_n);
+    const dev::comm_dev* t = dc.table();
+    dev::p2p_ops r0 = ops[0];
+    if (dc.emulated()) {
+        void* argv[] = { (void*)&t, (void*)&L, (void*)&r0, (void*)&tab, (void*)&emu };
+        CUDA_CHECK(cudaLaunchCooperativeKernel((const void*)dev::sendrecv_kernel, grid, dim3(threads), argv, 0, st));
+    }
+    else {
+        dev::sendrecv_kernel<<<grid, threads, 0, st>>>(t, L, r0, tab, emu);
+        CUDA_CHECK(cudaGetLastError());
     }
 }
 

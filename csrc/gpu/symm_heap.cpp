@@ -29,11 +29,11 @@ heap_regions plan_regions(int world, size_t heap_bytes, size_t staging_bytes, si
     r.flags_off = off;
     off += round_up((size_t)dev::MAX_BLOCKS * dev::MAX_RANKS * sizeof(uint32_t), 4096);
     r.p2p_flags_off = off;
-    off += round_up((size_t)dev::P2P_FLAG_WORDS * sizeof(uint32_t), 4096);
+    off += round_up((size_t)dev::P2P_PAGE_WORDS * sizeof(uint32_t), 4096);
     r.aux_flags_off = off;
     r.aux_flags_bytes = 1u << 20;
     off += r.aux_flags_bytes;
-    r.p2p_slot_bytes = 1u << 20;
+    r.p2p_slot_bytes = dev::P2P_SLOT_BYTES;
     r.p2p_data_off = off;
     off += (size_t)world * r.p2p_slot_bytes;
     off = round_up(off, 1u << 20);
@@ -42,7 +42,8 @@ heap_regions plan_regions(int world, size_t heap_bytes, size_t staging_bytes, si
     off += 2 * r.staging_bytes;
     off = round_up(off, 1u << 20);
     r.user_off = off;
-    r.total = round_up(std::max(off + (1u << 20), heap_bytes), granularity);
+    // the requested size covers flags, staging and the user part; the point-to-point slots come on top
+    r.total = round_up(std::max(off + (1u << 20), heap_bytes + (size_t)world * r.p2p_slot_bytes), granularity);
     return r;
 }
 

@@ -394,6 +394,57 @@ def test_barrier_and_sendrecv(group):
         assert torch.equal(dst[r], src[r - 1])
 
 
+@pytest.mark.parametrize("nbytes", [0, 1, 65536, 65537, 9 << 20, (40 << 20) + 12])
+def test_sendrecv_chunk_pipeline_sizes(group, nbytes):
+    """Messages from nothing to several times the pair's ring of stages, odd tails included; a second
+    exchange in the opposite direction continues the per-block chunk counters."""
+    W = group.world
+    gen = torch.Generator(device="cuda").manual_seed(nbytes % 977)
+    src = [torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda", generator=gen) for _ in range(W)]
+    for flip in (False, True):
+        dst = [torch.full((nbytes + 32,), 7, dtype=torch.uint8, device="cuda") for _ in range(W)]
+        peers, is_send = [], []
+        for r in range(W):
+            sender = (r % 2 == 0) != flip
+            partner = r + 1 if r % 2 == 0 else r - 1
+            peers.append(partner if partner < W else -1)
+            is_send.append(sender)
+        group.sendrecv(src, [d[:nbytes] for d in dst], peers, is_send)
+        torch.cuda.synchronize()
+        group.check()
+        for r in range(W):
+            if peers[r] >= 0 and not is_send[r]:
+                assert torch.equal(dst[r][:nbytes], src[peers[r]])
+                assert bool((dst[r][nbytes:] == 7).all())
+
+
+@pytest.mark.parametrize("max_blocks", [0, 3])
+def test_sendrecv_pull_mode_and_unequal_block_counts(monkeypatch, max_blocks):
+    """The ring at the sender with the receiver loading from it, and fewer blocks than lanes (a block then
+    serves several lanes one after the other)."""
+    from oneccl_b200 import _lib
+    from oneccl_b200.ops.device_group import DeviceGroup
+
+    monkeypatch.setenv("CCL_CUDA_P2P_PULL", "1")
+    monkeypatch.setenv("CCL_CUDA_P2P_MAX_BLOCKS", str(max_blocks))
+    _lib.load().cclx_env_reload()
+    g = DeviceGroup.emulated(2, heap_bytes=48 << 20, staging_bytes=1 << 20)
+    try:
+        for nbytes in (5, 3 << 20, (20 << 20) + 4):
+            src = [torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda") for _ in range(2)]
+            dst = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
+            g.sendrecv(src, dst, [1, 0], [True, False])
+            g.sendrecv(src, dst, [1, 0], [False, True])
+            torch.cuda.synchronize()
+            g.check()
+            assert torch.equal(dst[1], src[0]) and torch.equal(dst[0], src[1])
+    finally:
+        g.close()
+        monkeypatch.delenv("CCL_CUDA_P2P_PULL")
+        monkeypatch.delenv("CCL_CUDA_P2P_MAX_BLOCKS")
+        _lib.load().cclx_env_reload()
+
+
 def test_wait_timeout_reports_status():
     """A device-side wait that nothing satisfies runs out after its limit, the
     kernel returns, the status word says so and the context keeps working."""
