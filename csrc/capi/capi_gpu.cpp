@@ -317,6 +317,15 @@ CCLX_API int cclx_gemm_bf16_2sm(const void* A, const void* B, void* C, int M, in
         [&] { gemm_bf16_2sm(A, B, C, M, N, K, epilogue, clusters, (uint32_t*)err_words, (cudaStream_t)stream); });
 }
 
+// The same product over the first min(M, *rows_dev) rows of A: the count is read on the device, so a kernel in
+// front (the MoE dispatch) can decide it without the host in between.  M bounds the buffers.
+CCLX_API int cclx_gemm_bf16_rows(const void* A, const void* B, void* C, int M, int N, int K, int epilogue,
+                                 const void* rows_dev, void* err_words, void* stream) {
+    return capi::guard([&] {
+        gemm_bf16_2sm(A, B, C, M, N, K, epilogue, 0, (uint32_t*)err_words, (cudaStream_t)stream, (const int*)rows_dev);
+    });
+}
+
 CCLX_API void* cclx_fused_plan_create(void* dc, int mode, int M, int N, int K, int epilogue, int n_comm, int ctas) {
     fused_plan* p = nullptr;
     capi::guard([&] { p = fused_plan_create(*(device_comm*)dc, mode, M, N, K, epilogue, n_comm, ctas); });

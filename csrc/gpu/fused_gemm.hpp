@@ -17,7 +17,7 @@ void gemm_bf16_plain(const void* A, const void* B, void* C, int M, int N, int K,
 
 // the same product on CTA pairs (tcgen05.mma.cta_group::2, 256 x 256 tiles); `clusters` 0 = one pair per two SMs
 void gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int clusters,
-                   uint32_t* err, cudaStream_t st);
+                   uint32_t* err, cudaStream_t st, const int* rows_dev = nullptr);
 
 struct fused_plan; // opaque
 

@@ -40,6 +40,7 @@ struct gemm2_params {
     uint32_t* err;
     int M, N, K, epilogue;
     unsigned long long timeout_ns;
+    const int* rows; // optional device word: only the first min(M, *rows) rows of A are multiplied
 };
 
 namespace {
@@ -83,7 +84,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     const uint32_t cr = cluster_ctarank(); // 0 = leader
     const bool leader = cr == 0;
     const int n_clusters = gridDim.x >> 1, cluster = blockIdx.x >> 1;
-    const int tiles_m = (P.M + 255) / 256, tiles_n = (P.N + G2_BN - 1) / G2_BN;
+    // the row count may live on the device (rows that a kernel in front of this one delivered): every thread
+    // reads the same word, so all roles walk the same tiles
+    const int M = P.rows ? max(0, min(P.M, *P.rows)) : P.M;
+    const int tiles_m = (M + 255) / 256, tiles_n = (P.N + G2_BN - 1) / G2_BN;
     const int total_tiles = tiles_m * tiles_n;
     const int KB = (P.K + GEMM_BK - 1) / GEMM_BK;
     const unsigned long long limit = P.timeout_ns;
@@ -231,7 +235,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
                 for (int i = 0; i < 8; i++) {
                     const int rr = i * 4 + (lane >> 3);
                     const int grow = row0 + rr;
-                    if (grow < P.M && gcol < P.N) {
+                    if (grow < M && gcol < P.N) {
                         uint4 v = *reinterpret_cast<const uint4*>(stage + rr * GEMM_EPI_ROW_BYTES + (lane & 7) * 16);
                         *reinterpret_cast<uint4*>(P.C + (size_t)grow * P.N + gcol) = v;
                     }
@@ -256,7 +260,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 CUtensorMap make_bf16_kmajor_map(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 
 void gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int clusters,
-                   uint32_t* err, cudaStream_t st) {
+                   uint32_t* err, cudaStream_t st, const int* rows_dev) {
     CCL_THROW_IF_NOT(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "unsupported GEMM shape ", M, "x", N, "x", K);
     int dev_now = 0;
     CUDA_CHECK(cudaGetDevice(&dev_now));
@@ -276,6 +280,7 @@ void gemm_bf16_2sm(const void* A, const void* B, void* C, int M, int N, int K, i
     P.N = N;
     P.K = K;
     P.epilogue = epilogue;
+    P.rows = rows_dev;
     P.timeout_ns = (unsigned long long)env_data::get().wait_timeout_ms * 1000000ull;
     int dev = 0, sms = 0;
     CUDA_CHECK(cudaGetDevice(&dev));

@@ -66,6 +66,7 @@ def _proto(lib):
         "cclx_transpose_blocks": (i, [vp, vp, i, i, sz, vp]),
         "cclx_gemm_bf16": (i, [vp, vp, vp, i, i, i, i, i, vp, vp]),
         "cclx_gemm_bf16_2sm": (i, [vp, vp, vp, i, i, i, i, i, vp, vp]),
+        "cclx_gemm_bf16_rows": (i, [vp, vp, vp, i, i, i, i, vp, vp, vp]),
         "cclx_fused_plan_create": (vp, [vp, i, i, i, i, i, i, i]),
         "cclx_fused_plan_destroy": (i, [vp]),
         "cclx_fused_plan_x_shard": (vp, [vp, i]),

@@ -88,13 +88,50 @@ def main():
     res = {"config": {"experts": world, "topk": args.topk, "hidden": args.hidden, "ffn": args.ffn,
                       "tokens_per_gpu": args.tokens, "dtype": "bf16"},
            "max_abs_diff_vs_nccl_cublas": (a - b).abs().max().item(), "ref_abs_max": b.abs().max().item(),
-           "rows_received": moe.stats["recv_rows"]}
+           "rows_received": moe.recv_rows()}
     c = moe.forward_alltoall(x, logits).float()
     res["max_abs_diff_alltoall_path"] = (c - b).abs().max().item()
     res["ours_ms"] = timeit(ours)
     res["ours_alltoall_path_ms"] = timeit(lambda: moe.forward_alltoall(x, logits))
     res["nccl_cublas_ms"] = timeit(nccl_cublas)
     res["speedup_vs_nccl_cublas"] = res["nccl_cublas_ms"] / res["ours_ms"]
+    # phases of the fused forward (CUDA events at the phase boundaries, mean over the iterations, max over ranks)
+    # against what the hardware allows: rows that leave / come back over NVLink at the measured 770 GB/s per
+    # direction, the two expert GEMMs at the measured sustained bf16 GEMM rate
+    moe.phase_events = {}
+    for _ in range(args.iters):
+        ours()
+    torch.cuda.synchronize()
+    ev = moe.phase_events
+    moe.phase_events = None
+    names = ["start", "routed", "dispatched", "ffn", "combined"]
+    ph = torch.tensor([sum(a.elapsed_time(b) for a, b in zip(ev[names[i]], ev[names[i + 1]])) / args.iters
+                       for i in range(4)], device="cuda")
+    grp.allreduce(ph, ph, op="max")
+    rows_t = torch.tensor([float(moe.recv_rows())], device="cuda")
+    grp.allreduce(rows_t, rows_t, op="max")
+    torch.cuda.synchronize()
+    route_ms, dispatch_ms, ffn_ms, combine_ms = [float(v) for v in ph.tolist()]
+    rows = float(rows_t.item())  # the busiest expert sets the pace
+    peaks = {"nvlink_gbs_per_direction": 770.0, "bf16_tflops_sustained": 1400.3}
+    try:
+        import pathlib
+
+        mp = json.loads((pathlib.Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json").read_text())
+        peaks["bf16_tflops_sustained"] = float(mp.get("bf16_tflops_sustained", peaks["bf16_tflops_sustained"]))
+    except (OSError, ValueError):
+        pass
+    wire = rows * args.hidden * 2 * (world - 1) / world  # bytes into the busiest expert from other GPUs
+    wire_ms = wire / (peaks["nvlink_gbs_per_direction"] * 1e9) * 1e3
+    flops = 2.0 * rows * args.hidden * args.ffn * 2
+    ffn_floor_ms = flops / (peaks["bf16_tflops_sustained"] * 1e12) * 1e3
+    res["phases_ms"] = {"routing_torch": route_ms, "dispatch": dispatch_ms, "ffn": ffn_ms, "combine": combine_ms}
+    res["rows_busiest_expert"] = rows
+    res["floor_ms"] = {"dispatch": wire_ms, "ffn": ffn_floor_ms, "combine": wire_ms}
+    res["fraction_of_floor"] = {"dispatch": wire_ms / dispatch_ms, "ffn": ffn_floor_ms / ffn_ms,
+                                "combine": wire_ms / combine_ms,
+                                "layer": (2 * wire_ms + ffn_floor_ms) / res["ours_ms"]}
+    res["peaks_used"] = peaks
     if rank == 0:
         print(json.dumps(res), flush=True)
     dist.barrier()

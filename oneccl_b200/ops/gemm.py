@@ -31,9 +31,11 @@ def _err_buffer(device) -> torch.Tensor:
 
 
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epilogue=None, ctas: int = 0,
-              check: bool = False, kernel: str = "auto") -> torch.Tensor:
+              check: bool = False, kernel: str = "auto", rows: torch.Tensor | None = None) -> torch.Tensor:
     """``kernel``: "auto" (the library decides), "1sm" (one CTA per 128 x 256 tile) or "2sm" (CTA pairs,
-    tcgen05 cta_group::2, 256 x 256 tiles; ``ctas`` then counts CTAs, two per pair)."""
+    tcgen05 cta_group::2, 256 x 256 tiles; ``ctas`` then counts CTAs, two per pair).  ``rows``: an int32
+    device tensor whose first element says how many of ``a``'s rows to multiply (read by the kernel, so the
+    host never learns it; the other rows of ``out`` stay as they are)."""
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_cuda and w.is_cuda
     assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1]
     a = a.contiguous()
@@ -44,7 +46,11 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
     err = _err_buffer(a.device)
     lib = _lib.load()
-    if kernel == "2sm":
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.is_cuda
+        _lib.check(lib.cclx_gemm_bf16_rows(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, EPILOGUE[epilogue],
+                                           rows.data_ptr(), err.data_ptr(), _stream_ptr()))
+    elif kernel == "2sm":
         _lib.check(lib.cclx_gemm_bf16_2sm(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, EPILOGUE[epilogue],
                                           ctas // 2, err.data_ptr(), _stream_ptr()))
     else:

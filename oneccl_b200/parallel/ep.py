@@ -96,7 +96,7 @@ class ExpertParallelMoE:
         self.fused = fused
         self._cap = 0
         self._max_tokens = max_tokens
-        self._xrecv = self._yout = self._cnt = self._meta = None
+        self._xrecv = self._yout = self._cnt = self._meta = self._hmid = self._last = None
 
     def _buffers(self, tokens: int):
         cap = max(tokens, self._max_tokens) * self.topk * self.world
@@ -106,6 +106,7 @@ class ExpertParallelMoE:
                     self.group.symm_free(t)
             self._xrecv = self.group.symm_empty((cap, self.hidden), dtype=torch.bfloat16)
             self._yout = self.group.symm_empty((cap, self.hidden), dtype=torch.bfloat16)
+            self._hmid = torch.empty((cap, self.ffn), dtype=torch.bfloat16, device="cuda")  # FFN intermediate
             if self._cnt is None:
                 self._cnt = self.group.symm_empty((256 * self.world * self.world,), dtype=torch.int32)
                 self._meta = torch.zeros(2 * self.world + 2, dtype=torch.int32, device="cuda")
@@ -116,28 +117,53 @@ class ExpertParallelMoE:
         T, H = x.shape
         W, k = self.world, self.topk
         self._buffers(T)
+        mark = self._mark
+        mark("start")
         idx, wts = self.route(logits)
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         send_counts = torch.bincount(flat_e, minlength=W)
+        mark("routed")
         fused_dispatch(self.group, x, order, send_counts, self._meta, self._xrecv, self._cnt, k)
-        n_recv, over = self._meta[2 * W:2 * W + 2].tolist()  # the only host read: the GEMM needs its row count
-        if over:
-            raise RuntimeError("expert receive buffer overflow")
-        if n_recv > 0:
-            if self.use_native_gemm:
-                h = gemm_bf16(self._xrecv[:n_recv], self.w1, epilogue="silu")
-                gemm_bf16(h, self.w2, out=self._yout[:n_recv])
-                launches += 2
-            else:
+        # the number of rows that arrived stays on the device: the expert GEMMs read it there and skip the tiles
+        # behind it, so the host issues dispatch, FFN and combine without waiting for anything
+        n_dev = self._meta[2 * W:2 * W + 1]
+        mark("dispatched")
+        if self.use_native_gemm:
+            gemm_bf16(self._xrecv, self.w1, out=self._hmid, epilogue="silu", rows=n_dev)
+            gemm_bf16(self._hmid, self.w2, out=self._yout, rows=n_dev)
+            launches += 2
+        else:  # library GEMMs take their shape from the host: this form pays the read
+            n_recv = int(n_dev.item())
+            if n_recv > 0:
                 torch.matmul(torch.nn.functional.silu(self._xrecv[:n_recv] @ self.w1.t()), self.w2.t(),
                              out=self._yout[:n_recv])
+        mark("ffn")
         pos = torch.empty_like(order)
         pos[order] = torch.arange(order.numel(), device=order.device)
         out = torch.empty_like(x)
         fused_combine(self.group, flat_e, pos, wts.contiguous().view(-1), out, self._meta, self._yout, k)
-        self.stats = {"recv_rows": n_recv}
+        mark("combined")
+        self._last = self._meta[2 * W:2 * W + 2].clone()  # rows received, overflow flag: read on request
         return out
+
+    def _mark(self, name: str):
+        """With ``self.phase_events`` set to a dict, records a CUDA event per phase boundary of the fused
+        forward (start, routed, dispatched, ffn, combined) so that a benchmark can time the phases."""
+        ev = getattr(self, "phase_events", None)
+        if ev is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            ev.setdefault(name, []).append(e)
+
+    def recv_rows(self) -> int:
+        """Rows this rank's expert received in the last fused forward (a host read of two device words);
+        raises if the receive buffer had been too small for them."""
+        n_recv, over = self._last.tolist()
+        if over:
+            raise RuntimeError("expert receive buffer overflow")
+        self.stats = {"recv_rows": n_recv}
+        return n_recv
 
     def route(self, logits: torch.Tensor):
         """Returns expert ids [T, k] and normalised weights [T, k] (fp32)."""

@@ -163,3 +163,23 @@ def test_gemm_rs_emulated(world, variant, rows_per_rank):
             assert err <= 2.0e-2 * ref.abs().max().item() + 1e-3, (variant, err)
     plan.close()
     grp.close()
+
+
+@pytest.mark.parametrize("rows", [0, 1, 300, 700, 5000])
+def test_gemm_row_count_read_on_the_device(rows):
+    """The product over the first min(M, rows) rows of A, the count taken from device memory by the kernel: rows
+    behind it keep what the output held."""
+    from oneccl_b200.ops.gemm import gemm_bf16
+
+    M, N, K = 700, 384, 320
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.1).to(torch.bfloat16)
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    n_dev = torch.tensor([rows, 0], dtype=torch.int32, device="cuda")
+    gemm_bf16(a, w, out=out, epilogue="silu", rows=n_dev, check=True)
+    torch.cuda.synchronize()
+    n = min(rows, M)
+    ref = torch.nn.functional.silu(a[:n].float() @ w.float().t())
+    assert (out[:n].float() - ref).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item()) if n else True
+    assert bool((out[n:] == 7.0).all())
