@@ -113,14 +113,21 @@ elastic_group::view elastic_group::form(int timeout_ms) {
         registered_ = true;
     }
     const long long deadline = now_ms() + timeout_ms;
-    // the generation every live pod will try next: one past the newest adopted one
+    // Agreement in two phases per generation g.  (1) Every live pod publishes its member list under
+    // elastic/view/<g>/<id> and waits until all listed pods published the same list.  (2) Each then writes
+    // elastic/commit/<g>/<id> and returns the view only when all n commits are there.  A pod that wants to
+    // withdraw its list (it saw a different list, or the live set moved) first looks for commits of g: once any
+    // exists, everybody had published this very list, so it commits too instead of withdrawing.  A generation
+    // that failed is never tried again (its keys are stale): the failure raises elastic/floor, and every pod
+    // starts its next attempt at max(adopted + 1, floor), so the pods meet again at one number.
+    auto read_num = [&](const char* key) -> uint64_t {
+        kvs::bytes b;
+        return store_->raw().try_get(key, b) ? (uint64_t)std::atoll(to_s(b).c_str()) : 0;
+    };
     for (;;) {
         CCL_THROW_IF_NOT(now_ms() < deadline, "elastic group: no agreement on a member list within ", timeout_ms, " ms");
-        kvs::bytes gb;
-        uint64_t g = 1;
-        if (store_->raw().try_get("elastic/adopted", gb))
-            g = (uint64_t)std::atoll(to_s(gb).c_str()) + 1;
-        g = std::max<uint64_t>(g, view_.generation + 1);
+        const uint64_t g = std::max<uint64_t>({ read_num("elastic/adopted") + 1, read_num("elastic/floor"),
+                                                view_.generation + 1, floor_ });
         std::vector<std::string> mine = live_pods(dead_ms_);
         const size_t n = mine.size();
         resize_action act = resize_fn_ ? resize_fn_(n) : (n >= min_size_ ? resize_action::run : resize_action::wait);
@@ -133,8 +140,11 @@ elastic_group::view elastic_group::form(int timeout_ms) {
         for (auto& m : mine)
             list += (list.empty() ? "" : ",") + m;
         const std::string base = "elastic/view/" + std::to_string(g) + "/";
+        const std::string cbase = "elastic/commit/" + std::to_string(g) + "/";
         store_->raw().set(base + id_, list);
-        // wait until every listed member published the same list (or somebody disagrees / the set moves)
+        if (window_hook_)
+            window_hook_(g); // tests: something happens between publishing and agreeing
+        // phase 1: every listed member published the same list (or somebody disagrees / the set moves)
         bool agreed = false;
         const long long round_end = std::min<long long>(deadline, now_ms() + 4LL * dead_ms_);
         while (now_ms() < round_end) {
@@ -157,12 +167,47 @@ elastic_group::view elastic_group::form(int timeout_ms) {
                 break;
             std::this_thread::sleep_for(std::chrono::milliseconds(std::max(1, hb_ms_ / 4)));
         }
-        if (!agreed) {
-            store_->raw().del(base + id_); // a later attempt at this generation starts clean
+        if (!agreed && !store_->raw().list(cbase).empty())
+            agreed = true; // somebody saw all n lists equal, mine among them: the list stands
+        bool committed = false;
+        if (agreed) {
+            // phase 2: all n commit, or nobody adopts
+            store_->raw().set(cbase + id_, "1");
+            // no round limit here: the others have published this list and will commit unless they withdrew in
+            // the moment before my commit became visible, or died
+            while (now_ms() < deadline) {
+                size_t have = 0;
+                bool lost = false;
+                std::vector<std::string> live = live_pods(dead_ms_);
+                for (auto& m : mine) {
+                    kvs::bytes b;
+                    if (store_->raw().try_get(cbase + m, b))
+                        have++;
+                    else if (!store_->raw().try_get(base + m, b) || to_s(b) != list)
+                        lost = true; // it took its list back before it saw a commit: it will not commit
+                    else if (std::find(live.begin(), live.end(), m) == live.end())
+                        lost = true; // it died in between
+                }
+                if (have == n) {
+                    committed = true;
+                    break;
+                }
+                if (lost)
+                    break;
+                std::this_thread::sleep_for(std::chrono::milliseconds(std::max(1, hb_ms_ / 4)));
+            }
+        }
+        if (!committed) {
+            if (!agreed)
+                store_->raw().del(base + id_); // tells a pod that already waits for commits not to wait for mine
+            floor_ = g + 1;
+            if (read_num("elastic/floor") < floor_)
+                store_->raw().set("elastic/floor", std::to_string(floor_));
             std::this_thread::sleep_for(std::chrono::milliseconds(hb_ms_));
             continue;
         }
-        store_->raw().set("elastic/adopted", std::to_string(g));
+        if (read_num("elastic/adopted") < g)
+            store_->raw().set("elastic/adopted", std::to_string(g));
         view_.generation = g;
         view_.members = mine;
         view_.size = (int)n;

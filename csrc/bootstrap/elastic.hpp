@@ -72,6 +72,9 @@ public:
     // store view the communicator of the current generation bootstraps through
     std::shared_ptr<kvs::ikvs> generation_store();
     const std::string& id() const { return id_; }
+    // called by form() after this pod published its list for a generation and before it looks at the others'
+    // (a test makes a third pod register inside that window)
+    void set_window_hook(std::function<void(uint64_t)> fn) { window_hook_ = std::move(fn); }
 
 private:
     std::vector<std::string> live_pods(int settle_ms);
@@ -83,6 +86,8 @@ private:
     std::function<resize_action(size_t)> resize_fn_;
     bool registered_ = false;
     view view_;
+    uint64_t floor_ = 0; // generations below this one failed here
+    std::function<void(uint64_t)> window_hook_;
     std::thread beat_;
     std::atomic<bool> stop_{ false };
     // last observed heartbeat value and when it last changed (local steady clock, ms)

@@ -142,6 +142,18 @@ CCLX_API int cclx_elastic_form(void* h, int timeout_ms, long long* out3, char* m
         std::memcpy(members, list.c_str(), list.size() + 1);
     });
 }
+// Test hook: `fn(generation)` runs inside form() after this pod published its member list and before it reads
+// the others' (tests/test_elastic.py lets a third pod register in that window).
+CCLX_API int cclx_elastic_set_window_hook(void* h, void (*fn)(unsigned long long)) {
+    return capi::guard([&] {
+        auto* e = (elastic_handle*)h;
+        if (fn)
+            e->g->set_window_hook([fn](uint64_t g) { fn((unsigned long long)g); });
+        else
+            e->g->set_window_hook(nullptr);
+    });
+}
+
 CCLX_API int cclx_elastic_changed(void* h) {
     int r = -1;
     capi::guard([&] { r = ((elastic_handle*)h)->g->changed() ? 1 : 0; });

@@ -487,6 +487,17 @@ class ElasticGroup:
             self._cb = proto(lambda n: self._ACTIONS[resize_fn(int(n))])
             _lib.check(self._lib.cclx_elastic_set_resize_fn(self._h, C.cast(self._cb, C.c_void_p)))
 
+    def set_window_hook(self, fn):
+        """``fn(generation)`` runs inside ``form`` right after this pod published its member list for a
+        generation and before it reads the others' lists (tests use it to change the membership there)."""
+        if fn is None:
+            self._win = None
+            _lib.check(self._lib.cclx_elastic_set_window_hook(self._h, None))
+            return
+        proto = C.CFUNCTYPE(None, C.c_ulonglong)
+        self._win = proto(lambda g: fn(int(g)))
+        _lib.check(self._lib.cclx_elastic_set_window_hook(self._h, C.cast(self._win, C.c_void_p)))
+
     def form(self, timeout_ms: int = 60000):
         out = (C.c_longlong * 3)()
         buf = C.create_string_buffer(1 << 16)
