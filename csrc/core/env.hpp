@@ -142,6 +142,7 @@ struct env_data {
     size_t rs_nvls_max_block = 4u << 20; // reduce_scatter: per-rank blocks up to this size use multimem.ld_reduce, larger ones peer loads
     size_t ag_nvls_max_block = 1u << 20; // allgather: blocks up to this size go out as multimem.st, larger ones as peer stores
     bool auto_register = true; // ordinary device buffers are shared with the peers automatically (buffer_exchange)
+    int nvls_staged_min_ranks = 5; // from this many ranks on, ordinary buffers of allreduce / reduce_scatter are staged for the in-switch reduction instead of shared
     int p2p_lanes = 64; // independent chunk chains per ordered pair in send / recv (equal on all ranks, <= 128)
     bool p2p_pull = false; // send / recv: the receiver loads from a ring at the sender (else the sender stores into a ring at the receiver)
     int p2p_max_blocks = 0; // upper limit for the blocks of one send / recv operation (0: as many as lanes and the GPU allow)

@@ -440,6 +440,103 @@ __global__ void __launch_bounds__(1024) allreduce_pipelined_kernel(const comm_de
 }
 
 // ---------------------------------------------------------------------------
+// Inner loops of the zero-copy peer-load kernels for a world size known at compile time (2, 4, 8): the
+// per-peer values stay in registers (a loop over a run-time world size indexes its array dynamically, which
+// puts it into local memory), the peer pointers are read through constant indices, and every thread keeps
+// eight 16-byte loads in flight (8 / WT packs of WT peers each).
+// ---------------------------------------------------------------------------
+template <int WT>
+struct p2p_unroll {
+    static constexpr int U = WT >= 8 ? 1 : 8 / WT;
+};
+
+// allreduce: packs [i, end) of my slice, stride nt: load from every peer, reduce, store to every peer
+template <class T, class A, class Op, int N, int WT>
+__device__ __forceinline__ void ar_p2p_loop(const comm_dev& c, const coll_args& a, size_t i, size_t end, size_t nt,
+                                            bool scale) {
+    constexpr int U = p2p_unroll<WT>::U;
+    auto finish = [&](size_t at, const uint4 (&v)[WT]) {
+        A acc[N];
+        unpack16<T, A>(v[0], acc);
+#pragma unroll
+        for (int p = 1; p < WT; p++)
+            accum16<T, A, Op>(v[p], acc);
+        uint4 o;
+        T* t = reinterpret_cast<T*>(&o);
+#pragma unroll
+        for (int k = 0; k < N; k++)
+            t[k] = from_acc<T, A>(scale ? apply_scale<A>(acc[k], a.scale) : acc[k]);
+#pragma unroll
+        for (int k = 0; k < WT; k++)
+            st16(peer_out(c, a, (c.rank + k) % WT) + (at << 4), o);
+    };
+    for (; i + (U - 1) * nt < end; i += U * nt) {
+        uint4 v[U][WT];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int p = 0; p < WT; p++)
+                v[u][p] = ld_cv16(peer_in(c, a, p) + ((i + u * nt) << 4));
+#pragma unroll
+        for (int u = 0; u < U; u++)
+            finish(i + u * nt, v[u]);
+    }
+    for (; i < end; i += nt) {
+        uint4 v[WT];
+#pragma unroll
+        for (int p = 0; p < WT; p++)
+            v[p] = ld_cv16(peer_in(c, a, p) + (i << 4));
+        finish(i, v);
+    }
+}
+
+// reduce_scatter: packs [i, end) of my block (byte offset blk in every peer's input), result to recv
+template <class T, class A, class Op, int N, int WT>
+__device__ __forceinline__ size_t rs_p2p_loop(const comm_dev& c, const coll_args& a, size_t blk, T* recv, size_t rc,
+                                              bool vout, size_t i, size_t end, size_t nt) {
+    constexpr int U = p2p_unroll<WT>::U;
+    for (; i + (U - 1) * nt < end; i += U * nt) {
+        uint4 v[U][WT];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int p = 0; p < WT; p++)
+                v[u][p] = ld_cv16(peer_in(c, a, p) + blk + ((i + u * nt) << 4));
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            A acc[N];
+            unpack16<T, A>(v[u][0], acc);
+#pragma unroll
+            for (int p = 1; p < WT; p++)
+                accum16<T, A, Op>(v[u][p], acc);
+            store_pack<T, A, N>(recv, i + u * nt, rc, vout, acc, a.scale, a.do_scale != 0);
+        }
+    }
+    return i; // the caller's one-pack loop takes the rest
+}
+
+// alltoall: packs [i, end) of every block: block q of my send buffer goes to rank q, at my place (doff)
+template <int WT>
+__device__ __forceinline__ size_t a2a_p2p_loop(const comm_dev& c, const coll_args& a, const char* send, size_t b,
+                                               size_t doff, size_t i, size_t end, size_t nt) {
+    constexpr int U = p2p_unroll<WT>::U;
+    for (; i + (U - 1) * nt < end; i += U * nt) {
+        uint4 v[U][WT];
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int k = 0; k < WT; k++)
+                v[u][k] = *reinterpret_cast<const uint4*>(send + (size_t)((c.rank + k) % WT) * b + ((i + u * nt) << 4));
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+            for (int k = 0; k < WT; k++)
+                st16(peer_out(c, a, (c.rank + k) % WT) + doff + ((i + u * nt) << 4), v[u][k]);
+    }
+    return i;
+}
+
+// ---------------------------------------------------------------------------
 // two-shot allreduce on symmetric (registered) buffers, no staging copy.
 // P2P form: read my slice from every peer, reduce, write it to every peer.
 // NVLS form (sum of f32/bf16/f16): multimem.ld_reduce + multimem.st, the
@@ -522,20 +619,28 @@ __global__ void __launch_bounds__(1024) allreduce_symm_kernel(const comm_dev* ta
             };
             size_t i = mlo + lo + tid;
             const size_t end = mlo + hi;
-            for (; i + nt < end; i += 2 * nt) {
-                uint4 v0[MAX_RANKS], v1[MAX_RANKS];
-                for (int p = 0; p < W; p++) {
-                    v0[p] = ld_cv16(peer_in(c, a, p) + (i << 4));
-                    v1[p] = ld_cv16(peer_in(c, a, p) + ((i + nt) << 4));
+            if (W == 8)
+                ar_p2p_loop<T, A, Op, N, 8>(c, a, i, end, nt, scale);
+            else if (W == 4)
+                ar_p2p_loop<T, A, Op, N, 4>(c, a, i, end, nt, scale);
+            else if (W == 2)
+                ar_p2p_loop<T, A, Op, N, 2>(c, a, i, end, nt, scale);
+            else {
+                for (; i + nt < end; i += 2 * nt) {
+                    uint4 v0[MAX_RANKS], v1[MAX_RANKS];
+                    for (int p = 0; p < W; p++) {
+                        v0[p] = ld_cv16(peer_in(c, a, p) + (i << 4));
+                        v1[p] = ld_cv16(peer_in(c, a, p) + ((i + nt) << 4));
+                    }
+                    reduce_one(i, v0);
+                    reduce_one(i + nt, v1);
                 }
-                reduce_one(i, v0);
-                reduce_one(i + nt, v1);
-            }
-            for (; i < end; i += nt) {
-                uint4 v0[MAX_RANKS];
-                for (int p = 0; p < W; p++)
-                    v0[p] = ld_cv16(peer_in(c, a, p) + (i << 4));
-                reduce_one(i, v0);
+                for (; i < end; i += nt) {
+                    uint4 v0[MAX_RANKS];
+                    for (int p = 0; p < W; p++)
+                        v0[p] = ld_cv16(peer_in(c, a, p) + (i << 4));
+                    reduce_one(i, v0);
+                }
             }
         }
         if (blockIdx.x == 0 && tid < tail) {
@@ -750,7 +855,13 @@ __global__ void __launch_bounds__(1024) reduce_scatter_symm_kernel(const comm_de
             }
         }
         else {
-            // two packs x world peer loads in flight per thread
+            // eight peer loads in flight per thread, in registers for the usual world sizes
+            if (W == 8)
+                i = rs_p2p_loop<T, A, Op, N, 8>(c, a, blk, recv, rc, vout, i, hi, nt);
+            else if (W == 4)
+                i = rs_p2p_loop<T, A, Op, N, 4>(c, a, blk, recv, rc, vout, i, hi, nt);
+            else if (W == 2)
+                i = rs_p2p_loop<T, A, Op, N, 2>(c, a, blk, recv, rc, vout, i, hi, nt);
             for (; i + nt < hi; i += 2 * nt) {
                 uint4 v0[MAX_RANKS], v1[MAX_RANKS];
                 for (int p = 0; p < W; p++) {
@@ -1066,7 +1177,14 @@ static __global__ void __launch_bounds__(1024) alltoall_symm_kernel(const comm_d
     bool ok = peer_barrier(c, s, sig);
     if (ok) {
         const size_t doff = (size_t)c.rank * b;
-        for (size_t i = lo + tid; i < hi; i += nt) {
+        size_t i = lo + tid;
+        if (W == 8)
+            i = a2a_p2p_loop<8>(c, a, send, b, doff, i, hi, nt);
+        else if (W == 4)
+            i = a2a_p2p_loop<4>(c, a, send, b, doff, i, hi, nt);
+        else if (W == 2)
+            i = a2a_p2p_loop<2>(c, a, send, b, doff, i, hi, nt);
+        for (; i < hi; i += nt) {
             uint4 v[MAX_RANKS];
             for (int k = 0; k < W; k++)
                 v[k] = *reinterpret_cast<const uint4*>(send + (size_t)((c.rank + k) % W) * b + (i << 4));

@@ -135,15 +135,17 @@ inline char* view_ptr(const device_comm& dc, const zc_view& v, int q) {
 // torch tensor, then takes the zero-copy kernels as well, offsets may differ between ranks, and all ranks
 // reach the same verdict (zero-copy only if every rank's buffer can be shared).  The sizes are the same on
 // every rank, so either all ranks enter the exchange or none does.
+// `allow_exchange` = false keeps the local decision for large messages too (a caller that would rather stage an
+// ordinary buffer than share it; it must decide that from values that are equal on every rank).
 inline void zero_copy_views(device_comm& dc, const dev::rank_args* ra, bool want_in, size_t in_bytes, bool want_out,
-                            size_t out_bytes, zc_view& vin, zc_view& vout) {
+                            size_t out_bytes, zc_view& vin, zc_view& vout, bool allow_exchange = true) {
     if (want_in)
         vin = zero_copy_view(dc, ra, false, in_bytes);
     if (want_out)
         vout = zero_copy_view(dc, ra, true, out_bytes);
     buffer_exchange* bx = dc.exchange();
     const size_t big = std::max(want_in ? in_bytes : 0, want_out ? out_bytes : 0);
-    if (dc.emulated() || !bx || big < env_data::get().auto_register_min)
+    if (dc.emulated() || !bx || !allow_exchange || big < env_data::get().auto_register_min)
         return;
     shared_view in, out;
     bx->exchange(want_in ? ra[0].send : nullptr, in_bytes, want_out ? ra[0].recv : nullptr, out_bytes, in, out);

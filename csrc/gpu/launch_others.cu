@@ -31,9 +31,16 @@ void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t rc,
     a.do_scale = o.do_scale ? 1 : 0;
 
     // send buffers in the symmetric heap or in a registered allocation: pull (or NVLS) without staging
+    // From five ranks on the in-switch reduction beats peer loads up to blocks of 64 MiB, and an ordinary send buffer
+    // is better staged (chunk pipeline with the switch reducing) than shared up to 128 MiB in total (8 B200s,
+    // bf16, 32 MiB: 70 us staged, 73 us symmetric NVLS, 97 us shared + peer loads, NCCL 85 us; from 128 MiB on
+    // shared + peer loads is ahead: 247 against 259 us).
+    const env_data& env0 = env_data::get();
+    const bool many = dc.nvls() && nvls_type_ok(dt_in, op) && W >= std::max(env0.nvls_min_ranks, env0.nvls_staged_min_ranks);
+    const size_t nvls_max_block = many ? env0.rs_nvls_max_block * 16 : env0.rs_nvls_max_block;
     zc_view vin, vnone;
     if (dt_in == dt_out)
-        zero_copy_views(dc, ra, true, rc * esz * W, false, 0, vin, vnone);
+        zero_copy_views(dc, ra, true, rc * esz * W, false, 0, vin, vnone, !(many && rc * esz * W < (128u << 20)));
     const bool symmetric = vin.ok;
     const size_t in_off = vin.off;
     (void)entries;
@@ -43,7 +50,7 @@ void launch_reduce_scatter(device_comm& dc, const dev::rank_args* ra, size_t rc,
                    // the in-switch reduction wins while latency counts; large blocks are reduced faster from peer
                    // loads (measured on 4 B200s, 1 GiB: 1.28 ms by peer loads, 1.58 ms by multimem.ld_reduce, NCCL 1.38 ms)
                    ? ((dc.nvls() && nvls_type_ok(dt_in, op) && !vin.registered && W >= env_data::get().nvls_min_ranks &&
-                       rc * esz <= env_data::get().rs_nvls_max_block)
+                       rc * esz <= nvls_max_block)
                           ? ga_nvls
                           : ga_symm)
                    : ga_push;
