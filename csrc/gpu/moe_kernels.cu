@@ -96,6 +96,112 @@ CCLX_API int cclx_moe_combine(const void* y, const long long* pos, const float* 
 }
 
 // ---------------------------------------------------------------------------------------------
+// Routing on the device: top-k experts per token with softmax weights over the chosen logits, the number of
+// (token, slot) items per expert, and a permutation that groups the items by expert (with its inverse).  Two
+// small kernels replace topk / softmax / bincount / argsort / scatter of an eager implementation (six launches
+// and a sort).  Inside an expert's group the items stand in the order the atomics grant, which no consumer
+// depends on: the combine step finds every item through `pos`, and an expert's rows are computed independently
+// of their place.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr int ROUTE_MAX_EXPERTS = 64;
+constexpr int ROUTE_MAX_TOPK = 8;
+
+__global__ void __launch_bounds__(256)
+    route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int topk, long long* __restrict__ idx,
+                      float* __restrict__ wts, unsigned long long* __restrict__ counts) {
+    __shared__ unsigned int hist[ROUTE_MAX_EXPERTS];
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x)
+        hist[e] = 0;
+    __syncthreads();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n_tokens) {
+        const float* row = logits + (size_t)t * n_experts;
+        int best[ROUTE_MAX_TOPK];
+        float val[ROUTE_MAX_TOPK];
+        for (int s = 0; s < topk; s++) {
+            // largest logit not taken yet; ties go to the lower expert index (as torch.topk on a sorted scan would)
+            int be = -1;
+            float bv = 0.f;
+            for (int e = 0; e < n_experts; e++) {
+                bool taken = false;
+                for (int q = 0; q < s; q++)
+                    taken |= best[q] == e;
+                const float v = row[e];
+                if (!taken && (be < 0 || v > bv)) {
+                    be = e;
+                    bv = v;
+                }
+            }
+            best[s] = be;
+            val[s] = bv;
+        }
+        float sum = 0.f;
+        for (int s = 0; s < topk; s++) { // val[0] is the maximum
+            val[s] = __expf(val[s] - val[0]);
+            sum += val[s];
+        }
+        for (int s = 0; s < topk; s++) {
+            idx[(size_t)t * topk + s] = best[s];
+            wts[(size_t)t * topk + s] = val[s] / sum;
+            atomicAdd(&hist[best[s]], 1u);
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x)
+        if (hist[e])
+            atomicAdd(&counts[e], (unsigned long long)hist[e]);
+}
+
+// cursor[e] starts at zero; item i = token * topk + slot lands at offset(expert) + ticket
+__global__ void __launch_bounds__(256)
+    route_place_kernel(const long long* __restrict__ idx, size_t n_items, int n_experts,
+                       const unsigned long long* __restrict__ counts, unsigned int* __restrict__ cursor,
+                       long long* __restrict__ order, long long* __restrict__ pos) {
+    __shared__ unsigned long long offs[ROUTE_MAX_EXPERTS];
+    if (threadIdx.x == 0) {
+        unsigned long long acc = 0;
+        for (int e = 0; e < n_experts; e++) {
+            offs[e] = acc;
+            acc += counts[e];
+        }
+    }
+    __syncthreads();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_items) {
+        const int e = (int)idx[i];
+        const unsigned long long p = offs[e] + atomicAdd(&cursor[e], 1u);
+        order[p] = (long long)i;
+        pos[i] = (long long)p;
+    }
+}
+} // namespace
+
+// logits [n_tokens, n_experts] fp32 -> idx [n_tokens, topk] (int64), wts [n_tokens, topk] (fp32),
+// counts [n_experts] (int64), order / pos [n_tokens * topk] (int64).  scratch: n_experts 32-bit words.
+CCLX_API int cclx_moe_route(const float* logits, int n_tokens, int n_experts, int topk, long long* idx, float* wts,
+                            long long* counts, long long* order, long long* pos, void* scratch, void* stream) {
+    return cclx::capi::guard([&] {
+        CCL_THROW_IF_NOT(n_experts >= 1 && n_experts <= ROUTE_MAX_EXPERTS, "routing supports up to ", ROUTE_MAX_EXPERTS,
+                         " experts");
+        CCL_THROW_IF_NOT(topk >= 1 && topk <= ROUTE_MAX_TOPK && topk <= n_experts, "top-k must be between 1 and min(",
+                         ROUTE_MAX_TOPK, ", experts)");
+        cudaStream_t st = (cudaStream_t)stream;
+        CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(long long) * n_experts, st));
+        CUDA_CHECK(cudaMemsetAsync(scratch, 0, sizeof(unsigned int) * n_experts, st));
+        if (n_tokens == 0)
+            return;
+        route_topk_kernel<<<(n_tokens + 255) / 256, 256, 0, st>>>(logits, n_tokens, n_experts, topk, idx, wts,
+                                                                  (unsigned long long*)counts);
+        CUDA_CHECK(cudaGetLastError());
+        const size_t n_items = (size_t)n_tokens * topk;
+        route_place_kernel<<<(unsigned)((n_items + 255) / 256), 256, 0, st>>>(
+            idx, n_items, n_experts, (const unsigned long long*)counts, (unsigned int*)scratch, order, pos);
+        CUDA_CHECK(cudaGetLastError());
+    });
+}
+
+// ---------------------------------------------------------------------------------------------
 // Fused dispatch and combine over peer memory: the all-to-all of an expert-parallel layer without
 // staging buffers, send-side row gather or receive-side copies.
 //

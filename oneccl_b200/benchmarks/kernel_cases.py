@@ -9,8 +9,8 @@ than the 126 MB L2 and at most a few GB.  Each case prints the algorithmic bytes
 and its device time from CUDA events, so a summary can state achieved / measured peak next to the
 counters.
 
-Cases: ar_oneshot ar_twoshot ar_pipelined ar_symm rs_symm ag_symm a2a_symm bcast pack_fused
-       moe_dispatch_combine ln_fwd_bwd colsum xent adamw gemm_2sm ag_gemm gemm_rs
+Cases: ar_oneshot ar_twoshot ar_pipelined ar_symm rs_symm ag_symm a2a_symm bcast pack_fused sendrecv
+       moe_dispatch_combine moe_route gemm_rows ln_fwd_bwd colsum xent adamw gemm_2sm ag_gemm gemm_rs
 """
 from __future__ import annotations
 
@@ -89,12 +89,39 @@ def main():
         tensors = [[torch.randn(2048, device="cuda").to(dt) for _ in range(W)] for _ in range(256)]
         t = _time(lambda: g.allreduce_fused(tensors), args.launches)
         out.update(tensors=256, bytes_each=4096, seconds=t)
+    elif case == "sendrecv":
+        n = 64 << 20  # bytes per message; even ranks send to the next odd rank
+        g = emu(16)
+        src = [torch.empty(n, dtype=torch.uint8, device="cuda").random_(0, 255) for _ in range(W)]
+        dst = [torch.empty(n, dtype=torch.uint8, device="cuda") for _ in range(W)]
+        peers = [r + 1 if r % 2 == 0 else r - 1 for r in range(W)]
+        sends = [r % 2 == 0 for r in range(W)]
+        t = _time(lambda: g.sendrecv(src, dst, peers, sends), args.launches)
+        out.update(bytes_per_message=n, messages=W // 2, algorithmic_hbm_bytes=(W // 2) * n * 4, seconds=t)
+    elif case == "moe_route":
+        from oneccl_b200.parallel.ep import route_device
+
+        T, E, k = 1 << 20, 8, 2
+        logits = torch.randn(T, E, device="cuda")
+        t = _time(lambda: route_device(logits, k), args.launches)
+        out.update(tokens=T, experts=E, topk=k, algorithmic_hbm_bytes=T * (E * 4 + k * (8 + 4 + 8 + 8)), seconds=t)
+    elif case == "gemm_rows":
+        from oneccl_b200.ops.gemm import gemm_bf16
+
+        M, N, Kd = 16384, 4096, 4096  # buffers for 16384 rows, 10000 of them valid (the count lives on the device)
+        a = torch.randn(M, Kd, device="cuda").to(dt)
+        w = torch.randn(N, Kd, device="cuda").to(dt)
+        c = torch.empty(M, N, device="cuda", dtype=dt)
+        rows = torch.tensor([10000], dtype=torch.int32, device="cuda")
+        t = _time(lambda: gemm_bf16(a, w, out=c, rows=rows), args.launches)
+        out.update(M_cap=M, rows=10000, N=N, K=Kd, flops=2.0 * 10000 * N * Kd, seconds=t,
+                   tflops=2.0 * 10000 * N * Kd / t / 1e12)
     elif case == "moe_dispatch_combine":
         from oneccl_b200.parallel.ep import fused_combine, fused_dispatch
 
         T, H, topk = 1024, 4096, 2
         cap = T * topk * W
-        g = emu((cap * H * 2 >> 20) + 192)  # the heap also holds the flag, staging and point-to-point regions
+        g = emu((cap * H * 2 >> 20) + 192)  # the heap also holds the flag and staging regions
         xrecv = g.symm_empty((cap, H), dtype=dt)  # also stands in for the experts' output
         cnt = g.symm_empty((256 * W * W,), dtype=torch.int32)
         metas = [torch.zeros(2 * W + 2, dtype=torch.int32, device="cuda") for _ in range(W)]

@@ -76,6 +76,28 @@ def fused_combine(group: DeviceGroup, expert, pos, weight, out, meta, expert_out
     launches += 1
 
 
+def route_device(logits: torch.Tensor, topk: int):
+    """Top-k routing in two kernels: expert ids [T, k] (int64), softmax weights over the chosen logits [T, k]
+    (fp32), items per expert [E] (int64), a permutation ``order`` of the T * k (token, slot) items that groups
+    them by expert, and its inverse ``pos``.  What ``torch.topk`` + ``softmax`` + ``bincount`` + ``argsort`` +
+    a scatter compute, without the sort (the order inside an expert's group is arbitrary)."""
+    global launches
+    assert logits.is_cuda and logits.dim() == 2
+    lg = logits.float().contiguous()
+    T, E = lg.shape
+    dev = lg.device
+    idx = torch.empty((T, topk), dtype=torch.int64, device=dev)
+    wts = torch.empty((T, topk), dtype=torch.float32, device=dev)
+    counts = torch.empty((E,), dtype=torch.int64, device=dev)
+    order = torch.empty((T * topk,), dtype=torch.int64, device=dev)
+    pos = torch.empty((T * topk,), dtype=torch.int64, device=dev)
+    scratch = torch.empty((E,), dtype=torch.int32, device=dev)
+    _lib.check(_lib.load().cclx_moe_route(lg.data_ptr(), T, E, topk, idx.data_ptr(), wts.data_ptr(), counts.data_ptr(),
+                                          order.data_ptr(), pos.data_ptr(), scratch.data_ptr(), _stream_ptr()))
+    launches += 2
+    return idx, wts, counts, order, pos
+
+
 class ExpertParallelMoE:
     """x [T, H] bf16 on every rank -> y [T, H]: every token visits its top-k experts."""
 
@@ -119,10 +141,8 @@ class ExpertParallelMoE:
         self._buffers(T)
         mark = self._mark
         mark("start")
-        idx, wts = self.route(logits)
-        flat_e = idx.reshape(-1)
-        order = torch.argsort(flat_e, stable=True)
-        send_counts = torch.bincount(flat_e, minlength=W)
+        idx, wts, send_counts, order, pos = route_device(logits, k)
+        flat_e = idx.view(-1)
         mark("routed")
         fused_dispatch(self.group, x, order, send_counts, self._meta, self._xrecv, self._cnt, k)
         # the number of rows that arrived stays on the device: the expert GEMMs read it there and skip the tiles
@@ -139,10 +159,8 @@ class ExpertParallelMoE:
                 torch.matmul(torch.nn.functional.silu(self._xrecv[:n_recv] @ self.w1.t()), self.w2.t(),
                              out=self._yout[:n_recv])
         mark("ffn")
-        pos = torch.empty_like(order)
-        pos[order] = torch.arange(order.numel(), device=order.device)
         out = torch.empty_like(x)
-        fused_combine(self.group, flat_e, pos, wts.contiguous().view(-1), out, self._meta, self._yout, k)
+        fused_combine(self.group, flat_e, pos, wts.view(-1), out, self._meta, self._yout, k)
         mark("combined")
         self._last = self._meta[2 * W:2 * W + 2].clone()  # rows received, overflow flag: read on request
         return out

@@ -126,3 +126,24 @@ def test_graphed_train_step_matches_eager_steps():
     for a, b in zip(l0, l1):
         assert abs(a - b) < 1e-3, (l0, l1)
     torch.testing.assert_close(w0, w1, rtol=0, atol=2e-3)
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 2, 1), (97, 8, 2), (4096, 8, 2), (1000, 16, 4), (33, 4, 4)])
+def test_moe_routing_kernels_match_torch(T, E, k):
+    """Expert ids and weights against torch.topk + softmax, counts against bincount, and the permutation: it
+    groups the items by expert and `pos` is its inverse."""
+    from oneccl_b200.parallel.ep import route_device
+
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    logits = torch.randn(T, E, generator=g, device="cuda")
+    idx, wts, counts, order, pos = route_device(logits, k)
+    torch.cuda.synchronize()
+    val, ref_idx = torch.topk(logits, k, dim=-1)
+    assert torch.equal(idx, ref_idx)
+    torch.testing.assert_close(wts, torch.softmax(val, dim=-1), rtol=1e-5, atol=1e-6)
+    flat = ref_idx.reshape(-1)
+    assert torch.equal(counts, torch.bincount(flat, minlength=E))
+    assert torch.equal(torch.sort(order).values, torch.arange(T * k, device="cuda"))
+    assert torch.equal(order[pos], torch.arange(T * k, device="cuda"))
+    grouped = flat[order]
+    assert bool((grouped[1:] >= grouped[:-1]).all())
