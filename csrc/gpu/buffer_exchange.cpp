@@ -86,6 +86,14 @@ buf_desc buffer_exchange::describe(const void* p, size_t bytes) {
         return d;
     if (mtype != CU_MEMORYTYPE_DEVICE || !ipc_ok || bid == 0 || (const char*)p + bytes > (const char*)start + range)
         return d;
+    // Small cudaMalloc allocations are carved out of one 2 MiB page by the driver, and the IPC handle names the
+    // page: two such buffers would ask the peer to open one handle twice (cudaErrorAlreadyMapped), and the offset
+    // of a buffer inside the opened mapping would not be its offset from RANGE_START.  Share only allocations
+    // that own their pages: 2 MiB-aligned start, at least 2 MiB long (every block of PyTorch's caching allocator,
+    // every cudaMalloc from 2 MiB on).  The others are staged.
+    constexpr size_t PAGE = 2u << 20;
+    if ((((uintptr_t)start) & (PAGE - 1)) != 0 || range < PAGE)
+        return d;
     auto it = own_handles_.find(bid);
     if (it == own_handles_.end()) {
         cudaIpcMemHandle_t h;

@@ -137,8 +137,9 @@ __global__ void __launch_bounds__(256)
             val[s] = bv;
         }
         float sum = 0.f;
-        for (int s = 0; s < topk; s++) { // val[0] is the maximum
-            val[s] = __expf(val[s] - val[0]);
+        const float vmax = val[0]; // the first pick is the maximum
+        for (int s = 0; s < topk; s++) {
+            val[s] = __expf(val[s] - vmax);
             sum += val[s];
         }
         for (int s = 0; s < topk; s++) {

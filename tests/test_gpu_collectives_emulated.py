@@ -613,7 +613,8 @@ def test_registered_buffers_zero_copy(group):
         x.copy_(s)
     ref = torch.stack(src).sum(0)
     before = group.algo_hits("allreduce", "symm")
-    group.allreduce(xs, xs)  # in place, large enough for the zero-copy path
+    # in place; the automatic choice at this size is zero-copy too, except between two ranks (one-shot up to 8 MiB)
+    group.allreduce(xs, xs, algo="auto" if W > 2 else "symm")
     torch.cuda.synchronize()
     group.check()
     assert group.algo_hits("allreduce", "symm") == before + 1

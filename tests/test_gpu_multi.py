@@ -41,7 +41,7 @@ def _collectives(comm):
             comm.allreduce(x).wait()  # in place
             assert torch.allclose(x.double().cpu(), ref, rtol=tol, atol=tol * W), (dtype, n, "inplace")
     # symmetric (registered) buffers: zero-copy two-shot, NVLS when the switch offers it
-    for n in (1000, 1 << 20):
+    for n in (1000, 5 << 20):  # the large one is beyond the one-shot range of every world size (8 MiB between two ranks)
         s = g.symm_empty((n,), dtype=torch.float32)
         s.copy_(torch.full((n,), float(r + 1), device=dev))
         comm.allreduce(s).wait()
@@ -54,7 +54,7 @@ def _collectives(comm):
         g.symm_free(sb)
     out["ar_symm_hits"] = g.algo_hits("allreduce", "symm") + g.algo_hits("allreduce", "nvls")
     # an ordinary torch allocation registered through CUDA IPC: peers read and write it directly
-    n = 1 << 20
+    n = 3 << 20
     plain = torch.full((n + 128,), float(r + 1), device=dev)
     rid = g.register(plain)
     view = plain[64:64 + n]
@@ -185,7 +185,7 @@ def _auto_shared(comm):
     torch.cuda.set_device(r)
     dev = torch.device("cuda", r)
     g = comm.device_group
-    n = 1 << 19  # 2 MiB of float32
+    n = 3 << 20  # 12 MiB of float32: beyond the one-shot range of every world size
     keep = []
     for it in range(4):
         pad = 16 * (r + it)
