@@ -393,25 +393,39 @@ def main():
             out["config"]["step_launch"] = "one CUDA graph per step" if graph else "eager"
             out["config"]["buckets"] = res["buckets"]
             arms = {}
+
+            def aux(name, fn):
+                """A comparison arm must not take the headline down with it: an error that every rank raises is
+                recorded under the arm's name and the run goes on."""
+                try:
+                    return fn()
+                except Exception as e:  # noqa: BLE001 - reported, not hidden
+                    arms[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+                    return None
+
             if not args.no_arms:
                 # the same step launched eagerly (also what the per-bucket timeline is taken from)
-                r = arm_ours(h, False, None, e2e=False, timeline_path=args.timeline)
-                arms["ours_eager"] = {"value": r["value"], "ms_per_step": r["ms_per_step"]}
+                r = aux("ours_eager", lambda: arm_ours(h, False, None, e2e=False, timeline_path=args.timeline))
+                if r:
+                    arms["ours_eager"] = {"value": r["value"], "ms_per_step": r["ms_per_step"]}
                 h.group = None
                 init_torch_dist(h)
                 if world > 1:
-                    r = arm_ours(h, False, None, e2e=False, reducer="nccl")
-                    arms["nccl_flat_eager"] = {"value": r["value"], "ms_per_step": r["ms_per_step"],
-                                               "what": "this library's step with NCCL as the bucket allreduce"}
-                r = arm_torch_ddp(h, "nccl", e2e=True)
-                arms["nccl"] = {"value": r["value"], "ms_per_step": r["ms_per_step"], "e2e_value": r["e2e_value"],
-                                "what": "stock PyTorch modules, DistributedDataParallel over NCCL, torch fused AdamW"}
-                out["vs_baseline"] = out["value"] / r["value"]
-                out["e2e"]["vs_baseline"] = out["e2e"]["value"] / r["e2e_value"]
+                    r = aux("nccl_flat_eager", lambda: arm_ours(h, False, None, e2e=False, reducer="nccl"))
+                    if r:
+                        arms["nccl_flat_eager"] = {"value": r["value"], "ms_per_step": r["ms_per_step"],
+                                                   "what": "this library's step with NCCL as the bucket allreduce"}
+                r = aux("nccl", lambda: arm_torch_ddp(h, "nccl", e2e=True))
+                if r:
+                    arms["nccl"] = {"value": r["value"], "ms_per_step": r["ms_per_step"], "e2e_value": r["e2e_value"],
+                                    "what": "stock PyTorch modules, DistributedDataParallel over NCCL, torch fused AdamW"}
+                    out["vs_baseline"] = out["value"] / r["value"]
+                    out["e2e"]["vs_baseline"] = out["e2e"]["value"] / r["e2e_value"]
                 if world > 1:
-                    r = arm_torch_ddp(h, "ccl", e2e=False)
-                    arms["ccl_ddp"] = {"value": r["value"], "ms_per_step": r["ms_per_step"],
-                                       "what": "stock DistributedDataParallel over this library's torch backend"}
+                    r = aux("ccl_ddp", lambda: arm_torch_ddp(h, "ccl", e2e=False))
+                    if r:
+                        arms["ccl_ddp"] = {"value": r["value"], "ms_per_step": r["ms_per_step"],
+                                           "what": "stock DistributedDataParallel over this library's torch backend"}
                 out["arms"] = arms
                 out["baseline_note"] = ("the reference publishes no number; vs_baseline is value / arms.nccl.value "
                                         "measured in this run")

@@ -154,12 +154,17 @@ __global__ void __launch_bounds__(256)
             atomicAdd(&counts[e], (unsigned long long)hist[e]);
 }
 
-// cursor[e] starts at zero; item i = token * topk + slot lands at offset(expert) + ticket
+// cursor[e] starts at zero; item i = token * topk + slot lands at offset(expert) + ticket.  Tickets are drawn in
+// shared memory first and every block asks the global counters once per expert (a million items on eight
+// global counters would serialise on them).
 __global__ void __launch_bounds__(256)
     route_place_kernel(const long long* __restrict__ idx, size_t n_items, int n_experts,
                        const unsigned long long* __restrict__ counts, unsigned int* __restrict__ cursor,
                        long long* __restrict__ order, long long* __restrict__ pos) {
     __shared__ unsigned long long offs[ROUTE_MAX_EXPERTS];
+    __shared__ unsigned int local_n[ROUTE_MAX_EXPERTS], base[ROUTE_MAX_EXPERTS];
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x)
+        local_n[e] = 0;
     if (threadIdx.x == 0) {
         unsigned long long acc = 0;
         for (int e = 0; e < n_experts; e++) {
@@ -169,9 +174,18 @@ __global__ void __launch_bounds__(256)
     }
     __syncthreads();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int e = -1;
+    unsigned int ticket = 0;
     if (i < n_items) {
-        const int e = (int)idx[i];
-        const unsigned long long p = offs[e] + atomicAdd(&cursor[e], 1u);
+        e = (int)idx[i];
+        ticket = atomicAdd(&local_n[e], 1u);
+    }
+    __syncthreads();
+    for (int x = threadIdx.x; x < n_experts; x += blockDim.x)
+        base[x] = local_n[x] ? atomicAdd(&cursor[x], local_n[x]) : 0u;
+    __syncthreads();
+    if (e >= 0) {
+        const unsigned long long p = offs[e] + base[e] + ticket;
         order[p] = (long long)i;
         pos[i] = (long long)p;
     }
