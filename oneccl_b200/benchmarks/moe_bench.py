@@ -125,7 +125,7 @@ def main():
     wire_ms = wire / (peaks["nvlink_gbs_per_direction"] * 1e9) * 1e3
     flops = 2.0 * rows * args.hidden * args.ffn * 2
     ffn_floor_ms = flops / (peaks["bf16_tflops_sustained"] * 1e12) * 1e3
-    res["phases_ms"] = {"routing_torch": route_ms, "dispatch": dispatch_ms, "ffn": ffn_ms, "combine": combine_ms}
+    res["phases_ms"] = {"routing": route_ms, "dispatch": dispatch_ms, "ffn": ffn_ms, "combine": combine_ms}
     res["rows_busiest_expert"] = rows
     res["floor_ms"] = {"dispatch": wire_ms, "ffn": ffn_floor_ms, "combine": wire_ms}
     res["fraction_of_floor"] = {"dispatch": wire_ms / dispatch_ms, "ffn": ffn_floor_ms / ffn_ms,
