@@ -1008,6 +1008,153 @@ event_ptr hier_device_allgather(host_comm& comm, coll_param& p, const coll_attr&
     return make_completed_event();
 }
 
+// broadcast / reduce of device buffers across nodes (rank = node * L + local on every node, L ranks each).
+// broadcast: the root's buffer travels on the host path among the ranks that share the root's local index (one
+// per node), then every node broadcasts it on the device from that rank.  reduce: every node reduces on the
+// device to the rank with the root's local index, those ranks finish among themselves on the host path.  One rank
+// per node stages through pinned memory instead of every rank (the reference composes its scale-out broadcast and
+// reduce the same way: node stage, cross-node stage among equal local ranks; src/coll/algorithms/bcast.cpp:243,
+// reduce.cpp:222).
+bool hier_rooted_possible(host_comm& comm, const coll_param& p, const coll_attr& attr) {
+    const bool bc = p.ctype == coll_bcast || p.ctype == coll_broadcast;
+    if ((!bc && p.ctype != coll_reduce) || !env_data::get().cuda_kernels || !env_data::get().topo_algo || p.count == 0 ||
+        attr.out_dtype >= 0 || attr.do_scale)
+        return false;
+    if (p.ctype == coll_reduce && (attr.reduction_fn || p.reduction == red_custom))
+        return false;
+    const int L = comm.local_size();
+    if (L <= 0 || comm.size() % L != 0)
+        return false;
+    const std::vector<int>& h = comm.host_index();
+    for (int r = 0; r < comm.size(); r++)
+        if (h[r] != r / L)
+            return false;
+    return true;
+}
+
+namespace {
+// the node stage runs kernels that wait for the rank with the data: the others enter it only once that rank is
+// there too (it may have spent long on the network), so that their bounded device waits do not run out
+void node_host_barrier(host_comm& node) {
+    if (node.size() <= 1)
+        return;
+    coll_param b;
+    b.ctype = coll_barrier;
+    b.device = false;
+    coll_attr a;
+    coll_create(node, b, a)->wait();
+}
+} // namespace
+
+event_ptr hier_device_broadcast(host_comm& comm, coll_param& p, const coll_attr& attr) {
+    (void)attr;
+    auto node = comm.node_comm();
+    auto r2r = comm.r2r_comm();
+    const int L = node->size();
+    const int lroot = p.root % L, nroot = p.root / L;
+    cudaStream_t st = (cudaStream_t)p.stream;
+    stats().device_calls[p.ctype]++;
+    const size_t bytes = p.count * dtype_size(p.dtype);
+    if (comm.rank() == p.root && p.ctype == coll_broadcast && p.send_buf && p.send_buf != p.recv_buf)
+        CUDA_CHECK(cudaMemcpyAsync(p.recv_buf, p.send_buf, bytes, cudaMemcpyDeviceToDevice, st));
+    // 1. across the nodes, among the ranks with the root's local index
+    if (node->rank() == lroot && r2r->size() > 1) {
+        coll_param x;
+        x.ctype = coll_bcast;
+        x.recv_buf = p.recv_buf;
+        x.count = p.count;
+        x.dtype = p.dtype;
+        x.root = nroot;
+        x.device = true;
+        x.stream = p.stream;
+        coll_attr plain;
+        staged_device_coll(*r2r, x, plain);
+    }
+    // 2. inside every node, from that rank
+    node_host_barrier(*node);
+    coll_param nb;
+    nb.ctype = coll_bcast;
+    nb.recv_buf = p.recv_buf;
+    nb.count = p.count;
+    nb.dtype = p.dtype;
+    nb.root = lroot;
+    nb.device = true;
+    nb.stream = p.stream;
+    coll_attr none;
+    return device_coll(*node, nb, none);
+}
+
+event_ptr hier_device_reduce(host_comm& comm, coll_param& p, const coll_attr& attr) {
+    (void)attr;
+    auto node = comm.node_comm();
+    auto r2r = comm.r2r_comm();
+    const int L = node->size();
+    const int lroot = p.root % L, nroot = p.root / L;
+    cudaStream_t st = (cudaStream_t)p.stream;
+    stats().device_calls[coll_reduce]++;
+    const size_t bytes = p.count * dtype_size(p.dtype);
+    struct scratch {
+        cudaEvent_t last = nullptr;
+        void* dev = nullptr;
+        size_t cap = 0;
+        ~scratch() {
+            if (dev)
+                cudaFree(dev);
+            if (last)
+                cudaEventDestroy(last);
+        }
+    };
+    const bool holder = node->rank() == lroot; // receives its node's partial result
+    void* partial = nullptr;
+    if (holder && comm.rank() == p.root)
+        partial = p.recv_buf;
+    else if (holder) {
+        std::shared_ptr<void>& slot = comm.device_scratch(3);
+        if (!slot)
+            slot = std::make_shared<scratch>();
+        scratch& sc = *std::static_pointer_cast<scratch>(slot);
+        if (!sc.last)
+            CUDA_CHECK(cudaEventCreateWithFlags(&sc.last, cudaEventDisableTiming));
+        else
+            CUDA_CHECK(cudaStreamWaitEvent(st, sc.last, 0));
+        if (sc.cap < bytes) {
+            if (sc.dev)
+                CUDA_CHECK(cudaFree(sc.dev));
+            sc.dev = nullptr;
+            sc.cap = 0;
+            CUDA_CHECK(cudaMalloc(&sc.dev, bytes));
+            sc.cap = bytes;
+        }
+        partial = sc.dev;
+    }
+    // 1. inside the node, to the rank with the root's local index
+    coll_param nr = p;
+    nr.ctype = coll_reduce;
+    nr.recv_buf = partial;
+    nr.root = lroot;
+    nr.deps.clear();
+    coll_attr plain;
+    event_ptr ev = device_coll(*node, nr, plain);
+    // 2. across the nodes, among those ranks, to the root's node (synchronous: it stages through pinned memory)
+    if (holder && r2r->size() > 1) {
+        ev->wait();
+        coll_param x;
+        x.ctype = coll_reduce;
+        x.send_buf = partial;
+        x.recv_buf = r2r->rank() == nroot ? partial : nullptr;
+        x.count = p.count;
+        x.dtype = p.dtype;
+        x.reduction = p.reduction;
+        x.root = nroot;
+        x.device = true;
+        x.stream = p.stream;
+        coll_attr host_attr;
+        host_attr.scaleout = true;
+        return staged_device_coll(*r2r, x, host_attr);
+    }
+    return ev;
+}
+
 bool same_node(host_comm& comm) {
     const std::vector<int>& h = comm.host_index();
     for (int v : h)
@@ -1323,6 +1470,8 @@ event_ptr coll_create(host_comm& comm, coll_param& p, const coll_attr& attr) {
             ev = hier_device_reduce_scatter(comm, p, attr);
         else if (hier_allgather_possible(comm, p, attr))
             ev = hier_device_allgather(comm, p, attr);
+        else if (hier_rooted_possible(comm, p, attr))
+            ev = p.ctype == coll_reduce ? hier_device_reduce(comm, p, attr) : hier_device_broadcast(comm, p, attr);
         else
             ev = staged_device_coll(comm, p, attr);
         if (sync)

@@ -80,7 +80,7 @@ private:
     std::shared_ptr<host_comm> node_, r2r_;
     std::vector<int> host_idx_;
     sched_cache cache_;
-    std::shared_ptr<void> dev_scratch_[3]; // scratch of the hierarchical device collectives (released with the device state)
+    std::shared_ptr<void> dev_scratch_[4]; // scratch of the hierarchical device collectives (released with the device state)
     std::unique_ptr<gpu::bootstrap_if> dev_bs_; // outlives dev_: later handle exchanges (buffer registration) use it
     std::unique_ptr<gpu::device_comm> dev_;
     std::unique_ptr<pmi> dev_pm_;

@@ -560,6 +560,21 @@ def _fake_nodes(rank, world, addr_file, q):
         comm.allreduce(z).wait()  # in place
         torch.cuda.synchronize()
         ok = ok and bool(torch.all(z == 2 * torch.arange(1000, device="cuda") + 1))
+        # broadcast and reduce take the node stage on the device and cross the 'nodes' once, on the host path
+        from oneccl_b200.comm import stats
+
+        b = torch.full((5000,), float(rank + 7), device="cuda")
+        comm.broadcast(b, root=1).wait()
+        src = torch.arange(300, device="cuda", dtype=torch.float32) + 10 * rank
+        dst = torch.zeros(300, device="cuda")
+        comm.broadcast(src, root=0, recv=dst).wait()
+        o = torch.zeros(777, device="cuda")
+        comm.reduce(torch.full((777,), float(rank + 1), device="cuda"), o, root=1).wait()
+        torch.cuda.synchronize()
+        ok = ok and bool(torch.all(b == 8.0)) and bool(torch.all(dst == torch.arange(300, device="cuda")))
+        ok = ok and (rank != 1 or bool(torch.all(o == 3.0)))
+        ok = ok and stats("device_calls", "bcast") >= 1 and stats("device_calls", "broadcast") >= 1
+        ok = ok and stats("device_calls", "reduce") >= 1
         comm.barrier().wait()
         comm.close()
         q.put((rank, "ok", ok))
@@ -570,7 +585,7 @@ def _fake_nodes(rank, world, addr_file, q):
 
 
 @pytest.mark.skipif(_ngpu() < 1, reason="needs a GPU")
-def test_allreduce_across_fake_nodes_takes_the_hierarchical_path():
+def test_collectives_across_fake_nodes_take_the_hierarchical_path():
     import multiprocessing as mp
     import tempfile
 
