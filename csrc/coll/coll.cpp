@@ -732,40 +732,63 @@ event_ptr hier_device_allreduce(host_comm& comm, coll_param& p, const coll_attr&
         sc.cap = slice_bytes;
     }
 
-    // 1. inside the node: my slice of the node-wide sum
-    coll_param rs = p;
-    rs.ctype = coll_reduce_scatter;
-    rs.count = rc;
-    rs.recv_buf = sc.dev;
-    rs.deps.clear();
+    // The message travels in `chunks` parts (CCL_ALLREDUCE_PIPE_CHUNK_COUNT, as in the reference: 0 or 1 = one part):
+    // the node-level reduce_scatter of every part is queued on the stream at once, each followed by the copy of
+    // its slice to pinned memory; the host then takes the parts in order, so that the cross-node allreduce of part c
+    // runs while the GPU still reduces parts c + 1 .., and the node allgather of part c while the network carries
+    // part c + 1.  A part must split evenly among the node's ranks.
+    size_t chunks = std::max<size_t>(1, env_data::get().allreduce_pipe_chunk_count);
+    while (chunks > 1 && (p.count % (chunks * (size_t)L) != 0 || p.count / chunks < (size_t)L))
+        chunks--;
+    const size_t part = p.count / chunks; // elements of one part of the message
+    const size_t prc = part / (size_t)L, pbytes = prc * esz; // my slice of one part
+    const bool inplace = p.send_buf == p.recv_buf;
     coll_attr plain;
-    device_coll(*node, rs, plain)->wait();
-    // 2. across the nodes: same slice on the ranks with my local index
-    CUDA_CHECK(cudaMemcpyAsync(sc.host, sc.dev, slice_bytes, cudaMemcpyDeviceToHost, st));
-    CUDA_CHECK(cudaStreamSynchronize(st));
-    if (r2r->size() > 1) {
-        coll_param ar;
-        ar.ctype = coll_allreduce;
-        ar.send_buf = sc.host;
-        ar.recv_buf = sc.host;
-        ar.count = rc;
-        ar.dtype = p.dtype;
-        ar.reduction = p.reduction;
-        ar.device = false;
-        coll_attr host_attr;
-        host_attr.scaleout = true; // CCL_ALLREDUCE_SCALEOUT chooses the inter-node algorithm
-        coll_create(*r2r, ar, host_attr)->wait();
+    std::vector<cudaEvent_t> staged(chunks, nullptr);
+    std::vector<event_ptr> reduced(chunks);
+    // 1. inside the node: my slice of the node-wide sum, part by part
+    for (size_t c = 0; c < chunks; c++) {
+        coll_param rs = p;
+        rs.ctype = coll_reduce_scatter;
+        rs.send_buf = (const char*)p.send_buf + c * part * esz;
+        rs.count = prc;
+        rs.recv_buf = (char*)sc.dev + c * pbytes;
+        rs.deps.clear();
+        reduced[c] = device_coll(*node, rs, plain);
+        CUDA_CHECK(cudaMemcpyAsync((char*)sc.host + c * pbytes, (char*)sc.dev + c * pbytes, pbytes, cudaMemcpyDeviceToHost, st));
+        CUDA_CHECK(cudaEventCreateWithFlags(&staged[c], cudaEventDisableTiming));
+        CUDA_CHECK(cudaEventRecord(staged[c], st));
     }
-    CUDA_CHECK(cudaMemcpyAsync(sc.dev, sc.host, slice_bytes, cudaMemcpyHostToDevice, st));
-    // 3. inside the node: everybody gets every slice
-    coll_param ag = p;
-    ag.ctype = coll_allgather;
-    ag.send_buf = sc.dev;
-    ag.recv_buf = p.recv_buf;
-    ag.count = rc;
-    ag.deps.clear();
-    coll_attr none;
-    event_ptr done = device_coll(*node, ag, none);
+    (void)inplace;
+    event_ptr done;
+    for (size_t c = 0; c < chunks; c++) {
+        // 2. across the nodes: same slice on the ranks with my local index
+        reduced[c]->wait(); // reports a device-side failure of the node stage
+        CUDA_CHECK(cudaEventSynchronize(staged[c]));
+        CUDA_CHECK(cudaEventDestroy(staged[c]));
+        if (r2r->size() > 1) {
+            coll_param ar;
+            ar.ctype = coll_allreduce;
+            ar.send_buf = (char*)sc.host + c * pbytes;
+            ar.recv_buf = (char*)sc.host + c * pbytes;
+            ar.count = prc;
+            ar.dtype = p.dtype;
+            ar.reduction = p.reduction;
+            ar.device = false;
+            coll_attr host_attr;
+            host_attr.scaleout = true; // CCL_ALLREDUCE_SCALEOUT chooses the inter-node algorithm
+            coll_create(*r2r, ar, host_attr)->wait();
+        }
+        CUDA_CHECK(cudaMemcpyAsync((char*)sc.dev + c * pbytes, (char*)sc.host + c * pbytes, pbytes, cudaMemcpyHostToDevice, st));
+        // 3. inside the node: everybody gets every slice of the part
+        coll_param ag = p;
+        ag.ctype = coll_allgather;
+        ag.send_buf = (char*)sc.dev + c * pbytes;
+        ag.recv_buf = (char*)p.recv_buf + c * part * esz;
+        ag.count = prc;
+        ag.deps.clear();
+        done = device_coll(*node, ag, plain);
+    }
     CUDA_CHECK(cudaEventRecord(sc.last, st)); // the allgather still reads sc.dev: the next user of the scratch waits for it
     return done;
 }

@@ -321,6 +321,7 @@ void env_data::parse() {
 
     get_str("CCL_TOPO_COLOR", topo_color);
     get_bool("CCL_TOPO_ALGO", topo_algo);
+    get_size("CCL_ALLREDUCE_PIPE_CHUNK_COUNT", allreduce_pipe_chunk_count);
     get_str("CCL_TOPO_P2P_ACCESS", topo_p2p_access);
     get_bool("CCL_TOPO_FABRIC_VERTEX_CONNECTION_CHECK", topo_fabric_check);
     get_bool("CCL_TOPO_WA_FABRIC_VERTEX_CONNECTION_CHECK", topo_fabric_check); // the reference's spelling

@@ -111,6 +111,7 @@ struct env_data {
     // topology
     std::string topo_color = "fixed"; // fixed | cuda | env
     bool topo_algo = true;
+    size_t allreduce_pipe_chunk_count = 0; // parts of a hierarchical device allreduce whose stages overlap (0 / 1: one part)
     std::string topo_p2p_access = "auto"; // auto | 0 | 1
     bool topo_fabric_check = false; // check peer access between all ranks' GPUs before the heap is mapped
 

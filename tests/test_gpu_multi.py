@@ -526,7 +526,7 @@ def test_debug_scan_reports_non_finite_results():
     assert all(run_ranks(_nan_check, 2, env=dict(ENV, CCL_CUDA_CHECK_NAN="1"), timeout=200))
 
 
-def _fake_nodes(rank, world, addr_file, q):
+def _fake_nodes(rank, world, addr_file, q, chunks=0):
     """Two ranks that pretend to sit on different hosts and share GPU 0: the node communicators have one
     rank each (their kernels wait on nobody), the slice crosses the 'nodes' on the host path."""
     try:
@@ -534,6 +534,7 @@ def _fake_nodes(rank, world, addr_file, q):
         os.environ["CCL_CUDA_NVLS"] = "0"
         os.environ["CCL_CUDA_SYMM_HEAP_SIZE"] = "64M"
         os.environ["CCL_CUDA_TMP_BUF_SIZE"] = "8M"
+        os.environ["CCL_ALLREDUCE_PIPE_CHUNK_COUNT"] = str(chunks)
         import time
 
         from oneccl_b200.comm import KVS, Communicator
@@ -560,6 +561,15 @@ def _fake_nodes(rank, world, addr_file, q):
         comm.allreduce(z).wait()  # in place
         torch.cuda.synchronize()
         ok = ok and bool(torch.all(z == 2 * torch.arange(1000, device="cuda") + 1))
+        # a message of several parts (when chunks > 1), values that differ per element, out of place and in place
+        n = 3 * 7 * 1024
+        big = torch.arange(n, device="cuda", dtype=torch.float32) * (rank + 1)
+        out = torch.zeros_like(big)
+        comm.allreduce(big, out).wait()
+        comm.allreduce(big).wait()
+        torch.cuda.synchronize()
+        want = torch.arange(n, device="cuda", dtype=torch.float32) * 3
+        ok = ok and bool(torch.equal(out, want)) and bool(torch.equal(big, want))
         # broadcast and reduce take the node stage on the device and cross the 'nodes' once, on the host path
         from oneccl_b200.comm import stats
 
@@ -585,14 +595,15 @@ def _fake_nodes(rank, world, addr_file, q):
 
 
 @pytest.mark.skipif(_ngpu() < 1, reason="needs a GPU")
-def test_collectives_across_fake_nodes_take_the_hierarchical_path():
+@pytest.mark.parametrize("chunks", [0, 3, 5], ids=["one-part", "three-parts", "five-asked-four-fit"])
+def test_collectives_across_fake_nodes_take_the_hierarchical_path(chunks):
     import multiprocessing as mp
     import tempfile
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     addr = os.path.join(tempfile.mkdtemp(prefix="cclx_fn_"), "addr")
-    procs = [ctx.Process(target=_fake_nodes, args=(r, 2, addr, q)) for r in range(2)]
+    procs = [ctx.Process(target=_fake_nodes, args=(r, 2, addr, q, chunks)) for r in range(2)]
     for p in procs:
         p.start()
     res = {}
