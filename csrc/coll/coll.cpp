@@ -695,7 +695,7 @@ event_ptr hier_device_allreduce(host_comm& comm, coll_param& p, const coll_attr&
     cudaStream_t st = (cudaStream_t)p.stream;
     stats().device_calls[coll_allreduce]++;
 
-    // scratch: this rank's slice on the device, its mirror in pinned host memory (kept per thread, grown on demand)
+    // scratch: this rank's slice on the device, its mirror in pinned host memory (kept by the communicator, grown on demand)
     struct scratch {
         cudaEvent_t last = nullptr; // recorded behind the last asynchronous use
         void* dev = nullptr;
@@ -742,7 +742,6 @@ event_ptr hier_device_allreduce(host_comm& comm, coll_param& p, const coll_attr&
         chunks--;
     const size_t part = p.count / chunks; // elements of one part of the message
     const size_t prc = part / (size_t)L, pbytes = prc * esz; // my slice of one part
-    const bool inplace = p.send_buf == p.recv_buf;
     coll_attr plain;
     std::vector<cudaEvent_t> staged(chunks, nullptr);
     std::vector<event_ptr> reduced(chunks);
@@ -759,7 +758,7 @@ event_ptr hier_device_allreduce(host_comm& comm, coll_param& p, const coll_attr&
         CUDA_CHECK(cudaEventCreateWithFlags(&staged[c], cudaEventDisableTiming));
         CUDA_CHECK(cudaEventRecord(staged[c], st));
     }
-    (void)inplace;
+    // in place is safe: part c of recv is written only after every part of send has been reduced (stream order)
     event_ptr done;
     for (size_t c = 0; c < chunks; c++) {
         // 2. across the nodes: same slice on the ranks with my local index
