@@ -39,8 +39,12 @@ std::shared_ptr<host_comm> host_comm::create(int size, int rank, std::shared_ptr
                 if (!tr)
                     LOG_WARN("CCL_ATL_TRANSPORT=ofi: ", why, "; the socket transport carries the traffic");
             }
-            else if (env.atl_transport == atl_transport_t::mpi)
-                LOG_INFO("CCL_ATL_TRANSPORT=mpi: no MPI library is available, the socket transport carries the traffic");
+            else if (env.atl_transport == atl_transport_t::mpi) {
+                std::string why;
+                tr = create_mpi_transport(*pm, env.worker_count, why);
+                if (!tr)
+                    LOG_WARN("CCL_ATL_TRANSPORT=mpi: ", why, "; the socket transport carries the traffic");
+            }
             if (!tr)
                 tr = create_tcp_transport(*pm, env.worker_count);
             transports[key] = tr;

@@ -355,6 +355,7 @@ void env_data::parse() {
     get_size("CCL_CUDA_IPC_CACHE_ENTRIES", ipc_cache_entries);
     get_size("CCL_ATL_LARGE_MSG_SIZE", large_msg_size);
     get_str("CCL_OFI_LIBRARY_PATH", ofi_lib_path);
+    get_str("CCL_MPI_LIBRARY_PATH", mpi_lib_path);
     get_int("CCL_CUDA_NVLS_STAGED_MIN_RANKS", nvls_staged_min_ranks);
     get_int("CCL_CUDA_P2P_LANES", p2p_lanes);
     get_int("CCL_CUDA_P2P_MAX_BLOCKS", p2p_max_blocks);

@@ -6,8 +6,9 @@
 // by (source rank, tag) where tag = comm_id | sched_id | op_id.  Two transports sit
 // behind it: this library's own `tcp` (a socket mesh on any host, with single-producer
 // rings in POSIX shared memory and cross-memory rendezvous between ranks of one host),
-// and `ofi` (libfabric's tagged messages, the library opened with dlopen).  MPI is not
-// available in the image; CCL_ATL_TRANSPORT=mpi falls back to `tcp` with a notice.
+// `ofi` (libfabric's tagged messages) and `mpi` (MPI point-to-point messages of an MPICH-ABI
+// library); both libraries are opened with dlopen, and where one cannot be used on every rank
+// `tcp` carries the traffic with a notice.
 #pragma once
 #include <atomic>
 #include <cstddef>
@@ -96,6 +97,9 @@ std::shared_ptr<atl_transport> create_tcp_transport(pmi& pm, int ep_count);
 // libfabric (opened at run time) behind the same interface; null with the reason in `why` when some rank
 // cannot load the library
 std::shared_ptr<atl_transport> create_ofi_transport(pmi& pm, int ep_count, std::string& why);
+// an MPI library of the MPICH binary interface (opened at run time) behind the same interface; null with the
+// reason in `why` when some rank cannot use it (no library, Open MPI, not started by the MPI launcher)
+std::shared_ptr<atl_transport> create_mpi_transport(pmi& pm, int ep_count, std::string& why);
 
 // A communicator's view of the transport: rank translation + comm id.
 class atl_comm {
