@@ -2,6 +2,7 @@
 into build/lib-<sanitizer>/ and the all-operations C++ example runs against it as three ranks, in several
 runtime modes.  Two extra full builds: opt-in with CCLX_RUN_SANITIZERS=1."""
 import os
+import shutil
 import subprocess
 import tempfile
 from pathlib import Path
@@ -38,6 +39,27 @@ def test_all_operations_under_sanitizer(sanitizer):
         for o in outs:
             assert marker not in o and "LeakSanitizer" not in o, (mode, o[-4000:])
         assert outs[0].count("PASSED") == 71, (mode, outs[0][-2000:])
+    # the MPI transport with two worker threads per rank (their own endpoints; then one lock around every MPI call),
+    # against the stand-in MPI library of tests/mock_mpi
+    cc = shutil.which("cc") or shutil.which("gcc")
+    if cc:
+        mock = exe.parent / "libmockmpi.so"
+        subprocess.run([cc, "-shared", "-fPIC", "-O1", "-o", str(mock), str(ROOT / "tests" / "mock_mpi" / "mock_mpi.c"),
+                        "-lpthread"], check=True)
+        for level in ("3", "2"):
+            job = tempfile.mkdtemp(prefix="cclx_san_mpi_")
+            addr = os.path.join(job, "addr")
+            procs = []
+            for rk in range(3):
+                env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1", TSAN_OPTIONS="halt_on_error=0 report_signal_unsafe=0",
+                           CCL_ATL_TRANSPORT="mpi", CCL_MPI_LIBRARY_PATH=str(mock), CCL_WORKER_COUNT="2", MOCK_MPI_DIR=job,
+                           MOCK_MPI_RANK=str(rk), MOCK_MPI_SIZE="3", MOCK_MPI_THREAD_LEVEL=level)
+                procs.append(subprocess.Popen([str(exe), str(rk), "3", addr], stdout=subprocess.PIPE,
+                                              stderr=subprocess.STDOUT, text=True, env=env))
+            outs = [p.communicate(timeout=300)[0] for p in procs]
+            for o in outs:
+                assert marker not in o and "LeakSanitizer" not in o, ("mpi", level, o[-4000:])
+            assert outs[0].count("PASSED") == 71, ("mpi", level, outs[0][-2000:])
     # the functional matrix, thinly sampled, over the paths the example does not reach: one-sided writes
     # (as messages: the sanitizers cannot see a cross-memory copy), rendezvous for every message, bounded cache
     ft = exe.parent / f"functional_{sanitizer}"
