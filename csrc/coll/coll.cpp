@@ -1036,7 +1036,7 @@ event_ptr hier_device_allgather(host_comm& comm, coll_param& p, const coll_attr&
 // device to the rank with the root's local index, those ranks finish among themselves on the host path.  One rank
 // per node stages through pinned memory instead of every rank (the reference composes its scale-out broadcast and
 // reduce the same way: node stage, cross-node stage among equal local ranks; src/coll/algorithms/bcast.cpp:243,
-// reduce.cpp:222).
+// reduce.cpp:554).
 bool hier_rooted_possible(host_comm& comm, const coll_param& p, const coll_attr& attr) {
     const bool bc = p.ctype == coll_bcast || p.ctype == coll_broadcast;
     if ((!bc && p.ctype != coll_reduce) || !env_data::get().cuda_kernels || !env_data::get().topo_algo || p.count == 0 ||
