@@ -1,7 +1,8 @@
 // MPI transport: the ATL interface on MPI point-to-point messages.
 //
 // Counterpart of the reference's atl/mpi (src/atl/mpi/atl_mpi.cpp, atl_mpi_comm.cpp) and of its run-time
-// loader (src/common/api_wrapper/mpi_api_wrapper.cpp:27-103): the MPI library is opened with dlopen
+// loader (src/common/api_wrapper/mpi_api_wrapper.cpp:25-46, entry-point table in mpi_api_wrapper.hpp:26-103):
+// the MPI library is opened with dlopen
 // (CCL_MPI_LIBRARY_PATH, else libmpi.so.12 / libmpi.so from the loader's search path) and called through the
 // MPICH binary interface declared in mpi_abi.hpp.  The processes must have been started by that MPI's launcher,
 // so that MPI_COMM_WORLD spans the job; which MPI rank belongs to which rank of the communicator travels through

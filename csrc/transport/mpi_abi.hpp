@@ -1,6 +1,7 @@
 // The part of the MPI binary interface that the MPI transport calls, declared here so that the
 // library builds without an MPI installation and finds one at run time (dlopen), the way the reference
-// reaches MPI through a table of entry points (src/common/api_wrapper/mpi_api_wrapper.cpp:27-103).
+// reaches MPI through a table of entry points (src/common/api_wrapper/mpi_api_wrapper.hpp:26-103, loaded by
+// mpi_api_wrapper.cpp:25-46).
 //
 // Handles and constants are those of the MPICH binary interface (MPICH, Intel MPI, MVAPICH, Cray MPICH:
 // the common ABI of the MPICH ABI compatibility initiative): communicators, datatypes and requests are
