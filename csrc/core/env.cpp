@@ -7,6 +7,7 @@
 #include <mutex>
 #include <sstream>
 
+#include "bootstrap/pmix_client.hpp"
 #include "core/log.hpp"
 
 extern char** environ; // POSIX: the process environment
@@ -213,8 +214,21 @@ void env_data::parse() {
             ls = std::getenv("LOCAL_WORLD_SIZE");
         }
         else if (process_launcher == launcher_t::pmix) {
-            lr = std::getenv("PMIX_LOCAL_RANK");
-            ls = std::getenv("PMIX_LOCAL_SIZE");
+            // ask the PMIx server (the library is opened at run time); what some launchers export instead
+            get_str("CCL_PMIX_LIBRARY_PATH", pmix_lib_path);
+            int plr = -1, pls = -1;
+            std::string why;
+            if (pmix_local_coord(pmix_lib_path, plr, pls, why)) {
+                if (local_rank < 0 && local_size < 0) {
+                    local_rank = plr;
+                    local_size = pls;
+                }
+            }
+            else {
+                pmix_note = why;
+                lr = std::getenv("PMIX_LOCAL_RANK");
+                ls = std::getenv("PMIX_LOCAL_SIZE");
+            }
         }
         if (lr && ls && local_rank < 0 && local_size < 0) {
             local_rank = std::atoi(lr);
@@ -372,6 +386,8 @@ void env_data::print(int rank) const {
     ss << "configuration:";
     ss << "\n  CCL_LOG_LEVEL=" << log_level;
     ss << "\n  CCL_BACKEND=" << (backend == backend_t::native ? "native" : "stub");
+    if (!pmix_note.empty())
+        ss << "\n  CCL_PROCESS_LAUNCHER=pmix: the PMIx server was not asked (" << pmix_note << "); PMIX_LOCAL_RANK / PMIX_LOCAL_SIZE used if set";
     ss << "\n  CCL_PROCESS_LAUNCHER=" << (int)process_launcher << " local_rank=" << local_rank
        << " local_size=" << local_size;
     ss << "\n  CCL_WORKER_COUNT=" << worker_count << " CCL_WORKER_OFFLOAD=" << worker_offload

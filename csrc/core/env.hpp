@@ -140,6 +140,8 @@ struct env_data {
     size_t ipc_cache_entries = 1000; // registered allocations that may be open at once
     std::string ofi_lib_path; // CCL_OFI_LIBRARY_PATH: libfabric.so to open for CCL_ATL_TRANSPORT=ofi
     std::string mpi_lib_path; // CCL_MPI_LIBRARY_PATH: libmpi.so to open for CCL_ATL_TRANSPORT=mpi
+    std::string pmix_lib_path; // CCL_PMIX_LIBRARY_PATH: libpmix.so to open for CCL_PROCESS_LAUNCHER=pmix
+    std::string pmix_note; // why the PMIx server could not be asked (empty: it was, or was not needed)
     size_t large_msg_size = (size_t)1 << 30; // no single transport message of a split operation exceeds this
     size_t rs_nvls_max_block = 4u << 20; // reduce_scatter: per-rank blocks up to this size use multimem.ld_reduce, larger ones peer loads
     size_t ag_nvls_max_block = 1u << 20; // allgather: blocks up to this size go out as multimem.st, larger ones as peer stores

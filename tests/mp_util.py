@@ -15,6 +15,8 @@ def _child(fn, rank, world, addr_file, q, env, args):
         os.environ.update(env)
         os.environ["CCL_LOCAL_RANK"] = str(rank)
         os.environ["CCL_LOCAL_SIZE"] = str(world)
+        for name in env.get("CCLX_TEST_UNSET", "").split(","):  # a test of what happens without them
+            os.environ.pop(name, None)
         from oneccl_b200.comm import KVS, Communicator
 
         if rank == 0:
